@@ -1,0 +1,409 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-matmul path: decode (qmv, weight GB/s) and prefill (qmm, TFLOP/s).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload decode|prefill]
+
+One "step" of the default workload is one decode token through the quantized projections of a
+Qwen3-8B-shaped model (36 layers x {qkv, o, gate+up, down}, affine 4-bit, groups of 64, M = 1):
+144 few-row products streaming 3.9 GB of packed weights, far more than L2, so every launch
+reads its weights from HBM.  On N GPUs each projection is split along its output rows; every
+rank multiplies its slice and the slices are joined by an all-gather (NCCL) on the same stream.
+
+The JSON line printed by rank 0 carries:
+  value       whole-job weight GB/s with inputs resident in HBM (device-timed, max over ranks)
+  roofline    the qmv kernel against the measured HBM copy bandwidth
+  e2e         the same metric through the host-operand entry point (pinned H2D of x, D2H of y
+              inside the timed region)
+  cpu_baseline  the CPU port of the reference's path, timed on this host on a bounded sample
+  also        the prefill product (M = 2048, K = 4096, N = 12288) in TFLOP/s with its roofline
+
+`--impl reference` times the reference's CPU algorithm (the oracle port; the reference itself
+is Rust and cannot be built with this toolchain) on the same workload, one layer per step.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# Qwen3-8B projection shapes (N out, K in): qkv, o, gate+up, down.
+PROJECTIONS = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288)]
+LAYERS = 36
+GS, BITS = 64, 4
+PREFILL = (2048, 12288, 4096)  # M, N, K
+
+
+def qmv_bytes(M, N, K, bits=BITS, gs=GS, s=4):
+    """Algorithmic bytes of one few-row product: packed weights + scales/biases + x + y."""
+    return N * K * bits // 8 + N * (K // gs) * s + M * K * 2 + M * N * 2
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+# ── CPU arm: the oracle port of the reference's CPU path ────────────────────────────────────
+def cpu_layer_inputs(seed=0):
+    import oracle
+    rng = np.random.default_rng(seed)
+    out = []
+    for name, N, K in PROJECTIONS:
+        w = oracle.from_f32((rng.standard_normal((N, K), dtype=np.float32) * 0.02), oracle.BF16)
+        codes, scales, biases = oracle.quantize(w, oracle.BF16, oracle.AFFINE, GS, BITS)
+        x = oracle.from_f32(rng.standard_normal((1, K), dtype=np.float32), oracle.BF16)
+        out.append((name, N, K, x, codes, scales, biases))
+    return out
+
+
+def time_cpu_layer(inputs, reps):
+    """Seconds per layer (4 projections, M = 1) through the oracle's quantized_matmul, with the
+    reference's serial dequantize (kernels.rs:852-856) and parallel few-row product."""
+    import oracle
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for _, _, _, x, codes, scales, biases in inputs:
+            oracle.quantized_matmul(x, codes, scales, biases, oracle.BF16, oracle.AFFINE, GS, BITS, True,
+                                    parallel_dequant=False)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def reference_arm(args):
+    """`--impl reference`: the reference's CPU algorithm on this host (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    inputs = cpu_layer_inputs()
+    layer_bytes = sum(qmv_bytes(1, N, K) for _, N, K in PROJECTIONS)
+    for _ in range(max(args.warmup, 0)):
+        time_cpu_layer(inputs, 1)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        time_cpu_layer(inputs, 1)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    value = layer_bytes / dt / 1e9
+    sample = "one layer (qkv, o, gate+up, down at M=1) per step; a full token is 36 such layers"
+    line = {"impl": "reference", "metric": "quantized_matmul weight GB/s (M=1)", "value": value, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * LAYERS,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(gpus):
+    return {"workload": "qwen3-8b decode projections, M=1, affine 4-bit g64, 36 layers x (qkv 4096->6144, o 4096->4096, "
+                        "gate+up 4096->24576, down 12288->4096)",
+            "parallelism": f"N-sharded x{gpus} + all_gather" if gpus > 1 else "single GPU",
+            "l2": "inputs larger than L2 (3.9 GB of weights per step, 108 MB per layer)",
+            "weights": "one seeded layer (W ~ N(0, 0.02) -> bf16 -> nuvec quantize) replicated into 36 distinct buffers"}
+
+
+# ── GPU arm ────────────────────────────────────────────────────────────────────────────────
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--rows", type=int, default=1, help="rows of x per decode product (M)")
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every product from the host instead of replaying a recorded step")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = nv.Device.shared(local)
+    lib = _ffi.lib()
+    peaks = measured_peaks()
+    M = args.rows
+
+    # ── weights: one seeded layer, quantized on the device, replicated into distinct buffers ──
+    rng = np.random.default_rng(0)
+    quant = nv.Quant.affine(GS, BITS)
+    layers = []
+    base = []
+    for name, N, K in PROJECTIONS:
+        assert N % world == 0
+        n_local = N // world
+        w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02)[rank * n_local:(rank + 1) * n_local]
+        q = nv.quantize(dev.array(nv.f32_to_bf16(w), nv.BF16), quant)
+        x = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
+        base.append((name, N, K, n_local, q, x))
+    dev.synchronize()
+    for layer in range(args.layers):
+        projs = []
+        for name, N, K, n_local, q, x in base:
+            if layer == 0:
+                ql = q
+            else:
+                ql = nv.Quantized(dev.empty(q.weight.shape, nv.U32), dev.empty(q.scales.shape, nv.BF16),
+                                  dev.empty(q.biases.shape, nv.BF16), quant)
+                ql.weight.copy_from(q.weight), ql.scales.copy_from(q.scales), ql.biases.copy_from(q.biases)
+            # [world, M, n_local] gather buffer; this rank's product lands in its own slot.
+            y = dev.empty((world, M, n_local), nv.BF16)
+            projs.append((name, N, K, n_local, ql, x, y))
+        layers.append(projs)
+    dev.synchronize()
+
+    comm = None
+    if world > 1:
+        import torch
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            assert lib.nvc_comm_unique_id(buf) == 0, _ffi.last_error()
+            ident = torch.tensor(list(buf), dtype=torch.uint8, device="cuda")
+        dist.broadcast(ident, 0)
+        idb = (C.c_uint8 * 128)(*ident.cpu().tolist())
+        h = C.c_void_p()
+        assert lib.nvc_comm_init(dev._h, rank, world, idb, C.byref(h)) == 0, _ffi.last_error()
+        comm = h
+
+    qc = quant._c()
+
+    def step(gather=True):
+        for projs in layers:
+            for name, N, K, n_local, q, x, y in projs:
+                slot = C.c_void_p(y.ptr.value + rank * M * n_local * 2)
+                rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, q.weight.ptr, q.scales.ptr,
+                                              q.biases.ptr, None, M, n_local, K, K, 1, 0, 0, 0, slot)
+                assert rc == 0, _ffi.last_error()
+                if comm is not None and gather:
+                    rc = lib.nvc_all_gather(comm, slot, y.ptr, M * n_local * 2)
+                    assert rc == 0, _ffi.last_error()
+
+    def barrier():
+        dev.synchronize()
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = dev.event(), dev.event()
+        l0 = dev.launches
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        barrier()
+        ms = e0.elapsed_ms(e1)
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, dev.launches - l0
+
+    # The step is recorded once and replayed: 144 launches of a few microseconds each would
+    # otherwise be bound by the host's launch rate, not by the GPU.
+    step()
+    graph = dev.record(step) if not args.no_graph else None
+    run = graph.launch if graph is not None else step
+    for _ in range(args.warmup):
+        run()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms, launches = timed(run, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        step(gather=False)
+        graph_k = dev.record(lambda: step(gather=False)) if not args.no_graph else None
+        ms_kernel_only, _ = timed(graph_k.launch if graph_k is not None else (lambda: step(gather=False)), args.steps)
+    else:
+        ms_kernel_only = ms
+
+    step_bytes = args.layers * sum(qmv_bytes(M, N, K) for _, N, K in PROJECTIONS)  # whole job, all ranks
+    per_step_ms = ms / args.steps
+    value = step_bytes / (per_step_ms * 1e-3) / 1e9
+    n_kernels = args.layers * len(PROJECTIONS)
+    # Dominant kernel: the few-row product.  Per launch on this rank: the rank's share of bytes.
+    launch_bytes = step_bytes / world / n_kernels
+    launch_s = (ms_kernel_only / args.steps) * 1e-3 / n_kernels
+    achieved = launch_bytes / launch_s / 1e9
+    roofline = {"kernel": "qmv_affine_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "avg_launch_us": launch_s * 1e6, "algorithmic_bytes_per_launch": launch_bytes}
+
+    line = {"metric": "quantized_matmul weight GB/s (M=1)", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload_config(world), launch="recorded step replayed (CUDA graph)" if graph is not None else "host launches"),
+            "roofline": roofline, "gpu_launches": launches, "clocks": clocks}
+    if world > 1:
+        line["kernel_only"] = {"value": step_bytes / (ms_kernel_only / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                               "note": "same step without the all_gather after each product"}
+
+    # ── end to end through the host-operand entry point (rank-local x in, y out) ─────────────
+    if not args.no_e2e:
+        hx = {K: np.ascontiguousarray(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32))) for _, _, K in PROJECTIONS}
+        hy = {n: np.empty((M, n), np.uint16) for n in {p[3] for p in base}}
+
+        def step_host():
+            for projs in layers:
+                for name, N, K, n_local, q, x, y in projs:
+                    rc = lib.nvc_quantized_matmul_host(dev._h, C.byref(qc), nv.BF16, 1, hx[K].ctypes.data_as(C.c_void_p),
+                                                       q.weight.ptr, q.scales.ptr, q.biases.ptr, None, M, n_local, K,
+                                                       hy[n_local].ctypes.data_as(C.c_void_p))
+                    assert rc == 0, _ffi.last_error()
+
+        step_host()
+        barrier()
+        t0 = time.perf_counter()
+        e2e_steps = max(3, args.steps // 4)
+        for _ in range(e2e_steps):
+            step_host()
+        barrier()
+        wall = (time.perf_counter() - t0) / e2e_steps
+        if dist is not None:
+            import torch
+            t = torch.tensor([wall], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            wall = float(t.item())
+        line["e2e"] = {"value": step_bytes / wall / 1e9, "unit": "GB/s",
+                       "h2d_bytes_per_step": args.layers * sum(M * K * 2 for _, _, K in PROJECTIONS),
+                       "d2h_bytes_per_step": args.layers * sum(M * (N // world) * 2 for _, N, _ in PROJECTIONS),
+                       "ms_per_step": wall * 1e3,
+                       "note": "nvc_quantized_matmul_host per product: pinned H2D of x, kernel, D2H of y, wait; weights resident"}
+
+    # ── prefill product on tcgen05 (rank 0's view; N-sharded like the decode products) ───────
+    if not args.no_prefill:
+        line["also"] = [prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier)]
+
+    # ── CPU baseline on this host's cores (rank 0, bounded sample) ───────────────────────────
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import oracle
+        inputs = cpu_layer_inputs()
+        secs = time_cpu_layer(inputs, 3)
+        layer_bytes = sum(qmv_bytes(1, N, K) for _, N, K in PROJECTIONS)
+        line["cpu_baseline"] = {"value": layer_bytes / secs / 1e9, "unit": "GB/s", "cores": oracle.threads(),
+                                "kind": "port", "host_cores": os.cpu_count(),
+                                "sample": "one layer (4 products, M=1), best of 3; serial dequantize as the reference, "
+                                          "few-row product over all threads", "seconds_per_layer": secs}
+    if rank == 0:
+        print(json.dumps(line))
+    if comm is not None:
+        lib.nvc_comm_destroy(comm)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier):
+    M, N, K = PREFILL
+    n_local = N // world
+    rng = np.random.default_rng(1)
+    quant = nv.Quant.affine(GS, BITS)
+    w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02)[rank * n_local:(rank + 1) * n_local]
+    copies = 4  # 4 x (25 MB + x 16 MB + y 50 MB) per rank at N=1: larger than L2
+    qs = []
+    q0 = nv.quantize(dev.array(nv.f32_to_bf16(w), nv.BF16), quant)
+    x0 = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
+    for i in range(copies):
+        q = nv.Quantized(dev.empty(q0.weight.shape, nv.U32), dev.empty(q0.scales.shape, nv.BF16),
+                         dev.empty(q0.biases.shape, nv.BF16), quant)
+        q.weight.copy_from(q0.weight), q.scales.copy_from(q0.scales), q.biases.copy_from(q0.biases)
+        x = dev.empty(x0.shape, nv.BF16)
+        x.copy_from(x0)
+        qs.append((q, x, dev.empty((M, n_local), nv.BF16)))
+    lib, qc = _ffi.lib(), quant._c()
+
+    def step():
+        for q, x, y in qs:
+            rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, q.weight.ptr, q.scales.ptr,
+                                          q.biases.ptr, None, M, n_local, K, K, 1, 0, 0, 0, y.ptr)
+            assert rc == 0, _ffi.last_error()
+
+    for _ in range(3):
+        step()
+    steps = 10
+    ms, launches = timed(step, steps)
+    flops = 2.0 * M * N * K * copies  # whole job
+    tf = flops / (ms / steps * 1e-3) / 1e12
+    per_launch = 2.0 * M * n_local * K / ((ms / steps) * 1e-3 / copies) / 1e12
+    return {"workload": f"prefill qmm M={M} K={K} N={N} affine 4-bit g64", "metric": "quantized_matmul TFLOP/s (M=2048)",
+            "value": tf, "unit": "TFLOP/s", "ms_per_product": ms / steps / copies, "gpu_launches": launches,
+            "roofline": {"kernel": "qmm kernel", "bound": "tensor", "achieved": per_launch, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": per_launch / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " (burst)"}}
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,239 @@
+/*
+ * nuvec_cuda.h -- C ABI of the B200 (sm_100a) backend for nuvec's quantized-matmul path.
+ *
+ * The reference (hupe1980/nuvec, Rust) has no C ABI for this path: its evaluator calls GPU
+ * back ends through the `GpuEval` seam (crates/nuvec-core/src/gpu.rs:154-281) and its
+ * experimental CUDA runtime through Rust crates over the driver API
+ * (crates/nuvec-gpu/src/cuda/device.rs:40-227, memory.rs:35-306).  Each entry point below names
+ * the reference interface it serves; a Rust `mod cuda` beside `mod metal`/`mod stub` binds
+ * these with `extern "C"` and marshals `Primitive::{Quantize, Dequantize, QuantizedMatmul,
+ * SortedOffsets}` / `FastOp::GatherQmm` operands to them.
+ *
+ * Conventions
+ *  - Every function returns NVC_OK (0) or a negative nvc_status; the message of the last
+ *    failure on the calling thread is read with nvc_last_error().  Nothing aborts or throws
+ *    (the reference turns a failed op into a failed array, README.md:102).
+ *  - Unless a parameter is documented as a host pointer, every data pointer is a device
+ *    pointer, normally from nvc_alloc().  The caller owns inputs and outputs and keeps them
+ *    alive until the stream work that uses them has completed.
+ *  - All work is enqueued on the device handle's stream and returns without waiting
+ *    (the reference's GPU evaluations are asynchronous until `flush`, gpu.rs:1772-1795).
+ *  - A handle may be used from any thread, one call at a time per handle.
+ *  - dtype codes are nuvec's `DType` discriminants (crates/nuvec-core/src/dtype.rs order, as
+ *    used by its fixture files): U8 = 1, U32 = 3, I32 = 7, F16 = 9, BF16 = 10, F32 = 11.
+ *  - Empty operands (M == 0, N == 0, no rows) succeed as no-ops
+ *    (crates/nuvec-core/tests/quantized.rs:1052-1078).
+ */
+#ifndef NUVEC_CUDA_H
+#define NUVEC_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    NVC_OK = 0,
+    NVC_ERR_INVALID_ARGUMENT = -1, /* Error::InvalidArgument, crates/nuvec-core/src/error.rs:17-42 */
+    NVC_ERR_UNSUPPORTED = -2,      /* Error::unsupported_dtype / shape the kernels do not take */
+    NVC_ERR_OUT_OF_MEMORY = -3,    /* CudaError::OutOfMemory, crates/nuvec-gpu/src/cuda/error.rs:6-42 */
+    NVC_ERR_NO_DEVICE = -4,        /* CudaError::NoDevice */
+    NVC_ERR_DRIVER = -5,           /* CudaError::Driver{call,message} */
+    NVC_ERR_COMM = -6              /* a failed collective (names the call) */
+} nvc_status;
+
+enum { NVC_U8 = 1, NVC_U32 = 3, NVC_I32 = 7, NVC_F16 = 9, NVC_BF16 = 10, NVC_F32 = 11 };
+
+/* QuantMode, crates/nuvec-core/src/quantized.rs:24-35 */
+enum { NVC_AFFINE = 0, NVC_MXFP4 = 1, NVC_MXFP8 = 2, NVC_NVFP4 = 3 };
+
+/* Quant{mode, group_size, bits}, crates/nuvec-core/src/quantized.rs:94-101.  Checked by every
+ * op with the rules of Quant::checked (:137-167): affine group 32/64/128 and bits 1-6 or 8;
+ * mxfp4 32/4; mxfp8 32/8; nvfp4 16/4. */
+typedef struct {
+    int32_t mode;
+    int32_t group_size;
+    int32_t bits;
+} nvc_quant;
+
+typedef struct nvc_device nvc_device; /* opaque: ordinal, stream, pool, scratch */
+typedef struct nvc_event nvc_event;   /* opaque: a point on the device's stream */
+typedef struct nvc_comm nvc_comm;     /* opaque: one rank of an NCCL communicator */
+typedef struct nvc_graph nvc_graph;   /* opaque: a recorded sequence of stream work */
+
+/* DeviceInfo, crates/nuvec-gpu/src/cuda/device.rs:57-75 */
+typedef struct {
+    char name[128];
+    int32_t cc_major, cc_minor;
+    int32_t multiprocessors;
+    int32_t driver_version;
+    uint64_t total_memory;
+    uint64_t l2_bytes;
+} nvc_info;
+
+/* MemoryStats, crates/nuvec-gpu/src/cuda/memory.rs:16-32 */
+typedef struct {
+    uint64_t active;  /* bytes handed out and not yet freed */
+    uint64_t cached;  /* bytes held by the pool for reuse */
+    uint64_t peak;    /* high-water mark of `active` */
+    uint64_t limit;   /* allocation limit (default 95% of device memory, memory.rs:64) */
+    uint64_t cache_limit;
+    uint64_t allocations; /* cudaMalloc calls so far */
+} nvc_mem_stats;
+
+/* ── errors ──────────────────────────────────────────────────────────────────────────── */
+
+/* Copies the calling thread's last error message (NUL-terminated) into `buf`. */
+void nvc_last_error(char *buf, size_t len);
+const char *nvc_version(void);
+
+/* ── device and stream: Device::shared/info/synchronize, device.rs:77-227 ────────────── */
+
+/* Opens device `ordinal` with its own non-blocking stream.  Fails with NVC_ERR_NO_DEVICE when
+ * there is no device and NVC_ERR_UNSUPPORTED when it is not compute capability 10.x (the
+ * reference refuses devices it has no kernels for, device.rs:107-111). */
+int32_t nvc_device_open(int32_t ordinal, nvc_device **out);
+int32_t nvc_device_close(nvc_device *dev);
+int32_t nvc_device_info(nvc_device *dev, nvc_info *out);
+int32_t nvc_synchronize(nvc_device *dev);
+/* Adopts an existing cudaStream_t (for example the caller framework's current stream); NULL
+ * returns to the handle's own stream.  The previous stream is synchronized first. */
+int32_t nvc_device_set_stream(nvc_device *dev, void *cuda_stream);
+void *nvc_device_stream(nvc_device *dev);
+/* Kernels this handle has launched so far (the reference counts dispatches the same way for
+ * its tests, gpu.rs:27). */
+uint64_t nvc_launch_count(nvc_device *dev);
+
+/* ── memory: Buffer::new / pool, memory.rs:35-306; Storage, buffer.rs:17-68 ──────────── */
+
+/* Size classes follow memory.rs:54-60 (<= 8 -> 8; < 16 KiB -> next power of two; else whole
+ * 16 KiB pages).  Blocks are 256-byte aligned (the reference asks for at least 64,
+ * buffer.rs:12-15).  Device memory, not managed memory: host access goes through the copies
+ * below. */
+int32_t nvc_alloc(nvc_device *dev, size_t bytes, void **out);
+int32_t nvc_free(nvc_device *dev, void *ptr);
+int32_t nvc_memcpy_h2d(nvc_device *dev, void *dst, const void *host_src, size_t bytes);
+int32_t nvc_memcpy_d2h(nvc_device *dev, void *host_dst, const void *src, size_t bytes);
+int32_t nvc_memcpy_d2d(nvc_device *dev, void *dst, const void *src, size_t bytes);
+int32_t nvc_memset(nvc_device *dev, void *dst, int value, size_t bytes);
+/* Pinned host staging memory for the copies above (host pointers). */
+int32_t nvc_host_alloc(size_t bytes, void **out);
+int32_t nvc_host_free(void *ptr);
+int32_t nvc_mem_stats_get(nvc_device *dev, nvc_mem_stats *out);
+int32_t nvc_set_memory_limit(nvc_device *dev, uint64_t bytes);
+int32_t nvc_set_cache_limit(nvc_device *dev, uint64_t bytes);
+int32_t nvc_clear_cache(nvc_device *dev);
+int32_t nvc_reset_peak(nvc_device *dev);
+
+/* ── events (timing on the handle's stream; the reference's profiler sums GPU timestamps per
+ *    dispatch, crates/nuvec-gpu/src/metal/profile.rs:1-65) ───────────────────────────── */
+int32_t nvc_event_create(nvc_device *dev, nvc_event **out);
+int32_t nvc_event_destroy(nvc_event *ev);
+int32_t nvc_event_record(nvc_device *dev, nvc_event *ev);
+int32_t nvc_event_synchronize(nvc_event *ev);
+int32_t nvc_event_elapsed_ms(nvc_event *start, nvc_event *stop, float *out_ms);
+
+/* ── recorded command sequences ──────────────────────────────────────────────────────────
+ * The reference's evaluator encodes many dispatches into one command buffer and commits it
+ * once (`defer` / `commit` / `flush`, crates/nuvec-core/src/gpu.rs:154-281).  The equivalent
+ * here: everything enqueued on the handle between begin and end is recorded instead of run,
+ * and the recording replays with one launch.  Run the sequence once before recording it, so
+ * that scratch buffers exist; allocation, frees and host copies are not allowed while
+ * recording. */
+int32_t nvc_graph_begin(nvc_device *dev);
+int32_t nvc_graph_end(nvc_device *dev, nvc_graph **out);
+int32_t nvc_graph_launch(nvc_device *dev, nvc_graph *graph);
+int32_t nvc_graph_destroy(nvc_graph *graph);
+
+/* ── the path ────────────────────────────────────────────────────────────────────────── */
+
+/* Primitive::Quantize -> kernels::quantize / fp_quantize
+ * (crates/nuvec-core/src/kernels.rs:774-831, 914-971; shape rule primitive.rs:1223-1259).
+ * w: [rows, cols] of `dtype` (F16/BF16/F32), cols % group_size == 0.
+ * out_codes: uint32 [rows, cols*bits/32].  Affine: out_scales/out_biases [rows, cols/gs] of
+ * `dtype`.  Other modes: out_scales uint8, out_biases NULL.  global_scale: one float32 on the
+ * device (nvfp4 only) or NULL. */
+int32_t nvc_quantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *w,
+                     int64_t rows, int64_t cols, const float *global_scale,
+                     uint32_t *out_codes, void *out_scales, void *out_biases);
+
+/* Primitive::Dequantize -> kernels::dequantize / fp_dequantize (kernels.rs:835-859, 976-1009).
+ * Affine: `dtype` is the dtype of scales, biases and out; `fused` = 0 rounds the product and
+ * the sum separately (the reference's CPU result, bit for bit), `fused` = 1 rounds
+ * fma(code, scale, bias) once (its Metal kernel, quantized.h:2701-2705).  Other modes: `dtype`
+ * is the output dtype, scales are uint8, biases NULL. */
+int32_t nvc_dequantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const uint32_t *codes,
+                       const void *scales, const void *biases, const float *global_scale,
+                       int64_t rows, int64_t cols, void *out, int32_t fused);
+
+/* Primitive::QuantizedMatmul (crates/nuvec-core/src/quantized.rs:453-537, shape rule
+ * primitive.rs:1279-1323; CPU result kernels.rs:1091-1142).
+ *   y[b] = x[b] (M x K, row stride ldx) * dequantize(w[b])^T      (transpose != 0)
+ *   y[b] = x[b] (M x K)                 * dequantize(w[b])        (transpose == 0)
+ * for b in [0, batch).  w[b] is [N, K*bits/32] (transposed) or [K, N*bits/32]; scales/biases
+ * [N, K/gs] or [K, N/gs].  Batch strides are in elements of the operand (0 broadcasts);
+ * scales and biases share one batch stride.  `dtype` is the dtype of x, y and (affine) of
+ * scales/biases.  y is dense [batch, M, N].  global_scale: one float32 (nvfp4) or NULL. */
+int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int32_t dtype,
+                             int32_t transpose, const void *x, const uint32_t *w,
+                             const void *scales, const void *biases, const float *global_scale,
+                             int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t batch,
+                             int64_t x_batch_stride, int64_t w_batch_stride,
+                             int64_t s_batch_stride, void *y);
+
+/* Primitive::SortedOffsets -> kernels::sorted_offsets (kernels.rs:875-892):
+ * out_offsets[g] = number of indices < g, for g in [0, groups); int32. */
+int32_t nvc_sorted_offsets(nvc_device *dev, const uint32_t *indices, int64_t rows,
+                           int64_t groups, int32_t *out_offsets);
+
+/* FastOp::GatherQmm (crates/nuvec-core/src/quantized.rs:589-719, fast/imp.rs:261-274):
+ *   y[i] = x[lhs[i]] (M x K) * dequantize(w[rhs[i]])^T     for i in [0, rows)
+ * x: [x_batches, M, K] dense; w: [experts, N, K*bits/32]; scales/biases [experts, N, K/gs];
+ * lhs (NULL = 0,1,2,...) and rhs: uint32 [rows]; y: [rows, M, N].  global_scale: float32
+ * [experts] (nvfp4) or NULL.  `sorted` != 0 promises rhs is non-decreasing; with M == 1,
+ * lhs == NULL and the reference's `grouped(rows, experts)` rule (quantized.rs:724-731) the
+ * rows of one expert are multiplied together.  `offsets` (int32 [experts], from
+ * nvc_sorted_offsets) may be NULL, in which case it is computed into scratch. */
+int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32_t transpose,
+                       const void *x, const uint32_t *w, const void *scales, const void *biases,
+                       const float *global_scale, const uint32_t *lhs, const uint32_t *rhs,
+                       const int32_t *offsets, int32_t sorted, int64_t rows, int64_t x_batches,
+                       int64_t M, int64_t N, int64_t K, int64_t experts, void *y);
+
+/* The same product with HOST operands for the activations and the result: copies x in,
+ * multiplies, copies y out and waits.  This is what an evaluator whose arrays live in host
+ * memory calls per step (the reference's CPU arrays, buffer.rs:17-27); the weights stay
+ * resident on the device. */
+int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q, int32_t dtype,
+                                  int32_t transpose, const void *host_x, const uint32_t *w,
+                                  const void *scales, const void *biases,
+                                  const float *global_scale, int64_t M, int64_t N, int64_t K,
+                                  void *host_y);
+
+/* ── collectives: trait Communicator, crates/nuvec-core/src/distributed.rs:43-83 ────── */
+
+/* One rank per process and per GPU (distributed.rs:145-180).  The 128-byte id is created on
+ * rank 0 and carried to the other ranks by the caller's bootstrap (the reference uses a
+ * hostfile, crates/nuvec-distributed/src/backend.rs:79-100). */
+int32_t nvc_comm_unique_id(uint8_t out_id[128]);
+int32_t nvc_comm_init(nvc_device *dev, int32_t rank, int32_t size, const uint8_t id[128],
+                      nvc_comm **out);
+int32_t nvc_comm_rank(nvc_comm *comm);
+int32_t nvc_comm_size(nvc_comm *comm);
+/* Communicator::all_gather(&[u8], &mut [u8]) (distributed.rs:52; ring.rs:868-889): recv holds
+ * size * bytes_per_rank bytes, rank r's block at offset r * bytes_per_rank.  In place when
+ * send == recv + rank * bytes_per_rank. */
+int32_t nvc_all_gather(nvc_comm *comm, const void *send, void *recv, size_t bytes_per_rank);
+/* Communicator::all_reduce(op = sum, dtype, &mut [u8]) (distributed.rs:50). */
+int32_t nvc_all_reduce_sum(nvc_comm *comm, int32_t dtype, void *buf, size_t count);
+/* Communicator::health (distributed.rs:66-70): NVC_OK or NVC_ERR_COMM with the async error. */
+int32_t nvc_comm_health(nvc_comm *comm);
+int32_t nvc_comm_abort(nvc_comm *comm);
+int32_t nvc_comm_destroy(nvc_comm *comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUVEC_CUDA_H */

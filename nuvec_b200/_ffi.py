@@ -1,0 +1,110 @@
+"""ctypes binding of libnuvec_cuda.so (include/nuvec_cuda.h).
+
+The library is the product: importing this module fails loudly when the shared object is
+missing or does not load -- there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libnuvec_cuda.so"
+
+OK = 0
+ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_OUT_OF_MEMORY, ERR_NO_DEVICE, ERR_DRIVER, ERR_COMM = -1, -2, -3, -4, -5, -6
+U8, U32, I32, F16, BF16, F32 = 1, 3, 7, 9, 10, 11
+AFFINE, MXFP4, MXFP8, NVFP4 = 0, 1, 2, 3
+
+
+class Quant(C.Structure):
+    _fields_ = [("mode", C.c_int32), ("group_size", C.c_int32), ("bits", C.c_int32)]
+
+
+class Info(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
+                ("multiprocessors", C.c_int32), ("driver_version", C.c_int32),
+                ("total_memory", C.c_uint64), ("l2_bytes", C.c_uint64)]
+
+
+class MemStats(C.Structure):
+    _fields_ = [("active", C.c_uint64), ("cached", C.c_uint64), ("peak", C.c_uint64),
+                ("limit", C.c_uint64), ("cache_limit", C.c_uint64), ("allocations", C.c_uint64)]
+
+
+P, I32T, I64T, SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
+QP = C.POINTER(Quant)
+
+# name -> (restype, argtypes); every symbol include/nuvec_cuda.h declares.
+SIGNATURES = {
+    "nvc_last_error": (None, [C.c_char_p, SZ]),
+    "nvc_version": (C.c_char_p, []),
+    "nvc_device_open": (I32T, [I32T, C.POINTER(P)]),
+    "nvc_device_close": (I32T, [P]),
+    "nvc_device_info": (I32T, [P, C.POINTER(Info)]),
+    "nvc_synchronize": (I32T, [P]),
+    "nvc_device_set_stream": (I32T, [P, P]),
+    "nvc_device_stream": (P, [P]),
+    "nvc_launch_count": (C.c_uint64, [P]),
+    "nvc_alloc": (I32T, [P, SZ, C.POINTER(P)]),
+    "nvc_free": (I32T, [P, P]),
+    "nvc_memcpy_h2d": (I32T, [P, P, P, SZ]),
+    "nvc_memcpy_d2h": (I32T, [P, P, P, SZ]),
+    "nvc_memcpy_d2d": (I32T, [P, P, P, SZ]),
+    "nvc_memset": (I32T, [P, P, C.c_int, SZ]),
+    "nvc_host_alloc": (I32T, [SZ, C.POINTER(P)]),
+    "nvc_host_free": (I32T, [P]),
+    "nvc_mem_stats_get": (I32T, [P, C.POINTER(MemStats)]),
+    "nvc_set_memory_limit": (I32T, [P, C.c_uint64]),
+    "nvc_set_cache_limit": (I32T, [P, C.c_uint64]),
+    "nvc_clear_cache": (I32T, [P]),
+    "nvc_reset_peak": (I32T, [P]),
+    "nvc_event_create": (I32T, [P, C.POINTER(P)]),
+    "nvc_event_destroy": (I32T, [P]),
+    "nvc_event_record": (I32T, [P, P]),
+    "nvc_event_synchronize": (I32T, [P]),
+    "nvc_event_elapsed_ms": (I32T, [P, P, C.POINTER(C.c_float)]),
+    "nvc_graph_begin": (I32T, [P]),
+    "nvc_graph_end": (I32T, [P, C.POINTER(P)]),
+    "nvc_graph_launch": (I32T, [P, P]),
+    "nvc_graph_destroy": (I32T, [P]),
+    "nvc_quantize": (I32T, [P, QP, I32T, P, I64T, I64T, P, P, P, P]),
+    "nvc_dequantize": (I32T, [P, QP, I32T, P, P, P, P, I64T, I64T, P, I32T]),
+    "nvc_quantized_matmul": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, I64T, I64T,
+                                    I64T, I64T, I64T, P]),
+    "nvc_sorted_offsets": (I32T, [P, P, I64T, I64T, P]),
+    "nvc_gather_qmm": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, P, P, P, I32T, I64T, I64T, I64T, I64T,
+                              I64T, I64T, P]),
+    "nvc_quantized_matmul_host": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, P]),
+    "nvc_comm_unique_id": (I32T, [P]),
+    "nvc_comm_init": (I32T, [P, I32T, I32T, P, C.POINTER(P)]),
+    "nvc_comm_rank": (I32T, [P]),
+    "nvc_comm_size": (I32T, [P]),
+    "nvc_all_gather": (I32T, [P, P, P, SZ]),
+    "nvc_all_reduce_sum": (I32T, [P, I32T, P, SZ]),
+    "nvc_comm_health": (I32T, [P]),
+    "nvc_comm_abort": (I32T, [P]),
+    "nvc_comm_destroy": (I32T, [P]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library, with every signature set.  Raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m nuvec_b200.build` "
+                              "(there is no CPU fallback)")
+        handle = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the export is missing
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(512)
+    lib().nvc_last_error(buf, 512)
+    return buf.value.decode(errors="replace")

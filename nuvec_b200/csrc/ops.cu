@@ -1,0 +1,245 @@
+// Entry points of the product operations: argument checks with the reference's rules and
+// messages (crates/nuvec-core/src/quantized.rs:137-167, 363-379, 453-537, 589-673;
+// crates/nuvec-core/src/primitive.rs:1279-1323) and the choice of kernel, which plays the part
+// of the reference's Metal routing (crates/nuvec-core/src/gpu.rs:6934-7168, 7174-7294):
+// few rows -> qmv, many rows -> qmm on tcgen05, anything else -> the generic kernel.
+#include "qmm.cuh"
+#include "qmv.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace nvc {
+
+static int32_t check_product(const char *op, const nvc_quant *q, int32_t dtype, int32_t transpose, const void *biases,
+                             const float *global, int64_t M, int64_t N, int64_t K) {
+    NVC_TRY(check_quant(op, q));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_UNSUPPORTED, "%s: unsupported dtype %d", op, dtype);
+    if (q->mode == NVC_AFFINE && !biases)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: biases must be provided for affine quantization", op);
+    if (q->mode != NVC_AFFINE && biases)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: biases must be null for this quantization mode", op);
+    if (global && q->mode != NVC_NVFP4)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: a global scale is only supported for nvfp4", op);
+    if (M < 0 || N < 0 || K < 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: negative dimension", op);
+    int64_t cols = transpose ? K : N;
+    if (cols % q->group_size != 0)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: %lld columns are not divisible by the group size %d", op,
+                         (long long)cols, q->group_size);
+    return NVC_OK;
+}
+
+// The reference's rule for the grouped kernel (quantized.rs:724-731): at least 16 rows and 4
+// per expert on average.
+static bool grouped(int64_t rows, int64_t experts) { return rows >= 16 && rows / (experts > 0 ? experts : 1) >= 4; }
+
+// Rows from which a plain product goes to the tensor-core kernel.  Below it the weights
+// stream once through the few-row kernel per 8 rows.
+static int64_t qmm_threshold() {
+    static int64_t v = [] {
+        const char *e = getenv("NUVEC_QMM_MIN_ROWS");
+        return e ? atoll(e) : 17;
+    }();
+    return v;
+}
+
+__global__ void sorted_offsets_kernel(const uint32_t *__restrict__ idx, int64_t rows, int64_t groups,
+                                      int32_t *__restrict__ out) {
+    int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    int64_t lo = 0, hi = rows;  // first index whose value is not below g
+    while (lo < hi) {
+        int64_t mid = lo + (hi - lo) / 2;
+        if ((int64_t)idx[mid] < g) lo = mid + 1;
+        else hi = mid;
+    }
+    out[g] = (int32_t)lo;
+}
+
+static int32_t run_sorted_offsets(nvc_device *dev, const uint32_t *indices, int64_t rows, int64_t groups,
+                                  int32_t *out) {
+    if (groups == 0) return NVC_OK;
+    sorted_offsets_kernel<<<(unsigned)((groups + 127) / 128), 128, 0, dev->stream>>>(indices, rows, groups, out);
+    return check_launch(dev, "sorted_offsets_kernel");
+}
+
+}  // namespace nvc
+
+using namespace nvc;
+
+extern "C" int32_t nvc_sorted_offsets(nvc_device *dev, const uint32_t *indices, int64_t rows, int64_t groups,
+                                      int32_t *out_offsets) {
+    NVC_TRY(make_current(dev));
+    if (rows < 0 || groups < 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "sorted_offsets: negative size");
+    if (groups > 0 && !out_offsets) return set_error(NVC_ERR_INVALID_ARGUMENT, "sorted_offsets: null output");
+    if (rows > 0 && !indices) return set_error(NVC_ERR_INVALID_ARGUMENT, "sorted_offsets: null indices");
+    return run_sorted_offsets(dev, indices, rows, groups, out_offsets);
+}
+
+extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32_t transpose,
+                                        const void *x, const uint32_t *w, const void *scales, const void *biases,
+                                        const float *global_scale, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                        int64_t batch, int64_t x_batch_stride, int64_t w_batch_stride,
+                                        int64_t s_batch_stride, void *y) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_product("quantized_matmul", q, dtype, transpose, biases, global_scale, M, N, K));
+    if (batch < 0 || ldx < K || x_batch_stride < 0 || w_batch_stride < 0 || s_batch_stride < 0)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul: invalid strides (ldx %lld, K %lld)", (long long)ldx,
+                         (long long)K);
+    if (batch == 0 || M == 0 || N == 0) return NVC_OK;
+    if (!x || !w || !scales || !y) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul: null operand");
+    if (K == 0) {
+        NVC_CUDA(cudaMemsetAsync(y, 0, (size_t)(batch * M * N) * dtype_size(dtype), dev->stream));
+        return NVC_OK;
+    }
+    if (M <= 8 && qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx,
+                                      x_batch_stride, w, w_batch_stride)) {
+        QmvParams p{};
+        p.x = x; p.w = w; p.scales = scales; p.biases = biases; p.lhs = nullptr; p.rhs = nullptr; p.y = y;
+        p.N = N; p.K = K; p.ldx = ldx;
+        p.x_batch_stride = x_batch_stride; p.w_batch_stride = w_batch_stride; p.s_batch_stride = s_batch_stride;
+        p.M = (int32_t)M; p.gs = q->group_size;
+        p.x_vec = ((uintptr_t)x % 16 == 0) && (ldx % 8 == 0) && (x_batch_stride % 8 == 0);
+        return launch_qmv_affine(dev, q->bits, p, batch);
+    }
+    if (M >= qmm_threshold() && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
+        for (int64_t b = 0; b < batch; b++) {
+            QmmParams p{};
+            p.mode = q->mode; p.gs = q->group_size; p.bits = q->bits;
+            p.x = (const char *)x + b * x_batch_stride * dtype_size(dtype);
+            p.w = w + b * w_batch_stride;
+            size_t ssz = q->mode == NVC_AFFINE ? dtype_size(dtype) : 1;
+            p.scales = (const char *)scales + b * s_batch_stride * ssz;
+            p.biases = biases ? (const char *)biases + b * s_batch_stride * ssz : nullptr;
+            p.global = global_scale; p.expert_global = 0; p.offsets = nullptr; p.experts = 1;
+            p.rows = M; p.N = N; p.K = K; p.ldx = ldx;
+            p.y = (char *)y + b * M * N * dtype_size(dtype);
+            NVC_TRY(launch_qmm(dev, p));
+        }
+        return NVC_OK;
+    }
+    GenericParams g{};
+    g.mode = q->mode; g.gs = q->group_size; g.bits = q->bits; g.dtype = dtype; g.transpose = transpose;
+    g.scalar_global = global_scale != nullptr; g.expert_global = 0;
+    g.x = x; g.w = w; g.scales = scales; g.biases = biases; g.global = global_scale; g.lhs = nullptr; g.rhs = nullptr;
+    g.M = M; g.N = N; g.K = K; g.ldx = ldx; g.batch = batch;
+    g.x_batch_stride = x_batch_stride; g.w_batch_stride = w_batch_stride; g.s_batch_stride = s_batch_stride;
+    g.y = y;
+    return launch_generic(dev, g);
+}
+
+extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32_t transpose, const void *x,
+                                  const uint32_t *w, const void *scales, const void *biases,
+                                  const float *global_scale, const uint32_t *lhs, const uint32_t *rhs,
+                                  const int32_t *offsets, int32_t sorted, int64_t rows, int64_t x_batches, int64_t M,
+                                  int64_t N, int64_t K, int64_t experts, void *y) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_product("gather_qmm", q, dtype, transpose, biases, global_scale, M, N, K));
+    if (rows < 0 || x_batches < 0 || experts < 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "gather_qmm: negative size");
+    if (rows == 0 || M == 0 || N == 0) return NVC_OK;
+    if (!x || !w || !scales || !y || !rhs) return set_error(NVC_ERR_INVALID_ARGUMENT, "gather_qmm: null operand");
+    if (K == 0) {
+        NVC_CUDA(cudaMemsetAsync(y, 0, (size_t)(rows * M * N) * dtype_size(dtype), dev->stream));
+        return NVC_OK;
+    }
+    const int64_t w_stride = (transpose ? N : K) * ((transpose ? K : N) * q->bits / 32);
+    const int64_t s_stride = (transpose ? N : K) * ((transpose ? K : N) / q->group_size);
+    // Sorted rows of one expert multiplied together (the reference's grouped kernel).
+    if (sorted && !lhs && M == 1 && grouped(rows, experts) &&
+        qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, rows, N, K, x, K, w)) {
+        const int32_t *offs = offsets;
+        if (!offs) {
+            void *scratch = nullptr;
+            NVC_TRY(ensure_scratch(dev, (size_t)experts * sizeof(int32_t), &scratch));
+            NVC_TRY(run_sorted_offsets(dev, rhs, rows, experts, (int32_t *)scratch));
+            offs = (const int32_t *)scratch;
+        }
+        QmmParams p{};
+        p.mode = q->mode; p.gs = q->group_size; p.bits = q->bits;
+        p.x = x; p.w = w; p.scales = scales; p.biases = biases;
+        p.global = global_scale; p.expert_global = global_scale != nullptr;
+        p.offsets = offs; p.experts = experts;
+        p.rows = rows; p.N = N; p.K = K; p.ldx = K; p.y = y;
+        return launch_qmm(dev, p);
+    }
+    if (M <= 8 && !global_scale &&
+        qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, K, M * K, w, w_stride)) {
+        QmvParams p{};
+        p.x = x; p.w = w; p.scales = scales; p.biases = biases; p.lhs = lhs; p.rhs = rhs; p.y = y;
+        p.N = N; p.K = K; p.ldx = K;
+        p.x_batch_stride = M * K; p.w_batch_stride = w_stride; p.s_batch_stride = s_stride;
+        p.M = (int32_t)M; p.gs = q->group_size;
+        p.x_vec = ((uintptr_t)x % 16 == 0) && (K % 8 == 0);
+        // Row batches beyond the grid limit go in slices.
+        for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+            int64_t n = rows - r0 < 65535 ? rows - r0 : 65535;
+            QmvParams s = p;
+            s.lhs = lhs ? lhs + r0 : nullptr;
+            s.rhs = rhs + r0;
+            if (!lhs) s.x = (const char *)x + r0 * M * K * dtype_size(dtype);
+            s.y = (char *)y + r0 * M * N * dtype_size(dtype);
+            NVC_TRY(launch_qmv_affine(dev, q->bits, s, n));
+        }
+        return NVC_OK;
+    }
+    GenericParams g{};
+    g.mode = q->mode; g.gs = q->group_size; g.bits = q->bits; g.dtype = dtype; g.transpose = transpose;
+    g.scalar_global = 0; g.expert_global = global_scale != nullptr;
+    g.w = w; g.scales = scales; g.biases = biases; g.global = global_scale;
+    g.M = M; g.N = N; g.K = K; g.ldx = K;
+    g.x_batch_stride = M * K; g.w_batch_stride = w_stride; g.s_batch_stride = s_stride;
+    for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+        int64_t n = rows - r0 < 65535 ? rows - r0 : 65535;
+        g.lhs = lhs ? lhs + r0 : nullptr;
+        g.rhs = rhs + r0;
+        g.x = lhs ? x : (const void *)((const char *)x + r0 * M * K * dtype_size(dtype));
+        g.y = (char *)y + r0 * M * N * dtype_size(dtype);
+        g.batch = n;
+        NVC_TRY(launch_generic(dev, g));
+    }
+    return NVC_OK;
+}
+
+static int32_t ensure_staging(nvc_device *dev, size_t host_bytes, size_t dev_bytes) {
+    if (dev->pinned_bytes < host_bytes) {
+        NVC_CUDA(cudaStreamSynchronize(dev->stream));
+        if (dev->pinned) cudaFreeHost(dev->pinned);
+        dev->pinned = nullptr;
+        dev->pinned_bytes = 0;
+        NVC_CUDA(cudaHostAlloc(&dev->pinned, host_bytes, cudaHostAllocDefault));
+        dev->pinned_bytes = host_bytes;
+    }
+    if (dev->staging_bytes < dev_bytes) {
+        NVC_CUDA(cudaStreamSynchronize(dev->stream));
+        if (dev->staging) NVC_TRY(dev->pool.free(dev->staging));
+        dev->staging = nullptr;
+        dev->staging_bytes = 0;
+        NVC_TRY(dev->pool.alloc(dev_bytes, &dev->staging));
+        dev->staging_bytes = dev_bytes;
+    }
+    return NVC_OK;
+}
+
+extern "C" int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32_t transpose,
+                                             const void *host_x, const uint32_t *w, const void *scales,
+                                             const void *biases, const float *global_scale, int64_t M, int64_t N,
+                                             int64_t K, void *host_y) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_product("quantized_matmul", q, dtype, transpose, biases, global_scale, M, N, K));
+    if (M == 0 || N == 0) return NVC_OK;
+    if (!host_x || !host_y) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul: null host operand");
+    const size_t xb = (size_t)(M * K) * dtype_size(dtype), yb = (size_t)(M * N) * dtype_size(dtype);
+    const size_t xoff = 0, yoff = (xb + 255) / 256 * 256;
+    NVC_TRY(ensure_staging(dev, yoff + yb, yoff + yb));
+    char *hp = (char *)dev->pinned, *dp = (char *)dev->staging;
+    // Pageable caller memory goes through the pinned block so both copies are asynchronous
+    // DMA transfers on the stream; a caller that passes pinned memory skips nothing but a memcpy.
+    memcpy(hp + xoff, host_x, xb);
+    NVC_CUDA(cudaMemcpyAsync(dp + xoff, hp + xoff, xb, cudaMemcpyHostToDevice, dev->stream));
+    NVC_TRY(nvc_quantized_matmul(dev, q, dtype, transpose, dp + xoff, w, scales, biases, global_scale, M, N, K, K, 1, 0,
+                                 0, 0, dp + yoff));
+    NVC_CUDA(cudaMemcpyAsync(hp + yoff, dp + yoff, yb, cudaMemcpyDeviceToHost, dev->stream));
+    NVC_CUDA(cudaStreamSynchronize(dev->stream));
+    memcpy(host_y, hp + yoff, yb);
+    return NVC_OK;
+}

@@ -1,0 +1,42 @@
+// Parameter blocks and launch entry points of the few-row product kernels (qmv.cu).
+#pragma once
+#include "common.cuh"
+
+namespace nvc {
+
+// Any product the fast kernels do not take.
+struct GenericParams {
+    int32_t mode, gs, bits, dtype, transpose;
+    int32_t scalar_global, expert_global;  // how `global` applies (nvfp4)
+    const void *x;
+    const uint32_t *w;
+    const void *scales, *biases;
+    const float *global;
+    const uint32_t *lhs, *rhs;  // gathered batches (rhs == nullptr: plain batches)
+    int64_t M, N, K, ldx, batch;
+    int64_t x_batch_stride, w_batch_stride, s_batch_stride;  // elements (w: uint32 words)
+    void *y;
+};
+int32_t launch_generic(nvc_device *dev, const GenericParams &p);
+
+// Fast affine path: bfloat16, transposed weights, up to 8 rows.
+struct QmvParams {
+    const void *x;
+    const uint32_t *w;
+    const void *scales, *biases;
+    const uint32_t *lhs, *rhs;
+    void *y;
+    float *partials;     // [tiles][ksplit][128] float32, used when ksplit > 1
+    uint32_t *counters;  // [tiles], zero on entry and on exit
+    int64_t N, K, ldx;
+    int64_t x_batch_stride, w_batch_stride, s_batch_stride;
+    int32_t M, gs, kr, ksplit, x_vec;
+};
+// Returns NVC_ERR_UNSUPPORTED (without setting an error message) when the shape is not one
+// the fast kernel takes; the caller then uses the generic kernel.
+bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
+                         int64_t N, int64_t K, const void *x, int64_t ldx, int64_t x_batch_stride, const uint32_t *w,
+                         int64_t w_batch_stride);
+int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch);
+
+}  // namespace nvc

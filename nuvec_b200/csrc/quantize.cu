@@ -1,0 +1,307 @@
+// quantize / dequantize kernels: the parity gates of the path.
+//
+// Every rounding the reference's CPU kernels perform is performed here in the same order, so
+// the outputs are equal bit for bit (crates/nuvec-core/src/kernels.rs:774-859 for affine,
+// :914-1009 for mxfp4 / mxfp8 / nvfp4; codecs crates/nuvec-core/src/fp8.rs:18-129).
+// Intrinsics with explicit rounding (__fmul_rn, __fadd_rn, __fdiv_rn) keep the compiler from
+// contracting or approximating any step.
+#include "common.cuh"
+
+namespace nvc {
+
+// ── dequantize ─────────────────────────────────────────────────────────────────────────
+
+// One thread decodes 8 consecutive values (8 * bits bits = `bits` whole bytes), which never
+// straddle a group because every group size is a multiple of 8.
+template <typename T, int BITS, bool FUSED>
+__global__ void __launch_bounds__(256)
+dequantize_affine_kernel(const uint8_t *__restrict__ codes, const T *__restrict__ scales,
+                         const T *__restrict__ biases, T *__restrict__ out, size_t packs, int gs) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= packs) return;
+    const uint8_t *src = codes + i * BITS;
+    uint64_t stream = 0;
+#pragma unroll
+    for (int b = 0; b < BITS; b++) stream |= (uint64_t)src[b] << (8 * b);
+    size_t first = i * 8;
+    size_t g = first / (size_t)gs;
+    float s = DT<T>::load(scales, g), bias = DT<T>::load(biases, g);
+    float vals[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float c = (float)(uint32_t)((stream >> (j * BITS)) & ((1u << BITS) - 1u));
+        if (FUSED) {
+            vals[j] = __fmaf_rn(c, s, bias);  // rounded once on store
+        } else {
+            float p = DT<T>::round(__fmul_rn(c, s));  // product rounded to T
+            vals[j] = __fadd_rn(p, bias);             // sum rounded to T on store
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) DT<T>::store(out, first + j, vals[j]);
+}
+
+// Floating-point modes: BITS == 4 -> two E2M1 codes per byte, low nibble first; BITS == 8 ->
+// one E4M3 code per byte.  One thread decodes 8 values.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256)
+dequantize_fp_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales,
+                     const float *__restrict__ global, T *__restrict__ out, size_t packs, int gs) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= packs) return;
+    size_t first = i * 8;
+    uint32_t sc = scales[first / (size_t)gs];
+    float scale = ftz(gs == 32 ? e8m0_to_f32(sc) : e4m3_to_f32(sc));
+    if (global) {
+        float inv = ftz(__fdiv_rn(*global, 448.0f * 6.0f));
+        scale = ftz(__fmul_rn(scale, inv));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float v;
+        if (BITS == 8) v = e4m3_to_f32(codes[first + j]);
+        else v = e2m1_to_f32((codes[(first + j) >> 1] >> (4 * (j & 1))) & 0xFu);
+        DT<T>::store(out, first + j, canonical(ftz(__fmul_rn(scale, v))));
+    }
+}
+
+template <typename T, bool FUSED>
+static int32_t launch_dequantize_affine(nvc_device *dev, int bits, const uint8_t *codes, const void *scales,
+                                        const void *biases, void *out, size_t packs, int gs) {
+    unsigned blocks = (unsigned)((packs + 255) / 256);
+#define NVC_CASE(B)                                                                               \
+    case B:                                                                                       \
+        dequantize_affine_kernel<T, B, FUSED><<<blocks, 256, 0, dev->stream>>>(                   \
+            codes, (const T *)scales, (const T *)biases, (T *)out, packs, gs);                    \
+        break;
+    switch (bits) {
+        NVC_CASE(1) NVC_CASE(2) NVC_CASE(3) NVC_CASE(4) NVC_CASE(5) NVC_CASE(6) NVC_CASE(8)
+    default: return set_error(NVC_ERR_INVALID_ARGUMENT, "dequantize: %d bits", bits);
+    }
+#undef NVC_CASE
+    return check_launch(dev, "dequantize_affine_kernel");
+}
+
+// ── quantize ───────────────────────────────────────────────────────────────────────────
+
+// One thread per group.  The arithmetic is float32 throughout, in the reference's order.
+template <typename T>
+__global__ void __launch_bounds__(128)
+quantize_affine_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, T *__restrict__ scales,
+                       T *__restrict__ biases, size_t groups, int gs, int bits) {
+    size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    const size_t base = g * (size_t)gs;
+    float lo = __int_as_float(0x7F800000), hi = __int_as_float(0xFF800000);
+    for (int j = 0; j < gs; j++) {
+        float v = DT<T>::load(w, base + j);
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
+    }
+    const float n_bins = (float)((1u << bits) - 1u), eps = 1e-7f;
+    float scale, bias;
+    if (bits == 1) {
+        scale = fmaxf(__fsub_rn(hi, lo), eps);
+        bias = lo;
+    } else {
+        bool wide = fabsf(lo) > fabsf(hi);
+        scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), n_bins), eps);
+        scale = wide ? scale : -scale;
+        float edge = wide ? lo : hi;
+        float q0 = rintf(__fdiv_rn(edge, scale));
+        if (q0 == 0.0f) {
+            bias = 0.0f;
+        } else {
+            scale = __fdiv_rn(edge, q0);
+            bias = edge;
+        }
+    }
+    uint8_t *dst = codes + base * (size_t)bits / 8;
+    uint64_t acc = 0;
+    int have = 0;
+    for (int j = 0; j < gs; j++) {
+        float v = DT<T>::load(w, base + j);
+        float r = rintf(__fdiv_rn(__fsub_rn(v, bias), scale));
+        r = r < 0.0f ? 0.0f : (r > n_bins ? n_bins : r);
+        uint32_t q = (r != r) ? 0u : (uint32_t)r;
+        acc |= (uint64_t)q << have;
+        have += bits;
+        while (have >= 8) {
+            *dst++ = (uint8_t)acc;
+            acc >>= 8;
+            have -= 8;
+        }
+    }
+    DT<T>::store(scales, g, scale);
+    DT<T>::store(biases, g, bias);
+}
+
+// fp8.rs:18-36
+__device__ __forceinline__ uint32_t e4m3_from_f32(float x) {
+    const uint32_t FP8_MAX = 543u << 21, DENORM_MASK = 141u << 23;
+    uint32_t bits = __float_as_uint(x);
+    uint32_t sign = bits & 0x80000000u;
+    bits ^= sign;
+    uint32_t code;
+    if (bits >= FP8_MAX) {
+        code = 0x7E;
+    } else if (bits < (121u << 23)) {
+        float sum = __fadd_rn(__uint_as_float(bits), __uint_as_float(DENORM_MASK));
+        code = (__float_as_uint(sum) - DENORM_MASK) & 0xFFu;
+    } else {
+        uint32_t odd = (bits >> 20) & 1u;
+        bits += ((uint32_t)(7 - 127) << 23) + 0x7FFFFu;
+        bits += odd;
+        code = (bits >> 20) & 0xFFu;
+    }
+    return code | (sign >> 24);
+}
+
+// fp8.rs:48-73
+__device__ __forceinline__ uint32_t e2m1_from_f32(float x) {
+    if (x != x) return 0x7u;
+    uint32_t sign = (__float_as_uint(x) >> 31) ? 0x8u : 0x0u;
+    float a = fabsf(x);
+    uint32_t code = a > 5.0f ? 7u : a >= 3.5f ? 6u : a > 2.5f ? 5u : a >= 1.75f ? 4u
+                  : a > 1.25f ? 3u : a >= 0.75f ? 2u : a > 0.25f ? 1u : 0u;
+    return code | sign;
+}
+
+// The E8M0 code of mx_scale_round_up(x) for x >= 0 (fp8.rs:84-93, 124-130): the smallest
+// power of two that is not below x, i.e. the exponent field, plus one when any mantissa bit
+// is set, capped at 254; 0 for zero and 0xFF for Inf/NaN.
+__device__ __forceinline__ uint32_t mx_scale_code(float x) {
+    uint32_t u = __float_as_uint(x);
+    uint32_t e = (u >> 23) & 0xFFu, m = u & 0x7FFFFFu;
+    if (e == 0xFFu) return 0xFFu;
+    if (e == 0u) return 0u;  // x was flushed: zero
+    uint32_t code = e + (m != 0u ? 1u : 0u);
+    return code > 254u ? 254u : code;
+}
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(128)
+quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales,
+                   const float *__restrict__ global, size_t groups, int gs) {
+    size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    const size_t base = g * (size_t)gs;
+    const bool mx = gs == 32;
+    const float max_element = BITS == 4 ? 6.0f : 448.0f;
+    const bool has = global != nullptr;
+    const float scale_enc = has ? ftz(__fdiv_rn(448.0f * 6.0f, *global)) : 1.0f;
+    float amax = 0.0f;
+    for (int j = 0; j < gs; j++) amax = fmaxf(amax, fabsf(ftz(DT<T>::load(w, base + j))));
+    float scale = ftz(__fdiv_rn(amax, max_element));
+    if (has) scale = ftz(__fmul_rn(scale, scale_enc));
+    uint32_t code;
+    float decoded;
+    if (mx && !has) {
+        code = mx_scale_code(scale);
+        decoded = e8m0_to_f32(code);
+    } else {
+        code = e4m3_from_f32(scale);
+        decoded = e4m3_to_f32(code);
+    }
+    scales[g] = (uint8_t)code;
+    decoded = ftz(decoded);
+    float inverse = decoded == 0.0f ? 0.0f : ftz(__fdiv_rn(has ? scale_enc : 1.0f, decoded));
+    for (int j = 0; j < gs; j += 2) {
+        float a = canonical(ftz(__fmul_rn(ftz(DT<T>::load(w, base + j)), inverse)));
+        float b = canonical(ftz(__fmul_rn(ftz(DT<T>::load(w, base + j + 1)), inverse)));
+        if (BITS == 8) {
+            codes[base + j] = (uint8_t)e4m3_from_f32(a);
+            codes[base + j + 1] = (uint8_t)e4m3_from_f32(b);
+        } else {
+            codes[(base + j) >> 1] = (uint8_t)(e2m1_from_f32(a) | (e2m1_from_f32(b) << 4));
+        }
+    }
+}
+
+template <typename T>
+static int32_t quantize_typed(nvc_device *dev, const nvc_quant *q, const void *w, size_t count,
+                              const float *global, uint32_t *codes, void *scales, void *biases) {
+    size_t groups = count / (size_t)q->group_size;
+    unsigned blocks = (unsigned)((groups + 127) / 128);
+    if (q->mode == NVC_AFFINE) {
+        quantize_affine_kernel<T><<<blocks, 128, 0, dev->stream>>>((const T *)w, (uint8_t *)codes, (T *)scales,
+                                                                    (T *)biases, groups, q->group_size, q->bits);
+        return check_launch(dev, "quantize_affine_kernel");
+    }
+    if (q->bits == 4)
+        quantize_fp_kernel<T, 4><<<blocks, 128, 0, dev->stream>>>((const T *)w, (uint8_t *)codes, (uint8_t *)scales,
+                                                                   global, groups, q->group_size);
+    else
+        quantize_fp_kernel<T, 8><<<blocks, 128, 0, dev->stream>>>((const T *)w, (uint8_t *)codes, (uint8_t *)scales,
+                                                                   global, groups, q->group_size);
+    return check_launch(dev, "quantize_fp_kernel");
+}
+
+template <typename T>
+static int32_t dequantize_typed(nvc_device *dev, const nvc_quant *q, const uint32_t *codes, const void *scales,
+                                const void *biases, const float *global, size_t count, void *out, int fused) {
+    size_t packs = count / 8;
+    const uint8_t *bytes = (const uint8_t *)codes;
+    if (q->mode == NVC_AFFINE) {
+        return fused ? launch_dequantize_affine<T, true>(dev, q->bits, bytes, scales, biases, out, packs, q->group_size)
+                     : launch_dequantize_affine<T, false>(dev, q->bits, bytes, scales, biases, out, packs, q->group_size);
+    }
+    unsigned blocks = (unsigned)((packs + 255) / 256);
+    if (q->bits == 4)
+        dequantize_fp_kernel<T, 4><<<blocks, 256, 0, dev->stream>>>(bytes, (const uint8_t *)scales, global, (T *)out, packs, q->group_size);
+    else
+        dequantize_fp_kernel<T, 8><<<blocks, 256, 0, dev->stream>>>(bytes, (const uint8_t *)scales, global, (T *)out, packs, q->group_size);
+    return check_launch(dev, "dequantize_fp_kernel");
+}
+
+}  // namespace nvc
+
+using namespace nvc;
+
+extern "C" int32_t nvc_quantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *w, int64_t rows,
+                                int64_t cols, const float *global_scale, uint32_t *out_codes, void *out_scales,
+                                void *out_biases) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("quantize", q));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_UNSUPPORTED, "quantize: unsupported dtype %d", dtype);
+    if (rows < 0 || cols < 0 || cols % q->group_size != 0)
+        return set_error(NVC_ERR_INVALID_ARGUMENT,
+                         "quantize: needs at least 2 dimensions with the last divisible by the group size %d, got [%lld, %lld]",
+                         q->group_size, (long long)rows, (long long)cols);
+    if (global_scale && q->mode != NVC_NVFP4)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "quantize: a global scale is only supported for nvfp4");
+    if (q->mode == NVC_AFFINE && !out_biases) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantize: affine needs a biases output");
+    size_t count = (size_t)rows * (size_t)cols;
+    if (count == 0) return NVC_OK;
+    if (!w || !out_codes || !out_scales) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantize: null operand");
+    switch (dtype) {
+    case NVC_F32: return quantize_typed<float>(dev, q, w, count, global_scale, out_codes, out_scales, out_biases);
+    case NVC_F16: return quantize_typed<__half>(dev, q, w, count, global_scale, out_codes, out_scales, out_biases);
+    default: return quantize_typed<__nv_bfloat16>(dev, q, w, count, global_scale, out_codes, out_scales, out_biases);
+    }
+}
+
+extern "C" int32_t nvc_dequantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const uint32_t *codes,
+                                  const void *scales, const void *biases, const float *global_scale, int64_t rows,
+                                  int64_t cols, void *out, int32_t fused) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("dequantize", q));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_UNSUPPORTED, "dequantize: unsupported dtype %d", dtype);
+    if (q->mode == NVC_AFFINE && !biases)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "dequantize: biases must be provided for affine quantization");
+    if (q->mode != NVC_AFFINE && biases)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "dequantize: biases must be null for this quantization mode");
+    if (global_scale && q->mode != NVC_NVFP4)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "dequantize: a global scale is only supported for nvfp4");
+    if (rows < 0 || cols < 0 || cols % q->group_size != 0)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "dequantize: %lld columns are not divisible by the group size %d",
+                         (long long)cols, q->group_size);
+    size_t count = (size_t)rows * (size_t)cols;
+    if (count == 0) return NVC_OK;
+    if (!codes || !scales || !out) return set_error(NVC_ERR_INVALID_ARGUMENT, "dequantize: null operand");
+    switch (dtype) {
+    case NVC_F32: return dequantize_typed<float>(dev, q, codes, scales, biases, global_scale, count, out, fused);
+    case NVC_F16: return dequantize_typed<__half>(dev, q, codes, scales, biases, global_scale, count, out, fused);
+    default: return dequantize_typed<__nv_bfloat16>(dev, q, codes, scales, biases, global_scale, count, out, fused);
+    }
+}

@@ -1,0 +1,658 @@
+"""Host-side mirror of nuvec's quantized operations over the CUDA backend.
+
+Same names, argument meaning and error behaviour as the reference's op layer
+(crates/nuvec-core/src/ops.rs:967-1078 and quantized.rs): ``quantize``, ``dequantize``,
+``quantized_matmul``, ``gather_qmm``, the types ``QuantMode``, ``Quant``, ``Quantized`` and
+``GatherQmm``.  Every computation runs in libnuvec_cuda.so; this module only checks shapes,
+promotes dtypes, broadcasts batches and marshals pointers, as the reference's Rust layer does
+before it reaches a backend.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass, replace
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _ffi
+from ._ffi import BF16, F16, F32, I32, U8, U32
+
+__all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "NuvecError", "InvalidArgument",
+           "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
+           "f32_to_bf16", "bf16_to_f32"]
+
+
+# ── errors (crates/nuvec-core/src/error.rs:17-42) ──────────────────────────────────────────
+class NuvecError(Exception):
+    pass
+
+
+class InvalidArgument(NuvecError, ValueError):
+    pass
+
+
+class UnsupportedError(NuvecError):
+    pass
+
+
+class OutOfMemory(NuvecError, MemoryError):
+    pass
+
+
+class NoDevice(NuvecError):
+    pass
+
+
+class BackendError(NuvecError):
+    pass
+
+
+class CommError(NuvecError):
+    pass
+
+
+_ERRORS = {_ffi.ERR_INVALID_ARGUMENT: InvalidArgument, _ffi.ERR_UNSUPPORTED: UnsupportedError,
+           _ffi.ERR_OUT_OF_MEMORY: OutOfMemory, _ffi.ERR_NO_DEVICE: NoDevice,
+           _ffi.ERR_DRIVER: BackendError, _ffi.ERR_COMM: CommError}
+
+
+def _check(status: int):
+    if status != _ffi.OK:
+        raise _ERRORS.get(status, BackendError)(_ffi.last_error())
+
+
+# ── dtypes ─────────────────────────────────────────────────────────────────────────────────
+_ITEMSIZE = {U8: 1, U32: 4, I32: 4, F16: 2, BF16: 2, F32: 4}
+_NP = {U8: np.uint8, U32: np.uint32, I32: np.int32, F16: np.float16, BF16: np.uint16, F32: np.float32}
+_FLOATS = (F16, BF16, F32)
+DTYPE_NAMES = {U8: "uint8", U32: "uint32", I32: "int32", F16: "float16", BF16: "bfloat16", F32: "float32"}
+
+
+def f32_to_bf16(a) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns (uint16), round to nearest even."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    u = a.view(np.uint32)
+    nan = (u & 0x7FFFFFFF) > 0x7F800000
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return np.where(nan, ((u >> 16) | 0x40).astype(np.uint16), r)
+
+
+def bf16_to_f32(a) -> np.ndarray:
+    return (np.asarray(a, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def promote_types(a: int, b: int) -> int:
+    """The common float dtype of two float dtypes (MLX's promotion: unequal halves -> f32)."""
+    if a == b:
+        return a
+    return F32
+
+
+# ── device and arrays ──────────────────────────────────────────────────────────────────────
+class Device:
+    """One GPU with its stream and pool (crates/nuvec-gpu/src/cuda/device.rs:77-227)."""
+
+    _shared = {}
+
+    def __init__(self, ordinal: int = 0):
+        h = C.c_void_p()
+        _check(_ffi.lib().nvc_device_open(ordinal, C.byref(h)))
+        self._h, self.ordinal = h, ordinal
+
+    @classmethod
+    def shared(cls, ordinal: int = 0) -> "Device":
+        if ordinal not in cls._shared:
+            cls._shared[ordinal] = cls(ordinal)
+        return cls._shared[ordinal]
+
+    def close(self):
+        if self._h:
+            _check(_ffi.lib().nvc_device_close(self._h))
+            self._h = None
+            Device._shared.pop(self.ordinal, None)
+
+    def info(self) -> dict:
+        i = _ffi.Info()
+        _check(_ffi.lib().nvc_device_info(self._h, C.byref(i)))
+        return {"name": i.name.decode(), "compute_capability": (i.cc_major, i.cc_minor),
+                "multiprocessors": i.multiprocessors, "driver_version": i.driver_version,
+                "total_memory": i.total_memory, "l2_bytes": i.l2_bytes}
+
+    def synchronize(self):
+        _check(_ffi.lib().nvc_synchronize(self._h))
+
+    def set_stream(self, cuda_stream: Optional[int]):
+        _check(_ffi.lib().nvc_device_set_stream(self._h, C.c_void_p(cuda_stream or 0)))
+
+    @property
+    def launches(self) -> int:
+        return int(_ffi.lib().nvc_launch_count(self._h))
+
+    def memory(self) -> dict:
+        s = _ffi.MemStats()
+        _check(_ffi.lib().nvc_mem_stats_get(self._h, C.byref(s)))
+        return {k: int(getattr(s, k)) for k, _ in _ffi.MemStats._fields_}
+
+    def set_memory_limit(self, n: int):
+        _check(_ffi.lib().nvc_set_memory_limit(self._h, n))
+
+    def set_cache_limit(self, n: int):
+        _check(_ffi.lib().nvc_set_cache_limit(self._h, n))
+
+    def clear_cache(self):
+        _check(_ffi.lib().nvc_clear_cache(self._h))
+
+    def reset_peak(self):
+        _check(_ffi.lib().nvc_reset_peak(self._h))
+
+    # arrays
+    def empty(self, shape: Sequence[int], dtype: int) -> "Array":
+        return Array(self, tuple(int(d) for d in shape), dtype)
+
+    def array(self, data, dtype: Optional[int] = None) -> "Array":
+        """Uploads a numpy array.  bfloat16 travels as uint16 bit patterns with dtype=BF16."""
+        data = np.asarray(data)
+        if dtype is None:
+            dtype = {np.dtype(np.float32): F32, np.dtype(np.float16): F16, np.dtype(np.uint32): U32,
+                     np.dtype(np.uint8): U8, np.dtype(np.int32): I32}.get(data.dtype)
+            if dtype is None:
+                raise InvalidArgument(f"cannot infer a device dtype for numpy {data.dtype}; pass dtype=")
+        host = np.ascontiguousarray(data, dtype=_NP[dtype] if dtype != F16 else np.float16)
+        out = self.empty(host.shape, dtype)
+        if host.nbytes:
+            _check(_ffi.lib().nvc_memcpy_h2d(self._h, out.ptr, host.ctypes.data_as(C.c_void_p), host.nbytes))
+            self.synchronize()  # the numpy buffer may be pageable and go away
+        return out
+
+    def event(self) -> "Event":
+        return Event(self)
+
+    def record(self, fn) -> "Graph":
+        """Records the stream work `fn()` enqueues (run it once beforehand so scratch exists)
+        and returns a replayable graph -- the analogue of one committed command buffer."""
+        _check(_ffi.lib().nvc_graph_begin(self._h))
+        try:
+            fn()
+        finally:
+            h = C.c_void_p()
+            status = _ffi.lib().nvc_graph_end(self._h, C.byref(h))
+        _check(status)
+        return Graph(self, h)
+
+
+class Graph:
+    def __init__(self, dev: Device, h):
+        self._dev, self._h = dev, h
+
+    def launch(self):
+        _check(_ffi.lib().nvc_graph_launch(self._dev._h, self._h))
+
+    def __del__(self):
+        try:
+            if self._h:
+                _ffi.lib().nvc_graph_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class Event:
+    def __init__(self, dev: Device):
+        h = C.c_void_p()
+        _check(_ffi.lib().nvc_event_create(dev._h, C.byref(h)))
+        self._h, self._dev = h, dev
+
+    def record(self):
+        _check(_ffi.lib().nvc_event_record(self._dev._h, self._h))
+        return self
+
+    def synchronize(self):
+        _check(_ffi.lib().nvc_event_synchronize(self._h))
+
+    def elapsed_ms(self, later: "Event") -> float:
+        out = C.c_float()
+        _check(_ffi.lib().nvc_event_elapsed_ms(self._h, later._h, C.byref(out)))
+        return float(out.value)
+
+    def __del__(self):
+        try:
+            if self._h:
+                _ffi.lib().nvc_event_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class Array:
+    """A dense row-major device buffer with a shape and a dtype code.
+
+    `view` arrays share another array's storage at a byte offset (sliced weights, rows of x).
+    """
+
+    def __init__(self, dev: Device, shape, dtype: int, _base: "Array" = None, _offset: int = 0):
+        self.dev, self.shape, self.dtype = dev, tuple(shape), dtype
+        self._base, self._offset = _base, _offset
+        if _base is None:
+            p = C.c_void_p()
+            _check(_ffi.lib().nvc_alloc(dev._h, max(self.nbytes, 1), C.byref(p)))
+            self._ptr = p.value
+        else:
+            self._ptr = None
+
+    @property
+    def ptr(self) -> C.c_void_p:
+        base = self._ptr if self._base is None else self._base.ptr.value
+        return C.c_void_p(base + self._offset)
+
+    @property
+    def size(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    @property
+    def itemsize(self) -> int:
+        return _ITEMSIZE[self.dtype]
+
+    @property
+    def nbytes(self) -> int:
+        return self.size * self.itemsize
+
+    def reshape(self, *shape) -> "Array":
+        shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list)) else tuple(shape)
+        if -1 in shape:
+            known = -int(np.prod(shape))
+            shape = tuple(self.size // known if d == -1 else d for d in shape)
+        assert int(np.prod(shape)) == self.size, (shape, self.shape)
+        root = self if self._base is None else self._base
+        return Array(self.dev, shape, self.dtype, _base=root, _offset=self._offset)
+
+    def __getitem__(self, index) -> "Array":
+        """Leading-axis integer or slice (a contiguous view)."""
+        inner = int(np.prod(self.shape[1:])) if self.ndim > 1 else 1
+        root = self if self._base is None else self._base
+        if isinstance(index, slice):
+            start, stop, step = index.indices(self.shape[0])
+            assert step == 1
+            return Array(self.dev, (max(stop - start, 0),) + self.shape[1:], self.dtype, _base=root,
+                         _offset=self._offset + start * inner * self.itemsize)
+        i = int(index) % self.shape[0]
+        return Array(self.dev, self.shape[1:], self.dtype, _base=root,
+                     _offset=self._offset + i * inner * self.itemsize)
+
+    def to_numpy(self) -> np.ndarray:
+        host = np.empty(self.shape, dtype=_NP[self.dtype])
+        if host.nbytes:
+            _check(_ffi.lib().nvc_memcpy_d2h(self.dev._h, host.ctypes.data_as(C.c_void_p), self.ptr, host.nbytes))
+        return host
+
+    def to_f32(self) -> np.ndarray:
+        host = self.to_numpy()
+        return bf16_to_f32(host) if self.dtype == BF16 else host.astype(np.float32)
+
+    def astype(self, dtype: int) -> "Array":
+        """dtype conversion of float arrays (round to nearest even), done through the host: it
+        only runs where the reference promotes mismatched operand dtypes."""
+        if dtype == self.dtype:
+            return self
+        f = self.to_f32()
+        if dtype == BF16:
+            return self.dev.array(f32_to_bf16(f), BF16)
+        return self.dev.array(f.astype(_NP[dtype]), dtype)
+
+    def copy_from(self, other: "Array"):
+        assert other.nbytes == self.nbytes
+        _check(_ffi.lib().nvc_memcpy_d2d(self.dev._h, self.ptr, other.ptr, self.nbytes))
+
+    def __del__(self):
+        try:
+            if self._base is None and self._ptr and self.dev._h:
+                _ffi.lib().nvc_free(self.dev._h, C.c_void_p(self._ptr))
+                self._ptr = None
+        except Exception:
+            pass
+
+
+# ── quantization descriptors (crates/nuvec-core/src/quantized.rs:24-168, 195-359) ──────────
+class QuantMode(enum.Enum):
+    AFFINE = "affine"
+    MXFP4 = "mxfp4"
+    MXFP8 = "mxfp8"
+    NVFP4 = "nvfp4"
+
+    @classmethod
+    def parse(cls, s: str) -> "QuantMode":
+        try:
+            return cls(s)
+        except ValueError:
+            raise InvalidArgument(f"invalid quantization mode '{s}' (affine, mxfp4, mxfp8 or nvfp4)") from None
+
+    @property
+    def code(self) -> int:
+        return {"affine": 0, "mxfp4": 1, "mxfp8": 2, "nvfp4": 3}[self.value]
+
+    def defaults(self):
+        return {"affine": (64, 4), "mxfp4": (32, 4), "mxfp8": (32, 8), "nvfp4": (16, 4)}[self.value]
+
+
+@dataclass(frozen=True)
+class Quant:
+    mode: QuantMode = QuantMode.AFFINE
+    group_size: int = 64
+    bits: int = 4
+
+    @classmethod
+    def new(cls, mode: QuantMode) -> "Quant":
+        g, b = mode.defaults()
+        return cls(mode, g, b)
+
+    @classmethod
+    def affine(cls, group_size: int, bits: int) -> "Quant":
+        return cls(QuantMode.AFFINE, group_size, bits)
+
+    def with_group_size(self, g: int) -> "Quant":
+        return replace(self, group_size=g)
+
+    def with_bits(self, b: int) -> "Quant":
+        return replace(self, bits=b)
+
+    def checked(self, op: str):
+        """quantized.rs:137-167"""
+        g, b = self.group_size, self.bits
+        if self.mode == QuantMode.AFFINE:
+            if g not in (32, 64, 128):
+                raise InvalidArgument(f"{op}: group size {g} is not supported (32, 64 or 128)")
+            if b not in (1, 2, 3, 4, 5, 6, 8):
+                raise InvalidArgument(f"{op}: {b} bits are not supported (1, 2, 3, 4, 5, 6 or 8)")
+        else:
+            eg, eb = self.mode.defaults()
+            if g != eg:
+                raise InvalidArgument(f"{op}: {self.mode.value} quantization requires group size {eg} but got {g}")
+            if b != eb:
+                raise InvalidArgument(f"{op}: {self.mode.value} quantization requires bits to be {eb} but got {b}")
+        return g, b
+
+    def _c(self) -> _ffi.Quant:
+        return _ffi.Quant(self.mode.code, self.group_size, self.bits)
+
+
+@dataclass
+class Quantized:
+    """Packed codes (uint32), one scale per group, affine biases, an optional NVFP4 global
+    scale and how they were quantized (quantized.rs:195-278)."""
+    weight: Array
+    scales: Array
+    biases: Optional[Array] = None
+    quant: Quant = Quant()
+    global_scale: Optional[Array] = None
+
+    def with_global_scale(self, g: Array) -> "Quantized":
+        return replace(self, global_scale=g)
+
+    def dequantize(self, dtype: Optional[int] = None) -> Array:
+        return dequantize(self, dtype)
+
+
+@dataclass(frozen=True)
+class GatherQmm:
+    """Options of gather_qmm (quantized.rs:318-359)."""
+    transpose: bool = True
+    sorted_indices: bool = False
+
+    @staticmethod
+    def groups(rows: int, experts: int) -> bool:
+        """quantized.rs:724-731: the grouped kernel needs 16 rows and 4 per expert."""
+        return rows >= 16 and rows // max(experts, 1) >= 4
+
+    def with_transpose(self, t: bool) -> "GatherQmm":
+        return replace(self, transpose=t)
+
+    def with_sorted_indices(self, s: bool) -> "GatherQmm":
+        return replace(self, sorted_indices=s)
+
+
+def _check_groups(op: str, mode: QuantMode, scales: Array, biases: Optional[Array]):
+    """quantized.rs:363-379"""
+    if mode == QuantMode.AFFINE:
+        if biases is None:
+            raise InvalidArgument(f"{op}: biases must be provided for affine quantization")
+        return
+    if biases is not None:
+        raise InvalidArgument(f"{op}: biases must be null for quantization mode '{mode.value}'")
+    if scales.dtype != U8:
+        raise InvalidArgument(f"{op}: scale type must be uint8 but received type {DTYPE_NAMES[scales.dtype]}")
+
+
+def _check_global(op: str, quant: Quant, g: Optional[Array], experts_shape=None):
+    if g is None:
+        return
+    if quant.mode != QuantMode.NVFP4:
+        raise InvalidArgument(f"{op}: a global scale is only supported for nvfp4, got {quant.mode.value}")
+    if experts_shape is None:
+        if g.size != 1 or g.dtype != F32:
+            raise InvalidArgument(f"{op}: the global scale must be one float32 value, got "
+                                  f"{DTYPE_NAMES[g.dtype]} {list(g.shape)}")
+    else:
+        if g.dtype != F32:
+            raise InvalidArgument(f"{op}: global scale must have dtype float32 but got {DTYPE_NAMES[g.dtype]}")
+        if tuple(g.shape) != tuple(experts_shape):
+            raise InvalidArgument(f"{op}: global scale must have one entry per expert with shape "
+                                  f"{list(experts_shape)} but got {list(g.shape)}")
+
+
+def _ptr(a: Optional[Array]):
+    return None if a is None else a.ptr
+
+
+def _columns(op: str, w: Array, scales: Array, biases: Optional[Array], quant: Quant) -> int:
+    """Values per row of packed codes after the reference's checks (primitive.rs:1405-1460)."""
+    g, b = quant.checked(op)
+    if w.dtype != U32 or w.ndim < 2:
+        raise InvalidArgument(f"{op}: the packed weights must be uint32 with at least 2 dimensions, got "
+                              f"{DTYPE_NAMES[w.dtype]} {list(w.shape)}")
+    cols = w.shape[-1] * 32 // b
+    want = w.shape[:-1] + (cols // g,)
+    if cols % g != 0 or tuple(scales.shape) != want or (biases is not None and tuple(biases.shape) != want):
+        raise InvalidArgument(f"{op}: scales{'/biases' if biases is not None else ''} of shape {list(scales.shape)} "
+                              f"do not match weights {list(w.shape)} with group size {g} and {b} bits")
+    return cols
+
+
+# ── operations ─────────────────────────────────────────────────────────────────────────────
+def quantize(w: Array, quant=Quant(), global_scale: Optional[Array] = None) -> Quantized:
+    """ops::quantize (ops.rs:967-1009): quantizes the last axis of `w`."""
+    if isinstance(quant, QuantMode):
+        quant = Quant.new(quant)
+    g, b = quant.checked("quantize")
+    _check_global("quantize", quant, global_scale)
+    if w.dtype not in _FLOATS:
+        raise UnsupportedError(f"quantize: unsupported dtype {DTYPE_NAMES[w.dtype]}")
+    if w.ndim < 2 or w.shape[-1] % g != 0:
+        raise InvalidArgument(f"quantize: needs at least 2 dimensions with the last divisible by the group size "
+                              f"{g}, got shape {list(w.shape)}")
+    cols = w.shape[-1]
+    rows = w.size // cols if cols else 0
+    dev = w.dev
+    codes = dev.empty(w.shape[:-1] + (cols * b // 32,), U32)
+    gshape = w.shape[:-1] + (cols // g,)
+    affine = quant.mode == QuantMode.AFFINE
+    scales = dev.empty(gshape, w.dtype if affine else U8)
+    biases = dev.empty(gshape, w.dtype) if affine else None
+    q = quant._c()
+    _check(_ffi.lib().nvc_quantize(dev._h, C.byref(q), w.dtype, w.ptr, rows, cols, _ptr(global_scale), codes.ptr,
+                                   scales.ptr, _ptr(biases)))
+    return Quantized(codes, scales, biases, quant, global_scale)
+
+
+def dequantize(q: Quantized, dtype: Optional[int] = None, fused: bool = False) -> Array:
+    """ops::dequantize (ops.rs:1014-1027; quantized.rs:401-444).  `fused` selects the single
+    rounding of the reference's Metal kernel instead of its CPU result."""
+    quant = q.quant
+    quant.checked("dequantize")
+    _check_groups("dequantize", quant.mode, q.scales, q.biases)
+    if dtype is not None and dtype not in _FLOATS:
+        raise InvalidArgument(f"dequantize: only real floating types are supported but the output dtype is "
+                              f"{DTYPE_NAMES.get(dtype, dtype)}")
+    _check_global("dequantize", quant, q.global_scale)
+    cols = _columns("dequantize", q.weight, q.scales, q.biases, quant)
+    rows = q.weight.size // q.weight.shape[-1] if q.weight.shape[-1] else 0
+    dev = q.weight.dev
+    affine = quant.mode == QuantMode.AFFINE
+    if affine and q.scales.dtype != q.biases.dtype:
+        raise InvalidArgument("dequantize: scales and biases must share a dtype")
+    kernel_dtype = q.scales.dtype if affine else (dtype if dtype is not None else BF16)
+    out = dev.empty(q.weight.shape[:-1] + (cols,), kernel_dtype)
+    c = quant._c()
+    _check(_ffi.lib().nvc_dequantize(dev._h, C.byref(c), kernel_dtype, q.weight.ptr, q.scales.ptr, _ptr(q.biases),
+                                     _ptr(q.global_scale), rows, cols, out.ptr, int(fused)))
+    if affine and dtype is not None and dtype != kernel_dtype:
+        return out.astype(dtype)
+    return out
+
+
+def sorted_offsets(indices: Array, groups: int) -> Array:
+    """Primitive::SortedOffsets (quantized.rs:772-782)."""
+    if indices.dtype != U32:
+        raise InvalidArgument("sorted_offsets: indices must be uint32")
+    out = indices.dev.empty((groups,), I32)
+    _check(_ffi.lib().nvc_sorted_offsets(indices.dev._h, indices.ptr, indices.size, groups, out.ptr))
+    return out
+
+
+def _promote(op: str, x: Array, q: Quantized):
+    """quantized.rs:491-503: affine promotes x, scales and biases to one float dtype."""
+    if q.biases is not None:
+        dtype = promote_types(promote_types(x.dtype, q.scales.dtype), q.biases.dtype)
+    else:
+        dtype = x.dtype
+    if dtype not in _FLOATS:
+        raise UnsupportedError(f"{op}: unsupported dtype {DTYPE_NAMES.get(dtype, dtype)}")
+    x = x.astype(dtype)
+    scales, biases = q.scales, q.biases
+    if biases is not None:
+        scales, biases = scales.astype(dtype), biases.astype(dtype)
+    return dtype, x, scales, biases
+
+
+def quantized_matmul(x: Array, q: Quantized, transpose: bool = True) -> Array:
+    """ops::quantized_matmul (ops.rs:1031-1046; quantized.rs:453-537): `x @ dequantize(w).T`
+    (or without the transpose).  A 1-D x is a row vector; batch dimensions broadcast."""
+    quant = q.quant
+    g, b = quant.checked("quantized_matmul")
+    _check_groups("quantized_matmul", quant.mode, q.scales, q.biases)
+    w = q.weight
+    gscale = q.global_scale
+    if gscale is not None and (w.ndim > 2 or x.ndim > 2 or not transpose):
+        # quantized.rs:481-490: dequantize in x's dtype, then an ordinary product.
+        raise UnsupportedError("quantized_matmul: an nvfp4 global scale with batches or untransposed weights "
+                               "takes the reference's dense matmul, which this backend does not provide")
+    _check_global("quantized_matmul", quant, gscale)
+    if x.dtype not in _FLOATS:
+        raise UnsupportedError(f"quantized_matmul: unsupported dtype {DTYPE_NAMES.get(x.dtype, x.dtype)}")
+    dtype, x, scales, biases = _promote("quantized_matmul", x, q)
+    cols = _columns("quantized_matmul", w, scales, biases, quant)
+    rows = w.shape[-2]
+    inner, outer = (cols, rows) if transpose else (rows, cols)
+    vector = x.ndim == 1
+    if x.ndim == 0 or x.shape[-1] != inner:
+        raise InvalidArgument(f"quantized_matmul: shapes {list(x.shape)} and {list(w.shape)} do not match")
+    if vector:
+        x = x.reshape(1, x.shape[0])
+    M, K = x.shape[-2], x.shape[-1]
+    N = outer
+    bx, bw = x.shape[:-2], w.shape[:-2]
+    try:
+        batch = tuple(np.broadcast_shapes(bx, bw)) if bw else bx
+    except ValueError:
+        raise InvalidArgument(f"quantized_matmul: batch dimensions {list(bx)} and {list(bw)} do not broadcast") from None
+    dev = x.dev
+    out = dev.empty(batch + (M, N), dtype)
+    nb = int(np.prod(batch)) if batch else 1
+    c = quant._c()
+    lib = _ffi.lib()
+
+    def call(xa, wa, sa, ba, ya, count, xs, ws, ss):
+        _check(lib.nvc_quantized_matmul(dev._h, C.byref(c), dtype, int(transpose), xa, wa, sa, ba, _ptr(gscale),
+                                        M, N, K, K, count, xs, ws, ss, ya))
+
+    x_mat, w_mat, s_mat = M * K, w.shape[-2] * w.shape[-1], scales.shape[-2] * scales.shape[-1]
+    if not bw:
+        call(x.ptr, w.ptr, scales.ptr, _ptr(biases), out.ptr, nb, x_mat, 0, 0)
+    elif tuple(bx) == tuple(bw):
+        call(x.ptr, w.ptr, scales.ptr, _ptr(biases), out.ptr, nb, x_mat, w_mat, s_mat)
+    else:
+        # General broadcasting: one call per output batch with the operands' own batch index.
+        xi = np.broadcast_to(np.arange(int(np.prod(bx)) if bx else 1).reshape(bx or (1,)), batch).reshape(-1)
+        wi = np.broadcast_to(np.arange(int(np.prod(bw))).reshape(bw), batch).reshape(-1)
+        isz = _ITEMSIZE[dtype]
+        ssz = isz if biases is not None else 1
+        for i in range(nb):
+            off = lambda a, n, size: C.c_void_p(a.ptr.value + int(n) * size)
+            call(off(x, xi[i], x_mat * isz), off(w, wi[i], w_mat * 4), off(scales, wi[i], s_mat * ssz),
+                 None if biases is None else off(biases, wi[i], s_mat * ssz), off(out, i, M * N * isz), 1, 0, 0, 0)
+    return out.reshape(N) if vector and not batch else (out.reshape(batch + (N,)) if vector else out)
+
+
+def gather_qmm(x: Array, q: Quantized, lhs_indices: Optional[Array] = None, rhs_indices: Optional[Array] = None,
+               options: GatherQmm = GatherQmm(), offsets: Optional[Array] = None) -> Array:
+    """ops::gather_qmm (ops.rs:1050-1078; quantized.rs:589-673): output batch i is
+    ``x[lhs[i]] @ dequantize(w)[rhs[i]].T`` over the flattened batch dimensions."""
+    quant = q.quant
+    quant.checked("gather_qmm")
+    if lhs_indices is None and rhs_indices is None:
+        return quantized_matmul(x, q, options.transpose)
+    _check_groups("gather_qmm", quant.mode, q.scales, q.biases)
+    w = q.weight
+    if x.ndim < 2 or w.ndim < 2 or (q.biases is not None and q.scales.shape != q.biases.shape):
+        raise InvalidArgument(f"gather_qmm: x must be [..., M, K] and w [..., N, K'], got {list(x.shape)} and "
+                              f"{list(w.shape)}")
+    if q.global_scale is not None:
+        if quant.mode != QuantMode.NVFP4:
+            raise InvalidArgument("gather_qmm: global scale is only supported for 'nvfp4' quantization mode")
+        _check_global("gather_qmm", quant, q.global_scale, experts_shape=w.shape[:-2])
+    for name, idx in (("lhs", lhs_indices), ("rhs", rhs_indices)):
+        if idx is not None and idx.dtype not in (U32, I32):
+            raise InvalidArgument("gather_qmm: indices must be integers")
+    dtype, x, scales, biases = _promote("gather_qmm", x, q)
+    cols = _columns("gather_qmm", w, scales, biases, quant)
+    rows_w = w.shape[-2]
+    inner, N = (cols, rows_w) if options.transpose else (rows_w, cols)
+    M, K = x.shape[-2], x.shape[-1]
+    if K != inner:
+        raise InvalidArgument(f"gather_qmm: shapes {list(x.shape)} and {list(w.shape)} do not match")
+    x_batches = int(np.prod(x.shape[:-2])) if x.ndim > 2 else 1
+    experts = int(np.prod(w.shape[:-2])) if w.ndim > 2 else 1
+    dev = x.dev
+    # Indices broadcast together; either defaults to every batch of its operand in order
+    # (quantized.rs:739-767).  Explicit broadcasting is materialised on the host.
+    lshape = tuple(lhs_indices.shape) if lhs_indices is not None else tuple(x.shape[:-2])
+    rshape = tuple(rhs_indices.shape) if rhs_indices is not None else tuple(w.shape[:-2])
+    try:
+        ishape = tuple(np.broadcast_shapes(lshape, rshape))
+    except ValueError:
+        raise InvalidArgument(f"gather_qmm: index shapes {list(lshape)} and {list(rshape)} do not broadcast") from None
+    rows = int(np.prod(ishape)) if ishape else 1
+
+    def flat(idx, default_n, shape):
+        if idx is not None and tuple(idx.shape) == ishape:
+            return idx
+        host = idx.to_numpy().astype(np.uint32) if idx is not None else np.arange(default_n, dtype=np.uint32).reshape(shape)
+        return dev.array(np.ascontiguousarray(np.broadcast_to(host, ishape)), U32)
+
+    lhs_default = lhs_indices is None and lshape == ishape
+    lhs = None if lhs_default else flat(lhs_indices, x_batches, lshape)
+    rhs = flat(rhs_indices, experts, rshape)
+    out = dev.empty(ishape + (M, N), dtype)
+    c = quant._c()
+    _check(_ffi.lib().nvc_gather_qmm(dev._h, C.byref(c), dtype, int(options.transpose), x.ptr, w.ptr, scales.ptr,
+                                     _ptr(biases), _ptr(q.global_scale), _ptr(lhs), rhs.ptr, _ptr(offsets),
+                                     int(options.sorted_indices), rows, x_batches, M, N, K, experts, out.ptr))
+    return out

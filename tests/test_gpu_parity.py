@@ -1,0 +1,221 @@
+"""CUDA path vs the CPU oracle on seeded inputs (bit-exact where the path is integer/byte or
+rounding-specified; within 1e-2 * ||row||_inf for products, the bound the task states)."""
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+DT = {"bf16": oracle.BF16, "f16": oracle.F16, "f32": oracle.F32}
+
+
+@pytest.fixture(scope="module")
+def be():
+    from cuda_backend import CudaBackend
+    return CudaBackend()
+
+
+def rand(rng, shape, dtype, scale=1.0):
+    return oracle.from_f32((rng.standard_normal(shape) * scale).astype(np.float32), dtype)
+
+
+def assert_product_close(got, want, dtype, what=""):
+    g, w = oracle.to_f32(got, dtype).astype(np.float64), oracle.to_f32(want, dtype).astype(np.float64)
+    assert g.shape == w.shape
+    g2, w2 = g.reshape(-1, g.shape[-1]), w.reshape(-1, w.shape[-1])
+    bound = 1e-2 * np.abs(w2).max(axis=1, keepdims=True)   # 1e-2 * ||row||_inf
+    err = np.abs(g2 - w2)
+    assert np.all(err <= bound + 1e-30), f"{what}: max err {err.max():.4g}, worst ratio {(err / (bound + 1e-30)).max():.3f}"
+
+
+AFFINE = [(b, g) for b in (1, 2, 3, 4, 5, 6, 8) for g in (32, 64, 128)]
+
+
+@pytest.mark.parametrize("bits,gs", AFFINE)
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+def test_quantize_dequantize_bit_exact(be, bits, gs, dt):
+    dtype = DT[dt]
+    rng = np.random.default_rng(bits * 1000 + gs)
+    w = rand(rng, (37, 4 * gs), dtype, 0.02)
+    c0, s0, b0 = oracle.quantize(w, dtype, oracle.AFFINE, gs, bits)
+    c1, s1, b1 = be.quantize(w, dtype, oracle.AFFINE, gs, bits)
+    assert np.array_equal(c0, c1) and np.array_equal(s0, s1) and np.array_equal(b0, b1)
+    for fused in (False, True):
+        d0 = oracle.dequantize(c0, s0, b0, dtype, oracle.AFFINE, gs, bits, fused=fused)
+        d1 = be.dequantize(c0, s0, b0, dtype, oracle.AFFINE, gs, bits, fused=fused)
+        assert np.array_equal(d0, d1), f"fused={fused}"
+
+
+@pytest.mark.parametrize("mode,gs,bits", [(oracle.MXFP4, 32, 4), (oracle.MXFP8, 32, 8), (oracle.NVFP4, 16, 4)])
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+def test_fp_quantize_dequantize_bit_exact(be, mode, gs, bits, dt):
+    dtype = DT[dt]
+    rng = np.random.default_rng(mode * 10 + dtype)
+    w = rand(rng, (19, 8 * gs), dtype, 0.5)
+    w.reshape(-1)[:5] = oracle.from_f32(np.array([0.0, -0.0, 1e-30, 7.0, -448.0], np.float32), dtype)
+    for g in ([None] if mode != oracle.NVFP4 else [None, 3.5]):
+        c0, s0, _ = oracle.quantize(w, dtype, mode, gs, bits, g)
+        c1, s1, _ = be.quantize(w, dtype, mode, gs, bits, g)
+        assert np.array_equal(c0, c1) and np.array_equal(s0, s1), f"global={g}"
+        for out in (oracle.BF16, oracle.F16, oracle.F32):
+            d0 = oracle.dequantize(c0, s0, None, out, mode, gs, bits, g)
+            d1 = be.dequantize(c0, s0, None, out, mode, gs, bits, g)
+            assert np.array_equal(d0.view(np.uint8), d1.view(np.uint8)), f"global={g} out={out}"
+
+
+def test_dequantize_full_size_checksum(be):
+    # The headline decode matrix (4096 x 4096, 4 bits, groups of 64): bit-exact at full size.
+    rng = np.random.default_rng(0)
+    w = rand(rng, (4096, 4096), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    c1, s1, b1 = be.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    assert np.array_equal(c, c1) and np.array_equal(s, s1) and np.array_equal(b, b1)
+    d0 = oracle.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, 64, 4)
+    d1 = be.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, 64, 4)
+    assert np.array_equal(d0, d1)
+
+
+@pytest.mark.parametrize("bits,gs", AFFINE)
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_qmv_affine_bf16(be, bits, gs, M):
+    rng = np.random.default_rng(bits * 100 + gs + M)
+    N, K = 72, 1024
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits)
+    got = be.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits, True)
+    assert_product_close(got, want, oracle.BF16, f"b{bits} g{gs} M{M}")
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (6144, 4096), (4096, 12288), (512, 12288), (768, 2048), (2048, 768),
+                                 (40, 2880), (17, 64), (4096, 128)])
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_qmv_shapes_b4_g64(be, N, K, M):
+    rng = np.random.default_rng(N + K + M)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, b, oracle.BF16)
+    got = be.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, 64, 4, True)
+    assert_product_close(got, want, oracle.BF16, f"N{N} K{K} M{M}")
+
+
+def test_qmv_one_hot_rows_return_the_dequantized_weights(be):
+    # x = unit vectors: y[m, n] is exactly dequantize(w)[n, k_m] rounded to bf16 -- a
+    # size-independent check that no k-slot is permuted or dropped in the fast kernel.
+    rng = np.random.default_rng(5)
+    N, K = 64, 512
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    dense = oracle.to_f32(oracle.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, 64, 4), oracle.BF16)
+    ks = rng.permutation(K)[:64]
+    for k0 in range(0, 64, 8):
+        x = np.zeros((8, K), np.float32)
+        for i in range(8):
+            x[i, ks[k0 + i]] = 1.0
+        got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(x, oracle.BF16), c, s, b, oracle.BF16,
+                                                oracle.AFFINE, 64, 4, True), oracle.BF16)
+        want = dense[:, ks[k0:k0 + 8]].T
+        assert np.allclose(got, want, rtol=2 ** -7, atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32"])
+@pytest.mark.parametrize("transpose", [True, False])
+def test_generic_product_other_dtypes(be, dt, transpose):
+    dtype = DT[dt]
+    rng = np.random.default_rng(11)
+    N, K, M = 96, 256, 5
+    w = rand(rng, (N, K) if transpose else (K, N), dtype, 0.05)
+    c, s, b = oracle.quantize(w, dtype, oracle.AFFINE, 32, 6)
+    x = rand(rng, (M, K), dtype)
+    want = oracle.quantized_matmul(x, c, s, b, dtype, oracle.AFFINE, 32, 6, transpose)
+    got = be.quantized_matmul(x, c, s, b, dtype, oracle.AFFINE, 32, 6, transpose)
+    assert_product_close(got, want, dtype)
+
+
+@pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
+@pytest.mark.parametrize("M", [1, 4])
+def test_fp_product(be, mode, gs, M):
+    rng = np.random.default_rng(mode + M)
+    N, K = 80, 2880
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, _ = oracle.quantize(w, oracle.BF16, mode, gs, 4)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, None, oracle.BF16, mode, gs, 4)
+    got = be.quantized_matmul(x, c, s, None, oracle.BF16, mode, gs, 4, True)
+    assert_product_close(got, want, oracle.BF16)
+
+
+def test_sorted_offsets(be):
+    import nuvec_b200 as nv
+    rng = np.random.default_rng(2)
+    idx = np.sort(rng.integers(0, 128, 4096)).astype(np.uint32)
+    got = nv.sorted_offsets(be.up(idx, nv.U32), 128).to_numpy()
+    assert np.array_equal(got, oracle.sorted_offsets(idx, 128))
+    assert nv.sorted_offsets(be.up(np.zeros(0, np.uint32), nv.U32), 3).to_numpy().tolist() == [0, 0, 0]
+
+
+@pytest.mark.parametrize("T,E,topk,N,K", [(1, 128, 8, 768, 2048), (1, 128, 8, 2048, 768), (6, 16, 4, 96, 256)])
+def test_gather_rows_affine(be, T, E, topk, N, K):
+    rng = np.random.default_rng(T + E)
+    Ee = min(E, 16)  # keep the oracle's expert tensors small; ids are drawn from these
+    w = rand(rng, (Ee, N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    ids = np.concatenate([rng.permutation(Ee)[:topk] for _ in range(T)]).astype(np.uint32)
+    order = np.argsort(ids, kind="stable")
+    rhs = ids[order]
+    x = rand(rng, (T, K), oracle.BF16)
+    rows = np.repeat(np.arange(T), topk)[order]
+    xr = x[rows][:, None, :]
+    want = oracle.gather_qmm(xr, c, s, b, np.arange(len(rhs)), rhs, oracle.BF16)
+    got = be.gather_qmm(xr, c, s, b, None, rhs, oracle.BF16, oracle.AFFINE, 64, 4, True, None, True)
+    assert_product_close(got, want, oracle.BF16)
+
+
+def test_empty_operands_are_no_ops(be):
+    import nuvec_b200 as nv
+    rng = np.random.default_rng(0)
+    w = rand(rng, (8, 64), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    q = be.quantized(c, s, b, oracle.BF16, oracle.AFFINE, 64, 4)
+    out = nv.quantized_matmul(be.dev.empty((0, 64), nv.BF16), q)
+    assert out.shape == (0, 8)
+    q0 = be.quantized(c[:0], s[:0], b[:0], oracle.BF16, oracle.AFFINE, 64, 4)
+    out = nv.quantized_matmul(be.up(rand(rng, (3, 64), oracle.BF16), nv.BF16), q0)
+    assert out.shape == (3, 0)
+
+
+def test_invalid_arguments_raise(be):
+    import nuvec_b200 as nv
+    rng = np.random.default_rng(0)
+    w = rand(rng, (8, 64), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    x = be.up(rand(rng, (2, 64), oracle.BF16), nv.BF16)
+    with pytest.raises(nv.InvalidArgument):
+        nv.quantized_matmul(x, nv.Quantized(be.up(c, nv.U32), be.up(s, nv.BF16), None, nv.Quant.affine(64, 4)))
+    with pytest.raises(nv.InvalidArgument):
+        nv.quantized_matmul(x, be.quantized(c, s, b, oracle.BF16, oracle.AFFINE, 48, 4))
+    with pytest.raises(nv.InvalidArgument):
+        nv.quantized_matmul(be.up(rand(rng, (2, 32), oracle.BF16), nv.BF16), be.quantized(c, s, b, oracle.BF16, oracle.AFFINE, 64, 4))
+    with pytest.raises(nv.InvalidArgument):
+        nv.quantize(be.up(rand(rng, (8, 48), oracle.BF16), nv.BF16), nv.Quant.affine(64, 4))
+    with pytest.raises(nv.InvalidArgument):
+        nv.quantize(be.up(rand(rng, (8, 64), oracle.BF16), nv.BF16), nv.Quant(nv.QuantMode.MXFP4, 64, 4))
+
+
+def test_pool_reuses_blocks_and_reports_stats(be):
+    import nuvec_b200 as nv
+    dev = be.dev
+    dev.synchronize()
+    before = dev.memory()
+    a = dev.empty((1 << 20,), nv.F32)
+    mid = dev.memory()
+    assert mid["active"] >= before["active"] + (4 << 20)
+    ptr = a.ptr.value
+    del a
+    after = dev.memory()
+    assert after["active"] == before["active"] and after["cached"] >= 4 << 20
+    b = dev.empty((1 << 20,), nv.F32)
+    assert b.ptr.value == ptr and dev.memory()["allocations"] == mid["allocations"]
