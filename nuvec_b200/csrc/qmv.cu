@@ -9,10 +9,10 @@
 //    so the multiply-accumulate cannot be afforded on the FMA pipe; the unpacked codes are
 //    fed to the warp-level tensor-core MMA (m16n8k16, bf16 in, f32 accumulate) instead, used
 //    here purely as a wide dot-product unit: a warp multiplies 16 weight rows x 16 k-values
-//    by up to 8 activation rows per instruction.  Codes enter as the bfloat16 number
-//    128 + code (one LOP3 per two codes: the code bits are ORed into the mantissa of 128.0),
-//    per-group scale and bias are applied to the float32 group sums:
-//        sum_k x*(s*c + b) = s * sum_k x*(128 + c)  +  (b - 128 s) * sum_k x.
+//    by up to 8 activation rows per instruction.  Every weight is rebuilt in registers with the
+//    reference's own two bfloat16 roundings (packed fma/add), so the operands of the product
+//    are bit-identical to the reference's dequantized matrix; only the float32 summation order
+//    differs.
 //
 //  * qmv_generic_kernel -- every other case (all bit widths and modes, f32/f16/bf16, any
 //    K, both weight orientations).  It rebuilds each weight with exactly the reference's
@@ -148,11 +148,12 @@ int32_t launch_generic(nvc_device *dev, const GenericParams &p) {
 
 // ── fast affine kernel ─────────────────────────────────────────────────────────────────
 
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
@@ -160,32 +161,66 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint3
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
     return r;
 }
+// Packed bfloat16 arithmetic, each lane rounded to nearest even once.
+__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+// a + b as fma(a, 1, b): the same single rounding, and it stays on the FMA pipe (the packed
+// bfloat16 add was observed to issue on the quarter-rate conversion pipe).
+__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(0x3F803F80u), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 
-// Streaming loads of packed words: read-only path, no L1 allocation (each word is used once).
-__device__ __forceinline__ void ldg_stream(uint32_t (&v)[1], const uint32_t *p) {
-    asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];\n" : "=r"(v[0]) : "l"(p));
+// Asynchronous global -> shared copies of packed words (4, 8 or 16 bytes per lane).  Every lane
+// copies into a slot only it reads back, so completion is tracked per thread with
+// wait_group and no barrier is involved.  The 16-byte form bypasses L1.
+template <int BYTES> __device__ __forceinline__ void cp_async(uint32_t smem_addr, const void *gptr) {
+    if (BYTES == 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
+    else if (BYTES == 8)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
 }
-__device__ __forceinline__ void ldg_stream(uint32_t (&v)[2], const uint32_t *p) {
-    asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];\n" : "=r"(v[0]), "=r"(v[1]) : "l"(p));
-}
-__device__ __forceinline__ void ldg_stream(uint32_t (&v)[4], const uint32_t *p) {
-    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(p));
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// Per (row, group) constants: {s, s} and {b, b} as bfloat16 pairs staged in shared memory,
+// {-128 s, -128 s} derived from them.
+struct GroupConsts { uint32_t s2, ns2, b2; };
+__device__ __forceinline__ GroupConsts group_consts(uint2 sb) {
+    return GroupConsts{sb.x, bf2_mul(sb.x, 0xC300C300u), sb.y};  // -128 * s is exact
+}
+
+// Dequantization of one packed word into MMA operands with exactly the reference's two
+// roundings (kernels.rs:835-859): p = rn(code * scale), w = rn(p + bias), both in bfloat16.
+// A code enters as the bfloat16 number 128 + code (its bits ORed into the mantissa of 128.0);
+// fma(128 + c, s, -128 s) is the single rounding of the exact product c * s.
 template <int BITS> struct Unpack;
-// 4 bits: register i holds codes (i, i+4) of the word as the bf16 pair (128 + c_i, 128 + c_{i+4}).
 template <> struct Unpack<4> {
-    static constexpr int REGS = 4;      // bf16x2 registers per word
-    static constexpr int CODES = 8;     // codes per word
-    static constexpr int XREGS = 4;     // activation registers per word (bf16x2 each)
-    static constexpr float OFFSET = 128.0f;  // sum of the slot weights of one k, times 128
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&r)[4]) {
+    static constexpr int CODES = 8;   // codes per word
+    static constexpr int AREGS = 4;   // operand registers per word; MMAs per word = AREGS / 2
+    // register i = codes (i, i+4)
+    static __device__ __forceinline__ void run(uint32_t w, const GroupConsts &c, uint32_t (&r)[4]) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) r[i] = lop3_and_or(w >> (4 * i), 0x000F000Fu, 0x43004300u);
+        for (int i = 0; i < 4; i++) {
+            uint32_t m = lop3_and_or(w >> (4 * i), 0x000F000Fu, 0x43004300u);
+            r[i] = bf2_add(bf2_fma(m, c.s2, c.ns2), c.b2);
+        }
     }
     // Activation order matching run(): pairs (x0,x4) (x1,x5) (x2,x6) (x3,x7).
-    static __device__ __forceinline__ void permute(const __nv_bfloat16 *x, __nv_bfloat16 *out) {
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             out[2 * i] = x[i];
@@ -193,36 +228,37 @@ template <> struct Unpack<4> {
         }
     }
 };
-// 8 bits: each byte is split in its nibbles; a k-value occupies two MMA slots, the high nibble
-// meeting 16 * x.  Registers: (lo0,lo2) (hi0,hi2) (lo1,lo3) (hi1,hi3).
 template <> struct Unpack<8> {
-    static constexpr int REGS = 4;
     static constexpr int CODES = 4;
-    static constexpr int XREGS = 4;
-    static constexpr float OFFSET = 128.0f * 17.0f;
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&r)[4]) {
+    static constexpr int AREGS = 2;
+    // The byte is rebuilt from its nibbles, exactly: 16 * hi + lo <= 255 fits bfloat16.
+    // register 0 = codes (0, 2), register 1 = codes (1, 3)
+    static __device__ __forceinline__ void run(uint32_t w, const GroupConsts &c, uint32_t (&r)[2]) {
+        const uint32_t k16 = 0x41804180u, kn2048 = 0xC500C500u, kn128 = 0xC300C300u;
 #pragma unroll
-        for (int i = 0; i < 4; i++) r[i] = lop3_and_or(w >> (4 * i), 0x000F000Fu, 0x43004300u);
+        for (int i = 0; i < 2; i++) {
+            uint32_t lo = lop3_and_or(w >> (8 * i), 0x000F000Fu, 0x43004300u);
+            uint32_t hi = lop3_and_or(w >> (8 * i + 4), 0x000F000Fu, 0x43004300u);
+            uint32_t code = bf2_add(bf2_fma(hi, k16, kn2048), bf2_add(lo, kn128));  // 16*hi + lo, exact
+            r[i] = bf2_add(bf2_mul(code, c.s2), c.b2);
+        }
     }
-    static __device__ __forceinline__ void permute(const __nv_bfloat16 *x, __nv_bfloat16 *out) {
-        const float f[4] = {__bfloat162float(x[0]), __bfloat162float(x[1]), __bfloat162float(x[2]), __bfloat162float(x[3])};
-        out[0] = x[0]; out[1] = x[2];
-        out[2] = __float2bfloat16_rn(16.0f * f[0]); out[3] = __float2bfloat16_rn(16.0f * f[2]);
-        out[4] = x[1]; out[5] = x[3];
-        out[6] = __float2bfloat16_rn(16.0f * f[1]); out[7] = __float2bfloat16_rn(16.0f * f[3]);
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) {
+        out[0] = x[0]; out[1] = x[2]; out[2] = x[1]; out[3] = x[3];
     }
 };
-// 2 bits: register i holds codes (i, i+8).
 template <> struct Unpack<2> {
-    static constexpr int REGS = 8;
     static constexpr int CODES = 16;
-    static constexpr int XREGS = 8;
-    static constexpr float OFFSET = 128.0f;
-    static __device__ __forceinline__ void run(uint32_t w, uint32_t (&r)[8]) {
+    static constexpr int AREGS = 8;
+    // register i = codes (i, i+8)
+    static __device__ __forceinline__ void run(uint32_t w, const GroupConsts &c, uint32_t (&r)[8]) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) r[i] = lop3_and_or(w >> (2 * i), 0x00030003u, 0x43004300u);
+        for (int i = 0; i < 8; i++) {
+            uint32_t m = lop3_and_or(w >> (2 * i), 0x00030003u, 0x43004300u);
+            r[i] = bf2_add(bf2_fma(m, c.s2, c.ns2), c.b2);
+        }
     }
-    static __device__ __forceinline__ void permute(const __nv_bfloat16 *x, __nv_bfloat16 *out) {
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             out[2 * i] = x[i];
@@ -232,18 +268,41 @@ template <> struct Unpack<2> {
 };
 
 constexpr int QMV_WARPS = 8;
-constexpr int QMV_UNROLL = 4;  // iterations whose loads are issued together
+constexpr int QMV_THREADS = QMV_WARPS * 32;
+// Depth of each lane's ring of asynchronous weight copies (iterations in flight per warp).
+constexpr int QMV_STAGES = 4;
+// Most groups whose scale/bias are staged at a time (one k-chunk of a tile).
+constexpr int QMV_SEG_GROUPS = 16;
+// Row pitch (bfloat16 elements) of the staged scales: 48 bytes = 12 banks, a multiple of 16 bytes
+// (the widest copy); the 8 rows a warp reads together fall on different banks.
+constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 
-// Shared memory of one block:
-//   xs   [M][kr / CODES * XREGS] u32   permuted activations of the block's k-range (+4 pad words per row)
-//   xsum [8][groups] f32               per-group sums of x (rows >= M are zero)
-//   sb   [16][groups] u32              (scale, bias) bf16 pairs of the block's 16 weight rows
-//   red  [QMV_WARPS][128] f32          cross-warp reduction
+// The product is cut into iterations: iteration (tile, i) multiplies 16 weight rows ("tile") by
+// IK = 4 * WPL * CODES consecutive k-values.  All iterations of all tiles form one sequence, tile
+// after tile, and the warps of the grid take equal consecutive runs of it (stream-K): the load is
+// balanced to one iteration whatever N and K are.  A warp that holds a whole tile writes the
+// result; tiles cut by a run boundary leave float32 partials in scratch and the warp that
+// arrives last adds them in run order.  Warps share the staged activations and nothing else, so
+// the main loop has no block-wide barrier.
+//
+// Lane (r, t) = (lane / 4, lane % 4) holds rows r and r + 8 of the tile and, per iteration, WPL
+// consecutive words of each (a quad covers the IK k-values).  The words travel through a per-lane
+// ring of cp.async copies that keeps running across tile boundaries, so HBM requests stay in
+// flight while a tile is finished and the next one starts.
+//
+// Shared memory:
+//   xs    [M][pitch] u32      all activations in MMA operand order: the chunk of word j of lane t
+//                             in iteration i sits at ((i * WPL + j) * 4 + t) * XW
+//   zero  [64] u32            what lanes of activation rows >= M read
+//   per warp:
+//   sraw, braw [2][16][QMV_SPITCH] bf16   scales / biases of the current and the next k-chunk
+//   ring  [QMV_STAGES][2][32] x WPL u32   packed words in flight: slot (stage, row half, lane)
 template <int BITS, int WPL>
-__global__ void __launch_bounds__(QMV_WARPS * 32) qmv_affine_kernel(QmvParams p) {
+__global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
-    constexpr int CODES = U::CODES, REGS = U::REGS, XREGS = U::XREGS;
-    constexpr int IK = 4 * WPL * CODES;  // k-values per iteration (one quad covers them)
+    constexpr int CODES = U::CODES, AREGS = U::AREGS;
+    constexpr int IK = 4 * WPL * CODES;
+    constexpr int XW = AREGS;  // activation words per packed word (AREGS bf16 pairs)
     extern __shared__ __align__(16) uint32_t smem[];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -254,213 +313,286 @@ __global__ void __launch_bounds__(QMV_WARPS * 32) qmv_affine_kernel(QmvParams p)
         wb = p.rhs[b];
         xb = p.lhs ? p.lhs[b] : b;
     }
-    const int64_t n0 = (int64_t)blockIdx.x * 16;
-    const int ks = blockIdx.y;
-    const int64_t k0 = (int64_t)ks * p.kr;
-    const int kr = (int)min((int64_t)p.kr, p.K - k0);  // multiple of the group size
-    const int groups = kr / p.gs;
-    const int g0 = (int)(k0 / p.gs);
-    const int row_groups = (int)(p.K / p.gs);
-    const int64_t row_words = p.K * BITS / 32;
+    const int row_groups = (int)(p.K >> p.gs_shift);
+    const uint32_t row_words = (uint32_t)(p.K * BITS / 32);
+    const int ipt = (int)(p.K / IK);        // iterations per tile
+    const int ci = p.chunk_k / IK;          // iterations per k-chunk (scales are staged per chunk)
+    const int chunk_groups = p.chunk_k >> p.gs_shift;
+    const int tiles = (int)((p.N + 15) / 16);
+    const int last_row = (int)p.N - 1;
 
-    const int xs_pitch = p.kr / CODES * XREGS + 4;  // words
+    const int xs_pitch = (int)(p.K / CODES) * XW + 16;  // words; = 16 (mod 32) keeps two rows on disjoint banks
     uint32_t *xs = smem;
-    float *xsum = (float *)(xs + (size_t)p.M * xs_pitch);
-    uint32_t *sb = (uint32_t *)(xsum + 8 * (p.kr / p.gs));
-    float *red = (float *)(sb + 16 * (p.kr / p.gs));
+    uint32_t *zero = xs + (size_t)p.M * xs_pitch;
+    uint16_t *sraw = reinterpret_cast<uint16_t *>(zero + 64) + (size_t)warp * (4 * 16 * QMV_SPITCH);
+    uint16_t *braw = sraw + 2 * 16 * QMV_SPITCH;
+    uint32_t *ring = reinterpret_cast<uint32_t *>(reinterpret_cast<uint16_t *>(zero + 64) +
+                                                  (size_t)QMV_WARPS * (4 * 16 * QMV_SPITCH)) +
+                     (size_t)warp * (QMV_STAGES * 2 * 32 * WPL);
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * WPL);
+    constexpr uint32_t HALF_BYTES = 32 * WPL * 4, STAGE_BYTES = 2 * HALF_BYTES;
 
-    const uint32_t *wbase = p.w + wb * p.w_batch_stride;
-    const int64_t ra = min(n0 + r, p.N - 1), rb = min(n0 + r + 8, p.N - 1);
-    const uint32_t *wa = wbase + ra * row_words + k0 * BITS / 32 + t * WPL;
-    const uint32_t *wq = wbase + rb * row_words + k0 * BITS / 32 + t * WPL;
+    // ── this warp's run of iterations ───────────────────────────────────────────────────
+    const int64_t total = (int64_t)tiles * ipt;
+    // No more runs than iterations, so that no run is empty (surplus warps idle).
+    const int64_t warps = min((int64_t)gridDim.x * QMV_WARPS, total);
+    const int64_t gw = (int64_t)blockIdx.x * QMV_WARPS + warp;
+    const int64_t lo = gw < warps ? gw * total / warps : 0, hi = gw < warps ? (gw + 1) * total / warps : 0;
 
-    // The warp's iterations.
-    // The warp's iterations: whole groups, so every group is opened and closed by one warp.
-    const int ipg = p.gs / IK;  // iterations per group (>= 1)
-    const int it0 = (int)((int64_t)groups * warp / QMV_WARPS) * ipg;
-    const int it1 = (int)((int64_t)groups * (warp + 1) / QMV_WARPS) * ipg;
+    const uint32_t *wbase = p.w + wb * p.w_batch_stride + t * WPL;
+    const uint16_t *sc = (const uint16_t *)p.scales + wb * p.s_batch_stride;
+    const uint16_t *bi = (const uint16_t *)p.biases + wb * p.s_batch_stride;
+    __nv_bfloat16 *out = (__nv_bfloat16 *)p.y + b * p.M * p.N;
 
-    // Issue the first batch of weight loads before staging, so HBM latency overlaps it.
-    uint32_t qa[QMV_UNROLL][WPL], qb[QMV_UNROLL][WPL];
-#pragma unroll
-    for (int u = 0; u < QMV_UNROLL; u++) {
-        if (it0 + u < it1) {
-            ldg_stream(qa[u], wa + (int64_t)(it0 + u) * 4 * WPL);
-            ldg_stream(qb[u], wq + (int64_t)(it0 + u) * 4 * WPL);
+    // Copies the scales and biases of k-chunk `chunk` of `tile` into buffer `buf` (whole warp).
+    auto stage_scales = [&](int tile, int chunk, int buf) {
+        const int sg0 = chunk * chunk_groups;
+        uint16_t *sd = sraw + buf * 16 * QMV_SPITCH, *bd = braw + buf * 16 * QMV_SPITCH;
+        if (p.s_vec == 16) {  // 16-byte copies of 8 groups
+            const int chunks = chunk_groups >> 3;
+            for (int i = lane; i < 16 * chunks; i += 32) {
+                const int rr = i / chunks, c = i - rr * chunks;
+                const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + 8 * c;
+                cp_async<16>((uint32_t)__cvta_generic_to_shared(sd + rr * QMV_SPITCH + 8 * c), sc + at);
+                cp_async<16>((uint32_t)__cvta_generic_to_shared(bd + rr * QMV_SPITCH + 8 * c), bi + at);
+            }
+        } else if (p.s_vec == 4) {  // 4-byte copies of 2 groups
+            const int pairs = chunk_groups >> 1;
+            for (int i = lane; i < 16 * pairs; i += 32) {
+                const int rr = i / pairs, c = i - rr * pairs;
+                const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + 2 * c;
+                cp_async<4>((uint32_t)__cvta_generic_to_shared(sd + rr * QMV_SPITCH + 2 * c), sc + at);
+                cp_async<4>((uint32_t)__cvta_generic_to_shared(bd + rr * QMV_SPITCH + 2 * c), bi + at);
+            }
         } else {
-#pragma unroll
-            for (int j = 0; j < WPL; j++) qa[u][j] = qb[u][j] = 0u;
+            for (int i = lane; i < 16 * chunk_groups; i += 32) {
+                const int rr = i / chunk_groups, c = i - rr * chunk_groups;
+                const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + c;
+                sd[rr * QMV_SPITCH + c] = sc[at];
+                bd[rr * QMV_SPITCH + c] = bi[at];
+            }
         }
-    }
+    };
 
-    // ── stage activations (permuted), their group sums, and the scale/bias pairs ─────────
-    {
-        const __nv_bfloat16 *x = (const __nv_bfloat16 *)p.x + xb * p.x_batch_stride;
-        const int blocks_per_row = kr / CODES;
-        const int total = p.M * blocks_per_row;
-        const int seg = p.gs / CODES;  // staging threads per group: a power of two <= 32
-        for (int base = 0; base < total; base += QMV_WARPS * 32) {
-            const int i = base + tid;
-            const bool valid = i < total;
-            int m = 0, blk = 0;
-            float part = 0.f;
-            if (valid) {
-                m = i / blocks_per_row;
-                blk = i - m * blocks_per_row;
-                __nv_bfloat16 in[CODES], out[XREGS * 2];
-                const __nv_bfloat16 *src = x + (int64_t)m * p.ldx + k0 + (int64_t)blk * CODES;
-                if (p.x_vec) {
-                    constexpr int VEC = CODES * 2 / 16 > 0 ? CODES * 2 / 16 : 1;
-                    if (CODES * 2 >= 16) {
+    // Prefetch cursor: the iteration whose words are copied next.
+    int64_t pf = lo;
+    int pf_tile = (int)(lo / ipt), pf_it = (int)(lo - (int64_t)pf_tile * ipt);
+    const uint32_t *pf_a = nullptr, *pf_q = nullptr;
+    auto pf_rows = [&]() {
+        pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + pf_it * (4 * WPL);
+        pf_q = wbase + (size_t)min(pf_tile * 16 + r + 8, last_row) * row_words + pf_it * (4 * WPL);
+    };
+    // Issues the copies of one iteration into `stage` and always commits one group, so the
+    // group count seen by wait_group is the same for every lane and iteration.
+    auto prefetch = [&](int stage) {
+        if (pf < hi) {
+            cp_async<WPL * 4>(ring_s + stage * STAGE_BYTES, pf_a);
+            cp_async<WPL * 4>(ring_s + stage * STAGE_BYTES + HALF_BYTES, pf_q);
+            pf_a += 4 * WPL;
+            pf_q += 4 * WPL;
+            pf++;
+            if (++pf_it == ipt) {
+                pf_it = 0;
+                pf_tile++;
+                pf_rows();
+            }
+        }
+        cp_async_commit();
+    };
+
+    if (lo < hi) {
+        stage_scales(pf_tile, pf_it / ci, 0);
+        pf_rows();
+    }
 #pragma unroll
-                        for (int v = 0; v < VEC; v++)
-                            *reinterpret_cast<uint4 *>(in + 8 * v) = __ldg(reinterpret_cast<const uint4 *>(src) + v);
-                    } else {
-                        *reinterpret_cast<uint2 *>(in) = __ldg(reinterpret_cast<const uint2 *>(src));
-                    }
+    for (int st = 0; st < QMV_STAGES; st++) prefetch(st);
+
+    // ── stage the activations once per block (the first weight copies are already in flight) ──
+    {
+        const uint16_t *x = (const uint16_t *)p.x + xb * p.x_batch_stride;
+        const int blocks_per_row = (int)(p.K / CODES);
+        const int total_blocks = p.M * blocks_per_row;
+        for (int i = tid; i < total_blocks; i += QMV_THREADS) {
+            const int m = i / blocks_per_row, blk = i - m * blocks_per_row;
+            uint16_t in[CODES], outv[XW * 2];
+            const uint16_t *src = x + (int64_t)m * p.ldx + (int64_t)blk * CODES;
+            if (p.x_vec) {
+                if (CODES == 4) {
+                    *reinterpret_cast<uint2 *>(in) = __ldg(reinterpret_cast<const uint2 *>(src));
                 } else {
 #pragma unroll
-                    for (int j = 0; j < CODES; j++) in[j] = src[j];
+                    for (int v = 0; v < CODES / 8; v++)
+                        *reinterpret_cast<uint4 *>(in + 8 * v) = __ldg(reinterpret_cast<const uint4 *>(src) + v);
                 }
+            } else {
 #pragma unroll
-                for (int j = 0; j < CODES; j++) part += __bfloat162float(in[j]);
-                U::permute(in, out);
-                uint32_t *dst = xs + (size_t)m * xs_pitch + (size_t)blk * XREGS;
-#pragma unroll
-                for (int j = 0; j < XREGS; j++)
-                    dst[j] = (uint32_t)__bfloat16_as_ushort(out[2 * j]) | ((uint32_t)__bfloat16_as_ushort(out[2 * j + 1]) << 16);
+                for (int j = 0; j < CODES; j++) in[j] = src[j];
             }
-            // group sum over `seg` neighbouring lanes (segments never straddle a warp)
-            for (int o = 1; o < seg; o <<= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-            if (valid && (lane & (seg - 1)) == 0) xsum[m * groups + blk / seg] = part;
+            U::permute(in, outv);
+            // word `blk` of the row belongs to iteration blk / (4 WPL), lane t = (blk / WPL) % 4, word j = blk % WPL
+            const int it = blk / (4 * WPL), tt = (blk / WPL) & 3, j = blk % WPL;
+            uint32_t *dst = xs + (size_t)m * xs_pitch + (size_t)(((it * WPL + j) * 4 + tt) * XW);
+#pragma unroll
+            for (int v = 0; v < XW; v++) dst[v] = (uint32_t)outv[2 * v] | ((uint32_t)outv[2 * v + 1] << 16);
         }
-        for (int i = p.M * groups + tid; i < 8 * groups; i += QMV_WARPS * 32) xsum[i] = 0.f;
-        const __nv_bfloat16 *sc = (const __nv_bfloat16 *)p.scales + wb * p.s_batch_stride;
-        const __nv_bfloat16 *bi = (const __nv_bfloat16 *)p.biases + wb * p.s_batch_stride;
-        for (int i = tid; i < 16 * groups; i += QMV_WARPS * 32) {
-            int rr = i / groups, g = i - rr * groups;
-            int64_t row = min(n0 + rr, p.N - 1);
-            size_t at = (size_t)(row * row_groups + g0 + g);
-            sb[rr * groups + g] = (uint32_t)__bfloat16_as_ushort(sc[at]) | ((uint32_t)__bfloat16_as_ushort(bi[at]) << 16);
-        }
+        if (tid < 64) zero[tid] = 0u;
     }
-    __syncthreads();
+    __syncthreads();  // activations staged
 
-    // ── main loop ───────────────────────────────────────────────────────────────────────
-    float y[4] = {0.f, 0.f, 0.f, 0.f};    // rows r / r+8, activation rows 2t / 2t+1
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // the open group's sums
     const bool xrow = r < p.M;
-    const uint32_t *xl = xs + (size_t)(xrow ? r : 0) * xs_pitch;
+    const int x_it_step = xrow ? 4 * WPL * XW : 0;  // words per iteration in xs (0: stay on the zero page)
+    const uint32_t *xbase = xrow ? xs + (size_t)r * xs_pitch + t * XW : zero + t * XW;
+    int seg_count = 0;   // segments started so far (buffer parity)
+    int prev_iters = 0;  // iterations of the previous segment
+    int stage = 0;       // ring stage of the next iteration
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // rows r / r+8 x activation rows 2t / 2t+1
+    float acd[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the MMA dependency chain
 
-    for (int base = it0; base < it1; base += QMV_UNROLL) {
-#pragma unroll
-        for (int u = 0; u < QMV_UNROLL; u++) {
-            const int it = base + u;
-            if (it < it1) {
-#pragma unroll
-                for (int j = 0; j < WPL; j++) {
-                    uint32_t ra_[REGS], rb_[REGS];
-                    U::run(qa[u][j], ra_);
-                    U::run(qb[u][j], rb_);
-                    // activation registers of this word (zero for rows the product lacks)
-                    uint32_t xr[XREGS];
-                    const uint32_t *xp = xl + (size_t)((it * 4 + t) * WPL + j) * XREGS;
-                    if (xrow) {
-#pragma unroll
-                        for (int v = 0; v < XREGS; v += 4) {
-                            uint4 q = *reinterpret_cast<const uint4 *>(xp + v);
-                            xr[v] = q.x; xr[v + 1] = q.y; xr[v + 2] = q.z; xr[v + 3] = q.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < XREGS; v++) xr[v] = 0u;
-                    }
-#pragma unroll
-                    for (int h = 0; h < REGS / 2; h++) {
-                        uint32_t a[4] = {ra_[2 * h], rb_[2 * h], ra_[2 * h + 1], rb_[2 * h + 1]};
-                        mma_bf16_16816(acc, a, xr[2 * h], xr[2 * h + 1]);
-                    }
-                }
-                if ((it + 1) % ipg == 0) {
-                    // close the group: y += s * acc + (b - OFFSET * s) * xsum
-                    const int g = it / ipg;
-                    uint32_t sa = sb[r * groups + g], sq = sb[(r + 8) * groups + g];
-                    float s0 = __uint_as_float(sa << 16), b0 = __uint_as_float(sa & 0xFFFF0000u);
-                    float s1 = __uint_as_float(sq << 16), b1 = __uint_as_float(sq & 0xFFFF0000u);
-                    float x0 = xsum[(2 * t) * groups + g], x1 = xsum[(2 * t + 1) * groups + g];
-                    float c0 = __fmaf_rn(-U::OFFSET, s0, b0), c1 = __fmaf_rn(-U::OFFSET, s1, b1);
-                    y[0] += s0 * acc[0] + c0 * x0;
-                    y[1] += s0 * acc[1] + c0 * x1;
-                    y[2] += s1 * acc[2] + c1 * x0;
-                    y[3] += s1 * acc[3] + c1 * x1;
-                    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    for (int64_t f = lo; f < hi;) {
+        // Segment: the part of one k-chunk of one tile that lies in [f, hi).
+        const int tile = (int)(f / ipt), it0 = (int)(f - (int64_t)tile * ipt);
+        const int chunk = it0 / ci;
+        const int it1 = (int)min((int64_t)(chunk + 1) * ci, hi - (int64_t)tile * ipt);
+        const int64_t f1 = (int64_t)tile * ipt + it1;
+        const uint16_t *sd = sraw + (seg_count & 1) * 16 * QMV_SPITCH, *bd = braw + (seg_count & 1) * 16 * QMV_SPITCH;
+        // wait_group in the loop below covers a copy once QMV_STAGES groups were committed after it;
+        // a shorter previous segment (or the very first one) needs an explicit wait.  Then the
+        // copies of all lanes are made visible across the warp, and the next segment's scales
+        // start their way into the buffer the previous segment has finished with.
+        if (prev_iters <= QMV_STAGES) cp_async_wait<0>();
+        __syncwarp();
+        if (f1 < hi) {
+            const int ntile = (int)(f1 / ipt), nit = (int)(f1 - (int64_t)ntile * ipt);
+            stage_scales(ntile, nit / ci, (seg_count + 1) & 1);
+        }
+        prev_iters = it1 - it0;
+        seg_count++;
+        const int gofs = (it0 - chunk * ci) * IK + t * (WPL * CODES);  // k offset inside the chunk
+        const uint16_t *sa = sd + r * QMV_SPITCH, *sq = sd + (r + 8) * QMV_SPITCH;
+        const uint16_t *ba = bd + r * QMV_SPITCH, *bq = bd + (r + 8) * QMV_SPITCH;
+        const uint32_t *xp = xbase + (size_t)it0 * x_it_step;
+        for (int it = it0; it < it1; it++) {
+            cp_async_wait<QMV_STAGES - 1>();  // the oldest group, this iteration's words, has landed
+            uint32_t wa_[WPL], wq_[WPL];
+            {
+                const uint32_t *slot = ring + (size_t)stage * (2 * 32 * WPL) + lane * WPL;
+                if (WPL == 4) {
+                    uint4 a = *reinterpret_cast<const uint4 *>(slot), q = *reinterpret_cast<const uint4 *>(slot + 32 * WPL);
+                    wa_[0] = a.x; wa_[1 % WPL] = a.y; wa_[2 % WPL] = a.z; wa_[3 % WPL] = a.w;
+                    wq_[0] = q.x; wq_[1 % WPL] = q.y; wq_[2 % WPL] = q.z; wq_[3 % WPL] = q.w;
+                } else if (WPL == 2) {
+                    uint2 a = *reinterpret_cast<const uint2 *>(slot), q = *reinterpret_cast<const uint2 *>(slot + 32 * WPL);
+                    wa_[0] = a.x; wa_[1 % WPL] = a.y;
+                    wq_[0] = q.x; wq_[1 % WPL] = q.y;
+                } else {
+                    wa_[0] = slot[0];
+                    wq_[0] = slot[32 * WPL];
                 }
             }
-        }
-        // next batch of loads
+            const int g = (gofs + (it - it0) * IK) >> p.gs_shift;
+            GroupConsts ga, gq;
+            ga.s2 = (uint32_t)sa[g] * 0x10001u; ga.b2 = (uint32_t)ba[g] * 0x10001u;
+            gq.s2 = (uint32_t)sq[g] * 0x10001u; gq.b2 = (uint32_t)bq[g] * 0x10001u;
+            ga.ns2 = bf2_mul(ga.s2, 0xC300C300u);  // -128 s, exact
+            gq.ns2 = bf2_mul(gq.s2, 0xC300C300u);
 #pragma unroll
-        for (int u = 0; u < QMV_UNROLL; u++) {
-            const int it = base + QMV_UNROLL + u;
-            if (it < it1) {
-                ldg_stream(qa[u], wa + (int64_t)it * 4 * WPL);
-                ldg_stream(qb[u], wq + (int64_t)it * 4 * WPL);
+            for (int j = 0; j < WPL; j++) {
+                uint32_t ra[AREGS], rq[AREGS], xr[XW];
+                U::run(wa_[j], ga, ra);
+                U::run(wq_[j], gq, rq);
+                if (XW == 2) {
+                    uint2 q = *reinterpret_cast<const uint2 *>(xp + j * 4 * XW);
+                    xr[0] = q.x; xr[1] = q.y;
+                } else {
+#pragma unroll
+                    for (int v = 0; v < XW; v += 4) {
+                        uint4 q = *reinterpret_cast<const uint4 *>(xp + j * 4 * XW + v);
+                        xr[v] = q.x; xr[v + 1] = q.y; xr[v + 2] = q.z; xr[v + 3] = q.w;
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < AREGS / 2; h++) {
+                    if ((j * (AREGS / 2) + h) & 1)
+                        mma_bf16_16816(acd, ra[2 * h], rq[2 * h], ra[2 * h + 1], rq[2 * h + 1], xr[2 * h], xr[2 * h + 1]);
+                    else
+                        mma_bf16_16816(acc, ra[2 * h], rq[2 * h], ra[2 * h + 1], rq[2 * h + 1], xr[2 * h], xr[2 * h + 1]);
+                }
+            }
+            xp += x_it_step;
+            // Refill the slot just consumed (its words are in registers and already used).
+            prefetch(stage);
+            stage = stage + 1 == QMV_STAGES ? 0 : stage + 1;
+        }
+        f = f1;
+        if (it1 != ipt && f1 != hi) continue;  // the tile goes on in the next k-chunk
+
+        // ── the run leaves this tile: rows r, r + 8; activation rows 2t, 2t + 1 ─────────
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v[i] = acc[i] + acd[i];
+            acc[i] = acd[i] = 0.f;
+        }
+        const int n0 = tile * 16;
+        const int64_t t_lo = (int64_t)tile * ipt, t_hi = t_lo + ipt;
+        bool store = lo <= t_lo && hi >= t_hi;  // the whole tile was this warp's
+        if (!store) {
+            // The warps whose runs cut this tile: first .. last, this one is number `mine`.  Each
+            // leaves its 16 x 8 partial in scratch; the one that arrives last adds them in run
+            // order (so the result does not depend on arrival order) and rearms the counter.
+            const int64_t first = ((t_lo + 1) * warps - 1) / total, last = (t_hi * warps - 1) / total;
+            const int mine = (int)(gw - first), count = (int)(last - first + 1);
+            const int64_t slot = b * tiles + tile;
+            float *part = p.partials + slot * p.max_parts * 128;
+            __stcg(reinterpret_cast<float2 *>(part + mine * 128 + r * 8 + 2 * t), make_float2(v[0], v[1]));
+            __stcg(reinterpret_cast<float2 *>(part + mine * 128 + (r + 8) * 8 + 2 * t), make_float2(v[2], v[3]));
+            __threadfence();
+            __syncwarp();
+            uint32_t arrived = 0;
+            if (lane == 0) arrived = atomicAdd(p.counters + slot, 1u);
+            arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
+            if (arrived == (uint32_t)count - 1) {
+                __threadfence();
+                v[0] = v[1] = v[2] = v[3] = 0.f;
+                for (int s2 = 0; s2 < count; s2++) {
+                    float2 a = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + r * 8 + 2 * t));
+                    float2 q = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + (r + 8) * 8 + 2 * t));
+                    v[0] += a.x; v[1] += a.y; v[2] += q.x; v[3] += q.y;
+                }
+                if (lane == 0) p.counters[slot] = 0u;
+                store = true;
+            }
+        }
+        if (store) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = n0 + r + (i >> 1) * 8, col = 2 * t + (i & 1);
+                if (col < p.M && row <= last_row) out[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
             }
         }
     }
-
-    // ── reduce the warps' partial sums ──────────────────────────────────────────────────
-    red[warp * 128 + r * 8 + 2 * t] = y[0];
-    red[warp * 128 + r * 8 + 2 * t + 1] = y[1];
-    red[warp * 128 + (r + 8) * 8 + 2 * t] = y[2];
-    red[warp * 128 + (r + 8) * 8 + 2 * t + 1] = y[3];
-    __syncthreads();
-    const bool owner = tid < 128;  // thread (row, col) of the 16 x 8 output tile
-    const int row = (tid >> 3) & 15, col = tid & 7;
-    float total = 0.f;
-    if (owner) {
-#pragma unroll
-        for (int w = 0; w < QMV_WARPS; w++) total += red[w * 128 + tid];
-    }
-    __nv_bfloat16 *out = (__nv_bfloat16 *)p.y + b * p.M * p.N;
-    const bool store = owner && col < p.M && n0 + row < p.N;
-    if (p.ksplit == 1) {
-        if (store) out[(int64_t)col * p.N + n0 + row] = __float2bfloat16_rn(total);
-        return;
-    }
-    // Split K: every block leaves its 16 x 8 partial in scratch; the block that arrives last
-    // adds them in split order (so the result does not depend on arrival order) and rearms
-    // the counter for the next launch.
-    const int64_t tile = b * gridDim.x + blockIdx.x;
-    float *part = p.partials + (tile * p.ksplit) * 128;
-    if (owner) {
-        __stcg(part + (int64_t)ks * 128 + tid, total);
-        __threadfence();
-    }
-    __shared__ uint32_t arrived;
-    __syncthreads();
-    if (tid == 0) arrived = atomicAdd(p.counters + tile, 1u);
-    __syncthreads();
-    if (arrived != (uint32_t)p.ksplit - 1) return;
-    __threadfence();
-    if (owner) {
-        float sum = 0.f;
-        for (int s = 0; s < p.ksplit; s++) sum += __ldcg(part + (int64_t)s * 128 + tid);
-        if (store) out[(int64_t)col * p.N + n0 + row] = __float2bfloat16_rn(sum);
-    }
-    if (tid == 0) p.counters[tile] = 0u;
+    cp_async_wait<0>();
 }
 
 // ── host side ──────────────────────────────────────────────────────────────────────────
 
-static int wpl_for(int bits, int gs) {
-    // words per lane per iteration, so that one quad (4 lanes) covers IK = 4*WPL*codes k-values
-    // with IK dividing the group size
-    switch (bits) {
-    case 4: return gs == 32 ? 1 : gs == 64 ? 2 : 4;
-    case 8: return gs == 32 ? 2 : 4;
-    case 2: return gs == 64 ? 1 : gs == 128 ? 2 : 0;
-    default: return 0;
+static int codes_per_word(int bits) { return 32 / bits; }
+
+// Words per lane per iteration: the widest vector load whose 4-lane span divides K.
+static int wpl_for(int bits, int gs, int64_t K) {
+    if (bits != 2 && bits != 4 && bits != 8) return 0;
+    const int codes = codes_per_word(bits);
+    for (int wpl = bits == 2 ? 2 : 4; wpl >= 1; wpl >>= 1) {
+        if (wpl * codes > gs) continue;          // a lane's words stay inside one group
+        if (K % (4 * wpl * codes) == 0) return wpl;
     }
+    return 0;
+}
+
+static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
+    const int codes = codes_per_word(bits), xw = bits == 4 ? 4 : bits == 8 ? 2 : 8;
+    return (size_t)(M * (K / codes * xw + 16) + 64 + QMV_WARPS * (2 * 16 * QMV_SPITCH) +
+                    QMV_STAGES * 2 * QMV_THREADS * wpl) * 4 + 16;
 }
 
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
@@ -469,60 +601,77 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
     (void)x; (void)ldx; (void)x_batch_stride;
     if (mode != NVC_AFFINE || dtype != NVC_BF16 || !transpose) return false;
     if (M < 1 || M > 8 || N < 1 || K < gs) return false;
-    int wpl = wpl_for(bits, gs);
+    int wpl = wpl_for(bits, gs, K);
     if (wpl == 0) return false;
     int64_t row_words = K * bits / 32;
     if (row_words % wpl != 0 || w_batch_stride % wpl != 0 || ((uintptr_t)w % (4 * wpl)) != 0) return false;
-    return true;
+    if (N * (K / (4 * wpl * codes_per_word(bits))) > (int64_t)1 << 40) return false;
+    return qmv_smem((int)M, K, bits, wpl) <= 220 * 1024;  // all activations are staged in shared memory
 }
 
 template <int BITS, int WPL>
-static int32_t launch_qmv_cfg(nvc_device *dev, QmvParams &p, int64_t batch, size_t smem) {
+static int32_t launch_qmv_cfg(nvc_device *dev, QmvParams &p, dim3 grid, size_t smem) {
     auto kernel = qmv_affine_kernel<BITS, WPL>;
-    if (smem > 48 * 1024) NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((unsigned)((p.N + 15) / 16), (unsigned)p.ksplit, (unsigned)batch);
-    kernel<<<grid, QMV_WARPS * 32, smem, dev->stream>>>(p);
+    static size_t configured = 0;  // largest dynamic shared memory size set so far (per instantiation)
+    if (smem > 48 * 1024 && smem > configured) {
+        NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    kernel<<<grid, QMV_THREADS, smem, dev->stream>>>(p);
     return check_launch(dev, "qmv_affine_kernel");
+}
+
+static int64_t env_int(const char *name, int64_t fallback) {
+    const char *e = getenv(name);
+    return e && *e ? atoll(e) : fallback;
 }
 
 int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch) {
     if (batch == 0 || p.N == 0 || p.M == 0) return NVC_OK;
     if (batch > 65535) return set_error(NVC_ERR_UNSUPPORTED, "qmv: %lld batches exceed the grid limit", (long long)batch);
-    const int wpl = wpl_for(bits, p.gs);
-    const int codes = bits == 4 ? 8 : bits == 8 ? 4 : 16, xregs = bits == 2 ? 8 : 4;
-    const int64_t groups = p.K / p.gs;
-    const int64_t tiles = (p.N + 15) / 16 * batch;
-    auto smem_for = [&](int64_t kr) {
-        return (size_t)(p.M * (kr / codes * xregs + 4) + 24 * (kr / p.gs) + QMV_WARPS * 128) * 4;
-    };
-    // Split K until the grid covers the machine about twice, keeping at least one group per
-    // warp and the staged activations within 64 KiB.
-    int64_t want = (2 * (int64_t)dev->prop.multiProcessorCount + tiles - 1) / tiles;
-    int64_t max_split = groups / QMV_WARPS > 0 ? groups / QMV_WARPS : 1;
-    int64_t ksplit = want < 1 ? 1 : want > max_split ? max_split : want;
-    if (const char *e = getenv("NUVEC_QMV_KSPLIT")) {
-        int64_t v = atoll(e);
-        if (v >= 1) ksplit = v > groups ? groups : v;
+    const int wpl = wpl_for(bits, p.gs, p.K);
+    const int codes = codes_per_word(bits);
+    const int ik = 4 * wpl * codes;
+    p.gs_shift = p.gs == 32 ? 5 : p.gs == 64 ? 6 : 7;
+    const int64_t tiles = (p.N + 15) / 16, ipt = p.K / ik, total = tiles * ipt;
+    // k-chunk for staging scales: the largest power of two up to 64 groups (and 2048 values) that
+    // divides K and holds whole iterations and groups.
+    int64_t chunk = (int64_t)QMV_SEG_GROUPS * p.gs;
+    if (chunk > 2048) chunk = 2048;
+    const int64_t unit = ik > p.gs ? ik : p.gs;
+    while (chunk > unit && p.K % chunk != 0) chunk >>= 1;
+    if (p.K % chunk != 0) chunk = unit;
+    p.chunk_k = (int32_t)chunk;
+    {
+        // Widest aligned copy for staging scales and biases: 8 groups, 2 groups or single loads.
+        const int64_t rg = p.K / p.gs, cg = chunk / p.gs;
+        const uintptr_t al = (uintptr_t)p.scales | (uintptr_t)p.biases;
+        if (al % 16 == 0 && p.s_batch_stride % 8 == 0 && rg % 8 == 0 && cg % 8 == 0) p.s_vec = 16;
+        else if (al % 4 == 0 && p.s_batch_stride % 2 == 0 && rg % 2 == 0 && cg % 2 == 0) p.s_vec = 4;
+        else p.s_vec = 0;
     }
-    int64_t kr = (groups + ksplit - 1) / ksplit * p.gs;
-    while (smem_for(kr) > 64 * 1024 && kr > p.gs) {
-        ksplit++;
-        kr = (groups + ksplit - 1) / ksplit * p.gs;
-    }
-    ksplit = (p.K + kr - 1) / kr;
-    p.kr = (int32_t)kr;
-    p.ksplit = (int32_t)ksplit;
-    p.partials = nullptr;
-    p.counters = nullptr;
-    if (ksplit > 1) {
-        void *scratch = nullptr;
-        NVC_TRY(ensure_scratch(dev, (size_t)tiles * ksplit * 128 * sizeof(float), &scratch));
-        p.partials = (float *)scratch;
-        NVC_TRY(ensure_counters(dev, (size_t)tiles, &p.counters));
-    }
-    const size_t smem = smem_for(kr);
-#define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, batch, smem);
-    NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(2, 1) NVC_QMV(2, 2)
+    const size_t smem = qmv_smem(p.M, p.K, bits, wpl);
+    // Blocks: as many as stay resident (two per multiprocessor while shared memory allows), but
+    // no more than give every warp a few iterations.
+    const int64_t per_sm = smem <= 113 * 1024 ? 2 : 1;
+    int64_t blocks = per_sm * dev->prop.multiProcessorCount / batch;
+    const int64_t min_iters = env_int("NUVEC_QMV_MIN_ITERS", 4);
+    const int64_t useful = (total + QMV_WARPS * min_iters - 1) / (QMV_WARPS * min_iters);
+    if (blocks > useful) blocks = useful;
+    const int64_t env_blocks = env_int("NUVEC_QMV_BLOCKS", 0);
+    if (env_blocks > 0) blocks = env_blocks;
+    if (blocks < 1) blocks = 1;
+    // Tiles cut by run boundaries: at most ipt / floor(total / warps) + 2 runs meet in one tile.
+    const int64_t warps = blocks * QMV_WARPS < total ? blocks * QMV_WARPS : total;
+    const int64_t run = total / warps;
+    p.max_parts = (int32_t)(ipt / run + 2);
+    void *scratch = nullptr;
+    NVC_TRY(ensure_scratch(dev, (size_t)tiles * batch * p.max_parts * 128 * sizeof(float), &scratch));
+    p.partials = (float *)scratch;
+    NVC_TRY(ensure_counters(dev, (size_t)(tiles * batch), &p.counters));
+    dim3 grid((unsigned)blocks, 1, (unsigned)batch);
+#define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, grid, smem);
+    NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(2, 1) NVC_QMV(2, 2)
 #undef NVC_QMV
     return set_error(NVC_ERR_UNSUPPORTED, "qmv: no kernel for %d bits, group size %d", bits, p.gs);
 }

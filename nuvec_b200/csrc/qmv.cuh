@@ -26,11 +26,11 @@ struct QmvParams {
     const void *scales, *biases;
     const uint32_t *lhs, *rhs;
     void *y;
-    float *partials;     // [tiles][ksplit][128] float32, used when ksplit > 1
+    float *partials;     // [tiles][max_parts][128] float32: partial sums of tiles cut by run boundaries
     uint32_t *counters;  // [tiles], zero on entry and on exit
     int64_t N, K, ldx;
     int64_t x_batch_stride, w_batch_stride, s_batch_stride;
-    int32_t M, gs, kr, ksplit, x_vec;
+    int32_t M, gs, gs_shift, chunk_k, max_parts, x_vec, s_vec;
 };
 // Returns NVC_ERR_UNSUPPORTED (without setting an error message) when the shape is not one
 // the fast kernel takes; the caller then uses the generic kernel.

@@ -29,6 +29,17 @@ def assert_product_close(got, want, dtype, what=""):
     assert np.all(err <= bound + 1e-30), f"{what}: max err {err.max():.4g}, worst ratio {(err / (bound + 1e-30)).max():.3f}"
 
 
+def assert_product_tight(got, want, dtype, what=""):
+    """For kernels whose operands equal the oracle's dequantized weights bit for bit: only the
+    float32 summation order differs, so results agree to one rounding of the output dtype."""
+    g, w = oracle.to_f32(got, dtype).astype(np.float64), oracle.to_f32(want, dtype).astype(np.float64)
+    ulp = {oracle.BF16: 2.0 ** -7, oracle.F16: 2.0 ** -10, oracle.F32: 2.0 ** -22}[dtype]
+    rowmax = np.abs(w).reshape(-1, w.shape[-1]).max(axis=1, keepdims=True).reshape(w.shape[:-1] + (1,))
+    lim = ulp * np.abs(w) + 2e-5 * rowmax
+    err = np.abs(g - w)
+    assert np.all(err <= lim), f"{what}: max err {err.max():.4g}, worst ratio {(err / lim).max():.3f}"
+
+
 AFFINE = [(b, g) for b in (1, 2, 3, 4, 5, 6, 8) for g in (32, 64, 128)]
 
 
@@ -87,6 +98,7 @@ def test_qmv_affine_bf16(be, bits, gs, M):
     want = oracle.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits)
     got = be.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits, True)
     assert_product_close(got, want, oracle.BF16, f"b{bits} g{gs} M{M}")
+    assert_product_tight(got, want, oracle.BF16, f"b{bits} g{gs} M{M}")
 
 
 @pytest.mark.parametrize("N,K", [(4096, 4096), (6144, 4096), (4096, 12288), (512, 12288), (768, 2048), (2048, 768),
@@ -100,6 +112,7 @@ def test_qmv_shapes_b4_g64(be, N, K, M):
     want = oracle.quantized_matmul(x, c, s, b, oracle.BF16)
     got = be.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, 64, 4, True)
     assert_product_close(got, want, oracle.BF16, f"N{N} K{K} M{M}")
+    assert_product_tight(got, want, oracle.BF16, f"N{N} K{K} M{M}")
 
 
 def test_qmv_one_hot_rows_return_the_dequantized_weights(be):
@@ -118,7 +131,7 @@ def test_qmv_one_hot_rows_return_the_dequantized_weights(be):
         got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(x, oracle.BF16), c, s, b, oracle.BF16,
                                                 oracle.AFFINE, 64, 4, True), oracle.BF16)
         want = dense[:, ks[k0:k0 + 8]].T
-        assert np.allclose(got, want, rtol=2 ** -7, atol=1e-6)
+        assert np.array_equal(got, want)
 
 
 @pytest.mark.parametrize("dt", ["f16", "f32"])
