@@ -77,6 +77,8 @@ struct nvc_device {
     size_t pinned_bytes = 0;
     void *staging = nullptr;
     size_t staging_bytes = 0;
+    // Host-mapped word a kernel sets when one of its bounded waits gives up; read at synchronisation.
+    int32_t *error_word = nullptr, *error_word_dev = nullptr;
 };
 
 struct nvc_graph {

@@ -1,7 +1,666 @@
-// Placeholder until the tcgen05 kernel lands: nothing is eligible, callers use the other kernels.
+// Many-row quantized products on the 5th-generation tensor cores (tcgen05), for prefill and
+// for the grouped (sorted) mixture-of-experts product:
+//
+//     y[tok, n] = sum_k x[tok, k] * dequantize(w)[n, k]         (weights stored [N, K], "transposed")
+//
+// One persistent block per multiprocessor walks output tiles of 128 weight rows x BT tokens.
+// The weight tile is the UMMA "A" operand (M = 128), the activations the "B" operand (N = BT):
+// the accumulator D[128 x BT] (float32) lives in tensor memory, each dequantized weight is reused
+// by BT tokens, and a group of few tokens (an expert with 32 rows) still fills all 128 lanes.
+//
+// Warp roles (448 threads):
+//   warps 0-3   epilogue: tcgen05.ld the finished accumulator, round to bfloat16, store y
+//   warp  4     TMA producer: activation tiles (64 k x BT tokens, 128-byte swizzle) and packed
+//               weight slabs (128 rows x 128 bytes, 128-byte swizzle) into shared-memory rings
+//   warp  5     MMA issuer (one thread): 4 x tcgen05.mma.kind::f16 (K = 16) per 64-k block,
+//               tcgen05.commit releases the stages / publishes the accumulator
+//   warps 6-13  dequantizers: packed codes -> bfloat16 "A" tile in the canonical K-major
+//               128-byte-swizzled layout, with exactly the reference's two roundings
+//               (crates/nuvec-core/src/kernels.rs:835-859), so the tensor-core operands are
+//               bit-identical to the reference's dequantized matrix
+// Two accumulator buffers in tensor memory let the epilogue of one tile overlap the main loop
+// of the next.  All waits are bounded: a wait that gives up raises an abort flag that every
+// other wait observes, the block frees its tensor memory and returns, and the host reports the
+// failure at the next synchronisation.
+//
+// Reference behaviour covered: MLX/nuvec's qmm_t, qmm_t_splitk, nax qmm_t and gather_qmm_rhs
+// kernels (crates/nuvec-kernels/src/metal/quantized.h:1358-1485, 2388-2519, 3301-3449;
+// nax/quantized.metal); CPU result crates/nuvec-core/src/kernels.rs:1091-1142 and, for the
+// gather, crates/nuvec-core/src/quantized.rs:679-719.
 #include "qmm.cuh"
+
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
 namespace nvc {
-bool qmm_eligible(int32_t, int32_t, int32_t, int32_t, int32_t, int64_t, int64_t, int64_t, const void *, int64_t,
-                  const uint32_t *) { return false; }
-int32_t launch_qmm(nvc_device *, const QmmParams &) { return set_error(NVC_ERR_UNSUPPORTED, "qmm: not built"); }
+
+constexpr int QMM_BN = 128;  // weight rows per tile (UMMA M)
+constexpr int QMM_BK = 64;   // k-values per block: one 128-byte swizzle row of bfloat16
+constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 8;
+constexpr int QMM_THREADS = (QMM_EPI_WARPS + 2 + QMM_DQ_WARPS) * 32;
+constexpr int QMM_DQ_THREADS = QMM_DQ_WARPS * 32;
+constexpr int QMM_W_STAGES = 2;          // packed-weight slabs in flight
+constexpr uint32_t QMM_W_BYTES = 128 * 128;  // one slab: 128 rows x 128 bytes
+constexpr uint32_t QMM_A_BYTES = QMM_BN * QMM_BK * 2;
+constexpr uint32_t QMM_SPIN_LIMIT = 1u << 22;  // polls before a wait gives up (each poll may block ~microseconds)
+
+struct QmmKernelParams {
+    const uint16_t *scales, *biases;  // bfloat16 [weight rows, K / gs]
+    const uint8_t *fp_scales;         // uint8 codes for mxfp4 / nvfp4 (scales aliased), else nullptr
+    const float *global;              // nvfp4 global scale(s) or nullptr
+    uint16_t *y;                      // bfloat16 [rows, N]
+    const int32_t *offsets;           // grouped: first row of each expert, else nullptr
+    int32_t *error;                   // host-visible word: nonzero when a wait gave up
+    int32_t experts, rows, N, K;
+    int32_t gs_shift, row_groups, mode, expert_global;
+};
+
+// ── PTX wrappers ───────────────────────────────────────────────────────────────────────────
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait.  Returns false when it gave up or another thread of the block already did.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t spin = 0; spin < QMM_SPIN_LIMIT; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, f32 accumulate.
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups
+// 1024 bytes apart (the canonical layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;                          // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(QMM_BN >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t q_lop3(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
+    return r;
+}
+__device__ __forceinline__ uint32_t q_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t q_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t q_add(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t q_mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// ── dequantization of 32 k-values of one weight row into 64 bytes (4 chunks of 16) ─────────
+// Affine, reference arithmetic: p = rn(code * scale), w = rn(p + bias), both in bfloat16.
+// Codes enter as the bfloat16 number 128 + code (code bits ORed into the mantissa of 128.0);
+// fma(128 + c, s, -128 s) is the single rounding of the exact product c * s.
+struct Affine {
+    uint32_t s2, ns2, b2;
+    __device__ __forceinline__ uint32_t finish(uint32_t m) const { return q_add(q_fma(m, s2, ns2), b2); }
+};
+// 4 bits: word = 8 codes.  a = w, b = w >> 4: byte j of a has code 2j in its low nibble, byte j of
+// b has code 2j+1 there; prmt gathers the two bytes into the two halves, lop3 masks and ORs 128.0.
+__device__ __forceinline__ uint4 dequant_word4(uint32_t w, const Affine &q) {
+    const uint32_t b = w >> 4;
+    uint4 o;
+    // selector: result byte 0 <- a.byte j, result byte 2 <- b.byte j (bytes 1 and 3 are masked away)
+    o.x = q.finish(q_lop3(q_prmt(w, b, 0x0400u), 0x000F000Fu, 0x43004300u));
+    o.y = q.finish(q_lop3(q_prmt(w, b, 0x0501u), 0x000F000Fu, 0x43004300u));
+    o.z = q.finish(q_lop3(q_prmt(w, b, 0x0602u), 0x000F000Fu, 0x43004300u));
+    o.w = q.finish(q_lop3(q_prmt(w, b, 0x0703u), 0x000F000Fu, 0x43004300u));
+    return o;
+}
+// 8 bits: the byte is rebuilt exactly from its nibbles (16 * hi + lo <= 255 fits bfloat16), then
+// multiplied and biased with one rounding each.  Two words (8 codes) make one 16-byte chunk.
+__device__ __forceinline__ uint2 dequant_word8(uint32_t w, const Affine &q) {
+    const uint32_t k16 = 0x41804180u, kn2048 = 0xC500C500u, kn128 = 0xC300C300u;
+    const uint32_t h = w >> 4;
+    uint2 o;
+    {
+        uint32_t lo = q_lop3(q_prmt(w, w, 0x0100u), 0x000F000Fu, 0x43004300u);   // codes 0, 1 (low nibbles)
+        uint32_t hi = q_lop3(q_prmt(h, h, 0x0100u), 0x000F000Fu, 0x43004300u);   // their high nibbles
+        uint32_t code = q_add(q_fma(hi, k16, kn2048), q_add(lo, kn128));
+        o.x = q_add(q_mul(code, q.s2), q.b2);
+    }
+    {
+        uint32_t lo = q_lop3(q_prmt(w, w, 0x0302u), 0x000F000Fu, 0x43004300u);   // codes 2, 3
+        uint32_t hi = q_lop3(q_prmt(h, h, 0x0302u), 0x000F000Fu, 0x43004300u);
+        uint32_t code = q_add(q_fma(hi, k16, kn2048), q_add(lo, kn128));
+        o.y = q_add(q_mul(code, q.s2), q.b2);
+    }
+    return o;
+}
+// 2 bits: word = 16 codes; codes 2j, 2j+1 sit in bits [4j, 4j+4).
+__device__ __forceinline__ void dequant_word2(uint32_t w, const Affine &q, uint4 &o0, uint4 &o1) {
+    const uint32_t b = w >> 2;
+    uint32_t r[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        // byte j/2 holds codes 4(j/2) .. 4(j/2)+3; pair j = codes (2j, 2j+1): shift the byte pair by 4 (j odd)
+        const uint32_t sel = 0x0400u + 0x0101u * (uint32_t)(j >> 1);
+        uint32_t t = q_prmt(w, b, sel);
+        if (j & 1) t >>= 4;
+        r[j] = q.finish(q_lop3(t, 0x00030003u, 0x43004300u));
+    }
+    o0 = make_uint4(r[0], r[1], r[2], r[3]);
+    o1 = make_uint4(r[4], r[5], r[6], r[7]);
+}
+
+// E2M1 code pairs -> bfloat16 pairs times the group scale.  The code's three magnitude bits become
+// exponent[1:0] and mantissa[6] of a bfloat16 whose value is magnitude * 2^-126 (the subnormal
+// codes 0 and 0.5 included); multiplying by 2^126 restores the value and multiplying by the
+// scale (a power of two, or an E4M3 number with 4 significant bits) is exact: the product has at
+// most 6 significant bits.  It equals the reference's float32 value scale * code
+// (crates/nuvec-core/src/kernels.rs:976-1009).
+__device__ __forceinline__ uint4 dequant_word_fp4(uint32_t w, uint32_t scale2) {
+    const uint32_t b = w >> 4;
+    uint32_t t[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t p = q_prmt(w, b, 0x0400u + 0x0101u * (uint32_t)j);  // halves: codes 2j, 2j+1 in bits [3:0]
+        const uint32_t bits = ((p & 0x00070007u) << 6) | ((p & 0x00080008u) << 12);
+        t[j] = q_mul(q_mul(bits, 0x7E807E80u), scale2);
+    }
+    return make_uint4(t[0], t[1], t[2], t[3]);
+}
+// bfloat16 pair {s, s} of a scale code: E8M0 (2^(code - 127); code 0 decodes to a float32 subnormal
+// that the reference flushes to zero) or E4M3.
+__device__ __forceinline__ uint32_t fp_scale2(uint32_t code, bool e8m0) {
+    uint32_t h;
+    if (e8m0) h = code == 0u ? 0u : (code << 7);
+    else h = __float_as_uint(ftz(e4m3_to_f32(code))) >> 16;
+    return (h & 0xFFFFu) * 0x10001u;
+}
+
+template <int BITS> struct QmmBits;
+template <> struct QmmBits<4> { static constexpr int KPS = 4; };  // 64-k blocks per 128-byte packed slab row
+template <> struct QmmBits<8> { static constexpr int KPS = 2; };
+template <> struct QmmBits<2> { static constexpr int KPS = 8; };
+
+// Tile bookkeeping shared by the roles.
+struct TileInfo {
+    int n0;        // first weight row of the tile inside its matrix
+    int wrow0;     // first row in the stacked [experts * N] weight / scale arrays
+    int tok0;      // first token row of the tile
+    int tok_end;   // tokens at or past this row are not stored
+    int expert;
+};
+
+template <int BT>
+__device__ __forceinline__ bool tile_info(const QmmKernelParams &p, int tile, int n_tiles, TileInfo &ti) {
+    const int nt = tile % n_tiles, j = tile / n_tiles;
+    ti.n0 = nt * QMM_BN;
+    if (!p.offsets) {
+        ti.expert = 0;
+        ti.wrow0 = ti.n0;
+        ti.tok0 = j * BT;
+        ti.tok_end = p.rows;
+        return ti.tok0 < p.rows;
+    }
+    // grouped: token tile j of the concatenation of every expert's tiles
+    int seen = 0;
+    for (int e = 0; e < p.experts; e++) {
+        const int lo = p.offsets[e], hi = e + 1 < p.experts ? p.offsets[e + 1] : p.rows;
+        const int tiles_e = (hi - lo + BT - 1) / BT;
+        if (j < seen + tiles_e) {
+            ti.expert = e;
+            ti.wrow0 = e * p.N + ti.n0;
+            ti.tok0 = lo + (j - seen) * BT;
+            ti.tok_end = hi;
+            return true;
+        }
+        seen += tiles_e;
+    }
+    return false;
+}
+
+template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 3 nvfp4*/>
+__global__ void __launch_bounds__(QMM_THREADS, 1)
+qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, QmmKernelParams p,
+           int total_tiles, int n_tiles) {
+    constexpr int KPS = QmmBits<BITS>::KPS;
+    constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
+    constexpr int TMEM_COLS = 2 * BT < 32 ? 32 : 2 * BT;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *xs = smem;                                   // [STAGES][BT x 128 B]
+    uint8_t *as = xs + STAGES * X_BYTES;                  // [STAGES][128 x 128 B]
+    uint8_t *ws = as + STAGES * QMM_A_BYTES;              // [QMM_W_STAGES][128 x 128 B]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ws + QMM_W_STAGES * QMM_W_BYTES);
+    uint64_t *xfull = bars, *afull = xfull + STAGES, *empty = afull + STAGES;
+    uint64_t *wfull = empty + STAGES, *wempty = wfull + QMM_W_STAGES;
+    uint64_t *accfull = wempty + QMM_W_STAGES, *accempty = accfull + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accempty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kblocks = p.K / QMM_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(xfull + s, 1);
+            mbar_init(afull + s, QMM_DQ_WARPS);
+            mbar_init(empty + s, 1);
+        }
+        for (int s = 0; s < QMM_W_STAGES; s++) {
+            mbar_init(wfull + s, 1);
+            mbar_init(wempty + s, QMM_DQ_WARPS);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(accfull + s, 1);
+            mbar_init(accempty + s, QMM_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {  // tensor memory for two accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        // ── TMA producer ────────────────────────────────────────────────────────────────
+        if (lane == 0) {
+            uint32_t it = 0, wit = 0;  // k-blocks / weight slabs issued so far
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                TileInfo ti;
+                if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                    if (kb % KPS == 0) {
+                        const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
+                        ok = mbar_wait(wempty + s, ph ^ 1, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(wfull + s, QMM_W_BYTES);
+                        tma_load_2d(ws + s * QMM_W_BYTES, &tmap_w, (kb / KPS) * 128, ti.wrow0, wfull + s);
+                        wit++;
+                    }
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(xfull + s, X_BYTES);
+                    tma_load_2d(xs + s * X_BYTES, &tmap_x, kb * QMM_BK, ti.tok0, xfull + s);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ── MMA issuer ──────────────────────────────────────────────────────────────────
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BT);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                TileInfo ti;
+                if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+                const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
+                ok = mbar_wait(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BT;
+                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    ok = mbar_wait(xfull + s, ph, abort_flag) && mbar_wait(afull + s, ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t ad = umma_desc(smem_u32(as + s * QMM_A_BYTES));
+                    const uint64_t bd = umma_desc(smem_u32(xs + s * X_BYTES));
+#pragma unroll
+                    for (int k = 0; k < QMM_BK / 16; k++)  // 32 bytes further along K inside the swizzle row
+                        tc_mma_bf16(d, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                    tc_commit(empty + s);  // frees the stage once these MMAs have read it
+                }
+                if (ok) tc_commit(accfull + buf);
+                tcount++;
+            }
+        }
+    } else if (warp >= 6) {
+        // ── dequantizers: thread = (row, 32-k half) of the 128 x 64 tile ─────────────────
+        const int dt = tid - 6 * 32;
+        const int row = dt & 127, half = dt >> 7;
+        const int sw = row & 7;  // swizzle phase of this row
+        uint32_t it = 0, wit = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            TileInfo ti;
+            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            // rows past N (last tile) read the last valid row's scales; their outputs are not stored
+            const int wr = ti.wrow0 + min(row, p.N - 1 - ti.n0);
+            const uint16_t *sc = p.scales + (size_t)wr * p.row_groups;
+            const uint16_t *bi = p.biases ? p.biases + (size_t)wr * p.row_groups : nullptr;
+            const uint8_t *fsc = p.fp_scales ? p.fp_scales + (size_t)wr * p.row_groups : nullptr;
+            // scale/bias of the first block
+            uint32_t s_next = 0, b_next = 0;
+            {
+                const int g = (half * 32) >> p.gs_shift;
+                if (MODE == 0) { s_next = sc[g]; b_next = bi[g]; }
+                else s_next = fsc[g];
+                if (MODE == 3) b_next = fsc[(half * 32 + 16) >> p.gs_shift];
+            }
+            for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                const uint32_t s_cur = s_next, b_cur = b_next;
+                if (kb + 1 < kblocks) {  // prefetch the next block's constants
+                    const int g = ((kb + 1) * QMM_BK + half * 32) >> p.gs_shift;
+                    if (MODE == 0) { s_next = sc[g]; b_next = bi[g]; }
+                    else s_next = fsc[g];
+                    if (MODE == 3) b_next = fsc[((kb + 1) * QMM_BK + half * 32 + 16) >> p.gs_shift];
+                }
+                const uint32_t wsi = wit % QMM_W_STAGES, wph = (wit / QMM_W_STAGES) & 1;
+                if (kb % KPS == 0) ok = mbar_wait(wfull + wsi, wph, abort_flag);
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                ok = ok && mbar_wait(empty + s, ph ^ 1, abort_flag);
+                if (!ok) break;
+                const uint8_t *wrow = ws + wsi * QMM_W_BYTES + row * 128;
+                uint8_t *arow = as + s * QMM_A_BYTES + row * 128;
+                const int kq = kb % KPS;
+                if (MODE == 0) {
+                    Affine q;
+                    q.s2 = s_cur * 0x10001u;
+                    q.b2 = b_cur * 0x10001u;
+                    q.ns2 = q_mul(q.s2, 0xC300C300u);  // -128 s, exact
+                    if (BITS == 4) {
+                        const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
+                        const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word4(wv[j], q);
+                    } else if (BITS == 8) {
+#pragma unroll
+                        for (int c = 0; c < 2; c++) {
+                            const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 4 + half * 2 + c) ^ sw) << 4));
+                            const uint2 a = dequant_word8(pk.x, q), b2 = dequant_word8(pk.y, q);
+                            const uint2 c2 = dequant_word8(pk.z, q), d2 = dequant_word8(pk.w, q);
+                            *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c) ^ sw) << 4)) = make_uint4(a.x, a.y, b2.x, b2.y);
+                            *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c + 1) ^ sw) << 4)) = make_uint4(c2.x, c2.y, d2.x, d2.y);
+                        }
+                    } else {
+                        const uint2 pk = *reinterpret_cast<const uint2 *>(wrow + ((kq ^ sw) << 4) + half * 8);
+                        uint4 o0, o1;
+                        dequant_word2(pk.x, q, o0, o1);
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 0) ^ sw) << 4)) = o0;
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 1) ^ sw) << 4)) = o1;
+                        dequant_word2(pk.y, q, o0, o1);
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2) ^ sw) << 4)) = o0;
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 3) ^ sw) << 4)) = o1;
+                    }
+                } else {
+                    // mxfp4: one scale per 32 values; nvfp4: one per 16 (two per thread and block)
+                    const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
+                    const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+                    const uint32_t sa = fp_scale2(s_cur, MODE == 1);
+                    const uint32_t sb = MODE == 3 ? fp_scale2(b_cur, false) : sa;
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word_fp4(wv[j], j < 2 ? sa : sb);
+                }
+                fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(afull + s);
+                    if (kq == KPS - 1 || kb == kblocks - 1) mbar_arrive(wempty + wsi);
+                }
+                if (kq == KPS - 1 || kb == kblocks - 1) wit++;
+            }
+        }
+    } else {
+        // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            TileInfo ti;
+            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
+            ok = mbar_wait(accfull + buf, aph, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int n = ti.n0 + warp * 32 + lane;
+            float gmul = 1.0f;
+            if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
+#pragma unroll 1
+            for (int c = 0; c < BT / 32; c++) {
+                uint32_t v[32];
+                tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
+                tc_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int tok = ti.tok0 + c * 32 + j;
+                        if (tok < ti.tok_end) {
+                            float f = __uint_as_float(v[j]);
+                            if (MODE != 0) f *= gmul;
+                            p.y[(size_t)tok * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty + buf);
+            tcount++;
+        }
+    }
+
+    // ── teardown ────────────────────────────────────────────────────────────────────────
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag && p.error) *p.error = 1;
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+// ── host side ──────────────────────────────────────────────────────────────────────────────
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// 2-D tensor map: `inner` elements per row (contiguous), `rows` rows `pitch_bytes` apart.
+static int32_t make_map(CUtensorMap *map, CUtensorMapDataType type, const void *base, uint64_t inner, uint64_t rows,
+                        uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(NVC_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {inner, rows}, strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows}, estr[2] = {1, 1};
+    CUresult r = fn(map, type, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(NVC_ERR_DRIVER, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return NVC_OK;
+}
+
+bool qmm_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M, int64_t N,
+                  int64_t K, const void *x, int64_t ldx, const uint32_t *w) {
+    (void)gs;
+    if (getenv("NUVEC_QMM_DISABLE")) return false;
+    if (dtype != NVC_BF16 || !transpose) return false;
+    if (mode == NVC_AFFINE) {
+        if (bits != 2 && bits != 4 && bits != 8) return false;
+    } else if (mode != NVC_MXFP4 && mode != NVC_NVFP4) {
+        return false;
+    }
+    if (M < 1 || N < 1 || K < QMM_BK || K % QMM_BK != 0) return false;
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return false;
+    // TMA: 16-byte aligned bases and row pitches
+    if ((uintptr_t)x % 16 != 0 || (ldx * 2) % 16 != 0) return false;
+    if ((uintptr_t)w % 16 != 0 || (K * bits / 8) % 16 != 0) return false;
+    return true;
+}
+
+template <int BITS, int BT, int MODE>
+static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
+                          int total_tiles, int n_tiles) {
+    constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
+    // as many stages as fit beside the two weight slabs
+    constexpr int budget = 227 * 1024 - 1024 - QMM_W_STAGES * (int)QMM_W_BYTES - 512;
+    constexpr int fit = budget / (int)(X_BYTES + QMM_A_BYTES);
+    constexpr int STAGES = fit > 8 ? 8 : fit;
+    static_assert(STAGES >= 3, "not enough shared memory for the pipeline");
+    constexpr size_t smem = 1024 + STAGES * (X_BYTES + QMM_A_BYTES) + QMM_W_STAGES * QMM_W_BYTES + 512;
+    auto kernel = qmm_kernel<BITS, BT, STAGES, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    int grid = dev->prop.multiProcessorCount < total_tiles ? dev->prop.multiProcessorCount : total_tiles;
+    kernel<<<grid, QMM_THREADS, smem, dev->stream>>>(mx, mw, kp, total_tiles, n_tiles);
+    return check_launch(dev, "qmm_kernel");
+}
+
+template <int BITS, int MODE>
+static int32_t launch_bt(nvc_device *dev, int bt, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
+                         int total_tiles, int n_tiles) {
+    switch (bt) {
+    case 32: return launch_cfg<BITS, 32, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    case 64: return launch_cfg<BITS, 64, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    case 128: return launch_cfg<BITS, 128, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    default: return launch_cfg<BITS, 256, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    }
+}
+
+int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
+    if (p.rows == 0 || p.N == 0) return NVC_OK;
+    const int64_t experts = p.offsets ? p.experts : 1;
+    // Token tile: the largest that the rows (per expert, on average) fill reasonably.
+    const int64_t per = p.offsets ? (p.rows + experts - 1) / experts : p.rows;
+    int bt = per > 160 ? 256 : per > 80 ? 128 : per > 40 ? 64 : 32;
+    if (const char *e = getenv("NUVEC_QMM_BT")) {
+        int v = atoi(e);
+        if (v == 32 || v == 64 || v == 128 || v == 256) bt = v;
+    }
+    const int n_tiles = (int)((p.N + QMM_BN - 1) / QMM_BN);
+    int64_t token_tiles;
+    if (p.offsets) token_tiles = (p.rows + bt - 1) / bt + experts;  // upper bound: one partial tile per expert
+    else token_tiles = (p.rows + bt - 1) / bt;
+    const int64_t total = token_tiles * n_tiles;
+    if (total > INT32_MAX) return set_error(NVC_ERR_UNSUPPORTED, "qmm: too many tiles");
+
+    CUtensorMap mx, mw;
+    NVC_TRY(make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.x, (uint64_t)p.K, (uint64_t)p.rows, (uint64_t)p.ldx * 2,
+                     QMM_BK, (uint32_t)bt));
+    const uint64_t wrow_bytes = (uint64_t)p.K * p.bits / 8;
+    NVC_TRY(make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.w, wrow_bytes, (uint64_t)(experts * p.N), wrow_bytes, 128, 128));
+
+    if (!dev->error_word) {
+        NVC_CUDA(cudaHostAlloc((void **)&dev->error_word, sizeof(int32_t), cudaHostAllocMapped));
+        *dev->error_word = 0;
+        NVC_CUDA(cudaHostGetDevicePointer((void **)&dev->error_word_dev, dev->error_word, 0));
+    }
+    QmmKernelParams kp{};
+    const bool affine = p.mode == NVC_AFFINE;
+    kp.scales = affine ? (const uint16_t *)p.scales : nullptr;
+    kp.biases = affine ? (const uint16_t *)p.biases : nullptr;
+    kp.fp_scales = affine ? nullptr : (const uint8_t *)p.scales;
+    kp.global = p.global;
+    kp.y = (uint16_t *)p.y;
+    kp.offsets = p.offsets;
+    kp.error = dev->error_word_dev;
+    kp.experts = (int32_t)experts;
+    kp.rows = (int32_t)p.rows;
+    kp.N = (int32_t)p.N;
+    kp.K = (int32_t)p.K;
+    kp.gs_shift = p.gs == 16 ? 4 : p.gs == 32 ? 5 : p.gs == 64 ? 6 : 7;
+    kp.row_groups = (int32_t)(p.K / p.gs);
+    kp.mode = p.mode;
+    kp.expert_global = p.expert_global;
+    const int tt = (int)total;
+    if (affine) {
+        switch (p.bits) {
+        case 4: return launch_bt<4, 0>(dev, bt, mx, mw, kp, tt, n_tiles);
+        case 8: return launch_bt<8, 0>(dev, bt, mx, mw, kp, tt, n_tiles);
+        default: return launch_bt<2, 0>(dev, bt, mx, mw, kp, tt, n_tiles);
+        }
+    }
+    if (p.mode == NVC_MXFP4) return launch_bt<4, 1>(dev, bt, mx, mw, kp, tt, n_tiles);
+    return launch_bt<4, 3>(dev, bt, mx, mw, kp, tt, n_tiles);
+}
+
 }  // namespace nvc

@@ -246,6 +246,7 @@ int32_t nvc_device_close(nvc_device *dev) {
     if (dev->counters) dev->pool.free(dev->counters);
     if (dev->staging) dev->pool.free(dev->staging);
     if (dev->pinned) cudaFreeHost(dev->pinned);
+    if (dev->error_word) cudaFreeHost(dev->error_word);
     dev->pool.clear();
     cudaStreamDestroy(dev->own_stream);
     delete dev;
@@ -270,6 +271,10 @@ int32_t nvc_device_info(nvc_device *dev, nvc_info *out) {
 int32_t nvc_synchronize(nvc_device *dev) {
     NVC_TRY(make_current(dev));
     NVC_CUDA(cudaStreamSynchronize(dev->stream));
+    if (dev->error_word && *dev->error_word != 0) {
+        *dev->error_word = 0;
+        return set_error(NVC_ERR_DRIVER, "a kernel gave up waiting on its pipeline (bounded wait expired); results of the last work are invalid");
+    }
     return NVC_OK;
 }
 
@@ -307,8 +312,7 @@ int32_t nvc_memcpy_d2h(nvc_device *dev, void *dst, const void *src, size_t bytes
     NVC_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, dev->stream));
     // A host read must see the data: the reference's CPU access waits for GPU work
     // (crates/nuvec-core/src/buffer.rs:204-212).
-    NVC_CUDA(cudaStreamSynchronize(dev->stream));
-    return NVC_OK;
+    return nvc_synchronize(dev);
 }
 
 int32_t nvc_memcpy_d2d(nvc_device *dev, void *dst, const void *src, size_t bytes) {

@@ -232,3 +232,88 @@ def test_pool_reuses_blocks_and_reports_stats(be):
     assert after["active"] == before["active"] and after["cached"] >= 4 << 20
     b = dev.empty((1 << 20,), nv.F32)
     assert b.ptr.value == ptr and dev.memory()["allocations"] == mid["allocations"]
+
+
+# ── many-row products on the tensor-core kernel ────────────────────────────────────────────
+@pytest.mark.parametrize("bits,gs", [(4, 64), (4, 32), (4, 128), (8, 64), (8, 32), (2, 64), (2, 128)])
+@pytest.mark.parametrize("M,N,K", [(17, 128, 64), (64, 200, 256), (200, 384, 512), (300, 136, 2880 // 45 * 45)])
+def test_qmm_affine_bf16(be, bits, gs, M, N, K):
+    K = max(K // gs * gs, gs)
+    if K % 64:
+        K = (K // 64 + 1) * 64
+    rng = np.random.default_rng(bits * 7 + gs + M)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits)
+    got = be.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits, True)
+    assert_product_close(got, want, oracle.BF16, f"b{bits} g{gs} M{M} N{N} K{K}")
+    assert_product_tight(got, want, oracle.BF16, f"b{bits} g{gs} M{M} N{N} K{K}")
+
+
+@pytest.mark.parametrize("bits,gs", [(4, 64), (8, 64), (2, 64), (4, 32)])
+def test_qmm_unit_rows_return_the_dequantized_weights_bit_for_bit(be, bits, gs):
+    # x = 192 unit vectors: y[m, :] must equal column k_m of dequantize(w) exactly (products with
+    # 1.0 and sums with zeros are exact), which pins the tensor-core operands to the oracle's
+    # dequantized matrix bit for bit.
+    rng = np.random.default_rng(bits)
+    N, K, M = 256, 512, 192
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    dense = oracle.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, gs, bits)
+    ks = rng.permutation(K)[:M]
+    x = np.zeros((M, K), np.float32)
+    x[np.arange(M), ks] = 1.0
+    got = be.quantized_matmul(oracle.from_f32(x, oracle.BF16), c, s, b, oracle.BF16, oracle.AFFINE, gs, bits, True)
+    assert np.array_equal(got, dense[:, ks].T)
+
+
+@pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
+@pytest.mark.parametrize("M,N,K", [(40, 128, 128), (130, 200, 2880)])
+def test_qmm_fp4(be, mode, gs, M, N, K):
+    rng = np.random.default_rng(mode + M)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    w.reshape(-1)[:4] = oracle.from_f32(np.array([0.0, 0.011, -0.5, 3.0], np.float32), oracle.BF16)
+    c, s, _ = oracle.quantize(w, oracle.BF16, mode, gs, 4)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, None, oracle.BF16, mode, gs, 4)
+    got = be.quantized_matmul(x, c, s, None, oracle.BF16, mode, gs, 4, True)
+    assert_product_tight(got, want, oracle.BF16)
+    # unit rows: the operands are the oracle's float32 decode exactly
+    dense = oracle.to_f32(oracle.dequantize(c, s, None, oracle.F32, mode, gs, 4), oracle.F32)
+    ks = rng.permutation(K)[:64]
+    xu = np.zeros((64, K), np.float32)
+    xu[np.arange(64), ks] = 1.0
+    got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(xu, oracle.BF16), c, s, None, oracle.BF16, mode, gs, 4, True), oracle.BF16)
+    assert np.array_equal(got, dense[:, ks].T)
+
+
+def moe_case(rng, T, E, topk, N, K, mode=oracle.AFFINE, gs=64, bits=4):
+    w = rand(rng, (E, N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, mode, gs, bits)
+    ids = np.concatenate([rng.permutation(E)[:topk] for _ in range(T)]).astype(np.uint32)
+    order = np.argsort(ids, kind="stable")
+    rhs = ids[order]
+    x = rand(rng, (T, K), oracle.BF16)
+    xr = x[np.repeat(np.arange(T), topk)[order]][:, None, :]
+    return c, s, b, rhs, np.ascontiguousarray(xr)
+
+
+@pytest.mark.parametrize("T,E,topk,N,K", [(64, 16, 4, 256, 512), (100, 8, 2, 136, 256), (512, 128, 8, 768, 2048)])
+def test_gather_grouped_affine(be, T, E, topk, N, K):
+    rng = np.random.default_rng(T + E)
+    c, s, b, rhs, xr = moe_case(rng, T, E, topk, N, K)
+    want = oracle.gather_qmm(xr, c, s, b, np.arange(len(rhs)), rhs, oracle.BF16)
+    got = be.gather_qmm(xr, c, s, b, None, rhs, oracle.BF16, oracle.AFFINE, 64, 4, True, None, True)
+    assert_product_tight(got, want, oracle.BF16)
+
+
+@pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
+def test_gather_grouped_fp4(be, mode, gs):
+    rng = np.random.default_rng(mode)
+    T, E, topk, N, K = 96, 8, 4, 192, 2880
+    c, s, _, rhs, xr = moe_case(rng, T, E, topk, N, K, mode, gs, 4)
+    for g in ([None] if mode != oracle.NVFP4 else [None, (rng.random(E) * 4 + 0.5).astype(np.float32)]):
+        want = oracle.gather_qmm(xr, c, s, None, np.arange(len(rhs)), rhs, oracle.BF16, mode, gs, 4, True, g)
+        got = be.gather_qmm(xr, c, s, None, None, rhs, oracle.BF16, mode, gs, 4, True, g, True)
+        assert_product_tight(got, want, oracle.BF16, f"global={g is not None}")
