@@ -212,6 +212,26 @@ int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q, int32_t d
                                   const float *global_scale, int64_t M, int64_t N, int64_t K,
                                   void *host_y);
 
+/* No counterpart in the reference.  The few-row product for callers that may not allocate device
+ * memory while they run: code that executes between a memory reservation made up front and its
+ * release (a serving loop under a fixed memory budget, a plugin hosted by a runtime that owns
+ * the allocator), where a hidden cudaMalloc would either fail or break the budget.  The other
+ * entry points take their scratch (partial sums of tiles split across warps, arrival counters)
+ * from the handle's pool and may grow it; this one keeps that scratch in a 4 MiB array that is
+ * part of the library image -- every GPU that loads the library holds it until the process
+ * exits -- and calls no cudaMalloc, cudaFree or allocating routine.
+ *   x: bfloat16 [M, K] dense, 1 <= M <= 8;  w: affine 2-, 4- or 8-bit, [N, K*bits/32], K a multiple
+ *   of 32 values per vector-load step (any K the fast kernel of nvc_quantized_matmul takes);
+ *   scales/biases bfloat16 [N, K/gs];  y: bfloat16 [M, N].  Results equal nvc_quantized_matmul's.
+ * Limits: N <= 262144 and partial sums <= 4 MiB - 64 KiB, else NVC_ERR_UNSUPPORTED with the sizes
+ * in the message.  The first call on a device looks up the array's device address; make that
+ * call before any stream capture.  All calls share the one array: it keeps the last call's
+ * contents (the counters are cleared on the stream at the start of each call), and two calls
+ * whose kernels overlap on the GPU -- different streams, different handles -- race on it. */
+int32_t nvc_quantized_matmul_noalloc(nvc_device *dev, const nvc_quant *q, const void *x, const uint32_t *w,
+                                     const void *scales, const void *biases, int64_t M, int64_t N, int64_t K,
+                                     void *y);
+
 /* ── collectives: trait Communicator, crates/nuvec-core/src/distributed.rs:43-83 ────── */
 
 /* One rank per process and per GPU (distributed.rs:145-180).  The 128-byte id is created on

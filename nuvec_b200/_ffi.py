@@ -75,6 +75,7 @@ SIGNATURES = {
     "nvc_gather_qmm": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, P, P, P, I32T, I64T, I64T, I64T, I64T,
                               I64T, I64T, P]),
     "nvc_quantized_matmul_host": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, P]),
+    "nvc_quantized_matmul_noalloc": (I32T, [P, QP, P, P, P, P, I64T, I64T, I64T, P]),
     "nvc_comm_unique_id": (I32T, [P]),
     "nvc_comm_init": (I32T, [P, I32T, I32T, P, C.POINTER(P)]),
     "nvc_comm_rank": (I32T, [P]),

@@ -626,7 +626,7 @@ static int64_t env_int(const char *name, int64_t fallback) {
     return e && *e ? atoll(e) : fallback;
 }
 
-int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch) {
+int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch, const QmvScratch *fixed) {
     if (batch == 0 || p.N == 0 || p.M == 0) return NVC_OK;
     if (batch > 65535) return set_error(NVC_ERR_UNSUPPORTED, "qmv: %lld batches exceed the grid limit", (long long)batch);
     const int wpl = wpl_for(bits, p.gs, p.K);
@@ -665,10 +665,22 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     const int64_t warps = blocks * QMV_WARPS < total ? blocks * QMV_WARPS : total;
     const int64_t run = total / warps;
     p.max_parts = (int32_t)(ipt / run + 2);
-    void *scratch = nullptr;
-    NVC_TRY(ensure_scratch(dev, (size_t)tiles * batch * p.max_parts * 128 * sizeof(float), &scratch));
-    p.partials = (float *)scratch;
-    NVC_TRY(ensure_counters(dev, (size_t)(tiles * batch), &p.counters));
+    const size_t partial_bytes = (size_t)tiles * batch * p.max_parts * 128 * sizeof(float);
+    if (fixed) {
+        // Scratch of fixed capacity provided by the caller of this function: nothing is allocated.
+        if (partial_bytes > fixed->partial_bytes || (size_t)(tiles * batch) > fixed->counters_len)
+            return set_error(NVC_ERR_UNSUPPORTED,
+                             "qmv: this product needs %zu bytes of partial sums and %lld counters; the fixed scratch holds "
+                             "%zu bytes and %zu counters", partial_bytes, (long long)(tiles * batch), fixed->partial_bytes,
+                             fixed->counters_len);
+        p.partials = fixed->partials;
+        p.counters = fixed->counters;
+    } else {
+        void *scratch = nullptr;
+        NVC_TRY(ensure_scratch(dev, partial_bytes, &scratch));
+        p.partials = (float *)scratch;
+        NVC_TRY(ensure_counters(dev, (size_t)(tiles * batch), &p.counters));
+    }
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
 #define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, grid, smem);
     NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(2, 1) NVC_QMV(2, 2)
@@ -677,3 +689,71 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
 }
 
 }  // namespace nvc
+
+// ── the entry point that allocates nothing ─────────────────────────────────────────────────
+//
+// Scratch for nvc_quantized_matmul_noalloc: part of the library image, so every GPU that loads
+// the library holds these 4 MiB until the process exits.  Layout: float32 partial sums, then the
+// arrival counters.
+namespace {
+constexpr size_t NOALLOC_SCRATCH_BYTES = 4u << 20;
+constexpr size_t NOALLOC_COUNTERS = 16384;  // one per 16-row tile: N up to 262144
+constexpr size_t NOALLOC_PARTIAL_BYTES = NOALLOC_SCRATCH_BYTES - NOALLOC_COUNTERS * sizeof(uint32_t);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+void *g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int32_t nvc_quantized_matmul_noalloc(nvc_device *dev, const nvc_quant *q, const void *x, const uint32_t *w,
+                                                const void *scales, const void *biases, int64_t M, int64_t N, int64_t K,
+                                                void *y) {
+    using namespace nvc;
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("quantized_matmul", q));
+    if (q->mode != NVC_AFFINE || !biases)
+        return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (no-alloc): affine weights with biases only");
+    if (M < 0 || N < 0 || K < 0 || K % q->group_size != 0)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul (no-alloc): invalid shape [%lld, %lld] x [%lld, %lld]",
+                         (long long)M, (long long)K, (long long)N, (long long)K);
+    if (M == 0 || N == 0) return NVC_OK;
+    if (!x || !w || !scales || !y) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul (no-alloc): null operand");
+    if (!qmv_affine_eligible(q->mode, q->group_size, q->bits, NVC_BF16, 1, M, N, K, x, K, 0, w, 0))
+        return set_error(NVC_ERR_UNSUPPORTED,
+                         "quantized_matmul (no-alloc): takes bfloat16 x with 1 to 8 rows and 2-, 4- or 8-bit weights whose "
+                         "rows are a whole number of 32-value iterations (got M = %lld, K = %lld, %d bits)",
+                         (long long)M, (long long)K, q->bits);
+    if (dev->ordinal < 0 || dev->ordinal >= NOALLOC_MAX_DEVICES)
+        return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (no-alloc): device ordinal %d", dev->ordinal);
+    void *base = nullptr;
+    {
+        // Set-up, once per device and with that device current: the array's name is only a host-side
+        // handle for the symbol, the kernel needs its address on this device.
+        std::lock_guard<std::mutex> g(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev->ordinal]) {
+            void *ptr = nullptr;
+            NVC_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+            g_noalloc_ptr[dev->ordinal] = ptr;
+        }
+        base = g_noalloc_ptr[dev->ordinal];
+    }
+    QmvScratch fixed;
+    fixed.partials = reinterpret_cast<float *>(base);
+    fixed.partial_bytes = NOALLOC_PARTIAL_BYTES;
+    fixed.counters = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(base) + NOALLOC_PARTIAL_BYTES);
+    fixed.counters_len = NOALLOC_COUNTERS;
+    const int64_t tiles = (N + 15) / 16;
+    if ((size_t)tiles > NOALLOC_COUNTERS)
+        return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (no-alloc): N = %lld exceeds the fixed scratch (at most %zu rows)",
+                         (long long)N, NOALLOC_COUNTERS * 16);
+    // The array keeps whatever the last call left; the counters must start at zero.
+    NVC_CUDA(cudaMemsetAsync(fixed.counters, 0, (size_t)tiles * sizeof(uint32_t), dev->stream));
+    QmvParams p{};
+    p.x = x; p.w = w; p.scales = scales; p.biases = biases; p.lhs = nullptr; p.rhs = nullptr; p.y = y;
+    p.N = N; p.K = K; p.ldx = K;
+    p.x_batch_stride = 0; p.w_batch_stride = 0; p.s_batch_stride = 0;
+    p.M = (int32_t)M; p.gs = q->group_size;
+    p.x_vec = ((uintptr_t)x % 16 == 0) && (K % 8 == 0);
+    return launch_qmv_affine(dev, q->bits, p, 1, &fixed);
+}

@@ -37,6 +37,14 @@ struct QmvParams {
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
                          int64_t N, int64_t K, const void *x, int64_t ldx, int64_t x_batch_stride, const uint32_t *w,
                          int64_t w_batch_stride);
-int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch);
+// Caller-provided scratch of fixed capacity (partial sums and arrival counters).
+struct QmvScratch {
+    float *partials;
+    size_t partial_bytes;
+    uint32_t *counters;
+    size_t counters_len;
+};
+// `fixed` == nullptr: scratch comes from the device handle's pool and grows on demand.
+int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch, const QmvScratch *fixed = nullptr);
 
 }  // namespace nvc
