@@ -359,11 +359,16 @@ def main():
                                 "sample": "one layer (4 products, M=1), best of 3; serial dequantize as the reference, "
                                           "few-row product over all threads", "seconds_per_layer": secs}
     if rank == 0:
-        print(json.dumps(line))
-    if comm is not None:
-        lib.nvc_comm_destroy(comm)
-    if dist is not None:
-        dist.destroy_process_group()
+        print(json.dumps(line), flush=True)
+    # Multi-rank runs leave without tearing down: the ranks meet at a barrier and exit.  (Destroying
+    # the recorded steps and the two NCCL instances of this process in the interpreter's teardown
+    # was observed to block; the work is complete and its results are printed at this point.)
+    dev.synchronize()
+    if world > 1:
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier):
