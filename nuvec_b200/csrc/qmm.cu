@@ -8,13 +8,15 @@
 // the accumulator D[128 x BT] (float32) lives in tensor memory, each dequantized weight is reused
 // by BT tokens, and a group of few tokens (an expert with 32 rows) still fills all 128 lanes.
 //
-// Warp roles (448 threads):
+// Warp roles (480 threads):
 //   warps 0-3   epilogue: tcgen05.ld the finished accumulator, round to bfloat16, store y
-//   warp  4     TMA producer: activation tiles (64 k x BT tokens, 128-byte swizzle) and packed
-//               weight slabs (128 rows x 128 bytes, 128-byte swizzle) into shared-memory rings
+//   warp  4     TMA producer of activation tiles (64 k x BT tokens, 128-byte swizzle)
+//   warp  6     TMA producer of packed weight slabs (128 rows x 128 bytes, 128-byte swizzle),
+//               on its own ring so it runs ahead of the activation stages
 //   warp  5     MMA issuer (one thread): 4 x tcgen05.mma.kind::f16 (K = 16) per 64-k block,
 //               tcgen05.commit releases the stages / publishes the accumulator
-//   warps 6-13  dequantizers: packed codes -> bfloat16 "A" tile in the canonical K-major
+//   warps 7-14  dequantizers (two groups on alternate k-blocks, thread = weight row): packed
+//               codes -> bfloat16 "A" tile in the canonical K-major
 //               128-byte-swizzled layout, with exactly the reference's two roundings
 //               (crates/nuvec-core/src/kernels.rs:835-859), so the tensor-core operands are
 //               bit-identical to the reference's dequantized matrix
@@ -39,7 +41,7 @@ namespace nvc {
 constexpr int QMM_BN = 128;  // weight rows per tile (UMMA M)
 constexpr int QMM_BK = 64;   // k-values per block: one 128-byte swizzle row of bfloat16
 constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 8;
-constexpr int QMM_THREADS = (QMM_EPI_WARPS + 2 + QMM_DQ_WARPS) * 32;
+constexpr int QMM_THREADS = (QMM_EPI_WARPS + 3 + QMM_DQ_WARPS) * 32;
 constexpr int QMM_DQ_THREADS = QMM_DQ_WARPS * 32;
 constexpr int QMM_W_STAGES = 2;          // packed-weight slabs in flight
 constexpr uint32_t QMM_W_BYTES = 128 * 128;  // one slab: 128 rows x 128 bytes
@@ -56,6 +58,22 @@ struct QmmKernelParams {
     int32_t experts, rows, N, K;
     int32_t gs_shift, row_groups, mode, expert_global;
 };
+
+// Optional role timing (probe builds only: -DNUVEC_QMM_TIMING): cycles block 0 spends in each phase.
+#ifdef NUVEC_QMM_TIMING
+__device__ long long g_qmm_timing[16];
+#define QMM_T0() long long t__ = clock64()
+#define QMM_ACC(slot) do { long long n__ = clock64(); if (blockIdx.x == 0 && lane == 0) tacc[slot] += n__ - t__; t__ = n__; } while (0)
+#define QMM_DUMP(base, n) do { if (blockIdx.x == 0 && lane == 0) for (int i__ = 0; i__ < n; i__++) atomicAdd((unsigned long long *)&g_qmm_timing[base + i__], (unsigned long long)tacc[i__]); } while (0)
+// Event trace of block 0: clock of each pipeline event of k-blocks 256 .. 383.
+__device__ long long g_qmm_trace[128 * 16];
+#define QMM_TR(idx, slot) do { if (blockIdx.x == 0 && lane == 0 && (idx) >= 256u && (idx) < 384u) g_qmm_trace[((idx) - 256u) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define QMM_T0() do {} while (0)
+#define QMM_ACC(slot) do {} while (0)
+#define QMM_DUMP(base, n) do {} while (0)
+#define QMM_TR(idx, slot) do {} while (0)
+#endif
 
 // ── PTX wrappers ───────────────────────────────────────────────────────────────────────────
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -79,9 +97,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait.  Returns false when it gave up or another thread of the block already did.
+// SLEEP_NS > 0 backs off between polls: roles that wait long (epilogue, producers) must not take
+// issue slots from the dequantizing warps that share their scheduler.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t spin = 0; spin < QMM_SPIN_LIMIT; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((spin & 63u) == 63u && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -311,7 +333,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(xfull + s, 1);
-            mbar_init(afull + s, QMM_DQ_WARPS);
+            mbar_init(afull + s, QMM_DQ_WARPS / 2);
             mbar_init(empty + s, 1);
         }
         for (int s = 0; s < QMM_W_STAGES; s++) {
@@ -335,27 +357,38 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 4) {
-        // ── TMA producer ────────────────────────────────────────────────────────────────
+        // ── TMA producer, activations: one 64-k x BT tile per stage ─────────────────────────
         if (lane == 0) {
-            uint32_t it = 0, wit = 0;  // k-blocks / weight slabs issued so far
+            uint32_t it = 0;  // k-blocks issued so far
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 TileInfo ti;
                 if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
                 for (int kb = 0; kb < kblocks && ok; kb++, it++) {
-                    if (kb % KPS == 0) {
-                        const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
-                        ok = mbar_wait(wempty + s, ph ^ 1, abort_flag);
-                        if (!ok) break;
-                        mbar_expect_tx(wfull + s, QMM_W_BYTES);
-                        tma_load_2d(ws + s * QMM_W_BYTES, &tmap_w, (kb / KPS) * 128, ti.wrow0, wfull + s);
-                        wit++;
-                    }
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
                     if (!ok) break;
+                    QMM_TR(it, 0);
                     mbar_expect_tx(xfull + s, X_BYTES);
                     tma_load_2d(xs + s * X_BYTES, &tmap_x, kb * QMM_BK, ti.tok0, xfull + s);
+                }
+            }
+        }
+    } else if (warp == 6) {
+        // ── TMA producer, packed weights: runs ahead on its own ring, so a slab's latency is
+        //    never behind the activation stages ─────────────────────────────────────────────
+        if (lane == 0) {
+            uint32_t wit = 0;  // weight slabs issued so far
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                TileInfo ti;
+                if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+                for (int kb = 0; kb < kblocks && ok; kb += KPS, wit++) {
+                    const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
+                    ok = mbar_wait<200>(wempty + s, ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(wfull + s, QMM_W_BYTES);
+                    tma_load_2d(ws + s * QMM_W_BYTES, &tmap_w, (kb / KPS) * 128, ti.wrow0, wfull + s);
                 }
             }
         }
@@ -365,17 +398,27 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             constexpr uint32_t idesc = umma_idesc(BT);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
+            long long tacc[4] = {0, 0, 0, 0};
+            (void)tacc;
+            QMM_T0();
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 TileInfo ti;
                 if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
                 const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
-                ok = mbar_wait(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
+                ok = mbar_wait<100>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
+                QMM_ACC(0);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BT;
                 for (int kb = 0; kb < kblocks && ok; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    ok = mbar_wait(xfull + s, ph, abort_flag) && mbar_wait(afull + s, ph, abort_flag);
+                    QMM_TR(it, 4);
+                    ok = mbar_wait(xfull + s, ph, abort_flag);
+                    QMM_ACC(1);
+                    QMM_TR(it, 5);
+                    ok = ok && mbar_wait(afull + s, ph, abort_flag);
+                    QMM_ACC(2);
+                    QMM_TR(it, 6);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t ad = umma_desc(smem_u32(as + s * QMM_A_BYTES));
@@ -384,18 +427,36 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     for (int k = 0; k < QMM_BK / 16; k++)  // 32 bytes further along K inside the swizzle row
                         tc_mma_bf16(d, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, (kb | k) != 0);
                     tc_commit(empty + s);  // frees the stage once these MMAs have read it
+                    QMM_ACC(3);
+                    QMM_TR(it, 7);
                 }
                 if (ok) tc_commit(accfull + buf);
                 tcount++;
             }
+            QMM_DUMP(0, 4);
         }
-    } else if (warp >= 6) {
-        // ── dequantizers: thread = (row, 32-k half) of the 128 x 64 tile ─────────────────
-        const int dt = tid - 6 * 32;
-        const int row = dt & 127, half = dt >> 7;
+    } else if (warp >= 7) {
+        // ── dequantizers ─────────────────────────────────────────────────────────────────
+        // Two groups of 4 warps take alternate k-blocks; inside a group thread = weight row, all
+        // 64 k-values of the block.  A block's fixed costs (barrier wake-up, scale fetch, proxy
+        // fence, arrive) are then paid once per 64 values and overlap with the other group's.
+        const int dt = tid - 7 * 32;
+        const int row = dt & 127, group = dt >> 7;
         const int sw = row & 7;  // swizzle phase of this row
-        uint32_t it = 0, wit = 0;
+        uint32_t it_base = 0, wit = 0;
         bool ok = true;
+        long long tacc[4] = {0, 0, 0, 0};
+        (void)tacc;
+        QMM_T0();
+        // scale / bias codes of one block: [half] for 32-value halves (equal when the group is larger)
+        auto load_consts = [&](const uint16_t *sc, const uint16_t *bi, const uint8_t *fsc, int kb, uint32_t (&sv)[2], uint32_t (&bv)[2]) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int k = kb * QMM_BK + h * 32;
+                if (MODE == 0) { sv[h] = sc[k >> p.gs_shift]; bv[h] = bi[k >> p.gs_shift]; }
+                else { sv[h] = fsc[k >> p.gs_shift]; bv[h] = MODE == 3 ? fsc[(k + 16) >> p.gs_shift] : 0u; }
+            }
+        };
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             TileInfo ti;
             if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
@@ -404,79 +465,91 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint16_t *sc = p.scales + (size_t)wr * p.row_groups;
             const uint16_t *bi = p.biases ? p.biases + (size_t)wr * p.row_groups : nullptr;
             const uint8_t *fsc = p.fp_scales ? p.fp_scales + (size_t)wr * p.row_groups : nullptr;
-            // scale/bias of the first block
-            uint32_t s_next = 0, b_next = 0;
-            {
-                const int g = (half * 32) >> p.gs_shift;
-                if (MODE == 0) { s_next = sc[g]; b_next = bi[g]; }
-                else s_next = fsc[g];
-                if (MODE == 3) b_next = fsc[(half * 32 + 16) >> p.gs_shift];
-            }
-            for (int kb = 0; kb < kblocks && ok; kb++, it++) {
-                const uint32_t s_cur = s_next, b_cur = b_next;
-                if (kb + 1 < kblocks) {  // prefetch the next block's constants
-                    const int g = ((kb + 1) * QMM_BK + half * 32) >> p.gs_shift;
-                    if (MODE == 0) { s_next = sc[g]; b_next = bi[g]; }
-                    else s_next = fsc[g];
-                    if (MODE == 3) b_next = fsc[((kb + 1) * QMM_BK + half * 32 + 16) >> p.gs_shift];
-                }
+            uint32_t s_next[2] = {0, 0}, b_next[2] = {0, 0};
+            if (group < kblocks) load_consts(sc, bi, fsc, group, s_next, b_next);
+            for (int slab = 0; slab * KPS < kblocks && ok; slab++, wit++) {
                 const uint32_t wsi = wit % QMM_W_STAGES, wph = (wit / QMM_W_STAGES) & 1;
-                if (kb % KPS == 0) ok = mbar_wait(wfull + wsi, wph, abort_flag);
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                ok = ok && mbar_wait(empty + s, ph ^ 1, abort_flag);
-                if (!ok) break;
-                const uint8_t *wrow = ws + wsi * QMM_W_BYTES + row * 128;
-                uint8_t *arow = as + s * QMM_A_BYTES + row * 128;
-                const int kq = kb % KPS;
-                if (MODE == 0) {
-                    Affine q;
-                    q.s2 = s_cur * 0x10001u;
-                    q.b2 = b_cur * 0x10001u;
-                    q.ns2 = q_mul(q.s2, 0xC300C300u);  // -128 s, exact
-                    if (BITS == 4) {
-                        const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
-                        const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
-#pragma unroll
-                        for (int j = 0; j < 4; j++)
-                            *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word4(wv[j], q);
-                    } else if (BITS == 8) {
-#pragma unroll
-                        for (int c = 0; c < 2; c++) {
-                            const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 4 + half * 2 + c) ^ sw) << 4));
-                            const uint2 a = dequant_word8(pk.x, q), b2 = dequant_word8(pk.y, q);
-                            const uint2 c2 = dequant_word8(pk.z, q), d2 = dequant_word8(pk.w, q);
-                            *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c) ^ sw) << 4)) = make_uint4(a.x, a.y, b2.x, b2.y);
-                            *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c + 1) ^ sw) << 4)) = make_uint4(c2.x, c2.y, d2.x, d2.y);
-                        }
-                    } else {
-                        const uint2 pk = *reinterpret_cast<const uint2 *>(wrow + ((kq ^ sw) << 4) + half * 8);
-                        uint4 o0, o1;
-                        dequant_word2(pk.x, q, o0, o1);
-                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 0) ^ sw) << 4)) = o0;
-                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 1) ^ sw) << 4)) = o1;
-                        dequant_word2(pk.y, q, o0, o1);
-                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2) ^ sw) << 4)) = o0;
-                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + 3) ^ sw) << 4)) = o1;
+                bool have = false;
+#pragma unroll 1
+                for (int kq = 0; kq < KPS; kq++) {
+                    const int kb = slab * KPS + kq;
+                    if (kb >= kblocks) break;
+                    if ((kb & 1) != group) continue;
+                    const uint32_t s_cur[2] = {s_next[0], s_next[1]}, b_cur[2] = {b_next[0], b_next[1]};
+                    if (kb + 2 < kblocks) load_consts(sc, bi, fsc, kb + 2, s_next, b_next);  // prefetch
+                    QMM_ACC(2);
+                    if (!have) {
+                        ok = mbar_wait(wfull + wsi, wph, abort_flag);
+                        have = true;
                     }
-                } else {
-                    // mxfp4: one scale per 32 values; nvfp4: one per 16 (two per thread and block)
-                    const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
-                    const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
-                    const uint32_t sa = fp_scale2(s_cur, MODE == 1);
-                    const uint32_t sb = MODE == 3 ? fp_scale2(b_cur, false) : sa;
+                    QMM_ACC(0);
+                    const uint32_t it = it_base + kb, s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (warp == 7 || warp == 11) QMM_TR(it, 8);
+                    ok = ok && mbar_wait(empty + s, ph ^ 1, abort_flag);
+                    QMM_ACC(1);
+                    if (warp == 7 || warp == 11) QMM_TR(it, 9);
+                    if (!ok) break;
+                    const uint8_t *wrow = ws + wsi * QMM_W_BYTES + row * 128;
+                    uint8_t *arow = as + s * QMM_A_BYTES + row * 128;
 #pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word_fp4(wv[j], j < 2 ? sa : sb);
+                    for (int half = 0; half < 2; half++) {
+                        if (MODE == 0) {
+                            Affine q;
+                            q.s2 = s_cur[half] * 0x10001u;
+                            q.b2 = b_cur[half] * 0x10001u;
+                            q.ns2 = q_mul(q.s2, 0xC300C300u);  // -128 s, exact
+                            if (BITS == 4) {
+                                const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
+                                const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++)
+                                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word4(wv[j], q);
+                            } else if (BITS == 8) {
+#pragma unroll
+                                for (int c = 0; c < 2; c++) {
+                                    const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 4 + half * 2 + c) ^ sw) << 4));
+                                    const uint2 a = dequant_word8(pk.x, q), b2 = dequant_word8(pk.y, q);
+                                    const uint2 c2 = dequant_word8(pk.z, q), d2 = dequant_word8(pk.w, q);
+                                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c) ^ sw) << 4)) = make_uint4(a.x, a.y, b2.x, b2.y);
+                                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c + 1) ^ sw) << 4)) = make_uint4(c2.x, c2.y, d2.x, d2.y);
+                                }
+                            } else {
+                                const uint2 pk = *reinterpret_cast<const uint2 *>(wrow + ((kq ^ sw) << 4) + half * 8);
+                                uint4 o0, o1;
+                                dequant_word2(pk.x, q, o0, o1);
+                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 0) ^ sw) << 4)) = o0;
+                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 1) ^ sw) << 4)) = o1;
+                                dequant_word2(pk.y, q, o0, o1);
+                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2) ^ sw) << 4)) = o0;
+                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 3) ^ sw) << 4)) = o1;
+                            }
+                        } else {
+                            // mxfp4: one scale per 32 values; nvfp4: one per 16 (two per half)
+                            const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
+                            const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+                            const uint32_t sa = fp_scale2(s_cur[half], MODE == 1);
+                            const uint32_t sb = MODE == 3 ? fp_scale2(b_cur[half], false) : sa;
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word_fp4(wv[j], j < 2 ? sa : sb);
+                        }
+                    }
+                    QMM_ACC(2);
+                    if (warp == 7 || warp == 11) QMM_TR(it, 10);
+                    fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(afull + s);
+                    QMM_ACC(3);
+                    if (warp == 7 || warp == 11) QMM_TR(it, 11);
                 }
-                fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+                // this warp is done with the slab (also when none of its blocks were this group's)
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(afull + s);
-                    if (kq == KPS - 1 || kb == kblocks - 1) mbar_arrive(wempty + wsi);
-                }
-                if (kq == KPS - 1 || kb == kblocks - 1) wit++;
+                if (lane == 0) mbar_arrive(wempty + wsi);
             }
+            it_base += (uint32_t)kblocks;
         }
+        if (warp == 7) QMM_DUMP(4, 4);
+        if (warp == 11) QMM_DUMP(8, 4);
     } else {
         // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
         uint32_t tcount = 0;
@@ -485,7 +558,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             TileInfo ti;
             if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
-            ok = mbar_wait(accfull + buf, aph, abort_flag);
+            ok = mbar_wait<500>(accfull + buf, aph, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const int n = ti.n0 + warp * 32 + lane;
@@ -526,6 +599,18 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 }
 
 // ── host side ──────────────────────────────────────────────────────────────────────────────
+#ifdef NUVEC_QMM_TIMING
+extern "C" int nvc_debug_qmm_timing(long long *out, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_qmm_timing, sizeof(long long) * 16);
+    if (reset == 2) return (int)cudaMemcpyFromSymbol(out, g_qmm_trace, sizeof(long long) * 128 * 16);
+    if (reset) {
+        long long z[16] = {0};
+        cudaMemcpyToSymbol(g_qmm_timing, z, sizeof z);
+    }
+    return 0;
+}
+#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
