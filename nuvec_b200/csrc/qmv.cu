@@ -269,8 +269,9 @@ template <> struct Unpack<2> {
 
 constexpr int QMV_WARPS = 8;
 constexpr int QMV_THREADS = QMV_WARPS * 32;
-// Depth of each lane's ring of asynchronous weight copies (iterations in flight per warp).
-constexpr int QMV_STAGES = 4;
+// Depth of each lane's ring of asynchronous weight copies (iterations in flight per warp): the
+// bytes in flight per lane stay near 128 whatever the iteration's width.
+__host__ __device__ constexpr int qmv_stages(int wpl) { return wpl == 8 ? 3 : 4; }
 // Most groups whose scale/bias are staged at a time (one k-chunk of a tile).
 constexpr int QMV_SEG_GROUPS = 16;
 // Row pitch (bfloat16 elements) of the staged scales: 48 bytes = 12 banks, a multiple of 16 bytes
@@ -296,13 +297,19 @@ constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 //   zero  [64] u32            what lanes of activation rows >= M read
 //   per warp:
 //   sraw, braw [2][16][QMV_SPITCH] bf16   scales / biases of the current and the next k-chunk
-//   ring  [QMV_STAGES][2][32] x WPL u32   packed words in flight: slot (stage, row half, lane)
+//   ring  [stages][2][32] x WPL u32       packed words in flight: slot (stage, row half, lane);
+//                                         WPL = 8 keeps its two 16-byte chunks 512 bytes apart
+//                                         (chunk, lane) so that a quarter-warp reads 128
+//                                         consecutive bytes
 template <int BITS, int WPL>
 __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
     constexpr int CODES = U::CODES, AREGS = U::AREGS;
     constexpr int IK = 4 * WPL * CODES;
     constexpr int XW = AREGS;  // activation words per packed word (AREGS bf16 pairs)
+    constexpr int QMV_STAGES = qmv_stages(WPL);
+    constexpr int CPL = WPL == 8 ? 2 : 1;      // copies per lane and row half
+    constexpr int CW = WPL / CPL;              // words per copy
     extern __shared__ __align__(16) uint32_t smem[];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -329,7 +336,7 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
     uint32_t *ring = reinterpret_cast<uint32_t *>(reinterpret_cast<uint16_t *>(zero + 64) +
                                                   (size_t)QMV_WARPS * (4 * 16 * QMV_SPITCH)) +
                      (size_t)warp * (QMV_STAGES * 2 * 32 * WPL);
-    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * WPL);
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * CW);
     constexpr uint32_t HALF_BYTES = 32 * WPL * 4, STAGE_BYTES = 2 * HALF_BYTES;
 
     // ── this warp's run of iterations ───────────────────────────────────────────────────
@@ -386,8 +393,11 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
     // group count seen by wait_group is the same for every lane and iteration.
     auto prefetch = [&](int stage) {
         if (pf < hi) {
-            cp_async<WPL * 4>(ring_s + stage * STAGE_BYTES, pf_a);
-            cp_async<WPL * 4>(ring_s + stage * STAGE_BYTES + HALF_BYTES, pf_q);
+#pragma unroll
+            for (int c = 0; c < CPL; c++) {
+                cp_async<CW * 4>(ring_s + stage * STAGE_BYTES + c * (32 * CW * 4), pf_a + c * CW);
+                cp_async<CW * 4>(ring_s + stage * STAGE_BYTES + HALF_BYTES + c * (32 * CW * 4), pf_q + c * CW);
+            }
             pf_a += 4 * WPL;
             pf_q += 4 * WPL;
             pf++;
@@ -400,12 +410,17 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
         cp_async_commit();
     };
 
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled from now on,
+    // and this one starts copying weights (which no product writes) while the kernel before it is
+    // still finishing; only then does it wait for that kernel's results.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (lo < hi) {
         stage_scales(pf_tile, pf_it / ci, 0);
         pf_rows();
     }
 #pragma unroll
     for (int st = 0; st < QMV_STAGES; st++) prefetch(st);
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // activations, scratch and output belong to this kernel from here
 
     // ── stage the activations once per block (the first weight copies are already in flight) ──
     {
@@ -475,8 +490,16 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
             cp_async_wait<QMV_STAGES - 1>();  // the oldest group, this iteration's words, has landed
             uint32_t wa_[WPL], wq_[WPL];
             {
-                const uint32_t *slot = ring + (size_t)stage * (2 * 32 * WPL) + lane * WPL;
-                if (WPL == 4) {
+                const uint32_t *slot = ring + (size_t)stage * (2 * 32 * WPL) + lane * CW;
+                if (WPL == 8) {
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        uint4 a = *reinterpret_cast<const uint4 *>(slot + c * 128);
+                        uint4 q = *reinterpret_cast<const uint4 *>(slot + 32 * WPL + c * 128);
+                        wa_[(4 * c) % WPL] = a.x; wa_[(4 * c + 1) % WPL] = a.y; wa_[(4 * c + 2) % WPL] = a.z; wa_[(4 * c + 3) % WPL] = a.w;
+                        wq_[(4 * c) % WPL] = q.x; wq_[(4 * c + 1) % WPL] = q.y; wq_[(4 * c + 2) % WPL] = q.z; wq_[(4 * c + 3) % WPL] = q.w;
+                    }
+                } else if (WPL == 4) {
                     uint4 a = *reinterpret_cast<const uint4 *>(slot), q = *reinterpret_cast<const uint4 *>(slot + 32 * WPL);
                     wa_[0] = a.x; wa_[1 % WPL] = a.y; wa_[2 % WPL] = a.z; wa_[3 % WPL] = a.w;
                     wq_[0] = q.x; wq_[1 % WPL] = q.y; wq_[2 % WPL] = q.z; wq_[3 % WPL] = q.w;
@@ -582,7 +605,9 @@ static int codes_per_word(int bits) { return 32 / bits; }
 static int wpl_for(int bits, int gs, int64_t K) {
     if (bits != 2 && bits != 4 && bits != 8) return 0;
     const int codes = codes_per_word(bits);
-    for (int wpl = bits == 2 ? 2 : 4; wpl >= 1; wpl >>= 1) {
+    static const int cap = [] { const char *e = getenv("NUVEC_QMV_MAX_WPL"); return e && *e ? atoi(e) : 8; }();
+    for (int wpl = bits == 2 ? 2 : 8; wpl >= 1; wpl >>= 1) {
+        if (wpl > cap) continue;
         if (wpl * codes > gs) continue;          // a lane's words stay inside one group
         if (K % (4 * wpl * codes) == 0) return wpl;
     }
@@ -592,7 +617,7 @@ static int wpl_for(int bits, int gs, int64_t K) {
 static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
     const int codes = codes_per_word(bits), xw = bits == 4 ? 4 : bits == 8 ? 2 : 8;
     return (size_t)(M * (K / codes * xw + 16) + 64 + QMV_WARPS * (2 * 16 * QMV_SPITCH) +
-                    QMV_STAGES * 2 * QMV_THREADS * wpl) * 4 + 16;
+                    qmv_stages(wpl) * 2 * QMV_THREADS * wpl) * 4 + 16;
 }
 
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
@@ -604,7 +629,8 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
     int wpl = wpl_for(bits, gs, K);
     if (wpl == 0) return false;
     int64_t row_words = K * bits / 32;
-    if (row_words % wpl != 0 || w_batch_stride % wpl != 0 || ((uintptr_t)w % (4 * wpl)) != 0) return false;
+    const int cw = wpl == 8 ? 4 : wpl;  // words per asynchronous copy
+    if (row_words % cw != 0 || w_batch_stride % cw != 0 || ((uintptr_t)w % (4 * cw)) != 0) return false;
     if (N * (K / (4 * wpl * codes_per_word(bits))) > (int64_t)1 << 40) return false;
     return qmv_smem((int)M, K, bits, wpl) <= 220 * 1024;  // all activations are staged in shared memory
 }
@@ -617,7 +643,21 @@ static int32_t launch_qmv_cfg(nvc_device *dev, QmvParams &p, dim3 grid, size_t s
         NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    kernel<<<grid, QMV_THREADS, smem, dev->stream>>>(p);
+    // Launched with programmatic stream serialization: the kernel may start while its predecessor
+    // drains and synchronises with it on the device (griddepcontrol.wait) before it reads
+    // activations or writes anything.  NUVEC_PDL=0 restores plain stream order.
+    static const bool pdl = [] { const char *e = getenv("NUVEC_PDL"); return !(e && *e == '0'); }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(QMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    NVC_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return check_launch(dev, "qmv_affine_kernel");
 }
 
@@ -683,7 +723,8 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     }
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
 #define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, grid, smem);
-    NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(2, 1) NVC_QMV(2, 2)
+    NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(4, 8) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(8, 8)
+    NVC_QMV(2, 1) NVC_QMV(2, 2)
 #undef NVC_QMV
     return set_error(NVC_ERR_UNSUPPORTED, "qmv: no kernel for %d bits, group size %d", bits, p.gs);
 }
