@@ -301,6 +301,8 @@ constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 //                                         WPL = 8 keeps its two 16-byte chunks 512 bytes apart
 //                                         (chunk, lane) so that a quarter-warp reads 128
 //                                         consecutive bytes
+//   lpart [QMV_WARPS][2][128] f32         partial sums of tiles cut between warps of this block
+//   lcount[QMV_WARPS] u32                 their arrival counters
 template <int BITS, int WPL>
 __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
@@ -337,14 +339,35 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
                                                   (size_t)QMV_WARPS * (4 * 16 * QMV_SPITCH)) +
                      (size_t)warp * (QMV_STAGES * 2 * 32 * WPL);
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * CW);
+    float *lpart = reinterpret_cast<float *>(ring + (size_t)(QMV_WARPS - warp) * (QMV_STAGES * 2 * 32 * WPL));
+    uint32_t *lcount = reinterpret_cast<uint32_t *>(lpart + QMV_WARPS * 2 * 128);
     constexpr uint32_t HALF_BYTES = 32 * WPL * 4, STAGE_BYTES = 2 * HALF_BYTES;
 
     // ── this warp's run of iterations ───────────────────────────────────────────────────
-    const int64_t total = (int64_t)tiles * ipt;
-    // No more runs than iterations, so that no run is empty (surplus warps idle).
-    const int64_t warps = min((int64_t)gridDim.x * QMV_WARPS, total);
-    const int64_t gw = (int64_t)blockIdx.x * QMV_WARPS + warp;
-    const int64_t lo = gw < warps ? gw * total / warps : 0, hi = gw < warps ? (gw + 1) * total / warps : 0;
+    // Two levels: the blocks take consecutive runs of the sequence whose lengths differ by at most
+    // one (the first blk_r blocks hold blk_q + 1 iterations) and the warps of a block split the
+    // block's run the same way.  The launch gives every block at least QMV_WARPS iterations unless
+    // the grid is a single block, where surplus warps idle.  All of it is 32-bit arithmetic: the
+    // launch refuses sequences of 2^30 iterations or more.
+    const uint32_t blk_q = p.blk_q, blk_r = p.blk_r;
+    // Run of part `i` when `len`-sized work is cut into parts of q or q + 1 (the first rm parts).
+    auto part_lo = [](uint32_t i, uint32_t q, uint32_t rm) { return i * q + min(i, rm); };
+    auto part_of = [](uint32_t at, uint32_t q, uint32_t rm) {
+        const uint32_t big = rm * (q + 1u);
+        return at < big ? at / (q + 1u) : rm + (at - big) / q;
+    };
+    const uint32_t blk_lo = part_lo(blockIdx.x, blk_q, blk_r), blk_len = blk_q + (blockIdx.x < blk_r ? 1u : 0u);
+    const uint32_t nw = min((uint32_t)QMV_WARPS, blk_len);
+    const uint32_t wq = nw == QMV_WARPS ? blk_len / QMV_WARPS : 1u, wr = nw == QMV_WARPS ? blk_len % QMV_WARPS : 0u;
+    const uint32_t lo = (uint32_t)warp < nw ? blk_lo + part_lo(warp, wq, wr) : 0u;
+    const uint32_t hi = (uint32_t)warp < nw ? lo + wq + ((uint32_t)warp < wr ? 1u : 0u) : 0u;
+    // Block and warp whose run holds iteration i.
+    auto owner = [&](uint32_t i, uint32_t &cta, uint32_t &w) {
+        cta = part_of(i, blk_q, blk_r);
+        const uint32_t l = part_lo(cta, blk_q, blk_r), len = blk_q + (cta < blk_r ? 1u : 0u);
+        if (len >= QMV_WARPS) w = part_of(i - l, len / QMV_WARPS, len % QMV_WARPS);
+        else w = i - l;
+    };
 
     const uint32_t *wbase = p.w + wb * p.w_batch_stride + t * WPL;
     const uint16_t *sc = (const uint16_t *)p.scales + wb * p.s_batch_stride;
@@ -382,8 +405,9 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
     };
 
     // Prefetch cursor: the iteration whose words are copied next.
-    int64_t pf = lo;
-    int pf_tile = (int)(lo / ipt), pf_it = (int)(lo - (int64_t)pf_tile * ipt);
+    uint32_t pf = lo;
+    int pf_tile = (int)(lo / (uint32_t)ipt), pf_it = (int)(lo - (uint32_t)pf_tile * (uint32_t)ipt);
+    const int pf_tile0 = pf_tile, pf_it0 = pf_it;  // where this run starts
     const uint32_t *pf_a = nullptr, *pf_q = nullptr;
     auto pf_rows = [&]() {
         pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + pf_it * (4 * WPL);
@@ -451,6 +475,7 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
             for (int v = 0; v < XW; v++) dst[v] = (uint32_t)outv[2 * v] | ((uint32_t)outv[2 * v + 1] << 16);
         }
         if (tid < 64) zero[tid] = 0u;
+        if (tid < QMV_WARPS) lcount[tid] = 0u;
     }
     __syncthreads();  // activations staged
 
@@ -463,12 +488,12 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
     float acc[4] = {0.f, 0.f, 0.f, 0.f};  // rows r / r+8 x activation rows 2t / 2t+1
     float acd[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the MMA dependency chain
 
-    for (int64_t f = lo; f < hi;) {
+    int tile = pf_tile0, it0 = pf_it0;  // position of f in the sequence, kept without divisions
+    for (uint32_t f = lo; f < hi;) {
         // Segment: the part of one k-chunk of one tile that lies in [f, hi).
-        const int tile = (int)(f / ipt), it0 = (int)(f - (int64_t)tile * ipt);
         const int chunk = it0 / ci;
-        const int it1 = (int)min((int64_t)(chunk + 1) * ci, hi - (int64_t)tile * ipt);
-        const int64_t f1 = (int64_t)tile * ipt + it1;
+        const int it1 = (int)min((uint32_t)((chunk + 1) * ci), hi - f + (uint32_t)it0);
+        const uint32_t f1 = f + (uint32_t)(it1 - it0);
         const uint16_t *sd = sraw + (seg_count & 1) * 16 * QMV_SPITCH, *bd = braw + (seg_count & 1) * 16 * QMV_SPITCH;
         // wait_group in the loop below covers a copy once QMV_STAGES groups were committed after it;
         // a shorter previous segment (or the very first one) needs an explicit wait.  Then the
@@ -477,8 +502,8 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
         if (prev_iters <= QMV_STAGES) cp_async_wait<0>();
         __syncwarp();
         if (f1 < hi) {
-            const int ntile = (int)(f1 / ipt), nit = (int)(f1 - (int64_t)ntile * ipt);
-            stage_scales(ntile, nit / ci, (seg_count + 1) & 1);
+            const bool wrap = it1 == ipt;
+            stage_scales(wrap ? tile + 1 : tile, wrap ? 0 : it1 / ci, (seg_count + 1) & 1);
         }
         prev_iters = it1 - it0;
         seg_count++;
@@ -547,7 +572,15 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
             stage = stage + 1 == QMV_STAGES ? 0 : stage + 1;
         }
         f = f1;
-        if (it1 != ipt && f1 != hi) continue;  // the tile goes on in the next k-chunk
+        if (it1 != ipt && f1 != hi) {  // the tile goes on in the next k-chunk
+            it0 = it1;
+            continue;
+        }
+        const int done_tile = tile;
+        if (it1 == ipt) {
+            tile++;
+            it0 = 0;
+        } else it0 = it1;
 
         // ── the run leaves this tile: rows r, r + 8; activation rows 2t, 2t + 1 ─────────
         float v[4];
@@ -556,16 +589,47 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
             v[i] = acc[i] + acd[i];
             acc[i] = acd[i] = 0.f;
         }
-        const int n0 = tile * 16;
-        const int64_t t_lo = (int64_t)tile * ipt, t_hi = t_lo + ipt;
+        const int n0 = done_tile * 16;
+        const uint32_t t_lo = (uint32_t)done_tile * (uint32_t)ipt, t_hi = t_lo + (uint32_t)ipt;
         bool store = lo <= t_lo && hi >= t_hi;  // the whole tile was this warp's
+        uint32_t c1 = 0, w1 = 0, c2 = 0, w2 = 0;
         if (!store) {
-            // The warps whose runs cut this tile: first .. last, this one is number `mine`.  Each
-            // leaves its 16 x 8 partial in scratch; the one that arrives last adds them in run
+            owner(t_lo, c1, w1);
+            owner(t_hi - 1, c2, w2);
+        }
+        if (!store && c1 == c2) {
+            // Every warp that holds a part of this tile belongs to this block: the partials meet in
+            // shared memory.  A warp leaves at most two (the tile its run starts in and the one it
+            // ends in); the warp that arrives last adds them in run order.
+            float *mine = lpart + (warp * 2 + (done_tile == pf_tile0 ? 0 : 1)) * 128;
+            *reinterpret_cast<float2 *>(mine + r * 8 + 2 * t) = make_float2(v[0], v[1]);
+            *reinterpret_cast<float2 *>(mine + (r + 8) * 8 + 2 * t) = make_float2(v[2], v[3]);
+            __threadfence_block();
+            __syncwarp();
+            uint32_t arrived = 0;
+            if (lane == 0) arrived = atomicAdd(lcount + w1, 1u);
+            arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
+            if (arrived == w2 - w1) {
+                __threadfence_block();
+                v[0] = v[1] = v[2] = v[3] = 0.f;
+                for (uint32_t w = w1; w <= w2; w++) {
+                    // warp w left this tile's partial in its slot 0 if its run starts in the tile
+                    const uint32_t w_lo = blk_lo + part_lo(w, wq, wr);
+                    const float *src = lpart + (w * 2 + (w_lo >= t_lo ? 0 : 1)) * 128;
+                    float2 a = *reinterpret_cast<const float2 *>(src + r * 8 + 2 * t);
+                    float2 q = *reinterpret_cast<const float2 *>(src + (r + 8) * 8 + 2 * t);
+                    v[0] += a.x; v[1] += a.y; v[2] += q.x; v[3] += q.y;
+                }
+                store = true;
+            }
+        } else if (!store) {
+            // The tile is cut by a block boundary: the warps first .. last (numbered through the
+            // grid, every block of a multi-block grid runs all its warps), this one number `mine`,
+            // leave their 16 x 8 partials in scratch; the one that arrives last adds them in run
             // order (so the result does not depend on arrival order) and rearms the counter.
-            const int64_t first = ((t_lo + 1) * warps - 1) / total, last = (t_hi * warps - 1) / total;
-            const int mine = (int)(gw - first), count = (int)(last - first + 1);
-            const int64_t slot = b * tiles + tile;
+            const int first = (int)(c1 * QMV_WARPS + w1), last = (int)(c2 * QMV_WARPS + w2);
+            const int mine = (int)blockIdx.x * QMV_WARPS + warp - first, count = last - first + 1;
+            const int64_t slot = b * tiles + done_tile;
             float *part = p.partials + slot * p.max_parts * 128;
             __stcg(reinterpret_cast<float2 *>(part + mine * 128 + r * 8 + 2 * t), make_float2(v[0], v[1]));
             __stcg(reinterpret_cast<float2 *>(part + mine * 128 + (r + 8) * 8 + 2 * t), make_float2(v[2], v[3]));
@@ -617,7 +681,7 @@ static int wpl_for(int bits, int gs, int64_t K) {
 static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
     const int codes = codes_per_word(bits), xw = bits == 4 ? 4 : bits == 8 ? 2 : 8;
     return (size_t)(M * (K / codes * xw + 16) + 64 + QMV_WARPS * (2 * 16 * QMV_SPITCH) +
-                    qmv_stages(wpl) * 2 * QMV_THREADS * wpl) * 4 + 16;
+                    qmv_stages(wpl) * 2 * QMV_THREADS * wpl + QMV_WARPS * 2 * 128 + QMV_WARPS) * 4 + 16;
 }
 
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
@@ -631,7 +695,7 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
     int64_t row_words = K * bits / 32;
     const int cw = wpl == 8 ? 4 : wpl;  // words per asynchronous copy
     if (row_words % cw != 0 || w_batch_stride % cw != 0 || ((uintptr_t)w % (4 * cw)) != 0) return false;
-    if (N * (K / (4 * wpl * codes_per_word(bits))) > (int64_t)1 << 40) return false;
+    if (((N + 15) / 16) * (K / (4 * wpl * codes_per_word(bits))) >= (int64_t)1 << 30) return false;  // 32-bit iteration counts
     return qmv_smem((int)M, K, bits, wpl) <= 220 * 1024;  // all activations are staged in shared memory
 }
 
@@ -700,11 +764,26 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     if (blocks > useful) blocks = useful;
     const int64_t env_blocks = env_int("NUVEC_QMV_BLOCKS", 0);
     if (env_blocks > 0) blocks = env_blocks;
+    else if (env_int("NUVEC_QMV_ALIGN", 1) != 0 && blocks > 1) {
+        // A tile cut by a block boundary costs its warps a round trip through scratch; one cut between
+        // warps of a block is settled in shared memory.  So, while blocks hold only a few tiles,
+        // prefer a block count that divides the tiles if one lies within two fifths of the
+        // resident blocks (long runs amortise the round trip and want every block).
+        for (int64_t b = blocks; tiles < 4 * blocks && b * 5 >= blocks * 3 && b >= 1; b--)
+            if (tiles % b == 0) {
+                blocks = b;
+                break;
+            }
+    }
+    // Every block of a multi-block grid runs all its warps (the kernel numbers the warps that meet
+    // in a tile through the grid).
+    if (blocks > total / QMV_WARPS) blocks = total / QMV_WARPS;
     if (blocks < 1) blocks = 1;
-    // Tiles cut by run boundaries: at most ipt / floor(total / warps) + 2 runs meet in one tile.
-    const int64_t warps = blocks * QMV_WARPS < total ? blocks * QMV_WARPS : total;
-    const int64_t run = total / warps;
+    // Tiles cut by block boundaries: at most ipt / (shortest warp run) + 2 runs meet in one tile.
+    const int64_t run = total / blocks / QMV_WARPS > 0 ? total / blocks / QMV_WARPS : 1;
     p.max_parts = (int32_t)(ipt / run + 2);
+    p.blk_q = (uint32_t)(total / blocks);
+    p.blk_r = (uint32_t)(total % blocks);
     const size_t partial_bytes = (size_t)tiles * batch * p.max_parts * 128 * sizeof(float);
     if (fixed) {
         // Scratch of fixed capacity provided by the caller of this function: nothing is allocated.

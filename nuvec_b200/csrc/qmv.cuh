@@ -31,6 +31,7 @@ struct QmvParams {
     int64_t N, K, ldx;
     int64_t x_batch_stride, w_batch_stride, s_batch_stride;
     int32_t M, gs, gs_shift, chunk_k, max_parts, x_vec, s_vec;
+    uint32_t blk_q, blk_r;  // iterations per block: blk_q, one more in the first blk_r blocks
 };
 // Returns NVC_ERR_UNSUPPORTED (without setting an error message) when the shape is not one
 // the fast kernel takes; the caller then uses the generic kernel.
