@@ -33,14 +33,16 @@ static int32_t check_product(const char *op, const nvc_quant *q, int32_t dtype, 
 // per expert on average.
 static bool grouped(int64_t rows, int64_t experts) { return rows >= 16 && rows / (experts > 0 ? experts : 1) >= 4; }
 
-// Rows from which a plain product goes to the tensor-core kernel.  Below it the weights
-// stream once through the few-row kernel per 8 rows.
-static int64_t qmm_threshold() {
+// Rows from which a plain product goes to the tensor-core kernel.  Affine weights with up to 8
+// rows stream once through the few-row kernel; the 4-bit floating-point formats have no few-row
+// kernel and take the tensor-core kernel (with its smallest token tile) from the first row.
+static int64_t qmm_threshold(int32_t mode) {
     static int64_t v = [] {
         const char *e = getenv("NUVEC_QMM_MIN_ROWS");
-        return e ? atoll(e) : 17;
+        return e ? atoll(e) : 0;
     }();
-    return v;
+    if (v > 0) return v;
+    return mode == NVC_AFFINE ? 9 : 1;
 }
 
 __global__ void sorted_offsets_kernel(const uint32_t *__restrict__ idx, int64_t rows, int64_t groups,
@@ -102,7 +104,7 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
         p.x_vec = ((uintptr_t)x % 16 == 0) && (ldx % 8 == 0) && (x_batch_stride % 8 == 0);
         return launch_qmv_affine(dev, q->bits, p, batch);
     }
-    if (M >= qmm_threshold() && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
+    if (M >= qmm_threshold(q->mode) && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
         for (int64_t b = 0; b < batch; b++) {
             QmmParams p{};
             p.mode = q->mode; p.gs = q->group_size; p.bits = q->bits;
