@@ -40,12 +40,10 @@ namespace nvc {
 
 constexpr int QMM_BN = 128;  // weight rows per tile (UMMA M)
 constexpr int QMM_BK = 64;   // k-values per block: one 128-byte swizzle row of bfloat16
-constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 8;
+constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 16, QMM_DQ_GROUPS = 4;  // dequantizers: groups of 4 warps
 constexpr int QMM_THREADS = (QMM_EPI_WARPS + 3 + QMM_DQ_WARPS) * 32;
-constexpr int QMM_DQ_THREADS = QMM_DQ_WARPS * 32;
 constexpr int QMM_W_STAGES = 2;          // packed-weight slabs in flight
 constexpr uint32_t QMM_W_BYTES = 128 * 128;  // one slab: 128 rows x 128 bytes
-constexpr uint32_t QMM_A_BYTES = QMM_BN * QMM_BK * 2;
 constexpr uint32_t QMM_SPIN_LIMIT = 1u << 22;  // polls before a wait gives up (each poll may block ~microseconds)
 
 struct QmmKernelParams {
@@ -59,20 +57,17 @@ struct QmmKernelParams {
     int32_t gs_shift, row_groups, mode, expert_global;
 };
 
+
 // Optional role timing (probe builds only: -DNUVEC_QMM_TIMING): cycles block 0 spends in each phase.
 #ifdef NUVEC_QMM_TIMING
 __device__ long long g_qmm_timing[16];
-#define QMM_T0() long long t__ = clock64()
-#define QMM_ACC(slot) do { long long n__ = clock64(); if (blockIdx.x == 0 && lane == 0) tacc[slot] += n__ - t__; t__ = n__; } while (0)
-#define QMM_DUMP(base, n) do { if (blockIdx.x == 0 && lane == 0) for (int i__ = 0; i__ < n; i__++) atomicAdd((unsigned long long *)&g_qmm_timing[base + i__], (unsigned long long)tacc[i__]); } while (0)
-// Event trace of block 0: clock of each pipeline event of k-blocks 256 .. 383.
-__device__ long long g_qmm_trace[128 * 16];
-#define QMM_TR(idx, slot) do { if (blockIdx.x == 0 && lane == 0 && (idx) >= 256u && (idx) < 384u) g_qmm_trace[((idx) - 256u) * 16 + (slot)] = clock64(); } while (0)
+#define QMM_T0() long long tacc[4] = {0, 0, 0, 0}; long long t__ = clock64()
+#define QMM_ACC(slot) do { long long n__ = clock64(); tacc[slot] += n__ - t__; t__ = n__; } while (0)
+#define QMM_DUMP(base) do { if (blockIdx.x == 0 && lane == 0) for (int i__ = 0; i__ < 4; i__++) atomicAdd((unsigned long long *)&g_qmm_timing[base + i__], (unsigned long long)tacc[i__]); } while (0)
 #else
 #define QMM_T0() do {} while (0)
 #define QMM_ACC(slot) do {} while (0)
-#define QMM_DUMP(base, n) do {} while (0)
-#define QMM_TR(idx, slot) do {} while (0)
+#define QMM_DUMP(base) do {} while (0)
 #endif
 
 // ── PTX wrappers ───────────────────────────────────────────────────────────────────────────
@@ -117,9 +112,47 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Non-blocking test of two barriers; true when both phases are complete.  (A successful
+// mbarrier.try_wait was measured at ~200 cycles on an idle SM: it parks and wakes the warp.  The
+// MMA thread, whose inputs are normally ready long before it asks, tests first and only falls
+// back to the parking wait when it really has to wait.)
+__device__ __forceinline__ bool mbar_test2(uint32_t bar_a, uint32_t bar_b, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %3;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q, [%2], %3;\n\t"
+        "and.pred p, p, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar_a), "r"(bar_b), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ void tc_commit_addr(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem desc]: A is 128 lanes (rows) x 8 columns (16 bfloat16, two per column).
+__device__ __forceinline__ void tc_mma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Thread i of the warp writes 32 consecutive columns of lane (base lane + i).
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, f32 accumulate.
 __device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -307,20 +340,31 @@ __device__ __forceinline__ bool tile_info(const QmmKernelParams &p, int tile, in
     return false;
 }
 
+// Stages of the dequantized-weight ring in tensor memory: 32 columns each, in what the two
+// accumulators leave of the 512 columns.
+template <int BT> struct QmmTmem {
+    static constexpr int ACC_COLS = 2 * BT;
+    static constexpr int A_COL0 = ACC_COLS;
+    static constexpr int STAGES = (512 - ACC_COLS) / 32 > 8 ? 8 : (512 - ACC_COLS) / 32;
+    static_assert(STAGES >= 3, "token tile too wide for the weight ring");
+};
+
 template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 3 nvfp4*/>
 __global__ void __launch_bounds__(QMM_THREADS, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, QmmKernelParams p,
            int total_tiles, int n_tiles) {
     constexpr int KPS = QmmBits<BITS>::KPS;
     constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
-    constexpr int TMEM_COLS = 2 * BT < 32 ? 32 : 2 * BT;
+    constexpr int A_COL0 = QmmTmem<BT>::A_COL0;
+    static_assert(STAGES == QmmTmem<BT>::STAGES, "activation stages in shared memory and weight stages in tensor memory form one ring");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *xs = smem;                                   // [STAGES][BT x 128 B]
-    uint8_t *as = xs + STAGES * X_BYTES;                  // [STAGES][128 x 128 B]
-    uint8_t *ws = as + STAGES * QMM_A_BYTES;              // [QMM_W_STAGES][128 x 128 B]
+    uint8_t *ws = xs + STAGES * X_BYTES;                  // [QMM_W_STAGES][128 x 128 B]
     uint64_t *bars = reinterpret_cast<uint64_t *>(ws + QMM_W_STAGES * QMM_W_BYTES);
+    // empty[s]: the MMAs that read activation stage s (shared memory) and weight stage s (tensor
+    // memory) are done; the activation producer and the dequantizers both wait on it.
     uint64_t *xfull = bars, *afull = xfull + STAGES, *empty = afull + STAGES;
     uint64_t *wfull = empty + STAGES, *wempty = wfull + QMM_W_STAGES;
     uint64_t *accfull = wempty + QMM_W_STAGES, *accempty = accfull + 2;
@@ -333,7 +377,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(xfull + s, 1);
-            mbar_init(afull + s, QMM_DQ_WARPS / 2);
+            mbar_init(afull + s, QMM_DQ_WARPS / QMM_DQ_GROUPS);
             mbar_init(empty + s, 1);
         }
         for (int s = 0; s < QMM_W_STAGES; s++) {
@@ -347,8 +391,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {  // tensor memory for two accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+    if (warp == 5) {  // all of tensor memory: two accumulators and the dequantized-weight ring
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -368,7 +412,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
                     if (!ok) break;
-                    QMM_TR(it, 0);
                     mbar_expect_tx(xfull + s, X_BYTES);
                     tma_load_2d(xs + s * X_BYTES, &tmap_x, kb * QMM_BK, ti.tok0, xfull + s);
                 }
@@ -393,13 +436,17 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             }
         }
     } else if (warp == 5) {
-        // ── MMA issuer ──────────────────────────────────────────────────────────────────
+        // ── MMA issuer: A (weights) from tensor memory, B (activations) from shared memory ──
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BT);
-            uint32_t it = 0, tcount = 0;
+            // This thread's instruction stream is the pipeline's critical path (its inputs are ready
+            // long before it asks): ring position, barrier addresses and descriptors advance by
+            // additions, and both barriers of a block are polled together.
+            uint32_t tcount = 0, s = 0, ph = 0;
+            const uint32_t xfull0 = smem_u32(xfull), afull0 = smem_u32(afull);
+            const uint32_t empty0 = smem_u32(empty);
+            const uint64_t bd0 = umma_desc(smem_u32(xs));
             bool ok = true;
-            long long tacc[4] = {0, 0, 0, 0};
-            (void)tacc;
             QMM_T0();
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 TileInfo ti;
@@ -410,43 +457,49 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BT;
-                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    QMM_TR(it, 4);
-                    ok = mbar_wait(xfull + s, ph, abort_flag);
+                for (int kb = 0; kb < kblocks; kb++) {
+#ifdef NUVEC_QMM_TIMING
+                    if (blockIdx.x == 0) {
+                        g_qmm_timing[12] += mbar_test2(xfull0 + 8 * s, xfull0 + 8 * s, ph) ? 1 : 0;
+                        g_qmm_timing[13] += mbar_test2(afull0 + 8 * s, afull0 + 8 * s, ph) ? 1 : 0;
+                        g_qmm_timing[14] += 1;
+                    }
+#endif
+                    if (!mbar_test2(xfull0 + 8 * s, afull0 + 8 * s, ph)) {
+                        ok = mbar_wait(xfull + s, ph, abort_flag) && mbar_wait(afull + s, ph, abort_flag);
+                        if (!ok) break;
+                    }
                     QMM_ACC(1);
-                    QMM_TR(it, 5);
-                    ok = ok && mbar_wait(afull + s, ph, abort_flag);
-                    QMM_ACC(2);
-                    QMM_TR(it, 6);
-                    if (!ok) break;
                     tc_fence_after();
-                    const uint64_t ad = umma_desc(smem_u32(as + s * QMM_A_BYTES));
-                    const uint64_t bd = umma_desc(smem_u32(xs + s * X_BYTES));
+                    const uint32_t at = tmem_base + A_COL0 + s * 32;
+                    const uint64_t bd = bd0 + (uint64_t)(s * (X_BYTES >> 4));
 #pragma unroll
-                    for (int k = 0; k < QMM_BK / 16; k++)  // 32 bytes further along K inside the swizzle row
-                        tc_mma_bf16(d, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, (kb | k) != 0);
-                    tc_commit(empty + s);  // frees the stage once these MMAs have read it
+                    for (int k = 0; k < QMM_BK / 16; k++)  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
+                        tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                    QMM_ACC(2);
+                    tc_commit_addr(empty0 + 8 * s);  // frees both halves of the stage once these MMAs have read them
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                     QMM_ACC(3);
-                    QMM_TR(it, 7);
                 }
                 if (ok) tc_commit(accfull + buf);
                 tcount++;
             }
-            QMM_DUMP(0, 4);
+            QMM_DUMP(0);
         }
     } else if (warp >= 7) {
         // ── dequantizers ─────────────────────────────────────────────────────────────────
-        // Two groups of 4 warps take alternate k-blocks; inside a group thread = weight row, all
-        // 64 k-values of the block.  A block's fixed costs (barrier wake-up, scale fetch, proxy
-        // fence, arrive) are then paid once per 64 values and overlap with the other group's.
-        const int dt = tid - 7 * 32;
-        const int row = dt & 127, group = dt >> 7;
-        const int sw = row & 7;  // swizzle phase of this row
+        // Four groups of 4 warps take k-blocks in turn.  Thread = weight row = tensor-memory lane
+        // (a warp reaches the 32 lanes of its rank in the warpgroup): it rebuilds the 64 k-values of
+        // its row in registers and stores them as 32 columns of the block's stage, where the MMA
+        // reads its A operand.  Nothing dequantized passes through shared memory.
+        const int row = 32 * (warp & 3) + lane, group = (warp - 7) >> 2;
+        const int sw = row & 7;  // swizzle phase of this row in the packed slab
+        const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
         uint32_t it_base = 0, wit = 0;
         bool ok = true;
-        long long tacc[4] = {0, 0, 0, 0};
-        (void)tacc;
         QMM_T0();
         // scale / bias codes of one block: [half] for 32-value halves (equal when the group is larger)
         auto load_consts = [&](const uint16_t *sc, const uint16_t *bi, const uint8_t *fsc, int kb, uint32_t (&sv)[2], uint32_t (&bv)[2]) {
@@ -466,7 +519,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint16_t *bi = p.biases ? p.biases + (size_t)wr * p.row_groups : nullptr;
             const uint8_t *fsc = p.fp_scales ? p.fp_scales + (size_t)wr * p.row_groups : nullptr;
             uint32_t s_next[2] = {0, 0}, b_next[2] = {0, 0};
-            if (group < kblocks) load_consts(sc, bi, fsc, group, s_next, b_next);
+            // this group's blocks are those at ring positions = group (mod groups): the same warps
+            // always refill the same stages, so nobody is ever two phases ahead of a barrier
+            const int first = (group + QMM_DQ_GROUPS - (int)(it_base % QMM_DQ_GROUPS)) % QMM_DQ_GROUPS;
+            if (first < kblocks) load_consts(sc, bi, fsc, first, s_next, b_next);
             for (int slab = 0; slab * KPS < kblocks && ok; slab++, wit++) {
                 const uint32_t wsi = wit % QMM_W_STAGES, wph = (wit / QMM_W_STAGES) & 1;
                 bool have = false;
@@ -474,82 +530,91 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 for (int kq = 0; kq < KPS; kq++) {
                     const int kb = slab * KPS + kq;
                     if (kb >= kblocks) break;
-                    if ((kb & 1) != group) continue;
+                    if ((int)((it_base + kb) % QMM_DQ_GROUPS) != group) continue;
                     const uint32_t s_cur[2] = {s_next[0], s_next[1]}, b_cur[2] = {b_next[0], b_next[1]};
-                    if (kb + 2 < kblocks) load_consts(sc, bi, fsc, kb + 2, s_next, b_next);  // prefetch
+                    if (kb + QMM_DQ_GROUPS < kblocks) load_consts(sc, bi, fsc, kb + QMM_DQ_GROUPS, s_next, b_next);  // prefetch
                     QMM_ACC(2);
                     if (!have) {
                         ok = mbar_wait(wfull + wsi, wph, abort_flag);
                         have = true;
                     }
                     QMM_ACC(0);
-                    const uint32_t it = it_base + kb, s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (warp == 7 || warp == 11) QMM_TR(it, 8);
-                    ok = ok && mbar_wait(empty + s, ph ^ 1, abort_flag);
-                    QMM_ACC(1);
-                    if (warp == 7 || warp == 11) QMM_TR(it, 9);
-                    if (!ok) break;
                     const uint8_t *wrow = ws + wsi * QMM_W_BYTES + row * 128;
-                    uint8_t *arow = as + s * QMM_A_BYTES + row * 128;
+                    uint32_t v[32];  // 64 bfloat16: column c of the stage holds k = 2c, 2c + 1
+                    if (ok) {
+                        Affine q[2];
+                        uint32_t fa[2], fb[2];
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        if (MODE == 0) {
-                            Affine q;
-                            q.s2 = s_cur[half] * 0x10001u;
-                            q.b2 = b_cur[half] * 0x10001u;
-                            q.ns2 = q_mul(q.s2, 0xC300C300u);  // -128 s, exact
-                            if (BITS == 4) {
-                                const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
+                        for (int h = 0; h < 2; h++) {
+                            if (MODE == 0) {
+                                q[h].s2 = s_cur[h] * 0x10001u;
+                                q[h].b2 = b_cur[h] * 0x10001u;
+                                q[h].ns2 = q_mul(q[h].s2, 0xC300C300u);  // -128 s, exact
+                            } else {
+                                // mxfp4: one scale per 32 values; nvfp4: one per 16 (two per half)
+                                fa[h] = fp_scale2(s_cur[h], MODE == 1);
+                                fb[h] = MODE == 3 ? fp_scale2(b_cur[h], false) : fa[h];
+                            }
+                        }
+                        if (BITS == 4) {
+#pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + h) ^ sw) << 4));
                                 const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-                                for (int j = 0; j < 4; j++)
-                                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word4(wv[j], q);
-                            } else if (BITS == 8) {
-#pragma unroll
-                                for (int c = 0; c < 2; c++) {
-                                    const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 4 + half * 2 + c) ^ sw) << 4));
-                                    const uint2 a = dequant_word8(pk.x, q), b2 = dequant_word8(pk.y, q);
-                                    const uint2 c2 = dequant_word8(pk.z, q), d2 = dequant_word8(pk.w, q);
-                                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c) ^ sw) << 4)) = make_uint4(a.x, a.y, b2.x, b2.y);
-                                    *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2 * c + 1) ^ sw) << 4)) = make_uint4(c2.x, c2.y, d2.x, d2.y);
+                                for (int j = 0; j < 4; j++) {
+                                    const uint4 o = MODE == 0 ? dequant_word4(wv[j], q[h]) : dequant_word_fp4(wv[j], j < 2 ? fa[h] : fb[h]);
+                                    v[16 * h + 4 * j] = o.x; v[16 * h + 4 * j + 1] = o.y;
+                                    v[16 * h + 4 * j + 2] = o.z; v[16 * h + 4 * j + 3] = o.w;
                                 }
-                            } else {
-                                const uint2 pk = *reinterpret_cast<const uint2 *>(wrow + ((kq ^ sw) << 4) + half * 8);
-                                uint4 o0, o1;
-                                dequant_word2(pk.x, q, o0, o1);
-                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 0) ^ sw) << 4)) = o0;
-                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 1) ^ sw) << 4)) = o1;
-                                dequant_word2(pk.y, q, o0, o1);
-                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 2) ^ sw) << 4)) = o0;
-                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + 3) ^ sw) << 4)) = o1;
+                            }
+                        } else if (BITS == 8) {
+#pragma unroll
+                            for (int c = 0; c < 4; c++) {
+                                const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 4 + c) ^ sw) << 4));
+                                const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    const uint2 o = dequant_word8(wv[j], q[c >> 1]);
+                                    v[8 * c + 2 * j] = o.x; v[8 * c + 2 * j + 1] = o.y;
+                                }
                             }
                         } else {
-                            // mxfp4: one scale per 32 values; nvfp4: one per 16 (two per half)
-                            const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + (((kq * 2 + half) ^ sw) << 4));
+                            const uint4 pk = *reinterpret_cast<const uint4 *>(wrow + ((kq ^ sw) << 4));
                             const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
-                            const uint32_t sa = fp_scale2(s_cur[half], MODE == 1);
-                            const uint32_t sb = MODE == 3 ? fp_scale2(b_cur[half], false) : sa;
 #pragma unroll
-                            for (int j = 0; j < 4; j++)
-                                *reinterpret_cast<uint4 *>(arow + (((half * 4 + j) ^ sw) << 4)) = dequant_word_fp4(wv[j], j < 2 ? sa : sb);
+                            for (int j = 0; j < 4; j++) {
+                                uint4 o0, o1;
+                                dequant_word2(wv[j], q[j >> 1], o0, o1);
+                                v[8 * j] = o0.x; v[8 * j + 1] = o0.y; v[8 * j + 2] = o0.z; v[8 * j + 3] = o0.w;
+                                v[8 * j + 4] = o1.x; v[8 * j + 5] = o1.y; v[8 * j + 6] = o1.z; v[8 * j + 7] = o1.w;
+                            }
                         }
                     }
+                    const uint32_t it = it_base + kb, sa = it % STAGES, pha = (it / STAGES) & 1;
                     QMM_ACC(2);
-                    if (warp == 7 || warp == 11) QMM_TR(it, 10);
-                    fence_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+                    ok = ok && mbar_wait(empty + sa, pha ^ 1, abort_flag);  // the MMAs that read this stage are done
+                    QMM_ACC(1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    tc_st32(tmem_base + lane_base + A_COL0 + sa * 32, v);
+                    tc_st_wait();
+                    tc_fence_before();  // the stores are ordered before the arrive the MMA thread waits on
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(afull + s);
+                    if (lane == 0) mbar_arrive(afull + sa);
                     QMM_ACC(3);
-                    if (warp == 7 || warp == 11) QMM_TR(it, 11);
                 }
-                // this warp is done with the slab (also when none of its blocks were this group's)
+                // A warp none of whose blocks lay in this slab still waits for the slab before it
+                // releases it: otherwise it could run ahead and its arrival for a later slab would
+                // be counted into this one's phase.
+                if (!have && ok) ok = mbar_wait(wfull + wsi, wph, abort_flag);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(wempty + wsi);
             }
             it_base += (uint32_t)kblocks;
         }
-        if (warp == 7) QMM_DUMP(4, 4);
-        if (warp == 11) QMM_DUMP(8, 4);
+        if (warp == 7) QMM_DUMP(4);
+        if (warp == 19) QMM_DUMP(8);
     } else {
         // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
         uint32_t tcount = 0;
@@ -594,16 +659,14 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     if (tid == 0 && *abort_flag && p.error) *p.error = 1;
     if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
     }
 }
 
-// ── host side ──────────────────────────────────────────────────────────────────────────────
 #ifdef NUVEC_QMM_TIMING
 extern "C" int nvc_debug_qmm_timing(long long *out, int reset) {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out, g_qmm_timing, sizeof(long long) * 16);
-    if (reset == 2) return (int)cudaMemcpyFromSymbol(out, g_qmm_trace, sizeof(long long) * 128 * 16);
     if (reset) {
         long long z[16] = {0};
         cudaMemcpyToSymbol(g_qmm_timing, z, sizeof z);
@@ -611,6 +674,8 @@ extern "C" int nvc_debug_qmm_timing(long long *out, int reset) {
     return 0;
 }
 #endif
+
+// ── host side ──────────────────────────────────────────────────────────────────────────────
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -663,12 +728,10 @@ template <int BITS, int BT, int MODE>
 static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
                           int total_tiles, int n_tiles) {
     constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
-    // as many stages as fit beside the two weight slabs
-    constexpr int budget = 227 * 1024 - 1024 - QMM_W_STAGES * (int)QMM_W_BYTES - 512;
-    constexpr int fit = budget / (int)(X_BYTES + QMM_A_BYTES);
-    constexpr int STAGES = fit > 8 ? 8 : fit;
-    static_assert(STAGES >= 3, "not enough shared memory for the pipeline");
-    constexpr size_t smem = 1024 + STAGES * (X_BYTES + QMM_A_BYTES) + QMM_W_STAGES * QMM_W_BYTES + 512;
+    // one ring: activation stages in shared memory, weight stages in tensor memory
+    constexpr int STAGES = QmmTmem<BT>::STAGES;
+    static_assert(1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 <= 227 * 1024, "not enough shared memory for the pipeline");
+    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024;
     auto kernel = qmm_kernel<BITS, BT, STAGES, MODE>;
     static bool configured = false;
     if (!configured) {
@@ -687,7 +750,7 @@ static int32_t launch_bt(nvc_device *dev, int bt, const CUtensorMap &mx, const C
     case 32: return launch_cfg<BITS, 32, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     case 64: return launch_cfg<BITS, 64, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     case 128: return launch_cfg<BITS, 128, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
-    default: return launch_cfg<BITS, 256, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    default: return launch_cfg<BITS, 192, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     }
 }
 
@@ -696,10 +759,12 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     const int64_t experts = p.offsets ? p.experts : 1;
     // Token tile: the largest that the rows (per expert, on average) fill reasonably.
     const int64_t per = p.offsets ? (p.rows + experts - 1) / experts : p.rows;
-    int bt = per > 160 ? 256 : per > 80 ? 128 : per > 40 ? 64 : 32;
+    // 192 is the widest: two accumulators of 192 columns leave 128 of the 512 tensor-memory
+    // columns for the dequantized-weight ring.
+    int bt = per > 128 ? 192 : per > 64 ? 128 : per > 32 ? 64 : 32;
     if (const char *e = getenv("NUVEC_QMM_BT")) {
         int v = atoi(e);
-        if (v == 32 || v == 64 || v == 128 || v == 256) bt = v;
+        if (v == 32 || v == 64 || v == 128 || v == 192) bt = v;
     }
     const int n_tiles = (int)((p.N + QMM_BN - 1) / QMM_BN);
     int64_t token_tiles;

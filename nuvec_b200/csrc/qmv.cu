@@ -665,11 +665,13 @@ __global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p)
 
 static int codes_per_word(int bits) { return 32 / bits; }
 
-// Words per lane per iteration: the widest vector load whose 4-lane span divides K.
+// Words per lane per iteration: the widest vector load whose 4-lane span divides K.  Eight words
+// (two 16-byte copies) execute fewer instructions per weight but issue slower on the B200 than
+// four; they stay selectable with NUVEC_QMV_MAX_WPL=8.
 static int wpl_for(int bits, int gs, int64_t K) {
     if (bits != 2 && bits != 4 && bits != 8) return 0;
     const int codes = codes_per_word(bits);
-    static const int cap = [] { const char *e = getenv("NUVEC_QMV_MAX_WPL"); return e && *e ? atoi(e) : 8; }();
+    static const int cap = [] { const char *e = getenv("NUVEC_QMV_MAX_WPL"); return e && *e ? atoi(e) : 4; }();
     for (int wpl = bits == 2 ? 2 : 8; wpl >= 1; wpl >>= 1) {
         if (wpl > cap) continue;
         if (wpl * codes > gs) continue;          // a lane's words stay inside one group
