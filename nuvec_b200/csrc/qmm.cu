@@ -8,18 +8,26 @@
 // the accumulator D[128 x BT] (float32) lives in tensor memory, each dequantized weight is reused
 // by BT tokens, and a group of few tokens (an expert with 32 rows) still fills all 128 lanes.
 //
-// Warp roles (480 threads):
+// Warp roles (768 threads):
 //   warps 0-3   epilogue: tcgen05.ld the finished accumulator, round to bfloat16, store y
-//   warp  4     TMA producer of activation tiles (64 k x BT tokens, 128-byte swizzle)
+//   warp  4     TMA producer of activation tiles (64 k x BT tokens, 128-byte swizzle): the MMA's
+//               B operand, read from shared memory
 //   warp  6     TMA producer of packed weight slabs (128 rows x 128 bytes, 128-byte swizzle),
 //               on its own ring so it runs ahead of the activation stages
-//   warp  5     MMA issuer (one thread): 4 x tcgen05.mma.kind::f16 (K = 16) per 64-k block,
-//               tcgen05.commit releases the stages / publishes the accumulator
-//   warps 7-14  dequantizers (two groups on alternate k-blocks, thread = weight row): packed
-//               codes -> bfloat16 "A" tile in the canonical K-major
-//               128-byte-swizzled layout, with exactly the reference's two roundings
-//               (crates/nuvec-core/src/kernels.rs:835-859), so the tensor-core operands are
-//               bit-identical to the reference's dequantized matrix
+//   warps 7-22  dequantizers (four groups of four warps take k-blocks in turn; thread = weight
+//               row = tensor-memory lane): packed codes -> 64 bfloat16 in registers, with
+//               exactly the reference's two roundings (crates/nuvec-core/src/kernels.rs:835-859),
+//               so the tensor-core operands are bit-identical to the reference's dequantized
+//               matrix -> tcgen05.st into the block's stage of tensor memory: the MMA's A
+//               operand.  Dequantized weights never pass through shared memory, whose bandwidth
+//               (operand reads + TMA writes + the dequantizers' traffic) bounded an earlier version.
+//   warp  5     MMA issuer: 4 x tcgen05.mma.kind::f16 (K = 16, A from tensor memory) per 64-k
+//               block; tcgen05.commit releases the stage / publishes the accumulator.  It waits
+//               on hardware named barriers only
+//   warp  23    watcher: waits on the mbarriers for the MMA warp and hands each full stage over
+//               through a named barrier
+// Tensor memory (512 columns): two accumulators of BT columns, then the weight ring of 32 columns
+// per stage.
 // Two accumulator buffers in tensor memory let the epilogue of one tile overlap the main loop
 // of the next.  All waits are bounded: a wait that gives up raises an abort flag that every
 // other wait observes, the block frees its tensor memory and returns, and the host reports the
@@ -41,10 +49,12 @@ namespace nvc {
 constexpr int QMM_BN = 128;  // weight rows per tile (UMMA M)
 constexpr int QMM_BK = 64;   // k-values per block: one 128-byte swizzle row of bfloat16
 constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 16, QMM_DQ_GROUPS = 4;  // dequantizers: groups of 4 warps
-constexpr int QMM_THREADS = (QMM_EPI_WARPS + 3 + QMM_DQ_WARPS) * 32;
+constexpr int QMM_WATCH_WARP = QMM_EPI_WARPS + 3 + QMM_DQ_WARPS;  // the warp that waits on behalf of the MMA warp
+constexpr int QMM_THREADS = (QMM_WATCH_WARP + 1) * 32;
 constexpr int QMM_W_STAGES = 2;          // packed-weight slabs in flight
 constexpr uint32_t QMM_W_BYTES = 128 * 128;  // one slab: 128 rows x 128 bytes
-constexpr uint32_t QMM_SPIN_LIMIT = 1u << 22;  // polls before a wait gives up (each poll may block ~microseconds)
+constexpr unsigned long long QMM_WAIT_LIMIT_NS = 2000000000ull;  // a wait gives up after two seconds
+constexpr uint32_t QMM_PARK_NS = 20000;  // how long one try_wait may keep the warp parked
 
 struct QmmKernelParams {
     const uint16_t *scales, *biases;  // bfloat16 [weight rows, K / gs]
@@ -82,24 +92,35 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One wait attempt: the warp is parked in hardware (it takes no issue slots from the dequantizing
+// warps that share its scheduler) until the phase completes or the time hint runs out.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(QMM_PARK_NS) : "memory");
     return done != 0;
 }
-// Bounded wait.  Returns false when it gave up or another thread of the block already did.
-// SLEEP_NS > 0 backs off between polls: roles that wait long (epilogue, producers) must not take
-// issue slots from the dequantizing warps that share their scheduler.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false when it gave up (after QMM_WAIT_LIMIT_NS) or another thread of the
+// block already did.  The SLEEP_NS parameter is kept for call sites that used to back off between
+// polls; parking makes it unnecessary.
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t spin = 0; spin < QMM_SPIN_LIMIT; spin++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t spin = 0;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
-        if ((spin & 63u) == 63u && *abort_flag) return false;
+        if ((spin & 7u) == 7u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > QMM_WAIT_LIMIT_NS) break;
+        }
     }
     *abort_flag = 1;
     return false;
@@ -127,6 +148,9 @@ __device__ __forceinline__ bool mbar_test2(uint32_t bar_a, uint32_t bar_b, uint3
         : "=r"(done) : "r"(bar_a), "r"(bar_b), "r"(parity) : "memory");
     return done != 0;
 }
+// Hardware named barriers between the watcher warp and the MMA warp (64 threads).
+__device__ __forceinline__ void named_sync(uint32_t id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void named_arrive(uint32_t id) { asm volatile("bar.arrive %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void tc_commit_addr(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -343,10 +367,19 @@ __device__ __forceinline__ bool tile_info(const QmmKernelParams &p, int tile, in
 // Stages of the dequantized-weight ring in tensor memory: 32 columns each, in what the two
 // accumulators leave of the 512 columns.
 template <int BT> struct QmmTmem {
-    static constexpr int ACC_COLS = 2 * BT;
+    // Two accumulators (the epilogue of one tile overlaps the main loop of the next) while they
+    // leave 128 columns for the weight ring; the widest tile keeps a single one.
+    static constexpr int ACC_BUFS = 2 * BT + 128 <= 512 ? 2 : 1;
+    static constexpr int ACC_COLS = ACC_BUFS * BT;
     static constexpr int A_COL0 = ACC_COLS;
-    static constexpr int STAGES = (512 - ACC_COLS) / 32 > 8 ? 8 : (512 - ACC_COLS) / 32;
-    static_assert(STAGES >= 3, "token tile too wide for the weight ring");
+    // ring depth: what the tensor-memory columns and the shared memory (activation stages beside
+    // two packed-weight slabs) both allow, at most 8
+    static constexpr int BY_TMEM = (512 - ACC_COLS) / 32;
+    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 2 * 128 * 128) / (BT * 64 * 2);
+    static constexpr int FIT = BY_TMEM < BY_SMEM ? (BY_TMEM < 8 ? BY_TMEM : 8) : (BY_SMEM < 8 ? BY_SMEM : 8);
+    // a multiple of the dequantizer groups, so that a stage is always refilled by the same group
+    static constexpr int STAGES = FIT / QMM_DQ_GROUPS * QMM_DQ_GROUPS;
+    static_assert(STAGES >= QMM_DQ_GROUPS, "token tile too wide for the weight ring");
 };
 
 template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 3 nvfp4*/>
@@ -355,7 +388,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
            int total_tiles, int n_tiles) {
     constexpr int KPS = QmmBits<BITS>::KPS;
     constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
-    constexpr int A_COL0 = QmmTmem<BT>::A_COL0;
+    constexpr int A_COL0 = QmmTmem<BT>::A_COL0, ACC_BUFS = QmmTmem<BT>::ACC_BUFS;
     static_assert(STAGES == QmmTmem<BT>::STAGES, "activation stages in shared memory and weight stages in tensor memory form one ring");
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
@@ -437,59 +470,75 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         }
     } else if (warp == 5) {
         // ── MMA issuer: A (weights) from tensor memory, B (activations) from shared memory ──
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(BT);
-            // This thread's instruction stream is the pipeline's critical path (its inputs are ready
-            // long before it asks): ring position, barrier addresses and descriptors advance by
-            // additions, and both barriers of a block are polled together.
-            uint32_t tcount = 0, s = 0, ph = 0;
-            const uint32_t xfull0 = smem_u32(xfull), afull0 = smem_u32(afull);
-            const uint32_t empty0 = smem_u32(empty);
-            const uint64_t bd0 = umma_desc(smem_u32(xs));
-            bool ok = true;
-            QMM_T0();
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                TileInfo ti;
-                if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
-                const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
-                ok = mbar_wait<100>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
-                QMM_ACC(0);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d = tmem_base + buf * BT;
-                for (int kb = 0; kb < kblocks; kb++) {
-#ifdef NUVEC_QMM_TIMING
-                    if (blockIdx.x == 0) {
-                        g_qmm_timing[12] += mbar_test2(xfull0 + 8 * s, xfull0 + 8 * s, ph) ? 1 : 0;
-                        g_qmm_timing[13] += mbar_test2(afull0 + 8 * s, afull0 + 8 * s, ph) ? 1 : 0;
-                        g_qmm_timing[14] += 1;
-                    }
-#endif
-                    if (!mbar_test2(xfull0 + 8 * s, afull0 + 8 * s, ph)) {
-                        ok = mbar_wait(xfull + s, ph, abort_flag) && mbar_wait(afull + s, ph, abort_flag);
-                        if (!ok) break;
-                    }
-                    QMM_ACC(1);
+        // Any shared-memory load (an mbarrier test included) issued by the thread that issues
+        // tcgen05.mma was measured at ~270 cycles per round on the B200, more than four MMA issues;
+        // a hardware named barrier costs ~30.  So this warp never reads shared memory: the watcher
+        // warp waits on the mbarriers (stage full, accumulator drained) and passes each stage on
+        // through named barrier 1 + stage.  All lanes walk the loop; lane 0 issues.
+        constexpr uint32_t idesc = umma_idesc(BT);
+        uint32_t tcount = 0, s = 0;
+        const uint32_t empty0 = smem_u32(empty);
+        const uint64_t bd0 = umma_desc(smem_u32(xs));
+        QMM_T0();
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            TileInfo ti;
+            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            const uint32_t buf = tcount % ACC_BUFS;
+            const uint32_t d = tmem_base + buf * BT;
+            for (int kb = 0; kb < kblocks; kb++) {
+                QMM_ACC(2);
+                named_sync(1 + s);  // stage s is full (and, for kb = 0, the accumulator is drained)
+                QMM_ACC(1);
+                if (lane == 0) {
                     tc_fence_after();
                     const uint32_t at = tmem_base + A_COL0 + s * 32;
                     const uint64_t bd = bd0 + (uint64_t)(s * (X_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < QMM_BK / 16; k++)  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
                         tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, (kb | k) != 0);
-                    QMM_ACC(2);
-                    tc_commit_addr(empty0 + 8 * s);  // frees both halves of the stage once these MMAs have read them
-                    if (++s == STAGES) {
-                        s = 0;
-                        ph ^= 1;
-                    }
                     QMM_ACC(3);
+                    tc_commit_addr(empty0 + 8 * s);  // frees both halves of the stage once these MMAs have read them
                 }
-                if (ok) tc_commit(accfull + buf);
-                tcount++;
+                __syncwarp();
+                QMM_ACC(0);
+                if (++s == STAGES) s = 0;
             }
-            QMM_DUMP(0);
+            if (lane == 0) tc_commit(accfull + buf);
+            __syncwarp();
+            tcount++;
         }
-    } else if (warp >= 7) {
+        QMM_DUMP(0);
+    } else if (warp == QMM_WATCH_WARP) {
+        // ── watcher: the MMA warp's eyes.  It arrives on the named barrier of every stage exactly
+        //    once per k-block whatever happens (after a wait gave up it stops waiting, not
+        //    arriving), so the MMA warp can never be left behind in a barrier. ──
+        uint32_t tcount = 0, s = 0, ph = 0;
+        bool ok = true;
+        QMM_T0();
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            TileInfo ti;
+            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
+            QMM_ACC(3);
+            if (lane == 0 && ok) ok = mbar_wait<100>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
+            QMM_ACC(0);
+            for (int kb = 0; kb < kblocks; kb++) {
+                if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
+                QMM_ACC(1);
+                if (lane == 0 && ok) ok = mbar_wait(afull + s, ph, abort_flag);
+                QMM_ACC(2);
+                __syncwarp();
+                named_arrive(1 + s);
+                if (++s == STAGES) {
+                    s = 0;
+                    ph ^= 1;
+                }
+                QMM_ACC(3);
+            }
+            tcount++;
+        }
+        QMM_DUMP(12);
+    } else if (warp >= 7 && warp < QMM_WATCH_WARP) {
         // ── dequantizers ─────────────────────────────────────────────────────────────────
         // Four groups of 4 warps take k-blocks in turn.  Thread = weight row = tensor-memory lane
         // (a warp reaches the 32 lanes of its rank in the warpgroup): it rebuilds the 64 k-values of
@@ -622,7 +671,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             TileInfo ti;
             if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
-            const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
+            const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             ok = mbar_wait<500>(accfull + buf, aph, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -750,7 +799,8 @@ static int32_t launch_bt(nvc_device *dev, int bt, const CUtensorMap &mx, const C
     case 32: return launch_cfg<BITS, 32, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     case 64: return launch_cfg<BITS, 64, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     case 128: return launch_cfg<BITS, 128, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
-    default: return launch_cfg<BITS, 192, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    case 192: return launch_cfg<BITS, 192, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
+    default: return launch_cfg<BITS, 256, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     }
 }
 
@@ -759,12 +809,12 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     const int64_t experts = p.offsets ? p.experts : 1;
     // Token tile: the largest that the rows (per expert, on average) fill reasonably.
     const int64_t per = p.offsets ? (p.rows + experts - 1) / experts : p.rows;
-    // 192 is the widest: two accumulators of 192 columns leave 128 of the 512 tensor-memory
-    // columns for the dequantized-weight ring.
-    int bt = per > 128 ? 192 : per > 64 ? 128 : per > 32 ? 64 : 32;
+    // 256 tokens keep one accumulator in tensor memory (the epilogue then stalls the MMAs for a
+    // few per cent of a tile, which the wider MMA more than pays for); narrower tiles keep two.
+    int bt = per > 192 ? 256 : per > 128 ? 192 : per > 64 ? 128 : per > 32 ? 64 : 32;
     if (const char *e = getenv("NUVEC_QMM_BT")) {
         int v = atoi(e);
-        if (v == 32 || v == 64 || v == 128 || v == 192) bt = v;
+        if (v == 32 || v == 64 || v == 128 || v == 192 || v == 256) bt = v;
     }
     const int n_tiles = (int)((p.N + QMM_BN - 1) / QMM_BN);
     int64_t token_tiles;

@@ -268,6 +268,26 @@ def test_qmm_unit_rows_return_the_dequantized_weights_bit_for_bit(be, bits, gs):
     assert np.array_equal(got, dense[:, ks].T)
 
 
+@pytest.mark.parametrize("bits,gs,K", [(4, 64, 2048), (8, 64, 2048), (2, 64, 2048), (8, 32, 2880 // 64 * 64), (4, 128, 1920)])
+def test_qmm_unit_rows_through_a_long_persistent_run(be, bits, gs, K):
+    # More tiles than multiprocessors and many k-blocks per tile: every block of the persistent
+    # kernel walks several tiles, the activation / weight / packed-slab rings wrap many times and
+    # each dequantizer group meets slabs that hold none of its blocks.  Unit-vector rows make any
+    # stale or overwritten stage visible as a bit difference, at a size no product oracle is needed for.
+    rng = np.random.default_rng(bits + K)
+    N, M = 2560, 1600
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    dense = oracle.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, gs, bits)
+    ks = rng.integers(0, K, M)
+    x = np.zeros((M, K), np.float32)
+    x[np.arange(M), ks] = 1.0
+    xb = oracle.from_f32(x, oracle.BF16)
+    for _ in range(2):  # twice: the second launch starts on warm caches and different timing
+        got = be.quantized_matmul(xb, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits, True)
+        assert np.array_equal(got, dense[:, ks].T)
+
+
 @pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
 @pytest.mark.parametrize("M,N,K", [(40, 128, 128), (130, 200, 2880)])
 def test_qmm_fp4(be, mode, gs, M, N, K):
