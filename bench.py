@@ -201,6 +201,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="time every single-GPU configuration of the benchmark definition and print one JSON object")
     ap.add_argument("--no-graph", action="store_true", help="launch every product from the host instead of replaying a recorded step")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -224,6 +225,11 @@ def main():
     dev = nv.Device.shared(local)
     lib = _ffi.lib()
     peaks = measured_peaks()
+    if args.sweep:
+        if world > 1:
+            raise SystemExit("--sweep runs on one GPU")
+        print(json.dumps({"sweep": config_sweep(nv, _ffi, dev, peaks), "peaks": peaks}))
+        return
     M = args.rows
 
     # ── weights: one seeded layer, quantized on the device, replicated into distinct buffers ──
@@ -403,6 +409,126 @@ def main():
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+# ── the other configurations of the benchmark definition, one line each (--sweep) ────────────
+def config_sweep(nv, _ffi, dev, peaks):
+    """Times every single-GPU configuration the benchmark definition lists (decode projections
+    at M = 1, 4, 8; prefill at M = 2048 / 8192 and 4 / 8 bits; the two mixture-of-experts shapes
+    through gather_qmm with sorted indices) and returns one row per product.  Device time only
+    (CUDA events around replays of a recorded step); parity of the same shapes is what the GPU
+    tests check."""
+    lib = _ffi.lib()
+    rng = np.random.default_rng(0)
+    rows = []
+
+    def time_fn(fn, reps):
+        fn()
+        g = dev.record(fn)
+        for _ in range(3):
+            g.launch()
+        dev.synchronize()
+        e0, e1 = dev.event(), dev.event()
+        e0.record()
+        for _ in range(reps):
+            g.launch()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_ms(e1) * 1e3 / reps  # us per replay
+
+    def quantized(shape, quant):
+        """Random weights ~ N(0, 0.02) quantized on the device, expert by expert (bounded host memory)."""
+        lead = shape[:-2]
+        n = int(np.prod(lead)) if lead else 1
+        parts = []
+        for _ in range(n):
+            w = nv.f32_to_bf16(rng.standard_normal(shape[-2:], dtype=np.float32) * 0.02)
+            parts.append(nv.quantize(dev.array(w, nv.BF16), quant))
+        if not lead:
+            return parts[0]
+        def stack(get, dtype):
+            first = get(parts[0])
+            out = dev.empty(tuple(lead) + tuple(first.shape), dtype)
+            per = first.nbytes
+            for i, q in enumerate(parts):
+                lib.nvc_memcpy_d2d(dev._h, C.c_void_p(out.ptr.value + i * per), get(q).ptr, per)
+            return out
+        sdt = parts[0].scales.dtype
+        return nv.Quantized(stack(lambda q: q.weight, nv.U32), stack(lambda q: q.scales, sdt),
+                            None if parts[0].biases is None else stack(lambda q: q.biases, sdt), quant)
+
+    def dense(tag, M, N, K, quant, copies, reps):
+        q0 = quantized((N, K), quant)
+        x = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
+        sets = [q0]
+        for _ in range(copies - 1):
+            q = nv.Quantized(dev.empty(q0.weight.shape, nv.U32), dev.empty(q0.scales.shape, q0.scales.dtype),
+                             None if q0.biases is None else dev.empty(q0.biases.shape, q0.biases.dtype), quant)
+            q.weight.copy_from(q0.weight), q.scales.copy_from(q0.scales)
+            if q0.biases is not None:
+                q.biases.copy_from(q0.biases)
+            sets.append(q)
+        ys = [dev.empty((M, N), nv.BF16) for _ in sets]
+        qc = quant._c()
+        def step():
+            for q, y in zip(sets, ys):
+                rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, q.weight.ptr, q.scales.ptr,
+                                              None if q.biases is None else q.biases.ptr, None, M, N, K, K, 1, 0, 0, 0, y.ptr)
+                assert rc == 0, _ffi.last_error()
+        us = time_fn(step, reps) / copies
+        bits, gs = quant.bits, quant.group_size
+        sbytes = 4 if quant.mode == nv.QuantMode.AFFINE else 1
+        nbytes = N * K * bits / 8 + N * (K // gs) * sbytes + M * K * 2 + M * N * 2
+        flops = 2.0 * M * N * K
+        row = {"config": tag, "M": M, "N": N, "K": K, "quant": f"{quant.mode.name.lower()} b{bits} g{gs}", "us": us,
+               "GB/s": nbytes / us / 1e3, "TFLOP/s": flops / us / 1e6}
+        if M <= 8:
+            row["frac"], row["of"] = row["GB/s"] / peaks["hbm_gbs"], "measured HBM copy"
+        else:
+            row["frac"], row["of"] = row["TFLOP/s"] / peaks["bf16_tflops"], "measured bf16 burst"
+        rows.append(row)
+
+    a4 = nv.Quant.affine(GS, BITS)
+    dense("C1 qmv", 1, 4096, 4096, a4, 64, 20)
+    for M in (1, 4, 8):
+        for name, N, K in PROJECTIONS:
+            dense(f"C2 {name}", M, N, K, a4, max(2, int(600e6 // (N * K // 2))), 20)
+    for M in (2048, 8192):
+        for bits in (4, 8):
+            dense("C3 prefill", M, 12288, 4096, nv.Quant.affine(GS, bits), 3, 5)
+
+    def moe(tag, T, E, topk, N, K, quant, reps):
+        q = quantized((E, N, K), quant)
+        ids = np.concatenate([rng.permutation(E)[:topk] for _ in range(T)]).astype(np.uint32)
+        order = np.argsort(ids, kind="stable")
+        rhs = dev.array(ids[order], nv.U32)
+        xh = nv.f32_to_bf16(rng.standard_normal((T, K), dtype=np.float32))
+        x = dev.array(np.ascontiguousarray(xh[order // topk]).reshape(T * topk, 1, K), nv.BF16)
+        opts = nv.GatherQmm(transpose=True, sorted_indices=True)
+        keep = []
+        def step():
+            keep.clear()
+            keep.append(nv.gather_qmm(x, q, None, rhs, opts))
+        us = time_fn(step, reps)
+        bits, gs = quant.bits, quant.group_size
+        sbytes = 4 if quant.mode == nv.QuantMode.AFFINE else 1
+        touched = len(np.unique(ids))
+        nbytes = touched * (N * K * bits / 8 + N * (K // gs) * sbytes) + T * topk * (K + N) * 2
+        flops = 2.0 * T * topk * N * K
+        rows.append({"config": tag, "M": f"{T}x{topk}", "N": N, "K": K, "quant": f"{quant.mode.name.lower()} b{bits} g{gs}, {E} experts",
+                     "us": us, "GB/s": nbytes / us / 1e3, "TFLOP/s": flops / us / 1e6,
+                     "frac": (nbytes / us / 1e3) / peaks["hbm_gbs"] if T == 1 else (flops / us / 1e6) / peaks["bf16_tflops"],
+                     "of": "measured HBM copy (experts touched)" if T == 1 else "measured bf16 burst"})
+
+    for T in (1, 512):
+        moe("C4 moe gate+up", T, 128, 8, 1536, 2048, a4, 10)
+        moe("C4 moe down", T, 128, 8, 2048, 768, a4, 10)
+    for quant in (nv.Quant.new(nv.QuantMode.MXFP4), nv.Quant.new(nv.QuantMode.NVFP4)):
+        for T in (1, 1024):
+            moe("C5 moe gate+up", T, 32, 4, 5760, 2880, quant, 10)
+            moe("C5 moe down", T, 32, 4, 2880, 2880, quant, 10)
+    return rows
+
 
 
 def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier):

@@ -34,15 +34,17 @@ static int32_t check_product(const char *op, const nvc_quant *q, int32_t dtype, 
 static bool grouped(int64_t rows, int64_t experts) { return rows >= 16 && rows / (experts > 0 ? experts : 1) >= 4; }
 
 // Rows from which a plain product goes to the tensor-core kernel.  Affine weights with up to 8
-// rows stream once through the few-row kernel; the 4-bit floating-point formats have no few-row
-// kernel and take the tensor-core kernel (with its smallest token tile) from the first row.
-static int64_t qmm_threshold(int32_t mode) {
+// rows stream once through the few-row kernel when it takes the shape (it stages every activation
+// row in shared memory); everything else the tensor-core kernel is eligible for goes there, with
+// its smallest token tile for few rows: 9 to 16 rows, the 4-bit floating-point formats (which have
+// no few-row kernel) from the first row, and few-row affine products the few-row kernel refused.
+// NUVEC_QMM_MIN_ROWS raises the bar (products below it fall through to the generic kernel).
+static int64_t qmm_threshold() {
     static int64_t v = [] {
         const char *e = getenv("NUVEC_QMM_MIN_ROWS");
-        return e ? atoll(e) : 0;
+        return e ? atoll(e) : 1;
     }();
-    if (v > 0) return v;
-    return mode == NVC_AFFINE ? 9 : 1;
+    return v;
 }
 
 __global__ void sorted_offsets_kernel(const uint32_t *__restrict__ idx, int64_t rows, int64_t groups,
@@ -104,7 +106,7 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
         p.x_vec = ((uintptr_t)x % 16 == 0) && (ldx % 8 == 0) && (x_batch_stride % 8 == 0);
         return launch_qmv_affine(dev, q->bits, p, batch);
     }
-    if (M >= qmm_threshold(q->mode) && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
+    if (M >= qmm_threshold() && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
         for (int64_t b = 0; b < batch; b++) {
             QmmParams p{};
             p.mode = q->mode; p.gs = q->group_size; p.bits = q->bits;
@@ -146,8 +148,11 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
     }
     const int64_t w_stride = (transpose ? N : K) * ((transpose ? K : N) * q->bits / 32);
     const int64_t s_stride = (transpose ? N : K) * ((transpose ? K : N) / q->group_size);
-    // Sorted rows of one expert multiplied together (the reference's grouped kernel).
-    if (sorted && !lhs && M == 1 && grouped(rows, experts) &&
+    // Sorted rows of one expert multiplied together (the reference's grouped kernel).  The
+    // reference's row-count rule chooses between two algorithms with the same result; here it
+    // chooses between the tensor-core kernel and the few-row kernel, and the 4-bit floating-point
+    // formats, which have no few-row kernel, take the tensor-core kernel whatever the count.
+    if (sorted && !lhs && M == 1 && (grouped(rows, experts) || q->mode != NVC_AFFINE) &&
         qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, rows, N, K, x, K, w)) {
         const int32_t *offs = offsets;
         if (!offs) {
