@@ -77,6 +77,11 @@ struct nvc_device {
     size_t pinned_bytes = 0;
     void *staging = nullptr;
     size_t staging_bytes = 0;
+    // Scratch of the tensor-core kernel's K-split tiles (partial tiles, arrival counters).
+    void *qmm_partials = nullptr;
+    size_t qmm_partials_bytes = 0;
+    uint32_t *qmm_counters = nullptr;
+    size_t qmm_counters_len = 0;
     // Host-mapped word a kernel sets when one of its bounded waits gives up; read at synchronisation.
     int32_t *error_word = nullptr, *error_word_dev = nullptr;
 };

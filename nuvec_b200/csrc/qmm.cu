@@ -49,6 +49,7 @@ namespace nvc {
 constexpr int QMM_BN = 128;  // weight rows per tile (UMMA M)
 constexpr int QMM_BK = 64;   // k-values per block: one 128-byte swizzle row of bfloat16
 constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 16, QMM_DQ_GROUPS = 4;  // dequantizers: groups of 4 warps
+constexpr uint32_t QMM_EPI_BARRIER = 9;  // named barrier of the epilogue warps (1 .. 8 belong to the stages)
 constexpr int QMM_WATCH_WARP = QMM_EPI_WARPS + 3 + QMM_DQ_WARPS;  // the warp that waits on behalf of the MMA warp
 constexpr int QMM_THREADS = (QMM_WATCH_WARP + 1) * 32;
 constexpr int QMM_W_STAGES = 2;          // packed-weight slabs in flight
@@ -63,6 +64,9 @@ struct QmmKernelParams {
     uint16_t *y;                      // bfloat16 [rows, N]
     const int32_t *offsets;           // grouped: first row of each expert, else nullptr
     int32_t *error;                   // host-visible word: nonzero when a wait gave up
+    float *partials;                  // [tail tiles][splits][BT tokens][128 rows] float32 (K-split tiles)
+    uint32_t *counters;               // [tail tiles] arrivals, zero on entry and on exit
+    int32_t full_waves, tail_tiles, splits;  // the schedule, see Item
     int32_t experts, rows, N, K;
     int32_t gs_shift, row_groups, mode, expert_global;
 };
@@ -150,6 +154,7 @@ __device__ __forceinline__ bool mbar_test2(uint32_t bar_a, uint32_t bar_b, uint3
 }
 // Hardware named barriers between the watcher warp and the MMA warp (64 threads).
 __device__ __forceinline__ void named_sync(uint32_t id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void named_sync_n(uint32_t id, uint32_t threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 __device__ __forceinline__ void named_arrive(uint32_t id) { asm volatile("bar.arrive %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void tc_commit_addr(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -364,6 +369,34 @@ __device__ __forceinline__ bool tile_info(const QmmKernelParams &p, int tile, in
     return false;
 }
 
+// The schedule.  Every block first takes `full_waves` whole tiles (tile = block + wave * grid).  The
+// tiles left over (fewer than blocks) are cut along K into `splits` parts of whole packed-weight
+// slabs, one part per block, so that the last wave -- or a product with fewer tiles than
+// multiprocessors -- still keeps every multiprocessor busy.  Parts leave float32 partial tiles in
+// scratch; the block that arrives last adds them in part order and writes the result.
+struct Item {
+    int tile, kb0, kb1;  // k-blocks [kb0, kb1) of this tile
+    int part, parts, slot;
+};
+template <int KPS>
+__device__ __forceinline__ bool qmm_item(const QmmKernelParams &p, int kblocks, int j, Item &it) {
+    const int grid = (int)gridDim.x;
+    if (j < p.full_waves) {
+        it.tile = (int)blockIdx.x + j * grid;
+        it.kb0 = 0; it.kb1 = kblocks; it.part = 0; it.parts = 1; it.slot = 0;
+        return true;
+    }
+    if (j > p.full_waves || (int)blockIdx.x >= p.tail_tiles * p.splits) return false;
+    it.slot = (int)blockIdx.x / p.splits;
+    it.part = (int)blockIdx.x % p.splits;
+    it.parts = p.splits;
+    it.tile = p.full_waves * grid + it.slot;
+    const int slabs = (kblocks + KPS - 1) / KPS;  // the launch keeps splits <= slabs: no part is empty
+    it.kb0 = slabs * it.part / p.splits * KPS;
+    it.kb1 = min(slabs * (it.part + 1) / p.splits * KPS, kblocks);
+    return true;
+}
+
 // Stages of the dequantized-weight ring in tensor memory: 32 columns each, in what the two
 // accumulators leave of the 512 columns.
 template <int BT> struct QmmTmem {
@@ -403,6 +436,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     uint64_t *accfull = wempty + QMM_W_STAGES, *accempty = accfull + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accempty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *last_flag = abort_flag + 1;  // epilogue: this block arrived last at a K-split tile
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kblocks = p.K / QMM_BK;
@@ -422,6 +456,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             mbar_init(accempty + s, QMM_EPI_WARPS);
         }
         *abort_flag = 0;
+        *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {  // all of tensor memory: two accumulators and the dequantized-weight ring
@@ -438,10 +473,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         if (lane == 0) {
             uint32_t it = 0;  // k-blocks issued so far
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int j = 0; ok; j++) {
+                Item item;
+                if (!qmm_item<KPS>(p, kblocks, j, item)) break;
                 TileInfo ti;
-                if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
-                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+                for (int kb = item.kb0; kb < item.kb1 && ok; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
                     if (!ok) break;
@@ -456,10 +493,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         if (lane == 0) {
             uint32_t wit = 0;  // weight slabs issued so far
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int j = 0; ok; j++) {
+                Item item;
+                if (!qmm_item<KPS>(p, kblocks, j, item)) break;
                 TileInfo ti;
-                if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
-                for (int kb = 0; kb < kblocks && ok; kb += KPS, wit++) {
+                if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+                for (int kb = item.kb0; kb < item.kb1 && ok; kb += KPS, wit++) {
                     const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
                     ok = mbar_wait<200>(wempty + s, ph ^ 1, abort_flag);
                     if (!ok) break;
@@ -480,12 +519,14 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         const uint32_t empty0 = smem_u32(empty);
         const uint64_t bd0 = umma_desc(smem_u32(xs));
         QMM_T0();
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int j = 0;; j++) {
+            Item item;
+            if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS;
             const uint32_t d = tmem_base + buf * BT;
-            for (int kb = 0; kb < kblocks; kb++) {
+            for (int kb = item.kb0; kb < item.kb1; kb++) {
                 QMM_ACC(2);
                 named_sync(1 + s);  // stage s is full (and, for kb = 0, the accumulator is drained)
                 QMM_ACC(1);
@@ -495,7 +536,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     const uint64_t bd = bd0 + (uint64_t)(s * (X_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < QMM_BK / 16; k++)  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
-                        tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                        tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
                     QMM_ACC(3);
                     tc_commit_addr(empty0 + 8 * s);  // frees both halves of the stage once these MMAs have read them
                 }
@@ -515,14 +556,16 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         uint32_t tcount = 0, s = 0, ph = 0;
         bool ok = true;
         QMM_T0();
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int j = 0;; j++) {
+            Item item;
+            if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             QMM_ACC(3);
             if (lane == 0 && ok) ok = mbar_wait<100>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
             QMM_ACC(0);
-            for (int kb = 0; kb < kblocks; kb++) {
+            for (int kb = item.kb0; kb < item.kb1; kb++) {
                 if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
                 QMM_ACC(1);
                 if (lane == 0 && ok) ok = mbar_wait(afull + s, ph, abort_flag);
@@ -559,9 +602,11 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 else { sv[h] = fsc[k >> p.gs_shift]; bv[h] = MODE == 3 ? fsc[(k + 16) >> p.gs_shift] : 0u; }
             }
         };
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int j = 0; ok; j++) {
+            Item item;
+            if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
             // rows past N (last tile) read the last valid row's scales; their outputs are not stored
             const int wr = ti.wrow0 + min(row, p.N - 1 - ti.n0);
             const uint16_t *sc = p.scales + (size_t)wr * p.row_groups;
@@ -570,18 +615,18 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             uint32_t s_next[2] = {0, 0}, b_next[2] = {0, 0};
             // this group's blocks are those at ring positions = group (mod groups): the same warps
             // always refill the same stages, so nobody is ever two phases ahead of a barrier
-            const int first = (group + QMM_DQ_GROUPS - (int)(it_base % QMM_DQ_GROUPS)) % QMM_DQ_GROUPS;
-            if (first < kblocks) load_consts(sc, bi, fsc, first, s_next, b_next);
-            for (int slab = 0; slab * KPS < kblocks && ok; slab++, wit++) {
+            const int first = item.kb0 + (group + QMM_DQ_GROUPS - (int)(it_base % QMM_DQ_GROUPS)) % QMM_DQ_GROUPS;
+            if (first < item.kb1) load_consts(sc, bi, fsc, first, s_next, b_next);
+            for (int slab = item.kb0 / KPS; slab * KPS < item.kb1 && ok; slab++, wit++) {
                 const uint32_t wsi = wit % QMM_W_STAGES, wph = (wit / QMM_W_STAGES) & 1;
                 bool have = false;
 #pragma unroll 1
                 for (int kq = 0; kq < KPS; kq++) {
                     const int kb = slab * KPS + kq;
-                    if (kb >= kblocks) break;
-                    if ((int)((it_base + kb) % QMM_DQ_GROUPS) != group) continue;
+                    if (kb >= item.kb1) break;
+                    if ((int)((it_base + kb - item.kb0) % QMM_DQ_GROUPS) != group) continue;
                     const uint32_t s_cur[2] = {s_next[0], s_next[1]}, b_cur[2] = {b_next[0], b_next[1]};
-                    if (kb + QMM_DQ_GROUPS < kblocks) load_consts(sc, bi, fsc, kb + QMM_DQ_GROUPS, s_next, b_next);  // prefetch
+                    if (kb + QMM_DQ_GROUPS < item.kb1) load_consts(sc, bi, fsc, kb + QMM_DQ_GROUPS, s_next, b_next);  // prefetch
                     QMM_ACC(2);
                     if (!have) {
                         ok = mbar_wait(wfull + wsi, wph, abort_flag);
@@ -640,7 +685,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                             }
                         }
                     }
-                    const uint32_t it = it_base + kb, sa = it % STAGES, pha = (it / STAGES) & 1;
+                    const uint32_t it = it_base + (uint32_t)(kb - item.kb0), sa = it % STAGES, pha = (it / STAGES) & 1;
                     QMM_ACC(2);
                     ok = ok && mbar_wait(empty + sa, pha ^ 1, abort_flag);  // the MMAs that read this stage are done
                     QMM_ACC(1);
@@ -660,7 +705,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 __syncwarp();
                 if (lane == 0) mbar_arrive(wempty + wsi);
             }
-            it_base += (uint32_t)kblocks;
+            it_base += (uint32_t)(item.kb1 - item.kb0);
         }
         if (warp == 7) QMM_DUMP(4);
         if (warp == 19) QMM_DUMP(8);
@@ -668,36 +713,72 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
         uint32_t tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int jj = 0; ok; jj++) {
+            Item item;
+            if (!qmm_item<KPS>(p, kblocks, jj, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
-            ok = mbar_wait<500>(accfull + buf, aph, abort_flag);
-            if (!ok) break;
+            // After a wait gave up the warp keeps walking the items without touching data: the
+            // named barriers of K-split tiles below must still see all four epilogue warps.
+            if (ok) ok = mbar_wait<500>(accfull + buf, aph, abort_flag);
             tc_fence_after();
-            const int n = ti.n0 + warp * 32 + lane;
+            const int r = warp * 32 + lane;  // row of the tile
+            const int n = ti.n0 + r;
             float gmul = 1.0f;
             if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
+            if (item.parts == 1) {
 #pragma unroll 1
-            for (int c = 0; c < BT / 32; c++) {
-                uint32_t v[32];
-                tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
-                tc_ld_wait();
-                if (n < p.N) {
+                for (int c = 0; c < BT / 32 && ok; c++) {
+                    uint32_t v[32];
+                    tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
+                    tc_ld_wait();
+                    if (n < p.N) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int tok = ti.tok0 + c * 32 + j;
-                        if (tok < ti.tok_end) {
-                            float f = __uint_as_float(v[j]);
-                            if (MODE != 0) f *= gmul;
-                            p.y[(size_t)tok * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                        for (int j = 0; j < 32; j++) {
+                            const int tok = ti.tok0 + c * 32 + j;
+                            if (tok < ti.tok_end) {
+                                float f = __uint_as_float(v[j]);
+                                if (MODE != 0) f *= gmul;
+                                p.y[(size_t)tok * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                            }
                         }
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accempty + buf);
+            } else {
+                // One part of a tile cut along K: the float32 partial goes to scratch as
+                // [token][row] (a warp writes 128 consecutive bytes per token); the block that
+                // arrives last adds the parts in part order and rounds once.
+                float *mine = p.partials + ((size_t)item.slot * item.parts + item.part) * (size_t)(BT * QMM_BN);
+#pragma unroll 1
+                for (int c = 0; c < BT / 32 && ok; c++) {
+                    uint32_t v[32];
+                    tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (ti.tok0 + c * 32 + j < ti.tok_end) __stcg(mine + (size_t)(c * 32 + j) * QMM_BN + r, __uint_as_float(v[j]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accempty + buf);  // the accumulator is free again
+                __threadfence();
+                named_sync_n(QMM_EPI_BARRIER, QMM_EPI_WARPS * 32);
+                if (tid == 0) {
+                    bool last = false;
+                    if (ok) {
+                        const uint32_t arrived = atomicAdd(p.counters + item.slot, 1u);
+                        last = arrived == (uint32_t)item.parts - 1;
+                        if (last) p.counters[item.slot] = 0u;  // rearmed for the next launch
+                    }
+                    // A K-split part is always a block's last item: the whole block adds the parts
+                    // up after its roles have finished (below).
+                    *last_flag = last ? 1 : 0;
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(accempty + buf);
             tcount++;
         }
     }
@@ -706,6 +787,34 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && *abort_flag && p.error) *p.error = 1;
+    if (*last_flag && !*abort_flag) {
+        // This block arrived last at its K-split tile: all its threads add the float32 parts in
+        // part order (the sum does not depend on who arrived when), round once and store.
+        Item item;
+        TileInfo ti;
+        if (qmm_item<KPS>(p, kblocks, p.full_waves, item) && tile_info<BT>(p, item.tile, n_tiles, ti)) {
+            __threadfence();
+            float gmul = 1.0f;
+            if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
+            const float4 *base = reinterpret_cast<const float4 *>(p.partials + (size_t)item.slot * item.parts * (size_t)(BT * QMM_BN));
+            constexpr int TILE4 = BT * QMM_BN / 4;  // float4 per part
+            const int tokens = min(BT, ti.tok_end - ti.tok0);
+            for (int idx = tid; idx < tokens * (QMM_BN / 4); idx += QMM_THREADS) {
+                const int t = idx / (QMM_BN / 4), r4 = idx % (QMM_BN / 4);
+                float4 acc = __ldcg(base + idx);
+                for (int q = 1; q < item.parts; q++) {
+                    const float4 v = __ldcg(base + (size_t)q * TILE4 + idx);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+                const float f[4] = {acc.x, acc.y, acc.z, acc.w};
+                const int n = ti.n0 + 4 * r4;
+                uint16_t *dst = p.y + (size_t)(ti.tok0 + t) * p.N + n;
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (n + e < p.N) dst[e] = __bfloat16_as_ushort(__float2bfloat16_rn(MODE != 0 ? f[e] * gmul : f[e]));
+            }
+        }
+    }
     if (warp == 5) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
@@ -773,6 +882,33 @@ bool qmm_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t
     return true;
 }
 
+// Scratch of the K-split tiles: float32 partial tiles and their arrival counters, owned by the
+// device handle (kept apart from the few-row kernel's scratch, which a gather may be using for
+// its expert offsets at the same time).  Counters are zero between launches.
+static int32_t ensure_qmm_scratch(nvc_device *dev, size_t bytes, size_t counters) {
+    if (dev->qmm_partials_bytes < bytes) {
+        NVC_CUDA(cudaStreamSynchronize(dev->stream));
+        if (dev->qmm_partials) dev->pool.free(dev->qmm_partials);
+        dev->qmm_partials = nullptr;
+        dev->qmm_partials_bytes = 0;
+        NVC_TRY(dev->pool.alloc(bytes, &dev->qmm_partials));
+        dev->qmm_partials_bytes = bytes;
+    }
+    if (dev->qmm_counters_len < counters) {
+        NVC_CUDA(cudaStreamSynchronize(dev->stream));
+        if (dev->qmm_counters) dev->pool.free(dev->qmm_counters);
+        dev->qmm_counters = nullptr;
+        dev->qmm_counters_len = 0;
+        const size_t len = counters < 256 ? 256 : counters;
+        void *ptr = nullptr;
+        NVC_TRY(dev->pool.alloc(len * sizeof(uint32_t), &ptr));
+        NVC_CUDA(cudaMemsetAsync(ptr, 0, len * sizeof(uint32_t), dev->stream));
+        dev->qmm_counters = (uint32_t *)ptr;
+        dev->qmm_counters_len = len;
+    }
+    return NVC_OK;
+}
+
 template <int BITS, int BT, int MODE>
 static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
                           int total_tiles, int n_tiles) {
@@ -787,8 +923,33 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
         NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    int grid = dev->prop.multiProcessorCount < total_tiles ? dev->prop.multiProcessorCount : total_tiles;
-    kernel<<<grid, QMM_THREADS, smem, dev->stream>>>(mx, mw, kp, total_tiles, n_tiles);
+    // The schedule (see Item): whole tiles wave by wave, then the left-over tiles cut along K.
+    QmmKernelParams k = kp;
+    const int sms = dev->prop.multiProcessorCount;
+    const int kblocks = k.K / QMM_BK, slabs = (kblocks + QmmBits<BITS>::KPS - 1) / QmmBits<BITS>::KPS;
+    int grid = sms < total_tiles ? sms : total_tiles;
+    k.full_waves = total_tiles / grid;
+    k.tail_tiles = total_tiles % grid;
+    k.splits = 1;
+    if (total_tiles < sms) {  // fewer tiles than multiprocessors: all of them are "left over"
+        k.full_waves = 0;
+        k.tail_tiles = total_tiles;
+    }
+    if (k.tail_tiles > 0 && !getenv("NUVEC_QMM_NO_KSPLIT")) {
+        int s = sms / k.tail_tiles;           // parts per tile that fit the machine
+        if (s > slabs / 2) s = slabs / 2;     // at least two slabs of weights per part
+        if (s > 16) s = 16;
+        if (s < 1) s = 1;
+        k.splits = s;
+    }
+    if (k.full_waves == 0) grid = k.tail_tiles * k.splits;
+    if (k.splits > 1) {
+        const size_t need = (size_t)k.tail_tiles * k.splits * BT * QMM_BN * sizeof(float);
+        NVC_TRY(ensure_qmm_scratch(dev, need, (size_t)k.tail_tiles));
+        k.partials = (float *)dev->qmm_partials;
+        k.counters = dev->qmm_counters;
+    }
+    kernel<<<grid, QMM_THREADS, smem, dev->stream>>>(mx, mw, k, total_tiles, n_tiles);
     return check_launch(dev, "qmm_kernel");
 }
 
@@ -812,6 +973,10 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     // 256 tokens keep one accumulator in tensor memory (the epilogue then stalls the MMAs for a
     // few per cent of a tile, which the wider MMA more than pays for); narrower tiles keep two.
     int bt = per > 192 ? 256 : per > 128 ? 192 : per > 64 ? 128 : per > 32 ? 64 : 32;
+    // Experts' row counts scatter around the average, and a second token tile dequantizes the
+    // expert's weights a second time (the kernel's cost is the dequantization, not the MMA
+    // width): size the tile for the average plus half.
+    if (p.offsets) bt = per > 170 ? 256 : per > 128 ? 192 : per > 85 ? 192 : per > 42 ? 128 : per > 21 ? 64 : 32;
     if (const char *e = getenv("NUVEC_QMM_BT")) {
         int v = atoi(e);
         if (v == 32 || v == 64 || v == 128 || v == 192 || v == 256) bt = v;

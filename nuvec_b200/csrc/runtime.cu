@@ -243,6 +243,8 @@ int32_t nvc_device_close(nvc_device *dev) {
     NVC_TRY(make_current(dev));
     cudaStreamSynchronize(dev->stream);
     if (dev->scratch) dev->pool.free(dev->scratch);
+    if (dev->qmm_partials) dev->pool.free(dev->qmm_partials);
+    if (dev->qmm_counters) dev->pool.free(dev->qmm_counters);
     if (dev->counters) dev->pool.free(dev->counters);
     if (dev->staging) dev->pool.free(dev->staging);
     if (dev->pinned) cudaFreeHost(dev->pinned);
