@@ -269,6 +269,9 @@ template <> struct Unpack<2> {
 
 constexpr int QMV_WARPS = 8;
 constexpr int QMV_THREADS = QMV_WARPS * 32;
+// Resident blocks per multiprocessor the kernel is compiled for (128 registers per thread; three
+// blocks at 80 registers were measured slower at every size).
+constexpr int QMV_BLOCKS_PER_SM = 2;
 // Depth of each lane's ring of asynchronous weight copies (iterations in flight per warp): the
 // bytes in flight per lane stay near 128 whatever the iteration's width.
 __host__ __device__ constexpr int qmv_stages(int wpl) { return wpl == 8 ? 3 : 4; }
@@ -304,7 +307,7 @@ constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 //   lpart [QMV_WARPS][2][128] f32         partial sums of tiles cut between warps of this block
 //   lcount[QMV_WARPS] u32                 their arrival counters
 template <int BITS, int WPL>
-__global__ void __launch_bounds__(QMV_THREADS, 2) qmv_affine_kernel(QmvParams p) {
+__global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
     constexpr int CODES = U::CODES, AREGS = U::AREGS;
     constexpr int IK = 4 * WPL * CODES;
@@ -759,7 +762,11 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     const size_t smem = qmv_smem(p.M, p.K, bits, wpl);
     // Blocks: as many as stay resident (two per multiprocessor while shared memory allows), but
     // no more than give every warp a few iterations.
-    const int64_t per_sm = smem <= 113 * 1024 ? 2 : 1;
+    // (each block also takes 1 KB of shared memory the system reserves)
+    int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(smem + 1024);
+    if (per_sm > QMV_BLOCKS_PER_SM) per_sm = QMV_BLOCKS_PER_SM;
+    if (per_sm < 1) per_sm = 1;
+    per_sm = env_int("NUVEC_QMV_PER_SM", per_sm);
     int64_t blocks = per_sm * dev->prop.multiProcessorCount / batch;
     const int64_t min_iters = env_int("NUVEC_QMV_MIN_ITERS", 4);
     const int64_t useful = (total + QMV_WARPS * min_iters - 1) / (QMV_WARPS * min_iters);
