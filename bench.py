@@ -276,6 +276,46 @@ def main():
 
     qc = quant._c()
 
+    # ── fused product + gather over peer stores (the multi-GPU headline; NCCL stays as the check) ──
+    fused = None
+    if world > 1 and not os.environ.get("NUVEC_BENCH_NO_FUSED"):
+        try:
+            RES = 4096
+            offsets, at = [], RES
+            for projs in layers:
+                row = []
+                for name, N, K, n_local, q, x, y in projs:
+                    row.append(at)
+                    at += (world * M * n_local * 2 + 255) // 256 * 256
+                offsets.append(row)
+            region, handle = C.c_void_p(), (C.c_uint8 * 64)()
+            assert lib.nvc_symm_alloc(dev._h, at, C.byref(region), handle) == 0, _ffi.last_error()
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle))
+            bases = (C.c_void_p * world)()
+            for r in range(world):
+                if r == rank:
+                    bases[r] = region.value
+                else:
+                    hb = (C.c_uint8 * 64).from_buffer_copy(handles[r])
+                    ptr = C.c_void_p()
+                    assert lib.nvc_symm_open(dev._h, hb, C.byref(ptr)) == 0, _ffi.last_error()
+                    bases[r] = ptr.value
+            group = C.c_void_p()
+            assert lib.nvc_peer_group_create(dev._h, rank, world, bases, C.byref(group)) == 0, _ffi.last_error()
+            fused = {"region": region, "group": group, "offsets": offsets, "bytes": at}
+        except Exception as e:  # no peer access on this box: the NCCL path still runs
+            fused = None
+            if rank == 0:
+                print(f"fused gather unavailable: {e}", file=sys.stderr)
+
+    def step_fused():
+        for projs, offs in zip(layers, fused["offsets"]):
+            for (name, N, K, n_local, q, x, y), off in zip(projs, offs):
+                rc = lib.nvc_quantized_matmul_gather(dev._h, fused["group"], C.byref(qc), x.ptr, q.weight.ptr, q.scales.ptr,
+                                                     q.biases.ptr, M, n_local, K, off)
+                assert rc == 0, _ffi.last_error()
+
     def step(gather=True):
         for projs in layers:
             for name, N, K, n_local, q, x, y in projs:
@@ -319,6 +359,28 @@ def main():
     run = graph.launch if graph is not None else step
     for _ in range(args.warmup):
         run()
+    nccl_ms = None
+    fused_check = None
+    if fused is not None:
+        # The NCCL variant is timed first (it is also what the fused result is checked against).
+        nccl_ms, _ = timed(run, args.steps)
+        step_fused()
+        dev.synchronize()
+        # every rank's region must hold exactly what all_gather delivered
+        bad = 0
+        for projs, offs in zip(layers[-1:], fused["offsets"][-1:]):
+            for (name, N, K, n_local, q, x, y), off in zip(projs, offs):
+                got = np.empty((world, M, n_local), np.uint16)
+                assert lib.nvc_memcpy_d2h(dev._h, got.ctypes.data_as(C.c_void_p), C.c_void_p(fused["region"].value + off), got.nbytes) == 0
+                bad += int(np.count_nonzero(got != y.to_numpy().view(np.uint16).reshape(got.shape)))
+        import torch
+        t = torch.tensor([bad], device="cuda")
+        dist.all_reduce(t)
+        fused_check = "ok" if int(t.item()) == 0 else f"{int(t.item())} elements differ from the all_gather result"
+        graph_f = dev.record(step_fused) if not args.no_graph else None
+        run = graph_f.launch if graph_f is not None else step_fused
+        for _ in range(args.warmup):
+            run()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -350,7 +412,13 @@ def main():
             "roofline": roofline, "gpu_launches": launches, "clocks": clocks}
     if world > 1:
         line["kernel_only"] = {"value": step_bytes / (ms_kernel_only / args.steps * 1e-3) / 1e9, "unit": "GB/s",
-                               "note": "same step without the all_gather after each product"}
+                               "note": "same step without any gather after the products"}
+        if fused is not None:
+            line["config"]["parallelism"] = (f"N-sharded x{world}; every product stores its slice into all ranks' gathered "
+                                             "buffers (NVLink peer stores) and flags completion: no collective call")
+            line["fused_gather_check"] = fused_check
+            line["nccl_gather"] = {"value": step_bytes / (nccl_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                                   "note": "same step with ncclAllGather after each product instead of the fused stores"}
 
     # ── end to end through the host-operand entry point (rank-local x in, y out) ─────────────
     if not args.no_e2e:

@@ -253,6 +253,40 @@ int32_t nvc_comm_health(nvc_comm *comm);
 int32_t nvc_comm_abort(nvc_comm *comm);
 int32_t nvc_comm_destroy(nvc_comm *comm);
 
+/* ── the sharded product fused with its gather ─────────────────────────────────────────────
+ *
+ * Replaces the pair "quantized_matmul on this rank's rows of W, then Communicator::all_gather"
+ * (crates/nuvec-core/src/distributed.rs:52, 695-700) for few-row products: the kernel stores
+ * its [M, N_local] slice straight into slot `rank` of every rank's gathered buffer over NVLink
+ * peer stores, and when the last block of the kernel is done it raises this rank's flag in every
+ * rank's flag array.  The next product of the group waits on the device for all flags of the
+ * previous one before it reads its activations.  No collective library is involved.
+ *
+ * Set-up, once: every rank allocates a symmetric region (nvc_symm_alloc), the caller's bootstrap
+ * carries the 64-byte handles to the other ranks, every rank opens the others' regions
+ * (nvc_symm_open) and builds a group from the table of base addresses (its own included, at
+ * index `rank`).  A region starts zeroed; its first 4 KiB belong to the group (flags, sequence
+ * counter), the caller's buffers live behind NVC_SYMM_RESERVED. */
+#define NVC_SYMM_RESERVED 4096
+typedef struct { uint8_t bytes[64]; } nvc_ipc_handle;
+typedef struct nvc_peer_group nvc_peer_group; /* opaque: the ranks' region addresses on this device */
+
+int32_t nvc_symm_alloc(nvc_device *dev, size_t bytes, void **out_ptr, nvc_ipc_handle *out_handle);
+int32_t nvc_symm_open(nvc_device *dev, const nvc_ipc_handle *handle, void **out_peer_ptr);
+int32_t nvc_symm_close(nvc_device *dev, void *peer_ptr);
+int32_t nvc_symm_free(nvc_device *dev, void *ptr);
+int32_t nvc_peer_group_create(nvc_device *dev, int32_t rank, int32_t size, void *const *region_bases,
+                              nvc_peer_group **out);
+int32_t nvc_peer_group_destroy(nvc_peer_group *group);
+/* y of rank r lands at byte offset out_offset + r * M * N_local * 2 of every rank's region
+ * (out_offset >= NVC_SYMM_RESERVED, the same on all ranks): the [size, M, N_local] layout of
+ * all_gather.  Operands as nvc_quantized_matmul_noalloc (bfloat16, affine 2/4/8 bits, M <= 8).
+ * Every rank of the group must issue the same sequence of these calls.  A wait that gives up
+ * (about a second) sets the device's error word: nvc_synchronize reports it. */
+int32_t nvc_quantized_matmul_gather(nvc_device *dev, nvc_peer_group *group, const nvc_quant *q, const void *x,
+                                    const uint32_t *w, const void *scales, const void *biases, int64_t M,
+                                    int64_t N_local, int64_t K, size_t out_offset);
+
 #ifdef __cplusplus
 }
 #endif

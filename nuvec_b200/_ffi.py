@@ -33,6 +33,7 @@ class MemStats(C.Structure):
 
 P, I32T, I64T, SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
 QP = C.POINTER(Quant)
+PP = C.POINTER(C.c_void_p)
 
 # name -> (restype, argtypes); every symbol include/nuvec_cuda.h declares.
 SIGNATURES = {
@@ -85,6 +86,13 @@ SIGNATURES = {
     "nvc_comm_health": (I32T, [P]),
     "nvc_comm_abort": (I32T, [P]),
     "nvc_comm_destroy": (I32T, [P]),
+    "nvc_symm_alloc": (I32T, [P, SZ, PP, P]),
+    "nvc_symm_open": (I32T, [P, P, PP]),
+    "nvc_symm_close": (I32T, [P, P]),
+    "nvc_symm_free": (I32T, [P, P]),
+    "nvc_peer_group_create": (I32T, [P, I32T, I32T, PP, PP]),
+    "nvc_peer_group_destroy": (I32T, [P]),
+    "nvc_quantized_matmul_gather": (I32T, [P, P, QP, P, P, P, P, I64T, I64T, I64T, SZ]),
 }
 
 _lib = None

@@ -104,6 +104,7 @@ int32_t ensure_scratch(nvc_device *dev, size_t bytes, void **out);
 int32_t ensure_counters(nvc_device *dev, size_t count, uint32_t **out);
 int32_t check_quant(const char *op, const nvc_quant *q);
 int32_t check_launch(nvc_device *dev, const char *kernel);
+int32_t ensure_error_word(nvc_device *dev);  // the host-mapped word kernels report a bounded wait's failure in
 
 inline size_t dtype_size(int32_t dtype) { return dtype == NVC_F32 ? 4 : 2; }
 inline bool is_float_dtype(int32_t d) { return d == NVC_F32 || d == NVC_F16 || d == NVC_BF16; }

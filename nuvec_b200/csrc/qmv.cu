@@ -448,6 +448,29 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
 #pragma unroll
     for (int st = 0; st < QMV_STAGES; st++) prefetch(st);
     asm volatile("griddepcontrol.wait;" ::: "memory");  // activations, scratch and output belong to this kernel from here
+    // Fused gather: before the activations are read, every rank must have finished the previous
+    // fused product (its slice of that product's output may be what is read here).  Rank r has
+    // finished `n` products when flag r in this rank's region holds n; this rank's own count is
+    // at byte 64.  The wait is bounded; when it gives up the error word says so and the kernel
+    // goes on with what it has.
+    uint32_t peer_seq = 0;
+    if (p.peer) {
+        const uint32_t *own = static_cast<const uint32_t *>(p.peer->base[p.peer->rank]);
+        peer_seq = __ldcg(own + 16);
+        if (tid == 0) {
+            for (int rk = 0; rk < p.peer->size; rk++) {
+                uint32_t spins = 0, seen;
+                do {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own + rk) : "memory");
+                    if (seen >= peer_seq) break;
+                    __nanosleep(64);
+                } while (++spins < (1u << 22));
+                if (seen < peer_seq && p.error) *p.error = 2;
+            }
+        }
+        // (the barrier that follows the staging of the activations publishes the wait to the block)
+        __syncthreads();
+    }
 
     // ── stage the activations once per block (the first weight copies are already in flight) ──
     {
@@ -653,15 +676,45 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 store = true;
             }
         }
-        if (store) {
+        if (store && !p.peer) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int row = n0 + r + (i >> 1) * 8, col = 2 * t + (i & 1);
                 if (col < p.M && row <= last_row) out[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
             }
+        } else if (store) {
+            // the same values into slot `rank` of every rank's gathered buffer (peer stores over NVLink)
+            for (int rk = 0; rk < p.peer->size; rk++) {
+                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(p.peer->base[rk]) + p.peer_out_offset) +
+                                     (int64_t)p.peer->rank * p.M * p.N;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int row = n0 + r + (i >> 1) * 8, col = 2 * t + (i & 1);
+                    if (col < p.M && row <= last_row) dst[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
+                }
+            }
         }
     }
     cp_async_wait<0>();
+    if (p.peer) {
+        // Every thread's peer stores are made visible system-wide; the block that finishes last
+        // raises this rank's flag in every region and advances this rank's count.
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t *own = static_cast<uint32_t *>(p.peer->base[p.peer->rank]);
+            const uint32_t done = atomicAdd(own + 17, 1u);
+            if (done == gridDim.x * gridDim.z - 1) {
+                __threadfence_system();
+                own[17] = 0u;
+                for (int rk = 0; rk < p.peer->size; rk++) {
+                    uint32_t *flag = static_cast<uint32_t *>(p.peer->base[rk]) + p.peer->rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(peer_seq + 1u) : "memory");
+                }
+                __stcg(own + 16, peer_seq + 1u);
+            }
+        }
+    }
 }
 
 // ── host side ──────────────────────────────────────────────────────────────────────────

@@ -4,6 +4,14 @@
 
 namespace nvc {
 
+// The ranks' symmetric regions as seen from this device (device memory, read by the kernel).
+// Region layout, first bytes: uint32 flags[16] (flag r is raised by rank r), at 64 the count of
+// fused products this rank has finished, at 68 the blocks of the running kernel that are done.
+struct PeerTable {
+    void *base[16];
+    int32_t rank, size;
+};
+
 // Any product the fast kernels do not take.
 struct GenericParams {
     int32_t mode, gs, bits, dtype, transpose;
@@ -32,6 +40,10 @@ struct QmvParams {
     int64_t x_batch_stride, w_batch_stride, s_batch_stride;
     int32_t M, gs, gs_shift, chunk_k, max_parts, x_vec, s_vec;
     uint32_t blk_q, blk_r;  // iterations per block: blk_q, one more in the first blk_r blocks
+    // Fused gather (nullptr: plain product).  The result goes to every rank's region instead of y.
+    const struct PeerTable *peer;
+    uint64_t peer_out_offset;  // byte offset of the [size, M, N] gathered buffer inside a region
+    int32_t *error;            // host-visible word: 2 when the wait for the peers' flags gave up
 };
 // Returns NVC_ERR_UNSUPPORTED (without setting an error message) when the shape is not one
 // the fast kernel takes; the caller then uses the generic kernel.

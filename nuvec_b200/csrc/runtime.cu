@@ -41,6 +41,15 @@ int32_t check_launch(nvc_device *dev, const char *kernel) {
     return NVC_OK;
 }
 
+int32_t ensure_error_word(nvc_device *dev) {
+    if (!dev->error_word) {
+        NVC_CUDA(cudaHostAlloc((void **)&dev->error_word, sizeof(int32_t), cudaHostAllocMapped));
+        *dev->error_word = 0;
+        NVC_CUDA(cudaHostGetDevicePointer((void **)&dev->error_word_dev, dev->error_word, 0));
+    }
+    return NVC_OK;
+}
+
 int32_t check_quant(const char *op, const nvc_quant *q) {
     if (!q) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: null quantization", op);
     int gs = q->group_size, bits = q->bits;
@@ -275,7 +284,7 @@ int32_t nvc_synchronize(nvc_device *dev) {
     NVC_CUDA(cudaStreamSynchronize(dev->stream));
     if (dev->error_word && *dev->error_word != 0) {
         *dev->error_word = 0;
-        return set_error(NVC_ERR_DRIVER, "a kernel gave up waiting on its pipeline (bounded wait expired); results of the last work are invalid");
+        return set_error(NVC_ERR_DRIVER, "a kernel gave up waiting (on its pipeline, or on the other ranks of a fused gather); results of the last work are invalid");
     }
     return NVC_OK;
 }

@@ -1,0 +1,70 @@
+"""The product fused with its gather (nvc_quantized_matmul_gather), on one GPU: a peer group of a
+single rank exercises the kernel's whole protocol -- the wait on the flags of the previous
+product, the stores into the gathered buffer of the region, the flag and the sequence count --
+against the plain product.  The multi-rank case needs one process per GPU and is what
+`bench.py --gpus N` checks against ncclAllGather (`fused_gather_check`)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_single_rank_group_matches_the_plain_product():
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+    lib = _ffi.lib()
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(3)
+    quant = nv.Quant.affine(64, 4)
+    qc = quant._c()
+    shapes = [(1, 6144, 4096), (4, 1024, 2048), (8, 4096, 4096), (1, 40, 2880 // 64 * 64)]
+    RES = 4096
+    offsets, at = [], RES
+    for M, N, K in shapes:
+        offsets.append(at)
+        at += (M * N * 2 + 255) // 256 * 256
+    region, handle = C.c_void_p(), (C.c_uint8 * 64)()
+    assert lib.nvc_symm_alloc(dev._h, at, C.byref(region), handle) == 0, _ffi.last_error()
+    bases = (C.c_void_p * 1)(region.value)
+    group = C.c_void_p()
+    assert lib.nvc_peer_group_create(dev._h, 0, 1, bases, C.byref(group)) == 0, _ffi.last_error()
+    try:
+        cases = []
+        for M, N, K in shapes:
+            w = oracle.from_f32((rng.standard_normal((N, K)) * 0.02).astype(np.float32), oracle.BF16)
+            q = nv.quantize(dev.array(w, nv.BF16), quant)
+            x = dev.array(oracle.from_f32(rng.standard_normal((M, K)).astype(np.float32), oracle.BF16), nv.BF16)
+            cases.append((M, N, K, q, x, nv.quantized_matmul(x, q).to_numpy()))
+        for rounds in range(3):  # the sequence count and the flags advance from call to call
+            for (M, N, K, q, x, want), off in zip(cases, offsets):
+                rc = lib.nvc_quantized_matmul_gather(dev._h, group, C.byref(qc), x.ptr, q.weight.ptr, q.scales.ptr,
+                                                     q.biases.ptr, M, N, K, off)
+                assert rc == 0, _ffi.last_error()
+            dev.synchronize()
+            for (M, N, K, q, x, want), off in zip(cases, offsets):
+                got = np.empty((M, N), np.uint16)
+                assert lib.nvc_memcpy_d2h(dev._h, got.ctypes.data_as(C.c_void_p), C.c_void_p(region.value + off), got.nbytes) == 0
+                assert np.array_equal(got, want.view(np.uint16).reshape(M, N))
+        head = np.empty(18, np.uint32)
+        assert lib.nvc_memcpy_d2h(dev._h, head.ctypes.data_as(C.c_void_p), region, head.nbytes) == 0
+        assert head[0] == 3 * len(shapes) and head[16] == 3 * len(shapes) and head[17] == 0
+    finally:
+        lib.nvc_peer_group_destroy(group)
+        lib.nvc_symm_free(dev._h, region)
+
+
+def test_gather_arguments_are_checked():
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+    lib = _ffi.lib()
+    dev = nv.Device.shared(0)
+    region, handle = C.c_void_p(), (C.c_uint8 * 64)()
+    assert lib.nvc_symm_alloc(dev._h, 100, C.byref(region), handle) == _ffi.ERR_INVALID_ARGUMENT
+    bases = (C.c_void_p * 1)(None)
+    group = C.c_void_p()
+    assert lib.nvc_peer_group_create(dev._h, 0, 1, bases, C.byref(group)) == _ffi.ERR_INVALID_ARGUMENT
+    assert lib.nvc_peer_group_create(dev._h, 2, 2, bases, C.byref(group)) == _ffi.ERR_INVALID_ARGUMENT
