@@ -305,7 +305,7 @@ constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 //                                         (chunk, lane) so that a quarter-warp reads 128
 //                                         consecutive bytes
 //   lpart [QMV_WARPS][2][128] f32         partial sums of tiles cut between warps of this block
-//   lcount[QMV_WARPS] u32                 their arrival counters
+//   lcount[QMV_WARPS + 4] u32             their arrival counters; word QMV_WARPS: "this block finished last" (fused gather)
 template <int BITS, int WPL>
 __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
@@ -448,30 +448,6 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
 #pragma unroll
     for (int st = 0; st < QMV_STAGES; st++) prefetch(st);
     asm volatile("griddepcontrol.wait;" ::: "memory");  // activations, scratch and output belong to this kernel from here
-    // Fused gather: before the activations are read, every rank must have finished the previous
-    // fused product (its slice of that product's output may be what is read here).  Rank r has
-    // finished `n` products when flag r in this rank's region holds n; this rank's own count is
-    // at byte 64.  The wait is bounded; when it gives up the error word says so and the kernel
-    // goes on with what it has.
-    uint32_t peer_seq = 0;
-    if (p.peer) {
-        const uint32_t *own = static_cast<const uint32_t *>(p.peer->base[p.peer->rank]);
-        peer_seq = __ldcg(own + 16);
-        if (tid == 0) {
-            for (int rk = 0; rk < p.peer->size; rk++) {
-                uint32_t spins = 0, seen;
-                do {
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own + rk) : "memory");
-                    if (seen >= peer_seq) break;
-                    __nanosleep(64);
-                } while (++spins < (1u << 22));
-                if (seen < peer_seq && p.error) *p.error = 2;
-            }
-        }
-        // (the barrier that follows the staging of the activations publishes the wait to the block)
-        __syncthreads();
-    }
-
     // ── stage the activations once per block (the first weight copies are already in flight) ──
     {
         const uint16_t *x = (const uint16_t *)p.x + xb * p.x_batch_stride;
@@ -683,35 +659,68 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 if (col < p.M && row <= last_row) out[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
             }
         } else if (store) {
-            // the same values into slot `rank` of every rank's gathered buffer (peer stores over NVLink)
-            for (int rk = 0; rk < p.peer->size; rk++) {
-                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(p.peer->base[rk]) + p.peer_out_offset) +
-                                     (int64_t)p.peer->rank * p.M * p.N;
+            // fused gather: into slot `rank` of this rank's own gathered buffer; the block that
+            // finishes last sends the whole slice to the other ranks (end of the kernel)
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(p.peer->base[p.peer->rank]) + p.peer_out_offset) +
+                                 (int64_t)p.peer->rank * p.M * p.N;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int row = n0 + r + (i >> 1) * 8, col = 2 * t + (i & 1);
-                    if (col < p.M && row <= last_row) dst[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
-                }
+            for (int i = 0; i < 4; i++) {
+                const int row = n0 + r + (i >> 1) * 8, col = 2 * t + (i & 1);
+                if (col < p.M && row <= last_row) dst[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
             }
         }
     }
     cp_async_wait<0>();
     if (p.peer) {
-        // Every thread's peer stores are made visible system-wide; the block that finishes last
-        // raises this rank's flag in every region and advances this rank's count.
-        __threadfence_system();
+        // The block that finishes last copies this rank's slice from its own gathered buffer into
+        // every other rank's (16-byte peer stores over NVLink by all its threads), makes them
+        // visible system-wide, raises this rank's flag in every region, and then waits until every
+        // rank's flag in its own region shows the same product finished: when this kernel ends, the
+        // gathered buffer is complete on this rank, and the next kernel of the stream needs no
+        // wait of its own.  Rank r has finished n fused products when flag r holds n; this rank's
+        // own count is at byte 64.  (Fences by thread 0 after a block barrier cover the whole
+        // block's stores: the barrier orders them before the fence, and a fence is cumulative.)
+        // The wait is bounded; when it gives up the error word says so.
         __syncthreads();
+        uint32_t *own = static_cast<uint32_t *>(p.peer->base[p.peer->rank]);
         if (tid == 0) {
-            uint32_t *own = static_cast<uint32_t *>(p.peer->base[p.peer->rank]);
-            const uint32_t done = atomicAdd(own + 17, 1u);
-            if (done == gridDim.x * gridDim.z - 1) {
+            __threadfence();
+            lcount[QMV_WARPS] = atomicAdd(own + 17, 1u) == gridDim.x * gridDim.z - 1 ? 1u : 0u;
+            __threadfence();
+        }
+        __syncthreads();
+        if (lcount[QMV_WARPS]) {
+            const size_t slice = (size_t)p.M * p.N * 2, at = p.peer_out_offset + (size_t)p.peer->rank * slice;
+            const char *src = static_cast<const char *>(p.peer->base[p.peer->rank]) + at;
+            for (int rk = 0; rk < p.peer->size; rk++) {
+                if (rk == p.peer->rank) continue;
+                char *dst = static_cast<char *>(p.peer->base[rk]) + at;
+                if (slice % 16 == 0 && at % 16 == 0) {
+                    for (size_t i = (size_t)tid * 16; i < slice; i += (size_t)QMV_THREADS * 16)
+                        *reinterpret_cast<uint4 *>(dst + i) = __ldcg(reinterpret_cast<const uint4 *>(src + i));
+                } else {
+                    for (size_t i = (size_t)tid * 2; i < slice; i += (size_t)QMV_THREADS * 2)
+                        *reinterpret_cast<uint16_t *>(dst + i) = __ldcg(reinterpret_cast<const uint16_t *>(src + i));
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                const uint32_t seq = __ldcg(own + 16) + 1u;
                 __threadfence_system();
                 own[17] = 0u;
                 for (int rk = 0; rk < p.peer->size; rk++) {
                     uint32_t *flag = static_cast<uint32_t *>(p.peer->base[rk]) + p.peer->rank;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(peer_seq + 1u) : "memory");
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
                 }
-                __stcg(own + 16, peer_seq + 1u);
+                __stcg(own + 16, seq);
+                for (int rk = 0; rk < p.peer->size; rk++) {
+                    uint32_t spins = 0, seen;
+                    do {
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own + rk) : "memory");
+                        if (seen >= seq) break;
+                    } while (++spins < (1u << 24));
+                    if (seen < seq && p.error) *p.error = 2;
+                }
             }
         }
     }
@@ -739,7 +748,7 @@ static int wpl_for(int bits, int gs, int64_t K) {
 static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
     const int codes = codes_per_word(bits), xw = bits == 4 ? 4 : bits == 8 ? 2 : 8;
     return (size_t)(M * (K / codes * xw + 16) + 64 + QMV_WARPS * (2 * 16 * QMV_SPITCH) +
-                    qmv_stages(wpl) * 2 * QMV_THREADS * wpl + QMV_WARPS * 2 * 128 + QMV_WARPS) * 4 + 16;
+                    qmv_stages(wpl) * 2 * QMV_THREADS * wpl + QMV_WARPS * 2 * 128 + QMV_WARPS + 4) * 4 + 16;
 }
 
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
