@@ -692,35 +692,43 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         if (lcount[QMV_WARPS]) {
             const size_t slice = (size_t)p.M * p.N * 2, at = p.peer_out_offset + (size_t)p.peer->rank * slice;
             const char *src = static_cast<const char *>(p.peer->base[p.peer->rank]) + at;
-            for (int rk = 0; rk < p.peer->size; rk++) {
-                if (rk == p.peer->rank) continue;
-                char *dst = static_cast<char *>(p.peer->base[rk]) + at;
-                if (slice % 16 == 0 && at % 16 == 0) {
-                    for (size_t i = (size_t)tid * 16; i < slice; i += (size_t)QMV_THREADS * 16)
-                        *reinterpret_cast<uint4 *>(dst + i) = __ldcg(reinterpret_cast<const uint4 *>(src + i));
-                } else {
-                    for (size_t i = (size_t)tid * 2; i < slice; i += (size_t)QMV_THREADS * 2)
-                        *reinterpret_cast<uint16_t *>(dst + i) = __ldcg(reinterpret_cast<const uint16_t *>(src + i));
+            // each piece is read once and stored to every peer (the reads are L2 round trips)
+            if (slice % 16 == 0 && at % 16 == 0) {
+                for (size_t i = (size_t)tid * 16; i < slice; i += (size_t)QMV_THREADS * 16) {
+                    const uint4 piece = __ldcg(reinterpret_cast<const uint4 *>(src + i));
+                    for (int rk = 0; rk < p.peer->size; rk++)
+                        if (rk != p.peer->rank) *reinterpret_cast<uint4 *>(static_cast<char *>(p.peer->base[rk]) + at + i) = piece;
+                }
+            } else {
+                for (size_t i = (size_t)tid * 2; i < slice; i += (size_t)QMV_THREADS * 2) {
+                    const uint16_t piece = __ldcg(reinterpret_cast<const uint16_t *>(src + i));
+                    for (int rk = 0; rk < p.peer->size; rk++)
+                        if (rk != p.peer->rank) *reinterpret_cast<uint16_t *>(static_cast<char *>(p.peer->base[rk]) + at + i) = piece;
                 }
             }
             __syncthreads();
             if (tid == 0) {
                 const uint32_t seq = __ldcg(own + 16) + 1u;
-                __threadfence_system();
                 own[17] = 0u;
+                // one release fence for all flags (a releasing store per flag would fence each time)
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
                 for (int rk = 0; rk < p.peer->size; rk++) {
                     uint32_t *flag = static_cast<uint32_t *>(p.peer->base[rk]) + p.peer->rank;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
                 }
                 __stcg(own + 16, seq);
-                for (int rk = 0; rk < p.peer->size; rk++) {
-                    uint32_t spins = 0, seen;
-                    do {
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own + rk) : "memory");
-                        if (seen >= seq) break;
-                    } while (++spins < (1u << 24));
-                    if (seen < seq && p.error) *p.error = 2;
+                // all flags are polled together (relaxed loads that overlap), one fence acquires
+                bool all = false;
+                for (uint32_t spins = 0; spins < (1u << 24) && !all; spins++) {
+                    all = true;
+                    for (int rk = 0; rk < p.peer->size; rk++) {
+                        uint32_t seen;
+                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own + rk) : "memory");
+                        all = all && seen >= seq;
+                    }
                 }
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                if (!all && p.error) *p.error = 2;
             }
         }
     }
