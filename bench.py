@@ -568,6 +568,8 @@ def config_sweep(nv, _ffi, dev, peaks):
 
     a4 = nv.Quant.affine(GS, BITS)
     dense("C1 qmv", 1, 4096, 4096, a4, 64, 20)
+    for bits in (2, 3, 6, 8):  # 3- and 6-bit codes straddle words: generic kernel
+        dense(f"C1 qmv b{bits}", 1, 4096, 4096, nv.Quant.affine(GS, bits), 64, 10)
     for M in (1, 4, 8):
         for name, N, K in PROJECTIONS:
             dense(f"C2 {name}", M, N, K, a4, max(2, int(600e6 // (N * K // 2))), 20)
