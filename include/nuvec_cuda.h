@@ -220,7 +220,7 @@ int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q, int32_t d
  * from the handle's pool and may grow it; this one keeps that scratch in a 4 MiB array that is
  * part of the library image -- every GPU that loads the library holds it until the process
  * exits -- and calls no cudaMalloc, cudaFree or allocating routine.
- *   x: bfloat16 [M, K] dense, 1 <= M <= 8;  w: affine 2-, 4- or 8-bit, [N, K*bits/32], K a multiple
+ *   x: bfloat16 [M, K] dense, 1 <= M <= 8;  w: affine 2-, 3-, 4-, 6- or 8-bit, [N, K*bits/32], K a multiple
  *   of 32 values per vector-load step (any K the fast kernel of nvc_quantized_matmul takes);
  *   scales/biases bfloat16 [N, K/gs];  y: bfloat16 [M, N].  Results equal nvc_quantized_matmul's.
  * Limits: N <= 262144 and partial sums <= 4 MiB - 64 KiB, else NVC_ERR_UNSUPPORTED with the sizes
@@ -280,7 +280,7 @@ int32_t nvc_peer_group_create(nvc_device *dev, int32_t rank, int32_t size, void 
 int32_t nvc_peer_group_destroy(nvc_peer_group *group);
 /* y of rank r lands at byte offset out_offset + r * M * N_local * 2 of every rank's region
  * (out_offset >= NVC_SYMM_RESERVED, the same on all ranks): the [size, M, N_local] layout of
- * all_gather.  Operands as nvc_quantized_matmul_noalloc (bfloat16, affine 2/4/8 bits, M <= 8).
+ * all_gather.  Operands as nvc_quantized_matmul_noalloc (bfloat16, affine 2/3/4/6/8 bits, M <= 8).
  * Every rank of the group must issue the same sequence of these calls.  A wait that gives up
  * (about a second) sets the device's error word: nvc_synchronize reports it. */
 int32_t nvc_quantized_matmul_gather(nvc_device *dev, nvc_peer_group *group, const nvc_quant *q, const void *x,

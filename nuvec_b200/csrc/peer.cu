@@ -115,7 +115,7 @@ extern "C" int32_t nvc_quantized_matmul_gather(nvc_device *dev, nvc_peer_group *
     if (!x || !w || !scales) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul_gather: null operand");
     if (!qmv_affine_eligible(q->mode, q->group_size, q->bits, NVC_BF16, 1, M, N_local, K, x, K, 0, w, 0))
         return set_error(NVC_ERR_UNSUPPORTED,
-                         "quantized_matmul_gather: takes bfloat16 x with 1 to 8 rows and 2-, 4- or 8-bit weights whose rows are "
+                         "quantized_matmul_gather: takes bfloat16 x with 1 to 8 rows and 2-, 3-, 4-, 6- or 8-bit weights whose rows are "
                          "a whole number of iterations (got M = %lld, K = %lld, %d bits)", (long long)M, (long long)K, q->bits);
     NVC_TRY(ensure_error_word(dev));
     QmvParams p{};

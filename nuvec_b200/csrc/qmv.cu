@@ -209,10 +209,12 @@ __device__ __forceinline__ GroupConsts group_consts(uint2 sb) {
 // fma(128 + c, s, -128 s) is the single rounding of the exact product c * s.
 template <int BITS> struct Unpack;
 template <> struct Unpack<4> {
-    static constexpr int CODES = 8;   // codes per word
-    static constexpr int AREGS = 4;   // operand registers per word; MMAs per word = AREGS / 2
+    static constexpr int UW = 1;      // words per unit (the smallest run of words holding whole codes)
+    static constexpr int CODES = 8;   // codes per unit
+    static constexpr int AREGS = 4;   // operand registers per unit; MMAs per unit = AREGS / 2
     // register i = codes (i, i+4)
-    static __device__ __forceinline__ void run(uint32_t w, const GroupConsts &c, uint32_t (&r)[4]) {
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[4]) {
+        const uint32_t w = u[0];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             uint32_t m = lop3_and_or(w >> (4 * i), 0x000F000Fu, 0x43004300u);
@@ -229,11 +231,13 @@ template <> struct Unpack<4> {
     }
 };
 template <> struct Unpack<8> {
+    static constexpr int UW = 1;
     static constexpr int CODES = 4;
     static constexpr int AREGS = 2;
     // The byte is rebuilt from its nibbles, exactly: 16 * hi + lo <= 255 fits bfloat16.
     // register 0 = codes (0, 2), register 1 = codes (1, 3)
-    static __device__ __forceinline__ void run(uint32_t w, const GroupConsts &c, uint32_t (&r)[2]) {
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[2]) {
+        const uint32_t w = u[0];
         const uint32_t k16 = 0x41804180u, kn2048 = 0xC500C500u, kn128 = 0xC300C300u;
 #pragma unroll
         for (int i = 0; i < 2; i++) {
@@ -248,13 +252,80 @@ template <> struct Unpack<8> {
     }
 };
 template <> struct Unpack<2> {
+    static constexpr int UW = 1;
     static constexpr int CODES = 16;
     static constexpr int AREGS = 8;
     // register i = codes (i, i+8)
-    static __device__ __forceinline__ void run(uint32_t w, const GroupConsts &c, uint32_t (&r)[8]) {
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[8]) {
+        const uint32_t w = u[0];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             uint32_t m = lop3_and_or(w >> (2 * i), 0x00030003u, 0x43004300u);
+            r[i] = bf2_add(bf2_fma(m, c.s2, c.ns2), c.b2);
+        }
+    }
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            out[2 * i] = x[i];
+            out[2 * i + 1] = x[i + 8];
+        }
+    }
+};
+
+// 32 bits of a unit's bit stream starting at bit `pos` (a compile-time position once unrolled).
+__device__ __forceinline__ uint32_t window3(const uint32_t *u, int pos) {
+    const int idx = pos >> 5, sh = pos & 31;
+    if (sh == 0) return u[idx];
+    if (idx + 1 < 3) return __funnelshift_r(u[idx], u[idx + 1], sh);
+    return u[idx] >> sh;
+}
+// 3 bits: codes straddle words; the unit is 3 words = 32 codes at bit 3c.  Codes 6 apart are 18
+// bits apart, so one funnel shift brings code A to bits [2:0] and code A + 6 to bits [20:18] of
+// the same register: as bfloat16 mantissas these are 128 + a and 128 + 4 b, and
+// fma({128 + a, 128 + 4b}, {s, s/4}, {-128 s, -32 s}) is the single rounding of {a s, b s} (powers
+// of two scale exactly).  14 registers are such pairs -- (A, A + 6) for A = 0..5, 12..17, 24, 25 --
+// and the four codes left over, 26..29, make two pairs with one extraction per code.
+template <> struct Unpack<3> {
+    static constexpr int UW = 3;
+    static constexpr int CODES = 32;
+    static constexpr int AREGS = 16;
+    static __host__ __device__ constexpr int code_a(int i) { return i < 6 ? i : i < 12 ? i + 6 : i < 14 ? i + 12 : i == 14 ? 26 : 28; }
+    static __host__ __device__ constexpr int code_b(int i) { return i < 14 ? code_a(i) + 6 : code_a(i) + 1; }
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[16]) {
+        const uint32_t s4 = bf2_mul(c.s2, 0x3E803F80u);   // {s, s / 4}
+        const uint32_t ns4 = bf2_mul(s4, 0xC300C300u);    // {-128 s, -32 s}
+#pragma unroll
+        for (int i = 0; i < 14; i++) {
+            const uint32_t m = lop3_and_or(window3(u, 3 * code_a(i)), 0x001C0007u, 0x43004300u);
+            r[i] = bf2_add(bf2_fma(m, s4, ns4), c.b2);
+        }
+#pragma unroll
+        for (int i = 14; i < 16; i++) {
+            const uint32_t lo = lop3_and_or(window3(u, 3 * code_a(i)), 0x00000007u, 0x43004300u);
+            const uint32_t m = lop3_and_or(window3(u, 3 * code_b(i) - 16), 0x00070000u, lo);
+            r[i] = bf2_add(bf2_fma(m, c.s2, c.ns2), c.b2);
+        }
+    }
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            out[2 * i] = x[code_a(i)];
+            out[2 * i + 1] = x[code_b(i)];
+        }
+    }
+};
+// 6 bits: the unit is 3 words = 16 codes at bit 6c; codes up to 63 leave no room to scale the
+// upper one, so each code of a pair takes its own extraction.  register i = codes (i, i + 8).
+template <> struct Unpack<6> {
+    static constexpr int UW = 3;
+    static constexpr int CODES = 16;
+    static constexpr int AREGS = 8;
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[8]) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t lo = lop3_and_or(window3(u, 6 * i), 0x0000003Fu, 0x43004300u);
+            const uint32_t m = lop3_and_or(window3(u, 6 * (i + 8) - 16), 0x003F0000u, lo);
             r[i] = bf2_add(bf2_fma(m, c.s2, c.ns2), c.b2);
         }
     }
@@ -309,12 +380,14 @@ constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 template <int BITS, int WPL>
 __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
-    constexpr int CODES = U::CODES, AREGS = U::AREGS;
+    constexpr int CODES = U::CODES, AREGS = U::AREGS, UW = U::UW;
+    constexpr int LW = WPL * UW;               // words per lane, row half and iteration (WPL units of UW words)
     constexpr int IK = 4 * WPL * CODES;
-    constexpr int XW = AREGS;  // activation words per packed word (AREGS bf16 pairs)
+    constexpr int XW = AREGS;  // activation words per unit (AREGS bf16 pairs)
     constexpr int QMV_STAGES = qmv_stages(WPL);
-    constexpr int CPL = WPL == 8 ? 2 : 1;      // copies per lane and row half
-    constexpr int CW = WPL / CPL;              // words per copy
+    // copies per lane and row half: 3-word units are only 4-byte aligned and go word by word
+    constexpr int CPL = UW == 3 ? LW : WPL == 8 ? 2 : 1;
+    constexpr int CW = LW / CPL;               // words per copy
     extern __shared__ __align__(16) uint32_t smem[];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -340,11 +413,11 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     uint16_t *braw = sraw + 2 * 16 * QMV_SPITCH;
     uint32_t *ring = reinterpret_cast<uint32_t *>(reinterpret_cast<uint16_t *>(zero + 64) +
                                                   (size_t)QMV_WARPS * (4 * 16 * QMV_SPITCH)) +
-                     (size_t)warp * (QMV_STAGES * 2 * 32 * WPL);
+                     (size_t)warp * (QMV_STAGES * 2 * 32 * LW);
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * CW);
-    float *lpart = reinterpret_cast<float *>(ring + (size_t)(QMV_WARPS - warp) * (QMV_STAGES * 2 * 32 * WPL));
+    float *lpart = reinterpret_cast<float *>(ring + (size_t)(QMV_WARPS - warp) * (QMV_STAGES * 2 * 32 * LW));
     uint32_t *lcount = reinterpret_cast<uint32_t *>(lpart + QMV_WARPS * 2 * 128);
-    constexpr uint32_t HALF_BYTES = 32 * WPL * 4, STAGE_BYTES = 2 * HALF_BYTES;
+    constexpr uint32_t HALF_BYTES = 32 * LW * 4, STAGE_BYTES = 2 * HALF_BYTES;
 
     // ── this warp's run of iterations ───────────────────────────────────────────────────
     // Two levels: the blocks take consecutive runs of the sequence whose lengths differ by at most
@@ -372,7 +445,7 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         else w = i - l;
     };
 
-    const uint32_t *wbase = p.w + wb * p.w_batch_stride + t * WPL;
+    const uint32_t *wbase = p.w + wb * p.w_batch_stride + t * LW;
     const uint16_t *sc = (const uint16_t *)p.scales + wb * p.s_batch_stride;
     const uint16_t *bi = (const uint16_t *)p.biases + wb * p.s_batch_stride;
     __nv_bfloat16 *out = (__nv_bfloat16 *)p.y + b * p.M * p.N;
@@ -413,8 +486,8 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     const int pf_tile0 = pf_tile, pf_it0 = pf_it;  // where this run starts
     const uint32_t *pf_a = nullptr, *pf_q = nullptr;
     auto pf_rows = [&]() {
-        pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + pf_it * (4 * WPL);
-        pf_q = wbase + (size_t)min(pf_tile * 16 + r + 8, last_row) * row_words + pf_it * (4 * WPL);
+        pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + pf_it * (4 * LW);
+        pf_q = wbase + (size_t)min(pf_tile * 16 + r + 8, last_row) * row_words + pf_it * (4 * LW);
     };
     // Issues the copies of one iteration into `stage` and always commits one group, so the
     // group count seen by wait_group is the same for every lane and iteration.
@@ -425,8 +498,8 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 cp_async<CW * 4>(ring_s + stage * STAGE_BYTES + c * (32 * CW * 4), pf_a + c * CW);
                 cp_async<CW * 4>(ring_s + stage * STAGE_BYTES + HALF_BYTES + c * (32 * CW * 4), pf_q + c * CW);
             }
-            pf_a += 4 * WPL;
-            pf_q += 4 * WPL;
+            pf_a += 4 * LW;
+            pf_q += 4 * LW;
             pf++;
             if (++pf_it == ipt) {
                 pf_it = 0;
@@ -515,10 +588,16 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         const uint32_t *xp = xbase + (size_t)it0 * x_it_step;
         for (int it = it0; it < it1; it++) {
             cp_async_wait<QMV_STAGES - 1>();  // the oldest group, this iteration's words, has landed
-            uint32_t wa_[WPL], wq_[WPL];
+            uint32_t wa_[LW], wq_[LW];
             {
-                const uint32_t *slot = ring + (size_t)stage * (2 * 32 * WPL) + lane * CW;
-                if (WPL == 8) {
+                const uint32_t *slot = ring + (size_t)stage * (2 * 32 * LW) + lane * CW;
+                if (UW == 3) {
+#pragma unroll
+                    for (int c = 0; c < LW; c++) {
+                        wa_[c] = slot[c * 32];
+                        wq_[c] = slot[32 * LW + c * 32];
+                    }
+                } else if (WPL == 8) {
 #pragma unroll
                     for (int c = 0; c < 2; c++) {
                         uint4 a = *reinterpret_cast<const uint4 *>(slot + c * 128);
@@ -548,8 +627,8 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
 #pragma unroll
             for (int j = 0; j < WPL; j++) {
                 uint32_t ra[AREGS], rq[AREGS], xr[XW];
-                U::run(wa_[j], ga, ra);
-                U::run(wq_[j], gq, rq);
+                U::run(&wa_[j * UW], ga, ra);
+                U::run(&wq_[j * UW], gq, rq);
                 if (XW == 2) {
                     uint2 q = *reinterpret_cast<const uint2 *>(xp + j * 4 * XW);
                     xr[0] = q.x; xr[1] = q.y;
@@ -736,16 +815,18 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
 
 // ── host side ──────────────────────────────────────────────────────────────────────────
 
-static int codes_per_word(int bits) { return 32 / bits; }
+// A unit is the smallest run of words that holds whole codes: one word, or three for 3 and 6 bits.
+static int unit_words(int bits) { return bits == 3 || bits == 6 ? 3 : 1; }
+static int codes_per_word(int bits) { return unit_words(bits) * 32 / bits; }  // codes per unit
 
 // Words per lane per iteration: the widest vector load whose 4-lane span divides K.  Eight words
 // (two 16-byte copies) execute fewer instructions per weight but issue slower on the B200 than
 // four; they stay selectable with NUVEC_QMV_MAX_WPL=8.
 static int wpl_for(int bits, int gs, int64_t K) {
-    if (bits != 2 && bits != 4 && bits != 8) return 0;
+    if (bits != 2 && bits != 3 && bits != 4 && bits != 6 && bits != 8) return 0;
     const int codes = codes_per_word(bits);
     static const int cap = [] { const char *e = getenv("NUVEC_QMV_MAX_WPL"); return e && *e ? atoi(e) : 4; }();
-    for (int wpl = bits == 2 ? 2 : 8; wpl >= 1; wpl >>= 1) {
+    for (int wpl = bits == 3 ? 1 : bits == 2 || bits == 6 ? 2 : 8; wpl >= 1; wpl >>= 1) {
         if (wpl > cap) continue;
         if (wpl * codes > gs) continue;          // a lane's words stay inside one group
         if (K % (4 * wpl * codes) == 0) return wpl;
@@ -754,9 +835,9 @@ static int wpl_for(int bits, int gs, int64_t K) {
 }
 
 static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
-    const int codes = codes_per_word(bits), xw = bits == 4 ? 4 : bits == 8 ? 2 : 8;
+    const int codes = codes_per_word(bits), xw = codes / 2, lw = wpl * unit_words(bits);
     return (size_t)(M * (K / codes * xw + 16) + 64 + QMV_WARPS * (2 * 16 * QMV_SPITCH) +
-                    qmv_stages(wpl) * 2 * QMV_THREADS * wpl + QMV_WARPS * 2 * 128 + QMV_WARPS + 4) * 4 + 16;
+                    qmv_stages(wpl) * 2 * QMV_THREADS * lw + QMV_WARPS * 2 * 128 + QMV_WARPS + 4) * 4 + 16;
 }
 
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
@@ -768,7 +849,7 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
     int wpl = wpl_for(bits, gs, K);
     if (wpl == 0) return false;
     int64_t row_words = K * bits / 32;
-    const int cw = wpl == 8 ? 4 : wpl;  // words per asynchronous copy
+    const int cw = unit_words(bits) == 3 ? 1 : wpl == 8 ? 4 : wpl;  // words per asynchronous copy
     if (row_words % cw != 0 || w_batch_stride % cw != 0 || ((uintptr_t)w % (4 * cw)) != 0) return false;
     if (((N + 15) / 16) * (K / (4 * wpl * codes_per_word(bits))) >= (int64_t)1 << 30) return false;  // 32-bit iteration counts
     return qmv_smem((int)M, K, bits, wpl) <= 220 * 1024;  // all activations are staged in shared memory
@@ -882,7 +963,7 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
 #define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, grid, smem);
     NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(4, 8) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(8, 8)
-    NVC_QMV(2, 1) NVC_QMV(2, 2)
+    NVC_QMV(2, 1) NVC_QMV(2, 2) NVC_QMV(3, 1) NVC_QMV(6, 1) NVC_QMV(6, 2)
 #undef NVC_QMV
     return set_error(NVC_ERR_UNSUPPORTED, "qmv: no kernel for %d bits, group size %d", bits, p.gs);
 }
@@ -920,7 +1001,7 @@ extern "C" int32_t nvc_quantized_matmul_noalloc(nvc_device *dev, const nvc_quant
     if (!x || !w || !scales || !y) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul (no-alloc): null operand");
     if (!qmv_affine_eligible(q->mode, q->group_size, q->bits, NVC_BF16, 1, M, N, K, x, K, 0, w, 0))
         return set_error(NVC_ERR_UNSUPPORTED,
-                         "quantized_matmul (no-alloc): takes bfloat16 x with 1 to 8 rows and 2-, 4- or 8-bit weights whose "
+                         "quantized_matmul (no-alloc): takes bfloat16 x with 1 to 8 rows and 2-, 3-, 4-, 6- or 8-bit weights whose "
                          "rows are a whole number of 32-value iterations (got M = %lld, K = %lld, %d bits)",
                          (long long)M, (long long)K, q->bits);
     if (dev->ordinal < 0 || dev->ordinal >= NOALLOC_MAX_DEVICES)

@@ -115,21 +115,23 @@ def test_qmv_shapes_b4_g64(be, N, K, M):
     assert_product_tight(got, want, oracle.BF16, f"N{N} K{K} M{M}")
 
 
-def test_qmv_one_hot_rows_return_the_dequantized_weights(be):
+@pytest.mark.parametrize("bits,gs", [(4, 64), (2, 64), (3, 64), (6, 64), (8, 64), (3, 32), (6, 128)])
+def test_qmv_one_hot_rows_return_the_dequantized_weights(be, bits, gs):
     # x = unit vectors: y[m, n] is exactly dequantize(w)[n, k_m] rounded to bf16 -- a
-    # size-independent check that no k-slot is permuted or dropped in the fast kernel.
-    rng = np.random.default_rng(5)
+    # size-independent check that no k-slot is permuted or dropped in the fast kernel
+    # (3- and 6-bit codes straddle words and come out of funnel shifts).
+    rng = np.random.default_rng(5 + bits)
     N, K = 64, 512
     w = rand(rng, (N, K), oracle.BF16, 0.02)
-    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
-    dense = oracle.to_f32(oracle.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, 64, 4), oracle.BF16)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    dense = oracle.to_f32(oracle.dequantize(c, s, b, oracle.BF16, oracle.AFFINE, gs, bits), oracle.BF16)
     ks = rng.permutation(K)[:64]
     for k0 in range(0, 64, 8):
         x = np.zeros((8, K), np.float32)
         for i in range(8):
             x[i, ks[k0 + i]] = 1.0
         got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(x, oracle.BF16), c, s, b, oracle.BF16,
-                                                oracle.AFFINE, 64, 4, True), oracle.BF16)
+                                                oracle.AFFINE, gs, bits, True), oracle.BF16)
         want = dense[:, ks[k0:k0 + 8]].T
         assert np.array_equal(got, want)
 
