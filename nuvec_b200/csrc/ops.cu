@@ -122,6 +122,30 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
         }
         return NVC_OK;
     }
+    // Many rows of a bit width only the few-row kernel decodes fast (3 and 6 bits): eight rows at a
+    // time through it.  The weights are streamed once per eight rows (from L2 when they fit), which
+    // is far from the tensor-core kernel but two orders of magnitude ahead of the generic one.
+    if (M > 8 && qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, 8, N, K, x, ldx, 0, w, 0)) {
+        const size_t esz = dtype_size(dtype);
+        for (int64_t b = 0; b < batch; b++) {
+            for (int64_t r0 = 0; r0 < M; r0 += 8) {
+                const int64_t m = M - r0 < 8 ? M - r0 : 8;
+                QmvParams p{};
+                p.x = (const char *)x + (b * x_batch_stride + r0 * ldx) * esz;
+                p.w = w + b * w_batch_stride;
+                p.scales = (const char *)scales + b * s_batch_stride * esz;
+                p.biases = (const char *)biases + b * s_batch_stride * esz;
+                p.lhs = nullptr; p.rhs = nullptr;
+                p.y = (char *)y + (b * M + r0) * N * esz;
+                p.N = N; p.K = K; p.ldx = ldx;
+                p.x_batch_stride = 0; p.w_batch_stride = 0; p.s_batch_stride = 0;
+                p.M = (int32_t)m; p.gs = q->group_size;
+                p.x_vec = ((uintptr_t)p.x % 16 == 0) && (ldx % 8 == 0);
+                NVC_TRY(launch_qmv_affine(dev, q->bits, p, 1));
+            }
+        }
+        return NVC_OK;
+    }
     GenericParams g{};
     g.mode = q->mode; g.gs = q->group_size; g.bits = q->bits; g.dtype = dtype; g.transpose = transpose;
     g.scalar_global = global_scale != nullptr; g.expert_global = 0;

@@ -236,6 +236,21 @@ def test_pool_reuses_blocks_and_reports_stats(be):
     assert b.ptr.value == ptr and dev.memory()["allocations"] == mid["allocations"]
 
 
+@pytest.mark.parametrize("bits,gs", [(3, 64), (6, 32)])
+@pytest.mark.parametrize("M", [9, 20, 67])
+def test_many_rows_of_3_and_6_bit_weights_go_eight_at_a_time(be, bits, gs, M):
+    # no tensor-core decode for these widths: the few-row kernel takes the rows in blocks of eight
+    rng = np.random.default_rng(bits + M)
+    N, K = 200, 1024
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits)
+    got = be.quantized_matmul(x, c, s, b, oracle.BF16, oracle.AFFINE, gs, bits, True)
+    assert_product_close(got, want, oracle.BF16)
+    assert_product_tight(got, want, oracle.BF16)
+
+
 # ── many-row products on the tensor-core kernel ────────────────────────────────────────────
 @pytest.mark.parametrize("bits,gs", [(4, 64), (4, 32), (4, 128), (8, 64), (8, 32), (2, 64), (2, 128)])
 @pytest.mark.parametrize("M,N,K", [(17, 128, 64), (64, 200, 256), (200, 384, 512), (300, 136, 2880 // 45 * 45)])
