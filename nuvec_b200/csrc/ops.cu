@@ -36,8 +36,7 @@ static bool grouped(int64_t rows, int64_t experts) { return rows >= 16 && rows /
 // Rows from which a plain product goes to the tensor-core kernel.  Affine weights with up to 8
 // rows stream once through the few-row kernel when it takes the shape (it stages every activation
 // row in shared memory); everything else the tensor-core kernel is eligible for goes there, with
-// its smallest token tile for few rows: 9 to 16 rows, the 4-bit floating-point formats (which have
-// no few-row kernel) from the first row, and few-row affine products the few-row kernel refused.
+// its smallest token tile for few rows: 9 to 16 rows, and few-row products the few-row kernel refused.
 // NUVEC_QMM_MIN_ROWS raises the bar (products below it fall through to the generic kernel).
 static int64_t qmm_threshold() {
     static int64_t v = [] {
@@ -104,7 +103,8 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
         p.x_batch_stride = x_batch_stride; p.w_batch_stride = w_batch_stride; p.s_batch_stride = s_batch_stride;
         p.M = (int32_t)M; p.gs = q->group_size;
         p.x_vec = ((uintptr_t)x % 16 == 0) && (ldx % 8 == 0) && (x_batch_stride % 8 == 0);
-        return launch_qmv_affine(dev, q->bits, p, batch);
+        p.global = global_scale; p.expert_global = 0;
+        return launch_qmv_affine(dev, qmv_kind(q->mode, q->bits), p, batch);
     }
     if (M >= qmm_threshold() && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
         for (int64_t b = 0; b < batch; b++) {
@@ -125,7 +125,8 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
     // Many rows of a bit width only the few-row kernel decodes fast (3 and 6 bits): eight rows at a
     // time through it.  The weights are streamed once per eight rows (from L2 when they fit), which
     // is far from the tensor-core kernel but two orders of magnitude ahead of the generic one.
-    if (M > 8 && qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, 8, N, K, x, ldx, 0, w, 0)) {
+    if (M > 8 && q->mode == NVC_AFFINE &&
+        qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, 8, N, K, x, ldx, 0, w, 0)) {
         const size_t esz = dtype_size(dtype);
         for (int64_t b = 0; b < batch; b++) {
             for (int64_t r0 = 0; r0 < M; r0 += 8) {
@@ -174,9 +175,11 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
     const int64_t s_stride = (transpose ? N : K) * ((transpose ? K : N) / q->group_size);
     // Sorted rows of one expert multiplied together (the reference's grouped kernel).  The
     // reference's row-count rule chooses between two algorithms with the same result; here it
-    // chooses between the tensor-core kernel and the few-row kernel, and the 4-bit floating-point
-    // formats, which have no few-row kernel, take the tensor-core kernel whatever the count.
-    if (sorted && !lhs && M == 1 && (grouped(rows, experts) || q->mode != NVC_AFFINE) &&
+    // chooses between the tensor-core kernel and the few-row kernel, and shapes the few-row
+    // kernel does not take go to the tensor-core kernel whatever the count.
+    const bool few_rows_ok = M <= 8 && qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, K,
+                                                           M * K, w, w_stride);
+    if (sorted && !lhs && M == 1 && (grouped(rows, experts) || !few_rows_ok) &&
         qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, rows, N, K, x, K, w)) {
         const int32_t *offs = offsets;
         if (!offs) {
@@ -193,14 +196,14 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
         p.rows = rows; p.N = N; p.K = K; p.ldx = K; p.y = y;
         return launch_qmm(dev, p);
     }
-    if (M <= 8 && !global_scale &&
-        qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, K, M * K, w, w_stride)) {
+    if (few_rows_ok) {
         QmvParams p{};
         p.x = x; p.w = w; p.scales = scales; p.biases = biases; p.lhs = lhs; p.rhs = rhs; p.y = y;
         p.N = N; p.K = K; p.ldx = K;
         p.x_batch_stride = M * K; p.w_batch_stride = w_stride; p.s_batch_stride = s_stride;
         p.M = (int32_t)M; p.gs = q->group_size;
         p.x_vec = ((uintptr_t)x % 16 == 0) && (K % 8 == 0);
+        p.global = global_scale; p.expert_global = global_scale != nullptr;
         // Row batches beyond the grid limit go in slices.
         for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
             int64_t n = rows - r0 < 65535 ? rows - r0 : 65535;
@@ -209,7 +212,7 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
             s.rhs = rhs + r0;
             if (!lhs) s.x = (const char *)x + r0 * M * K * dtype_size(dtype);
             s.y = (char *)y + r0 * M * N * dtype_size(dtype);
-            NVC_TRY(launch_qmv_affine(dev, q->bits, s, n));
+            NVC_TRY(launch_qmv_affine(dev, qmv_kind(q->mode, q->bits), s, n));
         }
         return NVC_OK;
     }

@@ -209,6 +209,7 @@ __device__ __forceinline__ GroupConsts group_consts(uint2 sb) {
 // fma(128 + c, s, -128 s) is the single rounding of the exact product c * s.
 template <int BITS> struct Unpack;
 template <> struct Unpack<4> {
+    static constexpr int WBITS = 4, FP = 0;
     static constexpr int UW = 1;      // words per unit (the smallest run of words holding whole codes)
     static constexpr int CODES = 8;   // codes per unit
     static constexpr int AREGS = 4;   // operand registers per unit; MMAs per unit = AREGS / 2
@@ -231,6 +232,7 @@ template <> struct Unpack<4> {
     }
 };
 template <> struct Unpack<8> {
+    static constexpr int WBITS = 8, FP = 0;
     static constexpr int UW = 1;
     static constexpr int CODES = 4;
     static constexpr int AREGS = 2;
@@ -252,6 +254,7 @@ template <> struct Unpack<8> {
     }
 };
 template <> struct Unpack<2> {
+    static constexpr int WBITS = 2, FP = 0;
     static constexpr int UW = 1;
     static constexpr int CODES = 16;
     static constexpr int AREGS = 8;
@@ -287,6 +290,7 @@ __device__ __forceinline__ uint32_t window3(const uint32_t *u, int pos) {
 // of two scale exactly).  14 registers are such pairs -- (A, A + 6) for A = 0..5, 12..17, 24, 25 --
 // and the four codes left over, 26..29, make two pairs with one extraction per code.
 template <> struct Unpack<3> {
+    static constexpr int WBITS = 3, FP = 0;
     static constexpr int UW = 3;
     static constexpr int CODES = 32;
     static constexpr int AREGS = 16;
@@ -318,6 +322,7 @@ template <> struct Unpack<3> {
 // 6 bits: the unit is 3 words = 16 codes at bit 6c; codes up to 63 leave no room to scale the
 // upper one, so each code of a pair takes its own extraction.  register i = codes (i, i + 8).
 template <> struct Unpack<6> {
+    static constexpr int WBITS = 6, FP = 0;
     static constexpr int UW = 3;
     static constexpr int CODES = 16;
     static constexpr int AREGS = 8;
@@ -338,6 +343,42 @@ template <> struct Unpack<6> {
     }
 };
 
+// 4-bit floating point (E2M1 codes; kernel "bits" 40 = mxfp4: one E8M0 scale per 32 values,
+// 41 = nvfp4: one E4M3 scale per 16).  The code's three magnitude bits become exponent[1:0] and
+// mantissa[6] of a bfloat16 whose value is magnitude * 2^-126 (the subnormal codes 0 and 0.5
+// included); multiplying by 2^126 restores the value and multiplying by the scale (a power of
+// two, or an E4M3 number with 4 significant bits) is exact: at most 6 significant bits.  The
+// operand equals the reference's float32 decode (crates/nuvec-core/src/kernels.rs:976-1009).
+// register i = codes (i, i+4), as for 4-bit affine.  c.s2 holds the decoded scale pair.
+template <int KIND> struct UnpackFp4 {
+    static constexpr int WBITS = 4, FP = KIND;
+    static constexpr int UW = 1;
+    static constexpr int CODES = 8;
+    static constexpr int AREGS = 4;
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[4]) {
+        const uint32_t w = u[0];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            // magnitude bits [2:0] of both codes -> bits [8:6] of their halves; sign bit 3 -> bit 15
+            const uint32_t mag = 4 * i >= 6 ? (w >> (4 * i - 6)) : (w << (6 - 4 * i));
+            const uint32_t sgn = 4 * i >= 12 ? (w >> (4 * i - 12)) : (w << (12 - 4 * i));
+            const uint32_t bits = lop3_and_or(sgn, 0x80008000u, mag & 0x01C001C0u);
+            r[i] = bf2_mul(bf2_mul(bits, 0x7E807E80u), c.s2);
+        }
+    }
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) { Unpack<4>::permute(x, out); }
+};
+template <> struct Unpack<40> : UnpackFp4<1> {};
+template <> struct Unpack<41> : UnpackFp4<3> {};
+// bfloat16 pair {s, s} of a scale code: E8M0 (2^(code - 127); code 0 decodes to a float32 subnormal
+// that the reference flushes to zero) or E4M3 (subnormal results flushed likewise).
+__device__ __forceinline__ uint32_t fp4_scale2(uint32_t code, bool e8m0) {
+    uint32_t h;
+    if (e8m0) h = code == 0u ? 0u : (code << 7);
+    else h = __float_as_uint(ftz(e4m3_to_f32(code))) >> 16;
+    return (h & 0xFFFFu) * 0x10001u;
+}
+
 constexpr int QMV_WARPS = 8;
 constexpr int QMV_THREADS = QMV_WARPS * 32;
 // Resident blocks per multiprocessor the kernel is compiled for (128 registers per thread; three
@@ -351,6 +392,11 @@ constexpr int QMV_SEG_GROUPS = 16;
 // Row pitch (bfloat16 elements) of the staged scales: 48 bytes = 12 banks, a multiple of 16 bytes
 // (the widest copy); the 8 rows a warp reads together fall on different banks.
 constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
+// 4-bit floating point: up to 64 groups (bytes) of a row per k-chunk, rows 80 bytes apart (20 banks:
+// the 8 rows a warp reads together fall on different banks); 2 x 16 x 80 bytes fit the same area.
+constexpr int QMV_FP_SEG_GROUPS = 64;
+constexpr int QMV_FPITCH = 80;
+static_assert(2 * 16 * QMV_FPITCH <= 4 * 16 * QMV_SPITCH * 2, "the floating-point scale buffers fit the per-warp scale area");
 
 // The product is cut into iterations: iteration (tile, i) multiplies 16 weight rows ("tile") by
 // IK = 4 * WPL * CODES consecutive k-values.  All iterations of all tiles form one sequence, tile
@@ -399,7 +445,7 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         xb = p.lhs ? p.lhs[b] : b;
     }
     const int row_groups = (int)(p.K >> p.gs_shift);
-    const uint32_t row_words = (uint32_t)(p.K * BITS / 32);
+    const uint32_t row_words = (uint32_t)(p.K * U::WBITS / 32);
     const int ipt = (int)(p.K / IK);        // iterations per tile
     const int ci = p.chunk_k / IK;          // iterations per k-chunk (scales are staged per chunk)
     const int chunk_groups = p.chunk_k >> p.gs_shift;
@@ -449,10 +495,32 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     const uint16_t *sc = (const uint16_t *)p.scales + wb * p.s_batch_stride;
     const uint16_t *bi = (const uint16_t *)p.biases + wb * p.s_batch_stride;
     __nv_bfloat16 *out = (__nv_bfloat16 *)p.y + b * p.M * p.N;
+    // nvfp4 global scale: one value, or one per expert (quantized.rs:481-490, 700-712)
+    const float gmul = U::FP && p.global ? (p.expert_global ? p.global[wb] : p.global[0]) / (448.0f * 6.0f) : 1.0f;
 
     // Copies the scales and biases of k-chunk `chunk` of `tile` into buffer `buf` (whole warp).
     auto stage_scales = [&](int tile, int chunk, int buf) {
         const int sg0 = chunk * chunk_groups;
+        if (U::FP) {
+            // one scale byte per group, no biases: the two buffers share the whole per-warp area,
+            // 16 rows of QMV_FPITCH bytes each
+            const uint8_t *sc8 = (const uint8_t *)p.scales + wb * p.s_batch_stride;
+            uint8_t *fd = reinterpret_cast<uint8_t *>(sraw) + buf * (16 * QMV_FPITCH);
+            if (p.s_vec == 4) {
+                const int quads = chunk_groups >> 2;
+                for (int i = lane; i < 16 * quads; i += 32) {
+                    const int rr = i / quads, c = i - rr * quads;
+                    const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + 4 * c;
+                    cp_async<4>((uint32_t)__cvta_generic_to_shared(fd + rr * QMV_FPITCH + 4 * c), sc8 + at);
+                }
+            } else {
+                for (int i = lane; i < 16 * chunk_groups; i += 32) {
+                    const int rr = i / chunk_groups, c = i - rr * chunk_groups;
+                    fd[rr * QMV_FPITCH + c] = sc8[(int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + c];
+                }
+            }
+            return;
+        }
         uint16_t *sd = sraw + buf * 16 * QMV_SPITCH, *bd = braw + buf * 16 * QMV_SPITCH;
         if (p.s_vec == 16) {  // 16-byte copies of 8 groups
             const int chunks = chunk_groups >> 3;
@@ -569,7 +637,8 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         const int chunk = it0 / ci;
         const int it1 = (int)min((uint32_t)((chunk + 1) * ci), hi - f + (uint32_t)it0);
         const uint32_t f1 = f + (uint32_t)(it1 - it0);
-        const uint16_t *sd = sraw + (seg_count & 1) * 16 * QMV_SPITCH, *bd = braw + (seg_count & 1) * 16 * QMV_SPITCH;
+        const int seg_buf = seg_count & 1;
+        const uint16_t *sd = sraw + seg_buf * 16 * QMV_SPITCH, *bd = braw + seg_buf * 16 * QMV_SPITCH;
         // wait_group in the loop below covers a copy once QMV_STAGES groups were committed after it;
         // a shorter previous segment (or the very first one) needs an explicit wait.  Then the
         // copies of all lanes are made visible across the warp, and the next segment's scales
@@ -619,16 +688,30 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 }
             }
             const int g = (gofs + (it - it0) * IK) >> p.gs_shift;
-            GroupConsts ga, gq;
-            ga.s2 = (uint32_t)sa[g] * 0x10001u; ga.b2 = (uint32_t)ba[g] * 0x10001u;
-            gq.s2 = (uint32_t)sq[g] * 0x10001u; gq.b2 = (uint32_t)bq[g] * 0x10001u;
-            ga.ns2 = bf2_mul(ga.s2, 0xC300C300u);  // -128 s, exact
-            gq.ns2 = bf2_mul(gq.s2, 0xC300C300u);
+            GroupConsts ga, gq, ga1, gq1;  // (ga1, gq1: the second group of a lane's words, nvfp4 only)
+            if (U::FP) {
+                const uint8_t *fa = reinterpret_cast<const uint8_t *>(sraw) + seg_buf * (16 * QMV_FPITCH) + r * QMV_FPITCH;
+                const uint8_t *fq = fa + 8 * QMV_FPITCH;
+                ga.s2 = fp4_scale2(fa[g], U::FP == 1); gq.s2 = fp4_scale2(fq[g], U::FP == 1);
+                ga.b2 = gq.b2 = ga.ns2 = gq.ns2 = 0u;
+                ga1 = ga; gq1 = gq;
+                if (U::FP == 3 && WPL * CODES > 16) {
+                    ga1.s2 = fp4_scale2(fa[g + 1], false);
+                    gq1.s2 = fp4_scale2(fq[g + 1], false);
+                }
+            } else {
+                ga.s2 = (uint32_t)sa[g] * 0x10001u; ga.b2 = (uint32_t)ba[g] * 0x10001u;
+                gq.s2 = (uint32_t)sq[g] * 0x10001u; gq.b2 = (uint32_t)bq[g] * 0x10001u;
+                ga.ns2 = bf2_mul(ga.s2, 0xC300C300u);  // -128 s, exact
+                gq.ns2 = bf2_mul(gq.s2, 0xC300C300u);
+                ga1 = ga; gq1 = gq;
+            }
 #pragma unroll
             for (int j = 0; j < WPL; j++) {
                 uint32_t ra[AREGS], rq[AREGS], xr[XW];
-                U::run(&wa_[j * UW], ga, ra);
-                U::run(&wq_[j * UW], gq, rq);
+                const bool second = U::FP == 3 && j * CODES >= 16;  // nvfp4: 16 values per scale
+                U::run(&wa_[j * UW], second ? ga1 : ga, ra);
+                U::run(&wq_[j * UW], second ? gq1 : gq, rq);
                 if (XW == 2) {
                     uint2 q = *reinterpret_cast<const uint2 *>(xp + j * 4 * XW);
                     xr[0] = q.x; xr[1] = q.y;
@@ -731,6 +814,10 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 store = true;
             }
         }
+        if (store && U::FP) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] *= gmul;
+        }
         if (store && !p.peer) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -816,19 +903,29 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
 // ── host side ──────────────────────────────────────────────────────────────────────────
 
 // A unit is the smallest run of words that holds whole codes: one word, or three for 3 and 6 bits.
+// (`bits` below is the kernel's kind: the affine bit width, or 40 = mxfp4, 41 = nvfp4.)
+static bool kind_fp(int bits) { return bits == 40 || bits == 41; }
+static int code_bits(int bits) { return kind_fp(bits) ? 4 : bits; }
 static int unit_words(int bits) { return bits == 3 || bits == 6 ? 3 : 1; }
-static int codes_per_word(int bits) { return unit_words(bits) * 32 / bits; }  // codes per unit
+static int codes_per_word(int bits) { return unit_words(bits) * 32 / code_bits(bits); }  // codes per unit
+int qmv_kind(int32_t mode, int32_t bits) {
+    if (mode == NVC_AFFINE) return bits;
+    if (mode == NVC_MXFP4 && bits == 4) return 40;
+    if (mode == NVC_NVFP4 && bits == 4) return 41;
+    return 0;
+}
 
 // Words per lane per iteration: the widest vector load whose 4-lane span divides K.  Eight words
 // (two 16-byte copies) execute fewer instructions per weight but issue slower on the B200 than
 // four; they stay selectable with NUVEC_QMV_MAX_WPL=8.
 static int wpl_for(int bits, int gs, int64_t K) {
-    if (bits != 2 && bits != 3 && bits != 4 && bits != 6 && bits != 8) return 0;
+    if (bits != 2 && bits != 3 && bits != 4 && bits != 6 && bits != 8 && !kind_fp(bits)) return 0;
     const int codes = codes_per_word(bits);
     static const int cap = [] { const char *e = getenv("NUVEC_QMV_MAX_WPL"); return e && *e ? atoi(e) : 4; }();
-    for (int wpl = bits == 3 ? 1 : bits == 2 || bits == 6 ? 2 : 8; wpl >= 1; wpl >>= 1) {
+    const int span = bits == 41 ? 2 * gs : gs;   // nvfp4 lanes may hold two groups of 16
+    for (int wpl = bits == 3 ? 1 : bits == 2 || bits == 6 ? 2 : kind_fp(bits) ? 4 : 8; wpl >= 1; wpl >>= 1) {
         if (wpl > cap) continue;
-        if (wpl * codes > gs) continue;          // a lane's words stay inside one group
+        if (wpl * codes > span) continue;        // a lane's words stay inside one group
         if (K % (4 * wpl * codes) == 0) return wpl;
     }
     return 0;
@@ -844,11 +941,13 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
                          int64_t N, int64_t K, const void *x, int64_t ldx, int64_t x_batch_stride, const uint32_t *w,
                          int64_t w_batch_stride) {
     (void)x; (void)ldx; (void)x_batch_stride;
-    if (mode != NVC_AFFINE || dtype != NVC_BF16 || !transpose) return false;
+    if (dtype != NVC_BF16 || !transpose) return false;
+    bits = qmv_kind(mode, bits);
+    if (bits == 0) return false;
     if (M < 1 || M > 8 || N < 1 || K < gs) return false;
     int wpl = wpl_for(bits, gs, K);
     if (wpl == 0) return false;
-    int64_t row_words = K * bits / 32;
+    int64_t row_words = K * code_bits(bits) / 32;
     const int cw = unit_words(bits) == 3 ? 1 : wpl == 8 ? 4 : wpl;  // words per asynchronous copy
     if (row_words % cw != 0 || w_batch_stride % cw != 0 || ((uintptr_t)w % (4 * cw)) != 0) return false;
     if (((N + 15) / 16) * (K / (4 * wpl * codes_per_word(bits))) >= (int64_t)1 << 30) return false;  // 32-bit iteration counts
@@ -892,21 +991,25 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     const int wpl = wpl_for(bits, p.gs, p.K);
     const int codes = codes_per_word(bits);
     const int ik = 4 * wpl * codes;
-    p.gs_shift = p.gs == 32 ? 5 : p.gs == 64 ? 6 : 7;
+    p.gs_shift = p.gs == 16 ? 4 : p.gs == 32 ? 5 : p.gs == 64 ? 6 : 7;
     const int64_t tiles = (p.N + 15) / 16, ipt = p.K / ik, total = tiles * ipt;
-    // k-chunk for staging scales: the largest power of two up to 64 groups (and 2048 values) that
-    // divides K and holds whole iterations and groups.
-    int64_t chunk = (int64_t)QMV_SEG_GROUPS * p.gs;
+    // k-chunk for staging scales: the largest divisor of K that holds whole iterations and whole
+    // groups, up to the groups the staging area takes (and 2048 values).
+    const int64_t max_groups = kind_fp(bits) ? QMV_FP_SEG_GROUPS : QMV_SEG_GROUPS;
+    int64_t chunk = max_groups * p.gs;
     if (chunk > 2048) chunk = 2048;
-    const int64_t unit = ik > p.gs ? ik : p.gs;
-    while (chunk > unit && p.K % chunk != 0) chunk >>= 1;
-    if (p.K % chunk != 0) chunk = unit;
+    const int64_t unit = ik > p.gs ? ik : p.gs;  // both are powers of two: the larger is their common multiple
+    chunk = chunk / unit * unit;
+    while (chunk > unit && p.K % chunk != 0) chunk -= unit;
+    if (chunk < unit || p.K % chunk != 0) chunk = unit;
     p.chunk_k = (int32_t)chunk;
     {
-        // Widest aligned copy for staging scales and biases: 8 groups, 2 groups or single loads.
+        // Widest aligned copy for staging scales and biases: 8 groups, 2 groups or single loads
+        // (4-bit floating point: 4 scale bytes or single loads).
         const int64_t rg = p.K / p.gs, cg = chunk / p.gs;
         const uintptr_t al = (uintptr_t)p.scales | (uintptr_t)p.biases;
-        if (al % 16 == 0 && p.s_batch_stride % 8 == 0 && rg % 8 == 0 && cg % 8 == 0) p.s_vec = 16;
+        if (kind_fp(bits)) p.s_vec = (al % 4 == 0 && p.s_batch_stride % 4 == 0 && rg % 4 == 0 && cg % 4 == 0) ? 4 : 0;
+        else if (al % 16 == 0 && p.s_batch_stride % 8 == 0 && rg % 8 == 0 && cg % 8 == 0) p.s_vec = 16;
         else if (al % 4 == 0 && p.s_batch_stride % 2 == 0 && rg % 2 == 0 && cg % 2 == 0) p.s_vec = 4;
         else p.s_vec = 0;
     }
@@ -964,6 +1067,7 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
 #define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, grid, smem);
     NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(4, 8) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(8, 8)
     NVC_QMV(2, 1) NVC_QMV(2, 2) NVC_QMV(3, 1) NVC_QMV(6, 1) NVC_QMV(6, 2)
+    NVC_QMV(40, 1) NVC_QMV(40, 2) NVC_QMV(40, 4) NVC_QMV(41, 1) NVC_QMV(41, 2) NVC_QMV(41, 4)
 #undef NVC_QMV
     return set_error(NVC_ERR_UNSUPPORTED, "qmv: no kernel for %d bits, group size %d", bits, p.gs);
 }

@@ -40,6 +40,8 @@ struct QmvParams {
     int64_t x_batch_stride, w_batch_stride, s_batch_stride;
     int32_t M, gs, gs_shift, chunk_k, max_parts, x_vec, s_vec;
     uint32_t blk_q, blk_r;  // iterations per block: blk_q, one more in the first blk_r blocks
+    const float *global;       // nvfp4 global scale(s) or nullptr
+    int32_t expert_global;     // one value per expert (indexed like the weights' batch)
     // Fused gather (nullptr: plain product).  The result goes to every rank's region instead of y.
     const struct PeerTable *peer;
     uint64_t peer_out_offset;  // byte offset of the [size, M, N] gathered buffer inside a region
@@ -50,6 +52,8 @@ struct QmvParams {
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,
                          int64_t N, int64_t K, const void *x, int64_t ldx, int64_t x_batch_stride, const uint32_t *w,
                          int64_t w_batch_stride);
+// The fast kernel's kind of a (mode, bits) pair: the affine bit width, 40 = mxfp4, 41 = nvfp4, 0 = none.
+int qmv_kind(int32_t mode, int32_t bits);
 // Caller-provided scratch of fixed capacity (partial sums and arrival counters).
 struct QmvScratch {
     float *partials;

@@ -163,6 +163,28 @@ def test_fp_product(be, mode, gs, M):
     assert_product_close(got, want, oracle.BF16)
 
 
+@pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
+@pytest.mark.parametrize("N,K", [(80, 2880), (256, 4096), (48, 512)])
+def test_fp_few_rows_tight_and_unit_rows_bit_for_bit(be, mode, gs, N, K):
+    # the few-row kernel decodes E2M1 x scale exactly: products agree to one output rounding and
+    # unit-vector rows return the oracle's float32 decode (rounded to bfloat16) bit for bit
+    rng = np.random.default_rng(mode + N)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    w.reshape(-1)[:4] = oracle.from_f32(np.array([0.0, 0.011, -0.5, 3.0], np.float32), oracle.BF16)
+    c, s, _ = oracle.quantize(w, oracle.BF16, mode, gs, 4)
+    for M in (1, 5, 8):
+        x = rand(rng, (M, K), oracle.BF16)
+        want = oracle.quantized_matmul(x, c, s, None, oracle.BF16, mode, gs, 4)
+        got = be.quantized_matmul(x, c, s, None, oracle.BF16, mode, gs, 4, True)
+        assert_product_tight(got, want, oracle.BF16, f"M{M}")
+    dense = oracle.to_f32(oracle.dequantize(c, s, None, oracle.F32, mode, gs, 4), oracle.F32)
+    ks = rng.permutation(K)[:8]
+    xu = np.zeros((8, K), np.float32)
+    xu[np.arange(8), ks] = 1.0
+    got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(xu, oracle.BF16), c, s, None, oracle.BF16, mode, gs, 4, True), oracle.BF16)
+    assert np.array_equal(got, dense[:, ks].T)
+
+
 def test_sorted_offsets(be):
     import nuvec_b200 as nv
     rng = np.random.default_rng(2)
@@ -380,4 +402,21 @@ def test_gather_grouped_fp4(be, mode, gs):
     for g in ([None] if mode != oracle.NVFP4 else [None, (rng.random(E) * 4 + 0.5).astype(np.float32)]):
         want = oracle.gather_qmm(xr, c, s, None, np.arange(len(rhs)), rhs, oracle.BF16, mode, gs, 4, True, g)
         got = be.gather_qmm(xr, c, s, None, None, rhs, oracle.BF16, mode, gs, 4, True, g, True)
+        assert_product_tight(got, want, oracle.BF16, f"global={g is not None}")
+
+
+@pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
+@pytest.mark.parametrize("sorted_rows", [True, False])
+def test_gather_few_rows_fp4(be, mode, gs, sorted_rows):
+    # one decode token of a gpt-oss-shaped layer: 4 rows, one expert each -> the few-row kernel
+    # with per-row expert indices (and the per-expert nvfp4 global scale)
+    rng = np.random.default_rng(mode + sorted_rows)
+    T, E, topk, N, K = 1, 32, 4, 160, 2880
+    c, s, _, rhs, xr = moe_case(rng, T, E, topk, N, K, mode, gs, 4)
+    if not sorted_rows:
+        perm = rng.permutation(len(rhs))
+        rhs, xr = rhs[perm], xr[perm]
+    for g in ([None] if mode != oracle.NVFP4 else [None, (rng.random(E) * 4 + 0.5).astype(np.float32)]):
+        want = oracle.gather_qmm(xr, c, s, None, np.arange(len(rhs)), rhs, oracle.BF16, mode, gs, 4, True, g)
+        got = be.gather_qmm(xr, c, s, None, None, rhs, oracle.BF16, mode, gs, 4, True, g, sorted_rows)
         assert_product_tight(got, want, oracle.BF16, f"global={g is not None}")
