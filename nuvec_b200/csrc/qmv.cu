@@ -885,7 +885,7 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 __stcg(own + 16, seq);
                 // all flags are polled together (relaxed loads that overlap), one fence acquires
                 bool all = false;
-                for (uint32_t spins = 0; spins < (1u << 24) && !all; spins++) {
+                for (uint32_t spins = 0; spins < (1u << 20) && !all; spins++) {  // about a second
                     all = true;
                     for (int rk = 0; rk < p.peer->size; rk++) {
                         uint32_t seen;

@@ -284,6 +284,11 @@ int32_t nvc_synchronize(nvc_device *dev) {
     NVC_CUDA(cudaStreamSynchronize(dev->stream));
     if (dev->error_word && *dev->error_word != 0) {
         *dev->error_word = 0;
+        // A kernel that gave up may have left arrival counters half-counted: rearm them, so that
+        // the next product starts clean.
+        if (dev->counters) cudaMemsetAsync(dev->counters, 0, dev->counters_len * sizeof(uint32_t), dev->stream);
+        if (dev->qmm_counters) cudaMemsetAsync(dev->qmm_counters, 0, dev->qmm_counters_len * sizeof(uint32_t), dev->stream);
+        cudaStreamSynchronize(dev->stream);
         return set_error(NVC_ERR_DRIVER, "a kernel gave up waiting (on its pipeline, or on the other ranks of a fused gather); results of the last work are invalid");
     }
     return NVC_OK;

@@ -68,3 +68,47 @@ def test_gather_arguments_are_checked():
     group = C.c_void_p()
     assert lib.nvc_peer_group_create(dev._h, 0, 1, bases, C.byref(group)) == _ffi.ERR_INVALID_ARGUMENT
     assert lib.nvc_peer_group_create(dev._h, 2, 2, bases, C.byref(group)) == _ffi.ERR_INVALID_ARGUMENT
+
+
+def test_a_rank_that_never_shows_up_ends_the_wait_with_an_error():
+    """Failure detection without a fault: a group of two ranks whose second region is just more
+    memory of this GPU -- nobody ever raises rank 1's flag.  The kernel's bounded wait runs out
+    (about a second), the kernel returns, nvc_synchronize reports the failure, and the device
+    stays usable."""
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+    lib = _ffi.lib()
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(4)
+    quant = nv.Quant.affine(64, 4)
+    qc = quant._c()
+    M, N, K = 1, 256, 1024
+    size = 4096 + 2 * M * N * 2
+    r0, r1, h = C.c_void_p(), C.c_void_p(), (C.c_uint8 * 64)()
+    assert lib.nvc_symm_alloc(dev._h, size, C.byref(r0), h) == 0, _ffi.last_error()
+    assert lib.nvc_symm_alloc(dev._h, size, C.byref(r1), h) == 0, _ffi.last_error()
+    bases = (C.c_void_p * 2)(r0.value, r1.value)
+    group = C.c_void_p()
+    assert lib.nvc_peer_group_create(dev._h, 0, 2, bases, C.byref(group)) == 0, _ffi.last_error()
+    try:
+        w = oracle.from_f32((rng.standard_normal((N, K)) * 0.02).astype(np.float32), oracle.BF16)
+        q = nv.quantize(dev.array(w, nv.BF16), quant)
+        x = dev.array(oracle.from_f32(rng.standard_normal((M, K)).astype(np.float32), oracle.BF16), nv.BF16)
+        want = nv.quantized_matmul(x, q).to_numpy()
+        rc = lib.nvc_quantized_matmul_gather(dev._h, group, C.byref(qc), x.ptr, q.weight.ptr, q.scales.ptr,
+                                             q.biases.ptr, M, N, K, 4096)
+        assert rc == 0, _ffi.last_error()
+        assert lib.nvc_synchronize(dev._h) == _ffi.ERR_DRIVER
+        assert "gave up waiting" in _ffi.last_error()
+        # this rank's slice did reach both regions before the wait gave up
+        for region in (r0, r1):
+            got = np.empty((M, N), np.uint16)
+            assert lib.nvc_memcpy_d2h(dev._h, got.ctypes.data_as(C.c_void_p), C.c_void_p(region.value + 4096), got.nbytes) == 0
+            assert np.array_equal(got, want.view(np.uint16).reshape(M, N))
+        # and the device goes on working
+        assert lib.nvc_synchronize(dev._h) == 0
+        assert np.array_equal(nv.quantized_matmul(x, q).to_numpy(), want)
+    finally:
+        lib.nvc_peer_group_destroy(group)
+        lib.nvc_symm_free(dev._h, r0)
+        lib.nvc_symm_free(dev._h, r1)
