@@ -341,8 +341,17 @@ struct TileInfo {
     int expert;
 };
 
+// Grouped products: the experts' first rows and the number of token tiles before each expert, kept
+// in shared memory (filled once per block), so that finding a tile's expert is a binary search in
+// shared memory and not a walk over global memory by every role at every tile.
+constexpr int QMM_MAX_TABLE_EXPERTS = 512;
+struct GroupTable {
+    const int *off;    // [experts + 1] first row of each expert, then the row count; nullptr: no table
+    const int *tiles;  // [experts + 1] token tiles before each expert, then the total
+};
+
 template <int BT>
-__device__ __forceinline__ bool tile_info(const QmmKernelParams &p, int tile, int n_tiles, TileInfo &ti) {
+__device__ __forceinline__ bool tile_info(const QmmKernelParams &p, const GroupTable &gt, int tile, int n_tiles, TileInfo &ti) {
     const int nt = tile % n_tiles, j = tile / n_tiles;
     ti.n0 = nt * QMM_BN;
     if (!p.offsets) {
@@ -351,6 +360,19 @@ __device__ __forceinline__ bool tile_info(const QmmKernelParams &p, int tile, in
         ti.tok0 = j * BT;
         ti.tok_end = p.rows;
         return ti.tok0 < p.rows;
+    }
+    if (gt.off) {
+        if (j >= gt.tiles[p.experts]) return false;
+        int lo = 0, hi = p.experts;  // the expert e with tiles[e] <= j < tiles[e + 1]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (gt.tiles[mid] <= j) lo = mid; else hi = mid;
+        }
+        ti.expert = lo;
+        ti.wrow0 = lo * p.N + ti.n0;
+        ti.tok0 = gt.off[lo] + (j - gt.tiles[lo]) * BT;
+        ti.tok_end = gt.off[lo + 1];
+        return true;
     }
     // grouped: token tile j of the concatenation of every expert's tiles
     int seen = 0;
@@ -408,7 +430,7 @@ template <int BT> struct QmmTmem {
     // ring depth: what the tensor-memory columns and the shared memory (activation stages beside
     // two packed-weight slabs) both allow, at most 8
     static constexpr int BY_TMEM = (512 - ACC_COLS) / 32;
-    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 2 * 128 * 128) / (BT * 64 * 2);
+    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - 2 * 128 * 128) / (BT * 64 * 2);
     static constexpr int FIT = BY_TMEM < BY_SMEM ? (BY_TMEM < 8 ? BY_TMEM : 8) : (BY_SMEM < 8 ? BY_SMEM : 8);
     // a multiple of the dequantizer groups, so that a stage is always refilled by the same group
     static constexpr int STAGES = FIT / QMM_DQ_GROUPS * QMM_DQ_GROUPS;
@@ -437,6 +459,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accempty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *last_flag = abort_flag + 1;  // epilogue: this block arrived last at a K-split tile
+    int *table = reinterpret_cast<int *>(bars) + 256;  // behind the 1 KB of barriers and flags: 2 x (experts + 1) ints
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kblocks = p.K / QMM_BK;
@@ -463,10 +486,29 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    GroupTable gt{nullptr, nullptr};
+    const bool tabled = p.offsets && p.experts <= QMM_MAX_TABLE_EXPERTS;
+    if (tabled) {
+        for (int e = tid; e <= p.experts; e += QMM_THREADS) table[e] = e < p.experts ? p.offsets[e] : p.rows;
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (tabled) {
+        int *tiles = table + QMM_MAX_TABLE_EXPERTS + 1;
+        if (tid == 0) {
+            int seen = 0;
+            for (int e = 0; e < p.experts; e++) {
+                tiles[e] = seen;
+                seen += (table[e + 1] - table[e] + BT - 1) / BT;
+            }
+            tiles[p.experts] = seen;
+        }
+        __syncthreads();
+        gt.off = table;
+        gt.tiles = tiles;
+    }
 
     if (warp == 4) {
         // ── TMA producer, activations: one 64-k x BT tile per stage ─────────────────────────
@@ -477,7 +519,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 Item item;
                 if (!qmm_item<KPS>(p, kblocks, j, item)) break;
                 TileInfo ti;
-                if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+                if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
                 for (int kb = item.kb0; kb < item.kb1 && ok; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
@@ -497,7 +539,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 Item item;
                 if (!qmm_item<KPS>(p, kblocks, j, item)) break;
                 TileInfo ti;
-                if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+                if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
                 for (int kb = item.kb0; kb < item.kb1 && ok; kb += KPS, wit++) {
                     const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
                     ok = mbar_wait<200>(wempty + s, ph ^ 1, abort_flag);
@@ -523,7 +565,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             Item item;
             if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS;
             const uint32_t d = tmem_base + buf * BT;
             for (int kb = item.kb0; kb < item.kb1; kb++) {
@@ -560,7 +602,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             Item item;
             if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             QMM_ACC(3);
             if (lane == 0 && ok) ok = mbar_wait<100>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
@@ -606,7 +648,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             Item item;
             if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
             // rows past N (last tile) read the last valid row's scales; their outputs are not stored
             const int wr = ti.wrow0 + min(row, p.N - 1 - ti.n0);
             const uint16_t *sc = p.scales + (size_t)wr * p.row_groups;
@@ -717,7 +759,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             Item item;
             if (!qmm_item<KPS>(p, kblocks, jj, item)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             // After a wait gave up the warp keeps walking the items without touching data: the
             // named barriers of K-split tiles below must still see all four epilogue warps.
@@ -792,7 +834,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         // part order (the sum does not depend on who arrived when), round once and store.
         Item item;
         TileInfo ti;
-        if (qmm_item<KPS>(p, kblocks, p.full_waves, item) && tile_info<BT>(p, item.tile, n_tiles, ti)) {
+        if (qmm_item<KPS>(p, kblocks, p.full_waves, item) && tile_info<BT>(p, gt, item.tile, n_tiles, ti)) {
             __threadfence();
             float gmul = 1.0f;
             if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
@@ -915,8 +957,9 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
     // one ring: activation stages in shared memory, weight stages in tensor memory
     constexpr int STAGES = QmmTmem<BT>::STAGES;
-    static_assert(1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 <= 227 * 1024, "not enough shared memory for the pipeline");
-    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024;
+    static_assert(1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1) <= 227 * 1024, "not enough shared memory for the pipeline");
+    // alignment slack, activation stages, packed-weight slabs, 1 KB of barriers and flags, the grouped products' tables
+    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1);
     auto kernel = qmm_kernel<BITS, BT, STAGES, MODE>;
     static bool configured = false;
     if (!configured) {
