@@ -436,7 +436,10 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     constexpr int CW = LW / CPL;               // words per copy
     extern __shared__ __align__(16) uint32_t smem[];
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // the warp index read from lane 0: the compiler then knows that everything derived from it (run
+    // bounds, loop trip counts) is the same for the whole warp and keeps mma.sync free of re-convergence code
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
     const int r = lane >> 2, t = lane & 3;
     const int64_t b = blockIdx.z;
     int64_t xb = b, wb = b;
