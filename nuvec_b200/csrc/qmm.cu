@@ -66,7 +66,7 @@ struct QmmKernelParams {
     int32_t *error;                   // host-visible word: nonzero when a wait gave up
     float *partials;                  // [tail tiles][splits][BT tokens][128 rows] float32 (K-split tiles)
     uint32_t *counters;               // [tail tiles] arrivals, zero on entry and on exit
-    int32_t full_waves, tail_tiles, splits;  // the schedule, see Item
+    int32_t full_waves, tail_tiles, splits, tail_rounds;  // the schedule, see Item
     int32_t experts, rows, N, K;
     int32_t gs_shift, row_groups, mode, expert_global;
 };
@@ -399,18 +399,22 @@ __device__ __forceinline__ bool tile_info(const QmmKernelParams &p, const GroupT
 struct Item {
     int tile, kb0, kb1;  // k-blocks [kb0, kb1) of this tile
     int part, parts, slot;
+    int round;           // which of the block's (at most two) parts of left-over tiles this is
 };
 template <int KPS>
 __device__ __forceinline__ bool qmm_item(const QmmKernelParams &p, int kblocks, int j, Item &it) {
     const int grid = (int)gridDim.x;
     if (j < p.full_waves) {
         it.tile = (int)blockIdx.x + j * grid;
-        it.kb0 = 0; it.kb1 = kblocks; it.part = 0; it.parts = 1; it.slot = 0;
+        it.kb0 = 0; it.kb1 = kblocks; it.part = 0; it.parts = 1; it.slot = 0; it.round = 0;
         return true;
     }
-    if (j > p.full_waves || (int)blockIdx.x >= p.tail_tiles * p.splits) return false;
-    it.slot = (int)blockIdx.x / p.splits;
-    it.part = (int)blockIdx.x % p.splits;
+    // the parts of the left-over tiles are dealt round-robin, at most tail_rounds per block
+    it.round = j - p.full_waves;
+    const int pi = (int)blockIdx.x + it.round * grid;
+    if (it.round >= p.tail_rounds || pi >= p.tail_tiles * p.splits) return false;
+    it.slot = pi / p.splits;
+    it.part = pi % p.splits;
     it.parts = p.splits;
     it.tile = p.full_waves * grid + it.slot;
     const int slabs = (kblocks + KPS - 1) / KPS;  // the launch keeps splits <= slabs: no part is empty
@@ -816,9 +820,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                         last = arrived == (uint32_t)item.parts - 1;
                         if (last) p.counters[item.slot] = 0u;  // rearmed for the next launch
                     }
-                    // A K-split part is always a block's last item: the whole block adds the parts
-                    // up after its roles have finished (below).
-                    *last_flag = last ? 1 : 0;
+                    // K-split parts are a block's last items: the whole block adds the parts up
+                    // after its roles have finished (below).
+                    if (last) *last_flag = *last_flag | (1 << item.round);
                 }
             }
             tcount++;
@@ -829,12 +833,13 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && *abort_flag && p.error) *p.error = 1;
-    if (*last_flag && !*abort_flag) {
-        // This block arrived last at its K-split tile: all its threads add the float32 parts in
+    for (int round = 0; round < p.tail_rounds && !*abort_flag; round++) {
+        if (!(*last_flag & (1 << round))) continue;
+        // This block arrived last at this K-split tile: all its threads add the float32 parts in
         // part order (the sum does not depend on who arrived when), round once and store.
         Item item;
         TileInfo ti;
-        if (qmm_item<KPS>(p, kblocks, p.full_waves, item) && tile_info<BT>(p, gt, item.tile, n_tiles, ti)) {
+        if (qmm_item<KPS>(p, kblocks, p.full_waves + round, item) && tile_info<BT>(p, gt, item.tile, n_tiles, ti)) {
             __threadfence();
             float gmul = 1.0f;
             if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
@@ -974,18 +979,30 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     k.full_waves = total_tiles / grid;
     k.tail_tiles = total_tiles % grid;
     k.splits = 1;
+    k.tail_rounds = 1;
     if (total_tiles < sms) {  // fewer tiles than multiprocessors: all of them are "left over"
         k.full_waves = 0;
         k.tail_tiles = total_tiles;
     }
     if (k.tail_tiles > 0 && !getenv("NUVEC_QMM_NO_KSPLIT")) {
-        int s = sms / k.tail_tiles;           // parts per tile that fit the machine
-        if (s > slabs / 2) s = slabs / 2;     // at least two slabs of weights per part
-        if (s > 16) s = 16;
-        if (s < 1) s = 1;
-        k.splits = s;
+        // Parts per tile: whatever makes the left-over tiles finish soonest when the parts are dealt
+        // over the multiprocessors in one or two rounds (time ~ rounds / parts, plus a little for
+        // the partial sums); at least two slabs of weights per part, at most 16 parts.
+        int best = 1;
+        double best_cost = 1.0;
+        for (int s2 = 2; s2 <= 16 && s2 <= slabs / 2; s2++) {
+            const int rounds = (k.tail_tiles * s2 + sms - 1) / sms;
+            if (rounds > 2) break;
+            const double cost = (double)rounds / s2 + 0.05;
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = s2;
+            }
+        }
+        k.splits = best;
+        k.tail_rounds = (k.tail_tiles * best + sms - 1) / sms;
     }
-    if (k.full_waves == 0) grid = k.tail_tiles * k.splits;
+    if (k.full_waves == 0) grid = k.tail_tiles * k.splits < sms ? k.tail_tiles * k.splits : sms;
     if (k.splits > 1) {
         const size_t need = (size_t)k.tail_tiles * k.splits * BT * QMM_BN * sizeof(float);
         NVC_TRY(ensure_qmm_scratch(dev, need, (size_t)k.tail_tiles));
