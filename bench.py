@@ -460,7 +460,7 @@ def main():
                        "h2d_bytes_per_step": args.layers * sum(M * K * 2 for _, _, K in PROJECTIONS),
                        "d2h_bytes_per_step": args.layers * sum(M * (N // world) * 2 for _, N, _ in PROJECTIONS),
                        "ms_per_step": wall * 1e3,
-                       "note": "nvc_quantized_matmul_host per product: pinned H2D of x, kernel, D2H of y, wait; weights resident"}
+                       "note": "nvc_quantized_matmul_host per product: x through the pinned block and an H2D copy, kernel, y stored by the kernel into the pinned block over PCIe, wait; weights resident"}
 
     # ── prefill product on tcgen05 (rank 0's view; N-sharded like the decode products) ───────
     if not args.no_prefill:

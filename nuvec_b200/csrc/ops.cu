@@ -240,7 +240,7 @@ static int32_t ensure_staging(nvc_device *dev, size_t host_bytes, size_t dev_byt
         if (dev->pinned) cudaFreeHost(dev->pinned);
         dev->pinned = nullptr;
         dev->pinned_bytes = 0;
-        NVC_CUDA(cudaHostAlloc(&dev->pinned, host_bytes, cudaHostAllocDefault));
+        NVC_CUDA(cudaHostAlloc(&dev->pinned, host_bytes, cudaHostAllocMapped));
         dev->pinned_bytes = host_bytes;
     }
     if (dev->staging_bytes < dev_bytes) {
@@ -270,9 +270,15 @@ extern "C" int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q
     // DMA transfers on the stream; a caller that passes pinned memory skips nothing but a memcpy.
     memcpy(hp + xoff, host_x, xb);
     NVC_CUDA(cudaMemcpyAsync(dp + xoff, hp + xoff, xb, cudaMemcpyHostToDevice, dev->stream));
+    // A small result (a decode product: a few KB) is stored by the kernel straight into the pinned
+    // block through its device mapping, which saves a copy command and its latency; a large one
+    // goes to device memory and comes back as one DMA transfer.
+    void *ydev = dp + yoff;
+    const bool direct = yb <= 256 * 1024;
+    if (direct) NVC_CUDA(cudaHostGetDevicePointer(&ydev, hp + yoff, 0));
     NVC_TRY(nvc_quantized_matmul(dev, q, dtype, transpose, dp + xoff, w, scales, biases, global_scale, M, N, K, K, 1, 0,
-                                 0, 0, dp + yoff));
-    NVC_CUDA(cudaMemcpyAsync(hp + yoff, dp + yoff, yb, cudaMemcpyDeviceToHost, dev->stream));
+                                 0, 0, ydev));
+    if (!direct) NVC_CUDA(cudaMemcpyAsync(hp + yoff, dp + yoff, yb, cudaMemcpyDeviceToHost, dev->stream));
     NVC_CUDA(cudaStreamSynchronize(dev->stream));
     memcpy(host_y, hp + yoff, yb);
     return NVC_OK;

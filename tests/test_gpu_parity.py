@@ -420,3 +420,26 @@ def test_gather_few_rows_fp4(be, mode, gs, sorted_rows):
         want = oracle.gather_qmm(xr, c, s, None, np.arange(len(rhs)), rhs, oracle.BF16, mode, gs, 4, True, g)
         got = be.gather_qmm(xr, c, s, None, None, rhs, oracle.BF16, mode, gs, 4, True, g, sorted_rows)
         assert_product_tight(got, want, oracle.BF16, f"global={g is not None}")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 512, 1024), (600, 512, 1024)])
+def test_host_operand_entry_point_matches_the_device_one(be, M, N, K):
+    # nvc_quantized_matmul_host: x and y in host memory (small results come back through the
+    # pinned block's device mapping, large ones by a copy) -- same bits as the device-resident call
+    import ctypes as C
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+    rng = np.random.default_rng(M + N)
+    dev = nv.Device.shared(0)
+    quant = nv.Quant.affine(64, 4)
+    q = nv.quantize(dev.array(rand(rng, (N, K), oracle.BF16, 0.02), nv.BF16), quant)
+    xh = np.ascontiguousarray(rand(rng, (M, K), oracle.BF16))
+    want = nv.quantized_matmul(dev.array(xh, nv.BF16), q).to_numpy()
+    got = np.zeros((M, N), np.uint16)
+    qc = quant._c()
+    for _ in range(2):
+        rc = _ffi.lib().nvc_quantized_matmul_host(dev._h, C.byref(qc), nv.BF16, 1, xh.ctypes.data_as(C.c_void_p), q.weight.ptr,
+                                                  q.scales.ptr, q.biases.ptr, None, M, N, K, got.ctypes.data_as(C.c_void_p))
+        assert rc == 0, _ffi.last_error()
+        assert np.array_equal(got, want.view(np.uint16).reshape(M, N))
+        got[:] = 0
