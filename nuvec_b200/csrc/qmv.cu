@@ -603,11 +603,11 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
             const uint16_t *src = x + (int64_t)m * p.ldx + (int64_t)blk * CODES;
             if (p.x_vec) {
                 if (CODES == 4) {
-                    *reinterpret_cast<uint2 *>(in) = __ldg(reinterpret_cast<const uint2 *>(src));
+                    *reinterpret_cast<uint2 *>(in) = __ldcg(reinterpret_cast<const uint2 *>(src));
                 } else {
 #pragma unroll
                     for (int v = 0; v < CODES / 8; v++)
-                        *reinterpret_cast<uint4 *>(in + 8 * v) = __ldg(reinterpret_cast<const uint4 *>(src) + v);
+                        *reinterpret_cast<uint4 *>(in + 8 * v) = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
                 }
             } else {
 #pragma unroll
