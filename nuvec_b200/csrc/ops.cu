@@ -165,6 +165,9 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
     NVC_TRY(make_current(dev));
     NVC_TRY(check_product("gather_qmm", q, dtype, transpose, biases, global_scale, M, N, K));
     if (rows < 0 || x_batches < 0 || experts < 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "gather_qmm: negative size");
+    if (rows > 0 && (experts < 1 || x_batches < 1 || experts > 0xFFFFFFFFll || x_batches > 0xFFFFFFFFll))
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "gather_qmm: %lld rows gathered from %lld weight batches and %lld activation batches",
+                         (long long)rows, (long long)experts, (long long)x_batches);
     if (rows == 0 || M == 0 || N == 0) return NVC_OK;
     if (!x || !w || !scales || !y || !rhs) return set_error(NVC_ERR_INVALID_ARGUMENT, "gather_qmm: null operand");
     if (K == 0) {
@@ -204,6 +207,7 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
         p.M = (int32_t)M; p.gs = q->group_size;
         p.x_vec = ((uintptr_t)x % 16 == 0) && (K % 8 == 0);
         p.global = global_scale; p.expert_global = global_scale != nullptr;
+        p.experts = (uint32_t)experts; p.x_batches = (uint32_t)x_batches;
         // Row batches beyond the grid limit go in slices.
         for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
             int64_t n = rows - r0 < 65535 ? rows - r0 : 65535;
@@ -219,6 +223,7 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
     GenericParams g{};
     g.mode = q->mode; g.gs = q->group_size; g.bits = q->bits; g.dtype = dtype; g.transpose = transpose;
     g.scalar_global = 0; g.expert_global = global_scale != nullptr;
+    g.experts = (uint32_t)experts; g.x_batches = (uint32_t)x_batches;
     g.w = w; g.scales = scales; g.biases = biases; g.global = global_scale;
     g.M = M; g.N = N; g.K = K; g.ldx = K;
     g.x_batch_stride = M * K; g.w_batch_stride = w_stride; g.s_batch_stride = s_stride;

@@ -23,6 +23,8 @@
 // 6934-7168); CPU result crates/nuvec-core/src/kernels.rs:1091-1142.
 #include "qmv.cuh"
 
+#include <utility>
+
 namespace nvc {
 
 // ── generic kernels ────────────────────────────────────────────────────────────────────
@@ -56,9 +58,9 @@ __global__ void __launch_bounds__(128) qmv_generic_t_kernel(GenericParams p) {
     const int64_t b = blockIdx.y;
     if (n >= p.N) return;
     int64_t xb = b, wb = b;
-    if (p.rhs) {
-        wb = p.rhs[b];
-        xb = p.lhs ? p.lhs[b] : b;
+    if (p.rhs) {  // indices past the end select the last batch (the reference's `take` clamps, kernels.rs:120-129)
+        wb = min(p.rhs[b], p.experts - 1u);
+        xb = p.lhs ? (int64_t)min(p.lhs[b], p.x_batches - 1u) : b;
     }
     const T *x = (const T *)p.x + xb * p.x_batch_stride;
     const uint8_t *w = (const uint8_t *)(p.w + wb * p.w_batch_stride);
@@ -96,9 +98,9 @@ __global__ void __launch_bounds__(128) qmv_generic_n_kernel(GenericParams p) {
     const int64_t b = blockIdx.y;
     if (n >= p.N) return;
     int64_t xb = b, wb = b;
-    if (p.rhs) {
-        wb = p.rhs[b];
-        xb = p.lhs ? p.lhs[b] : b;
+    if (p.rhs) {  // indices past the end select the last batch (the reference's `take` clamps, kernels.rs:120-129)
+        wb = min(p.rhs[b], p.experts - 1u);
+        xb = p.lhs ? (int64_t)min(p.lhs[b], p.x_batches - 1u) : b;
     }
     const T *x = (const T *)p.x + xb * p.x_batch_stride;
     const uint8_t *w = (const uint8_t *)(p.w + wb * p.w_batch_stride);
@@ -387,6 +389,9 @@ constexpr int QMV_BLOCKS_PER_SM = 2;
 // Depth of each lane's ring of asynchronous weight copies (iterations in flight per warp): the
 // bytes in flight per lane stay near 128 whatever the iteration's width.
 __host__ __device__ constexpr int qmv_stages(int wpl) { return wpl == 8 ? 3 : 4; }
+// Words of the all-zero page that lanes of activation rows >= M read instead of activations: four
+// iterations' worth, so that such a lane needs no address update inside a round of four.
+__host__ __device__ constexpr int qmv_zero_words(int wpl, int xw) { return 16 * wpl * xw < 64 ? 64 : 16 * wpl * xw; }
 // Most groups whose scale/bias are staged at a time (one k-chunk of a tile).
 constexpr int QMV_SEG_GROUPS = 16;
 // Row pitch (bfloat16 elements) of the staged scales: 48 bytes = 12 banks, a multiple of 16 bytes
@@ -396,7 +401,16 @@ constexpr int QMV_SPITCH = QMV_SEG_GROUPS + 8;
 // the 8 rows a warp reads together fall on different banks); 2 x 16 x 80 bytes fit the same area.
 constexpr int QMV_FP_SEG_GROUPS = 64;
 constexpr int QMV_FPITCH = 80;
-static_assert(2 * 16 * QMV_FPITCH <= 4 * 16 * QMV_SPITCH * 2, "the floating-point scale buffers fit the per-warp scale area");
+// Per-warp scale area (bytes).  Affine: the raw scales and biases of the next k-chunk as they are
+// copied from global memory (2 x 16 rows x QMV_SPITCH bf16), then the current chunk's constants
+// repacked per (group, row) as the pairs {s, s}, {b, b} the dequantization consumes: QMV_SEG_GROUPS
+// groups, QMV_PKPITCH bytes apart (16 rows x 8 bytes + 32: two neighbouring groups read together by a
+// half-warp fall on different banks).  4-bit floating point: two buffers of 16 x QMV_FPITCH bytes.
+constexpr int QMV_PKPITCH = 16 * 8 + 32;
+constexpr int QMV_RAW_BYTES = 2 * 16 * QMV_SPITCH * 2;
+constexpr int QMV_SCALE_AREA = 4096;
+static_assert(QMV_RAW_BYTES + QMV_SEG_GROUPS * QMV_PKPITCH <= QMV_SCALE_AREA, "raw and repacked scales fit the per-warp scale area");
+static_assert(2 * 16 * QMV_FPITCH <= QMV_SCALE_AREA, "the floating-point scale buffers fit the per-warp scale area");
 
 // The product is cut into iterations: iteration (tile, i) multiplies 16 weight rows ("tile") by
 // IK = 4 * WPL * CODES consecutive k-values.  All iterations of all tiles form one sequence, tile
@@ -416,13 +430,148 @@ static_assert(2 * 16 * QMV_FPITCH <= 4 * 16 * QMV_SPITCH * 2, "the floating-poin
 //                             in iteration i sits at ((i * WPL + j) * 4 + t) * XW
 //   zero  [64] u32            what lanes of activation rows >= M read
 //   per warp:
-//   sraw, braw [2][16][QMV_SPITCH] bf16   scales / biases of the current and the next k-chunk
+//   scale area (QMV_SCALE_AREA bytes)     raw scales / biases of the next k-chunk and the repacked
+//                                         constants of the current one (see QMV_PKPITCH)
 //   ring  [stages][2][32] x WPL u32       packed words in flight: slot (stage, row half, lane);
 //                                         WPL = 8 keeps its two 16-byte chunks 512 bytes apart
 //                                         (chunk, lane) so that a quarter-warp reads 128
 //                                         consecutive bytes
 //   lpart [QMV_WARPS][2][128] f32         partial sums of tiles cut between warps of this block
 //   lcount[QMV_WARPS + 4] u32             their arrival counters; word QMV_WARPS: "this block finished last" (fused gather)
+// Shared-memory loads by 32-bit shared address plus a compile-time offset (the main loop keeps a
+// few base addresses in registers and reaches everything else through the offset field).
+template <int OFS> __device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4 + %5];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFS));
+    return v;
+}
+template <int OFS> __device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2 + %3];\n" : "=r"(v.x), "=r"(v.y) : "r"(a), "n"(OFS));
+    return v;
+}
+template <int OFS> __device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1 + %2];\n" : "=r"(v) : "r"(a), "n"(OFS));
+    return v;
+}
+template <int OFS> __device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1 + %2];\n" : "=r"(v) : "r"(a), "n"(OFS));
+    return v;
+}
+template <int OFS> __device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.u32 [%0 + %1], {%2, %3};\n" ::"r"(a), "n"(OFS), "r"(x), "r"(y) : "memory");
+}
+// cp_async with compile-time offsets on both addresses.
+template <int BYTES, int SOFS, int GOFS> __device__ __forceinline__ void cp_async_at(uint32_t smem_addr, const void *gptr) {
+    if (BYTES == 16)
+        asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %3], 16;\n" ::"r"(smem_addr), "l"(gptr), "n"(SOFS), "n"(GOFS) : "memory");
+    else if (BYTES == 8)
+        asm volatile("cp.async.ca.shared.global [%0 + %2], [%1 + %3], 8;\n" ::"r"(smem_addr), "l"(gptr), "n"(SOFS), "n"(GOFS) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global [%0 + %2], [%1 + %3], 4;\n" ::"r"(smem_addr), "l"(gptr), "n"(SOFS), "n"(GOFS) : "memory");
+}
+// f(integral_constant<int, 0>) ... f(integral_constant<int, N - 1>): a loop whose index is a constant
+// expression inside the body (offsets of the loads above).
+template <class F, int... Is> __device__ __forceinline__ void static_for_impl(F &&f, std::integer_sequence<int, Is...>) {
+    (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, class F> __device__ __forceinline__ void static_for(F &&f) {
+    static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
+
+// Partial sums of a tile that a run boundary cuts.  Kept out of line: only such tiles come here, and
+// the main loop's registers stay free of it.  `v` holds this warp's partial sums (rows r / r + 8 x
+// activation rows 2t / 2t + 1); returns true, with the complete sums in `v`, in the warp that
+// arrives last at the tile, which then stores the result.
+struct QmvCut {
+    uint32_t lo, hi;            // this warp's run
+    uint32_t blk_lo, blk_len;   // this block's run
+    uint32_t wq, wr;            // the block's warps hold wq iterations, the first wr one more
+    uint32_t blk_q, blk_r;      // the grid's blocks hold blk_q iterations, the first blk_r one more
+    uint32_t t_lo, t_hi;        // the tile's iterations
+    int32_t warp, lane, first_tile;  // first_tile: 1 when the tile is the one the warp's run starts in
+    int32_t max_parts;
+    float *lpart;
+    uint32_t *lcount;
+    float *part;                // the tile's slots in global scratch
+    uint32_t *counter;          // the tile's arrival counter in global scratch
+};
+__device__ __noinline__ bool qmv_meet_partials(const QmvCut c, float4 &v) {
+    const int lane = c.lane, r = lane >> 2, t = lane & 3, warp = c.warp;
+    auto part_lo = [](uint32_t i, uint32_t q, uint32_t rm) { return i * q + min(i, rm); };
+    auto part_of = [](uint32_t at, uint32_t q, uint32_t rm) {
+        const uint32_t big = rm * (q + 1u);
+        return at < big ? at / (q + 1u) : rm + (at - big) / q;
+    };
+    if (c.t_lo >= c.blk_lo && c.t_hi <= c.blk_lo + c.blk_len) {
+        // Every warp that holds a part of this tile belongs to this block: the partials meet in
+        // shared memory.  A warp leaves at most two (the tile its run starts in and the one it
+        // ends in); the warp that arrives last adds them in run order.  The tile's first and last
+        // warp are found by walking from this warp's run, a step per warp and no division.
+        uint32_t l = c.lo, h = c.hi, w1 = (uint32_t)warp, w2 = (uint32_t)warp;
+        while (l > c.t_lo) {
+            w1--;
+            l -= c.wq + (w1 < c.wr ? 1u : 0u);
+        }
+        while (h < c.t_hi) {
+            w2++;
+            h += c.wq + (w2 < c.wr ? 1u : 0u);
+        }
+        float *mine = c.lpart + (warp * 2 + (c.first_tile ? 0 : 1)) * 128;
+        *reinterpret_cast<float2 *>(mine + r * 8 + 2 * t) = make_float2(v.x, v.y);
+        *reinterpret_cast<float2 *>(mine + (r + 8) * 8 + 2 * t) = make_float2(v.z, v.w);
+        __threadfence_block();
+        __syncwarp();
+        uint32_t arrived = 0;
+        if (lane == 0) arrived = atomicAdd(c.lcount + w1, 1u);
+        arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
+        if (arrived != w2 - w1) return false;
+        __threadfence_block();
+        v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t w = w1; w <= w2; w++) {
+            // warp w left this tile's partial in its slot 0 if its run starts in the tile
+            const uint32_t w_lo = c.blk_lo + part_lo(w, c.wq, c.wr);
+            const float *src = c.lpart + (w * 2 + (w_lo >= c.t_lo ? 0 : 1)) * 128;
+            float2 a = *reinterpret_cast<const float2 *>(src + r * 8 + 2 * t);
+            float2 q = *reinterpret_cast<const float2 *>(src + (r + 8) * 8 + 2 * t);
+            v.x += a.x; v.y += a.y; v.z += q.x; v.w += q.y;
+        }
+        return true;
+    }
+    // The tile is cut by a block boundary: the warps first .. last (numbered through the grid, every
+    // block of a multi-block grid runs all its warps), this one number `mine`, leave their 16 x 8
+    // partials in scratch; the one that arrives last adds them in run order (so the result does not
+    // depend on arrival order) and rearms the counter.
+    auto owner = [&](uint32_t i) {  // number, through the grid, of the warp whose run holds iteration i
+        const uint32_t cta = part_of(i, c.blk_q, c.blk_r);
+        const uint32_t l = part_lo(cta, c.blk_q, c.blk_r), len = c.blk_q + (cta < c.blk_r ? 1u : 0u);
+        const uint32_t w = len >= QMV_WARPS ? part_of(i - l, len / QMV_WARPS, len % QMV_WARPS) : i - l;
+        return (int)(cta * QMV_WARPS + w);
+    };
+    const int first = owner(c.t_lo), last = owner(c.t_hi - 1);
+    const int mine = (int)blockIdx.x * QMV_WARPS + warp - first, count = last - first + 1;
+    float *part = c.part;
+    __stcg(reinterpret_cast<float2 *>(part + mine * 128 + r * 8 + 2 * t), make_float2(v.x, v.y));
+    __stcg(reinterpret_cast<float2 *>(part + mine * 128 + (r + 8) * 8 + 2 * t), make_float2(v.z, v.w));
+    __threadfence();
+    __syncwarp();
+    uint32_t arrived = 0;
+    if (lane == 0) arrived = atomicAdd(c.counter, 1u);
+    arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
+    if (arrived != (uint32_t)count - 1) return false;
+    __threadfence();
+    v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = 0; s2 < count; s2++) {
+        float2 a = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + r * 8 + 2 * t));
+        float2 q = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + (r + 8) * 8 + 2 * t));
+        v.x += a.x; v.y += a.y; v.z += q.x; v.w += q.y;
+    }
+    if (lane == 0) *c.counter = 0u;
+    return true;
+}
+
 template <int BITS, int WPL>
 __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_kernel(QmvParams p) {
     using U = Unpack<BITS>;
@@ -444,29 +593,36 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     const int64_t b = blockIdx.z;
     int64_t xb = b, wb = b;
     if (p.rhs) {
-        wb = p.rhs[b];
-        xb = p.lhs ? p.lhs[b] : b;
+        // indices past the end select the last expert / activation batch, as the reference's `take`
+        // clamps them (crates/nuvec-core/src/kernels.rs:120-129)
+        wb = min(p.rhs[b], p.experts - 1u);
+        xb = p.lhs ? (int64_t)min(p.lhs[b], p.x_batches - 1u) : b;
     }
-    const int row_groups = (int)(p.K >> p.gs_shift);
-    const uint32_t row_words = (uint32_t)(p.K * U::WBITS / 32);
-    const int ipt = (int)(p.K / IK);        // iterations per tile
-    const int ci = p.chunk_k / IK;          // iterations per k-chunk (scales are staged per chunk)
-    const int chunk_groups = p.chunk_k >> p.gs_shift;
-    const int tiles = (int)((p.N + 15) / 16);
+    // Everything the loops divide by comes from the host: the kernel itself never divides on its
+    // per-iteration or per-chunk paths.
+    const int row_groups = p.row_groups;    // K / group size
+    const uint32_t row_words = p.row_words; // K * bits / 32
+    const int ipt = p.ipt;                  // iterations per tile, K / IK
+    const int ci = p.ci;                    // iterations per k-chunk (scales are staged per chunk)
+    const int chunk_groups = p.chunk_groups;
+    const int tiles = p.tiles;
     const int last_row = (int)p.N - 1;
 
-    const int xs_pitch = (int)(p.K / CODES) * XW + 16;  // words; = 16 (mod 32) keeps two rows on disjoint banks
+    const int xs_pitch = p.xs_pitch;  // words; = 16 (mod 32) keeps two rows on disjoint banks
+    constexpr int X_IT_WORDS = 4 * WPL * XW;              // activation words of one iteration (one row)
+    constexpr int ZERO_WORDS = qmv_zero_words(WPL, XW);   // four iterations' worth: lanes of rows >= M never leave it
     uint32_t *xs = smem;
     uint32_t *zero = xs + (size_t)p.M * xs_pitch;
-    uint16_t *sraw = reinterpret_cast<uint16_t *>(zero + 64) + (size_t)warp * (4 * 16 * QMV_SPITCH);
-    uint16_t *braw = sraw + 2 * 16 * QMV_SPITCH;
-    uint32_t *ring = reinterpret_cast<uint32_t *>(reinterpret_cast<uint16_t *>(zero + 64) +
-                                                  (size_t)QMV_WARPS * (4 * 16 * QMV_SPITCH)) +
-                     (size_t)warp * (QMV_STAGES * 2 * 32 * LW);
+    uint16_t *sraw = reinterpret_cast<uint16_t *>(zero + ZERO_WORDS) + (size_t)warp * (QMV_SCALE_AREA / 2);
+    uint16_t *braw = sraw + 16 * QMV_SPITCH;
+    uint32_t *ring = zero + ZERO_WORDS + QMV_WARPS * (QMV_SCALE_AREA / 4) + (size_t)warp * (QMV_STAGES * 2 * 32 * LW);
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * CW);
+    const uint32_t sraw_s = (uint32_t)__cvta_generic_to_shared(sraw);
     float *lpart = reinterpret_cast<float *>(ring + (size_t)(QMV_WARPS - warp) * (QMV_STAGES * 2 * 32 * LW));
     uint32_t *lcount = reinterpret_cast<uint32_t *>(lpart + QMV_WARPS * 2 * 128);
     constexpr uint32_t HALF_BYTES = 32 * LW * 4, STAGE_BYTES = 2 * HALF_BYTES;
+    constexpr int RAWB_OFS = 16 * QMV_SPITCH * 2;  // raw biases sit behind the raw scales
+    const uint32_t cpk_s = sraw_s + QMV_RAW_BYTES;   // repacked constants of the current chunk
 
     // ── this warp's run of iterations ───────────────────────────────────────────────────
     // Two levels: the blocks take consecutive runs of the sequence whose lengths differ by at most
@@ -477,22 +633,11 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     const uint32_t blk_q = p.blk_q, blk_r = p.blk_r;
     // Run of part `i` when `len`-sized work is cut into parts of q or q + 1 (the first rm parts).
     auto part_lo = [](uint32_t i, uint32_t q, uint32_t rm) { return i * q + min(i, rm); };
-    auto part_of = [](uint32_t at, uint32_t q, uint32_t rm) {
-        const uint32_t big = rm * (q + 1u);
-        return at < big ? at / (q + 1u) : rm + (at - big) / q;
-    };
     const uint32_t blk_lo = part_lo(blockIdx.x, blk_q, blk_r), blk_len = blk_q + (blockIdx.x < blk_r ? 1u : 0u);
     const uint32_t nw = min((uint32_t)QMV_WARPS, blk_len);
     const uint32_t wq = nw == QMV_WARPS ? blk_len / QMV_WARPS : 1u, wr = nw == QMV_WARPS ? blk_len % QMV_WARPS : 0u;
     const uint32_t lo = (uint32_t)warp < nw ? blk_lo + part_lo(warp, wq, wr) : 0u;
     const uint32_t hi = (uint32_t)warp < nw ? lo + wq + ((uint32_t)warp < wr ? 1u : 0u) : 0u;
-    // Block and warp whose run holds iteration i.
-    auto owner = [&](uint32_t i, uint32_t &cta, uint32_t &w) {
-        cta = part_of(i, blk_q, blk_r);
-        const uint32_t l = part_lo(cta, blk_q, blk_r), len = blk_q + (cta < blk_r ? 1u : 0u);
-        if (len >= QMV_WARPS) w = part_of(i - l, len / QMV_WARPS, len % QMV_WARPS);
-        else w = i - l;
-    };
 
     const uint32_t *wbase = p.w + wb * p.w_batch_stride + t * LW;
     const uint16_t *sc = (const uint16_t *)p.scales + wb * p.s_batch_stride;
@@ -501,252 +646,350 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     // nvfp4 global scale: one value, or one per expert (quantized.rs:481-490, 700-712)
     const float gmul = U::FP && p.global ? (p.expert_global ? p.global[wb] : p.global[0]) / (448.0f * 6.0f) : 1.0f;
 
-    // Copies the scales and biases of k-chunk `chunk` of `tile` into buffer `buf` (whole warp).
+    const uint32_t sfast_dst = sraw_s + (lane >> 1) * (QMV_SPITCH * 2) + (lane & 1) * 16;
+    // Copies the scales and biases of k-chunk `chunk` of `tile` into buffer `buf` (whole warp): two
+    // lanes per row, each taking every other piece of the row's chunk.
     auto stage_scales = [&](int tile, int chunk, int buf) {
-        const int sg0 = chunk * chunk_groups;
+        const int rr = lane >> 1;
+        const int64_t at0 = (int64_t)min(tile * 16 + rr, last_row) * row_groups + chunk * chunk_groups;
         if (U::FP) {
             // one scale byte per group, no biases: the two buffers share the whole per-warp area,
             // 16 rows of QMV_FPITCH bytes each
-            const uint8_t *sc8 = (const uint8_t *)p.scales + wb * p.s_batch_stride;
-            uint8_t *fd = reinterpret_cast<uint8_t *>(sraw) + buf * (16 * QMV_FPITCH);
+            const uint8_t *src = (const uint8_t *)p.scales + wb * p.s_batch_stride + at0;
+            uint8_t *fd = reinterpret_cast<uint8_t *>(sraw) + buf * (16 * QMV_FPITCH) + rr * QMV_FPITCH;
             if (p.s_vec == 4) {
-                const int quads = chunk_groups >> 2;
-                for (int i = lane; i < 16 * quads; i += 32) {
-                    const int rr = i / quads, c = i - rr * quads;
-                    const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + 4 * c;
-                    cp_async<4>((uint32_t)__cvta_generic_to_shared(fd + rr * QMV_FPITCH + 4 * c), sc8 + at);
-                }
+                for (int c = lane & 1; c < (chunk_groups >> 2); c += 2)
+                    cp_async<4>((uint32_t)__cvta_generic_to_shared(fd + 4 * c), src + 4 * c);
             } else {
-                for (int i = lane; i < 16 * chunk_groups; i += 32) {
-                    const int rr = i / chunk_groups, c = i - rr * chunk_groups;
-                    fd[rr * QMV_FPITCH + c] = sc8[(int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + c];
-                }
+                for (int c = lane & 1; c < chunk_groups; c += 2) fd[c] = src[c];
             }
             return;
         }
-        uint16_t *sd = sraw + buf * 16 * QMV_SPITCH, *bd = braw + buf * 16 * QMV_SPITCH;
+        const uint16_t *ss = sc + at0, *bs = bi + at0;
+        if (p.s_vec == 32) {  // the usual case, 16 groups per chunk in 16-byte pieces: one piece of each array per lane
+            cp_async_at<16, 0, 0>(sfast_dst, ss + 8 * (lane & 1));
+            cp_async_at<16, RAWB_OFS, 0>(sfast_dst, bs + 8 * (lane & 1));
+            return;
+        }
+        uint16_t *sd = sraw + rr * QMV_SPITCH;  // (affine: one raw buffer, repacked before the next copy starts)
+        uint16_t *bd = braw + rr * QMV_SPITCH;
         if (p.s_vec == 16) {  // 16-byte copies of 8 groups
-            const int chunks = chunk_groups >> 3;
-            for (int i = lane; i < 16 * chunks; i += 32) {
-                const int rr = i / chunks, c = i - rr * chunks;
-                const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + 8 * c;
-                cp_async<16>((uint32_t)__cvta_generic_to_shared(sd + rr * QMV_SPITCH + 8 * c), sc + at);
-                cp_async<16>((uint32_t)__cvta_generic_to_shared(bd + rr * QMV_SPITCH + 8 * c), bi + at);
+            for (int c = lane & 1; c < (chunk_groups >> 3); c += 2) {
+                cp_async<16>((uint32_t)__cvta_generic_to_shared(sd + 8 * c), ss + 8 * c);
+                cp_async<16>((uint32_t)__cvta_generic_to_shared(bd + 8 * c), bs + 8 * c);
             }
         } else if (p.s_vec == 4) {  // 4-byte copies of 2 groups
-            const int pairs = chunk_groups >> 1;
-            for (int i = lane; i < 16 * pairs; i += 32) {
-                const int rr = i / pairs, c = i - rr * pairs;
-                const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + 2 * c;
-                cp_async<4>((uint32_t)__cvta_generic_to_shared(sd + rr * QMV_SPITCH + 2 * c), sc + at);
-                cp_async<4>((uint32_t)__cvta_generic_to_shared(bd + rr * QMV_SPITCH + 2 * c), bi + at);
+            for (int c = lane & 1; c < (chunk_groups >> 1); c += 2) {
+                cp_async<4>((uint32_t)__cvta_generic_to_shared(sd + 2 * c), ss + 2 * c);
+                cp_async<4>((uint32_t)__cvta_generic_to_shared(bd + 2 * c), bs + 2 * c);
             }
         } else {
-            for (int i = lane; i < 16 * chunk_groups; i += 32) {
-                const int rr = i / chunk_groups, c = i - rr * chunk_groups;
-                const int64_t at = (int64_t)min(tile * 16 + rr, last_row) * row_groups + sg0 + c;
-                sd[rr * QMV_SPITCH + c] = sc[at];
-                bd[rr * QMV_SPITCH + c] = bi[at];
+            for (int c = lane & 1; c < chunk_groups; c += 2) {
+                sd[c] = ss[c];
+                bd[c] = bs[c];
             }
         }
     };
 
+    // Start of the run: the only divisions of the kernel outside tiles cut by a run boundary.
+    const int tile0 = (int)(lo / (uint32_t)ipt), it_first = (int)(lo - (uint32_t)tile0 * (uint32_t)ipt);
+    const int chunk0 = it_first / ci;
+
     // Prefetch cursor: the iteration whose words are copied next.
-    uint32_t pf = lo;
-    int pf_tile = (int)(lo / (uint32_t)ipt), pf_it = (int)(lo - (uint32_t)pf_tile * (uint32_t)ipt);
-    const int pf_tile0 = pf_tile, pf_it0 = pf_it;  // where this run starts
+    uint32_t pf_left = hi - lo;      // iterations of the run not yet requested
+    int pf_tile = tile0;
+    int pf_wrap = ipt - it_first;    // iterations until the cursor enters the next tile
     const uint32_t *pf_a = nullptr, *pf_q = nullptr;
-    auto pf_rows = [&]() {
-        pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + pf_it * (4 * LW);
-        pf_q = wbase + (size_t)min(pf_tile * 16 + r + 8, last_row) * row_words + pf_it * (4 * LW);
+    auto pf_rows = [&](int it) {
+        pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + it * (4 * LW);
+        pf_q = wbase + (size_t)min(pf_tile * 16 + r + 8, last_row) * row_words + it * (4 * LW);
     };
-    // Issues the copies of one iteration into `stage` and always commits one group, so the
-    // group count seen by wait_group is the same for every lane and iteration.
-    auto prefetch = [&](int stage) {
-        if (pf < hi) {
-#pragma unroll
-            for (int c = 0; c < CPL; c++) {
-                cp_async<CW * 4>(ring_s + stage * STAGE_BYTES + c * (32 * CW * 4), pf_a + c * CW);
-                cp_async<CW * 4>(ring_s + stage * STAGE_BYTES + HALF_BYTES + c * (32 * CW * 4), pf_q + c * CW);
-            }
+    // Issues the copies of one iteration into the stage at shared address `slot` and always commits
+    // one group, so the group count seen by wait_group is the same for every lane and iteration.
+    auto prefetch = [&](uint32_t slot) {
+        if (pf_left != 0u) {
+            static_for<CPL>([&](auto c_) {
+                constexpr int c = decltype(c_)::value;
+                cp_async_at<CW * 4, c * (32 * CW * 4), c * CW * 4>(slot, pf_a);
+                cp_async_at<CW * 4, HALF_BYTES + c * (32 * CW * 4), c * CW * 4>(slot, pf_q);
+            });
             pf_a += 4 * LW;
             pf_q += 4 * LW;
-            pf++;
-            if (++pf_it == ipt) {
-                pf_it = 0;
+            pf_left--;
+            if (--pf_wrap == 0) {
+                pf_wrap = ipt;
                 pf_tile++;
-                pf_rows();
+                pf_rows(0);
             }
         }
         cp_async_commit();
     };
+    // The ring stage of an iteration is its index in the tile modulo the ring depth whenever tiles
+    // and k-chunks are whole rounds of the ring (p.rounds): aligned rounds then know their stages at
+    // compile time.
+    const uint32_t first_stage = (uint32_t)it_first % QMV_STAGES;
 
     // Programmatic dependent launch: the next kernel of the stream may be scheduled from now on,
     // and this one starts copying weights (which no product writes) while the kernel before it is
     // still finishing; only then does it wait for that kernel's results.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (p.early_weights) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    } else {
+        // the caller's stream may hold a kernel that writes these weights: nothing is read early
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     if (lo < hi) {
-        stage_scales(pf_tile, pf_it / ci, 0);
-        pf_rows();
+        stage_scales(tile0, chunk0, 0);
+        pf_rows(it_first);
     }
 #pragma unroll
-    for (int st = 0; st < QMV_STAGES; st++) prefetch(st);
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // activations, scratch and output belong to this kernel from here
+    for (int st = 0; st < QMV_STAGES; st++) prefetch(ring_s + ((first_stage + st) % QMV_STAGES) * STAGE_BYTES);
+    if (p.early_weights)
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // activations, scratch and output belong to this kernel from here
     // ── stage the activations once per block (the first weight copies are already in flight) ──
     {
         const uint16_t *x = (const uint16_t *)p.x + xb * p.x_batch_stride;
-        const int blocks_per_row = (int)(p.K / CODES);
-        const int total_blocks = p.M * blocks_per_row;
-        for (int i = tid; i < total_blocks; i += QMV_THREADS) {
-            const int m = i / blocks_per_row, blk = i - m * blocks_per_row;
-            uint16_t in[CODES], outv[XW * 2];
-            const uint16_t *src = x + (int64_t)m * p.ldx + (int64_t)blk * CODES;
-            if (p.x_vec) {
-                if (CODES == 4) {
-                    *reinterpret_cast<uint2 *>(in) = __ldcg(reinterpret_cast<const uint2 *>(src));
+        const int blocks_per_row = (int)(row_words / UW);  // units (8-, 4-, 16- or 32-value blocks) per row
+        for (int m = 0; m < p.M; m++) {
+            const uint16_t *xrow_src = x + (int64_t)m * p.ldx;
+            uint32_t *xrow_dst = xs + (size_t)m * xs_pitch;
+            if (CODES == 8 && p.x_vec) {
+                // eight values per unit (4-bit codes): the pairs (x0,x4) (x1,x5) (x2,x6) (x3,x7) come out
+                // of one 16-byte load with four byte permutations and go back as one 16-byte store
+                for (int blk = tid; blk < blocks_per_row; blk += QMV_THREADS) {
+                    const uint4 in = __ldcg(reinterpret_cast<const uint4 *>(xrow_src) + blk);
+                    uint4 o;
+                    o.x = __byte_perm(in.x, in.z, 0x5410); o.y = __byte_perm(in.x, in.z, 0x7632);
+                    o.z = __byte_perm(in.y, in.w, 0x5410); o.w = __byte_perm(in.y, in.w, 0x7632);
+                    const int it = blk / (4 * WPL), tt = (blk / WPL) & 3, j = blk % WPL;
+                    *reinterpret_cast<uint4 *>(xrow_dst + (size_t)(((it * WPL + j) * 4 + tt) * XW)) = o;
+                }
+                continue;
+            }
+            for (int blk = tid; blk < blocks_per_row; blk += QMV_THREADS) {
+                uint16_t in[CODES], outv[XW * 2];
+                const uint16_t *src = xrow_src + (int64_t)blk * CODES;
+                if (p.x_vec) {
+                    if (CODES == 4) {
+                        *reinterpret_cast<uint2 *>(in) = __ldcg(reinterpret_cast<const uint2 *>(src));
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < CODES / 8; v++)
+                            *reinterpret_cast<uint4 *>(in + 8 * v) = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
+                    }
                 } else {
 #pragma unroll
-                    for (int v = 0; v < CODES / 8; v++)
-                        *reinterpret_cast<uint4 *>(in + 8 * v) = __ldcg(reinterpret_cast<const uint4 *>(src) + v);
+                    for (int j = 0; j < CODES; j++) in[j] = src[j];
                 }
-            } else {
+                U::permute(in, outv);
+                // unit `blk` of the row belongs to iteration blk / (4 WPL), lane t = (blk / WPL) % 4, unit j = blk % WPL
+                const int it = blk / (4 * WPL), tt = (blk / WPL) & 3, j = blk % WPL;
+                uint32_t *dst = xrow_dst + (size_t)(((it * WPL + j) * 4 + tt) * XW);
 #pragma unroll
-                for (int j = 0; j < CODES; j++) in[j] = src[j];
+                for (int v = 0; v < XW; v++) dst[v] = (uint32_t)outv[2 * v] | ((uint32_t)outv[2 * v + 1] << 16);
             }
-            U::permute(in, outv);
-            // word `blk` of the row belongs to iteration blk / (4 WPL), lane t = (blk / WPL) % 4, word j = blk % WPL
-            const int it = blk / (4 * WPL), tt = (blk / WPL) & 3, j = blk % WPL;
-            uint32_t *dst = xs + (size_t)m * xs_pitch + (size_t)(((it * WPL + j) * 4 + tt) * XW);
-#pragma unroll
-            for (int v = 0; v < XW; v++) dst[v] = (uint32_t)outv[2 * v] | ((uint32_t)outv[2 * v + 1] << 16);
         }
-        if (tid < 64) zero[tid] = 0u;
+        for (int i = tid; i < ZERO_WORDS; i += QMV_THREADS) zero[i] = 0u;
         if (tid < QMV_WARPS) lcount[tid] = 0u;
     }
     __syncthreads();  // activations staged
 
     const bool xrow = r < p.M;
-    const int x_it_step = xrow ? 4 * WPL * XW : 0;  // words per iteration in xs (0: stay on the zero page)
-    const uint32_t *xbase = xrow ? xs + (size_t)r * xs_pitch + t * XW : zero + t * XW;
+    const uint32_t x_it_bytes = xrow ? X_IT_WORDS * 4 : 0;  // bytes per iteration in xs (0: stay on the zero page)
+    const uint32_t xbase_s = (uint32_t)__cvta_generic_to_shared(xrow ? xs + (size_t)r * xs_pitch + t * XW : zero + t * XW);
     int seg_count = 0;   // segments started so far (buffer parity)
     int prev_iters = 0;  // iterations of the previous segment
-    int stage = 0;       // ring stage of the next iteration
+    uint32_t rs = ring_s + first_stage * STAGE_BYTES;  // this lane's slot in the ring stage consumed next
+    const uint32_t rs_end = ring_s + QMV_STAGES * STAGE_BYTES;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};  // rows r / r+8 x activation rows 2t / 2t+1
     float acd[4] = {0.f, 0.f, 0.f, 0.f};  // second accumulator: halves the MMA dependency chain
+    // per-segment state of the iteration body
+    uint32_t kofs = 0;    // k offset of this lane's words inside the chunk
+    uint32_t srow_s = 0;  // staged scale of (row r, group 0) of the segment's buffer; row r + 8, the biases
+                          // and the group are offsets from it
+    uint32_t xa = 0;      // this lane's activation words of the current iteration
 
-    int tile = pf_tile0, it0 = pf_it0;  // position of f in the sequence, kept without divisions
+    // One iteration.  J >= 0: the iteration is number J of an aligned round of QMV_STAGES whose ring
+    // stages, activation words and weight addresses are compile-time offsets from round-invariant
+    // registers, and whose copies need no end-of-run or end-of-tile checks; J < 0: anywhere, with
+    // every position kept in registers.
+    auto iteration = [&](auto stage_c, auto copy_c) {
+        constexpr int J = decltype(stage_c)::value;
+        constexpr bool FIX = J >= 0;
+        constexpr bool COPY = decltype(copy_c)::value;  // (rounds only) refill the stage; false once the run's last words are requested
+        constexpr int SO = FIX ? J * (int)STAGE_BYTES : 0;   // offset of the stage from the base address
+        constexpr int XO = FIX ? J * X_IT_WORDS * 4 : 0;     // offset of the iteration's activations
+        const uint32_t sb = FIX ? ring_s : rs;
+        cp_async_wait<QMV_STAGES - 1>();  // the oldest group, this iteration's words, has landed
+        uint32_t wa_[LW], wq_[LW];
+        if constexpr (UW == 3) {
+            static_for<LW>([&](auto c_) {
+                constexpr int c = decltype(c_)::value;
+                wa_[c] = lds32<SO + c * 128>(sb);
+                wq_[c] = lds32<SO + (int)HALF_BYTES + c * 128>(sb);
+            });
+        } else if constexpr (WPL == 8) {
+            static_for<2>([&](auto c_) {
+                constexpr int c = decltype(c_)::value;
+                uint4 a = lds128<SO + c * 512>(sb);
+                uint4 q = lds128<SO + (int)HALF_BYTES + c * 512>(sb);
+                wa_[(4 * c) % WPL] = a.x; wa_[(4 * c + 1) % WPL] = a.y; wa_[(4 * c + 2) % WPL] = a.z; wa_[(4 * c + 3) % WPL] = a.w;
+                wq_[(4 * c) % WPL] = q.x; wq_[(4 * c + 1) % WPL] = q.y; wq_[(4 * c + 2) % WPL] = q.z; wq_[(4 * c + 3) % WPL] = q.w;
+            });
+        } else if constexpr (WPL == 4) {
+            uint4 a = lds128<SO>(sb), q = lds128<SO + (int)HALF_BYTES>(sb);
+            wa_[0] = a.x; wa_[1 % WPL] = a.y; wa_[2 % WPL] = a.z; wa_[3 % WPL] = a.w;
+            wq_[0] = q.x; wq_[1 % WPL] = q.y; wq_[2 % WPL] = q.z; wq_[3 % WPL] = q.w;
+        } else if constexpr (WPL == 2) {
+            uint2 a = lds64<SO>(sb), q = lds64<SO + (int)HALF_BYTES>(sb);
+            wa_[0] = a.x; wa_[1 % WPL] = a.y;
+            wq_[0] = q.x; wq_[1 % WPL] = q.y;
+        } else {
+            wa_[0] = lds32<SO>(sb);
+            wq_[0] = lds32<SO + (int)HALF_BYTES>(sb);
+        }
+        const uint32_t g = (kofs + (FIX ? J * IK : 0)) >> p.gs_shift;
+        if (!FIX) kofs += IK;
+        GroupConsts ga, gq, ga1, gq1;  // (ga1, gq1: the second group of a lane's words, nvfp4 only)
+        if constexpr (U::FP != 0) {
+            const uint32_t fa = srow_s + g;
+            ga.s2 = fp4_scale2(lds_u8<0>(fa), U::FP == 1); gq.s2 = fp4_scale2(lds_u8<8 * QMV_FPITCH>(fa), U::FP == 1);
+            ga.b2 = gq.b2 = ga.ns2 = gq.ns2 = 0u;
+            ga1 = ga; gq1 = gq;
+            if (U::FP == 3 && WPL * CODES > 16) {
+                ga1.s2 = fp4_scale2(lds_u8<1>(fa), false);
+                gq1.s2 = fp4_scale2(lds_u8<8 * QMV_FPITCH + 1>(fa), false);
+            }
+        } else {
+            const uint32_t ca = srow_s + g * QMV_PKPITCH;
+            const uint2 ea = lds64<0>(ca), eq = lds64<8 * 8>(ca);
+            ga.s2 = ea.x; ga.b2 = ea.y;
+            gq.s2 = eq.x; gq.b2 = eq.y;
+            ga.ns2 = bf2_mul(ga.s2, 0xC300C300u);  // -128 s, exact
+            gq.ns2 = bf2_mul(gq.s2, 0xC300C300u);
+            ga1 = ga; gq1 = gq;
+        }
+        static_for<WPL>([&](auto j_) {
+            constexpr int j = decltype(j_)::value;
+            uint32_t ra[AREGS], rq[AREGS], xr[XW];
+            constexpr bool second = U::FP == 3 && j * CODES >= 16;  // nvfp4: 16 values per scale
+            U::run(&wa_[j * UW], second ? ga1 : ga, ra);
+            U::run(&wq_[j * UW], second ? gq1 : gq, rq);
+            if constexpr (XW == 2) {
+                uint2 q = lds64<XO + j * (4 * XW * 4)>(xa);
+                xr[0] = q.x; xr[1] = q.y;
+            } else {
+                static_for<XW / 4>([&](auto v_) {
+                    constexpr int v = 4 * decltype(v_)::value;
+                    uint4 q = lds128<XO + j * (4 * XW * 4) + v * 4>(xa);
+                    xr[v] = q.x; xr[v + 1] = q.y; xr[v + 2] = q.z; xr[v + 3] = q.w;
+                });
+            }
+#pragma unroll
+            for (int h = 0; h < AREGS / 2; h++) {
+                if ((j * (AREGS / 2) + h) & 1)
+                    mma_bf16_16816(acd, ra[2 * h], rq[2 * h], ra[2 * h + 1], rq[2 * h + 1], xr[2 * h], xr[2 * h + 1]);
+                else
+                    mma_bf16_16816(acc, ra[2 * h], rq[2 * h], ra[2 * h + 1], rq[2 * h + 1], xr[2 * h], xr[2 * h + 1]);
+            }
+        });
+        // Refill the slot just consumed (its words are in registers and already used).
+        if constexpr (FIX) {
+            if constexpr (COPY) {
+                static_for<CPL>([&](auto c_) {
+                    constexpr int c = decltype(c_)::value;
+                    cp_async_at<CW * 4, SO + c * (32 * CW * 4), (J * 4 * LW + c * CW) * 4>(ring_s, pf_a);
+                    cp_async_at<CW * 4, SO + (int)HALF_BYTES + c * (32 * CW * 4), (J * 4 * LW + c * CW) * 4>(ring_s, pf_q);
+                });
+            }
+            cp_async_commit();
+        } else {
+            xa += x_it_bytes;
+            prefetch(rs);
+            rs += STAGE_BYTES;
+            if (rs == rs_end) rs = ring_s;
+        }
+    };
+    const bool rounds = p.rounds != 0;
+
+    int tile = tile0, it0 = it_first, chunk = chunk0;  // position of f in the sequence, kept without divisions
     for (uint32_t f = lo; f < hi;) {
         // Segment: the part of one k-chunk of one tile that lies in [f, hi).
-        const int chunk = it0 / ci;
-        const int it1 = (int)min((uint32_t)((chunk + 1) * ci), hi - f + (uint32_t)it0);
+        const int cend = (chunk + 1) * ci;
+        const int it1 = (int)min((uint32_t)cend, hi - f + (uint32_t)it0);
         const uint32_t f1 = f + (uint32_t)(it1 - it0);
         const int seg_buf = seg_count & 1;
-        const uint16_t *sd = sraw + seg_buf * 16 * QMV_SPITCH, *bd = braw + seg_buf * 16 * QMV_SPITCH;
         // wait_group in the loop below covers a copy once QMV_STAGES groups were committed after it;
         // a shorter previous segment (or the very first one) needs an explicit wait.  Then the
-        // copies of all lanes are made visible across the warp, and the next segment's scales
-        // start their way into the buffer the previous segment has finished with.
+        // copies of all lanes are made visible across the warp.
         if (prev_iters <= QMV_STAGES) cp_async_wait<0>();
         __syncwarp();
-        if (f1 < hi) {
+        if constexpr (U::FP == 0) {
+            // Repack this chunk's raw scales and biases: lane (row rr, half hh) turns eight groups of its
+            // row into the pairs {s, s}, {b, b} at [group][row]; every (row, group) is then one 8-byte
+            // load per iteration instead of two 2-byte loads and two duplications.
+            const int rr = lane >> 1, hh = lane & 1;
+            const uint32_t raw = sraw_s + rr * (QMV_SPITCH * 2) + hh * 16;
+            const uint4 sv = lds128<0>(raw), bv = lds128<RAWB_OFS>(raw);
+            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+            const uint32_t dst = cpk_s + hh * (8 * QMV_PKPITCH) + rr * 8;
+            static_for<8>([&](auto i_) {
+                constexpr int i = decltype(i_)::value;
+                constexpr uint32_t sel = (i & 1) ? 0x3232u : 0x1010u;
+                sts64<i * QMV_PKPITCH>(dst, __byte_perm(sw[i >> 1], 0u, sel), __byte_perm(bw[i >> 1], 0u, sel));
+            });
+            __syncwarp();  // the constants are complete and the raw buffer is free
+        }
+        // The next segment's scales start their way into the buffer this one no longer needs.
+        if (f1 < hi) {  // the run goes on, so this segment ends with its chunk
             const bool wrap = it1 == ipt;
-            stage_scales(wrap ? tile + 1 : tile, wrap ? 0 : it1 / ci, (seg_count + 1) & 1);
+            stage_scales(wrap ? tile + 1 : tile, wrap ? 0 : chunk + 1, (seg_count + 1) & 1);
         }
         prev_iters = it1 - it0;
         seg_count++;
-        const int gofs = (it0 - chunk * ci) * IK + t * (WPL * CODES);  // k offset inside the chunk
-        const uint16_t *sa = sd + r * QMV_SPITCH, *sq = sd + (r + 8) * QMV_SPITCH;
-        const uint16_t *ba = bd + r * QMV_SPITCH, *bq = bd + (r + 8) * QMV_SPITCH;
-        const uint32_t *xp = xbase + (size_t)it0 * x_it_step;
-        for (int it = it0; it < it1; it++) {
-            cp_async_wait<QMV_STAGES - 1>();  // the oldest group, this iteration's words, has landed
-            uint32_t wa_[LW], wq_[LW];
-            {
-                const uint32_t *slot = ring + (size_t)stage * (2 * 32 * LW) + lane * CW;
-                if (UW == 3) {
-#pragma unroll
-                    for (int c = 0; c < LW; c++) {
-                        wa_[c] = slot[c * 32];
-                        wq_[c] = slot[32 * LW + c * 32];
+        kofs = (uint32_t)((it0 - chunk * ci) * IK + t * (WPL * CODES));
+        srow_s = U::FP ? sraw_s + seg_buf * (16 * QMV_FPITCH) + r * QMV_FPITCH : cpk_s + r * 8;
+        xa = xbase_s + (uint32_t)it0 * x_it_bytes;
+        int it = it0;
+        while (it < it1) {
+            // An aligned round: QMV_STAGES iterations that start at a multiple of the ring depth and
+            // whose copies (the QMV_STAGES iterations behind them) all lie inside the run; the cursor
+            // can only reach the end of its tile after the last of them.
+            if (QMV_STAGES == 4 && rounds && (it & 3) == 0 && it + 4 <= it1 && (pf_left >= 4u || pf_left == 0u)) {
+                if (pf_left != 0u) {
+                    static_for<4>([&](auto j_) { iteration(j_, std::true_type{}); });
+                    pf_a += 4 * 4 * LW;
+                    pf_q += 4 * 4 * LW;
+                    pf_left -= 4u;
+                    pf_wrap -= 4;
+                    if (pf_wrap == 0) {
+                        pf_wrap = ipt;
+                        pf_tile++;
+                        pf_rows(0);
                     }
-                } else if (WPL == 8) {
-#pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        uint4 a = *reinterpret_cast<const uint4 *>(slot + c * 128);
-                        uint4 q = *reinterpret_cast<const uint4 *>(slot + 32 * WPL + c * 128);
-                        wa_[(4 * c) % WPL] = a.x; wa_[(4 * c + 1) % WPL] = a.y; wa_[(4 * c + 2) % WPL] = a.z; wa_[(4 * c + 3) % WPL] = a.w;
-                        wq_[(4 * c) % WPL] = q.x; wq_[(4 * c + 1) % WPL] = q.y; wq_[(4 * c + 2) % WPL] = q.z; wq_[(4 * c + 3) % WPL] = q.w;
-                    }
-                } else if (WPL == 4) {
-                    uint4 a = *reinterpret_cast<const uint4 *>(slot), q = *reinterpret_cast<const uint4 *>(slot + 32 * WPL);
-                    wa_[0] = a.x; wa_[1 % WPL] = a.y; wa_[2 % WPL] = a.z; wa_[3 % WPL] = a.w;
-                    wq_[0] = q.x; wq_[1 % WPL] = q.y; wq_[2 % WPL] = q.z; wq_[3 % WPL] = q.w;
-                } else if (WPL == 2) {
-                    uint2 a = *reinterpret_cast<const uint2 *>(slot), q = *reinterpret_cast<const uint2 *>(slot + 32 * WPL);
-                    wa_[0] = a.x; wa_[1 % WPL] = a.y;
-                    wq_[0] = q.x; wq_[1 % WPL] = q.y;
                 } else {
-                    wa_[0] = slot[0];
-                    wq_[0] = slot[32 * WPL];
+                    static_for<4>([&](auto j_) { iteration(j_, std::false_type{}); });
                 }
-            }
-            const int g = (gofs + (it - it0) * IK) >> p.gs_shift;
-            GroupConsts ga, gq, ga1, gq1;  // (ga1, gq1: the second group of a lane's words, nvfp4 only)
-            if (U::FP) {
-                const uint8_t *fa = reinterpret_cast<const uint8_t *>(sraw) + seg_buf * (16 * QMV_FPITCH) + r * QMV_FPITCH;
-                const uint8_t *fq = fa + 8 * QMV_FPITCH;
-                ga.s2 = fp4_scale2(fa[g], U::FP == 1); gq.s2 = fp4_scale2(fq[g], U::FP == 1);
-                ga.b2 = gq.b2 = ga.ns2 = gq.ns2 = 0u;
-                ga1 = ga; gq1 = gq;
-                if (U::FP == 3 && WPL * CODES > 16) {
-                    ga1.s2 = fp4_scale2(fa[g + 1], false);
-                    gq1.s2 = fp4_scale2(fq[g + 1], false);
-                }
+                it += 4;
+                kofs += 4 * IK;
+                xa += 4 * x_it_bytes;
             } else {
-                ga.s2 = (uint32_t)sa[g] * 0x10001u; ga.b2 = (uint32_t)ba[g] * 0x10001u;
-                gq.s2 = (uint32_t)sq[g] * 0x10001u; gq.b2 = (uint32_t)bq[g] * 0x10001u;
-                ga.ns2 = bf2_mul(ga.s2, 0xC300C300u);  // -128 s, exact
-                gq.ns2 = bf2_mul(gq.s2, 0xC300C300u);
-                ga1 = ga; gq1 = gq;
+                iteration(std::integral_constant<int, -1>{}, std::true_type{});
+                it++;
             }
-#pragma unroll
-            for (int j = 0; j < WPL; j++) {
-                uint32_t ra[AREGS], rq[AREGS], xr[XW];
-                const bool second = U::FP == 3 && j * CODES >= 16;  // nvfp4: 16 values per scale
-                U::run(&wa_[j * UW], second ? ga1 : ga, ra);
-                U::run(&wq_[j * UW], second ? gq1 : gq, rq);
-                if (XW == 2) {
-                    uint2 q = *reinterpret_cast<const uint2 *>(xp + j * 4 * XW);
-                    xr[0] = q.x; xr[1] = q.y;
-                } else {
-#pragma unroll
-                    for (int v = 0; v < XW; v += 4) {
-                        uint4 q = *reinterpret_cast<const uint4 *>(xp + j * 4 * XW + v);
-                        xr[v] = q.x; xr[v + 1] = q.y; xr[v + 2] = q.z; xr[v + 3] = q.w;
-                    }
-                }
-#pragma unroll
-                for (int h = 0; h < AREGS / 2; h++) {
-                    if ((j * (AREGS / 2) + h) & 1)
-                        mma_bf16_16816(acd, ra[2 * h], rq[2 * h], ra[2 * h + 1], rq[2 * h + 1], xr[2 * h], xr[2 * h + 1]);
-                    else
-                        mma_bf16_16816(acc, ra[2 * h], rq[2 * h], ra[2 * h + 1], rq[2 * h + 1], xr[2 * h], xr[2 * h + 1]);
-                }
-            }
-            xp += x_it_step;
-            // Refill the slot just consumed (its words are in registers and already used).
-            prefetch(stage);
-            stage = stage + 1 == QMV_STAGES ? 0 : stage + 1;
         }
         f = f1;
         if (it1 != ipt && f1 != hi) {  // the tile goes on in the next k-chunk
             it0 = it1;
+            chunk++;
             continue;
         }
         const int done_tile = tile;
         if (it1 == ipt) {
             tile++;
             it0 = 0;
+            chunk = 0;
         } else it0 = it1;
 
         // ── the run leaves this tile: rows r, r + 8; activation rows 2t, 2t + 1 ─────────
@@ -759,63 +1002,18 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         const int n0 = done_tile * 16;
         const uint32_t t_lo = (uint32_t)done_tile * (uint32_t)ipt, t_hi = t_lo + (uint32_t)ipt;
         bool store = lo <= t_lo && hi >= t_hi;  // the whole tile was this warp's
-        uint32_t c1 = 0, w1 = 0, c2 = 0, w2 = 0;
         if (!store) {
-            owner(t_lo, c1, w1);
-            owner(t_hi - 1, c2, w2);
-        }
-        if (!store && c1 == c2) {
-            // Every warp that holds a part of this tile belongs to this block: the partials meet in
-            // shared memory.  A warp leaves at most two (the tile its run starts in and the one it
-            // ends in); the warp that arrives last adds them in run order.
-            float *mine = lpart + (warp * 2 + (done_tile == pf_tile0 ? 0 : 1)) * 128;
-            *reinterpret_cast<float2 *>(mine + r * 8 + 2 * t) = make_float2(v[0], v[1]);
-            *reinterpret_cast<float2 *>(mine + (r + 8) * 8 + 2 * t) = make_float2(v[2], v[3]);
-            __threadfence_block();
-            __syncwarp();
-            uint32_t arrived = 0;
-            if (lane == 0) arrived = atomicAdd(lcount + w1, 1u);
-            arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
-            if (arrived == w2 - w1) {
-                __threadfence_block();
-                v[0] = v[1] = v[2] = v[3] = 0.f;
-                for (uint32_t w = w1; w <= w2; w++) {
-                    // warp w left this tile's partial in its slot 0 if its run starts in the tile
-                    const uint32_t w_lo = blk_lo + part_lo(w, wq, wr);
-                    const float *src = lpart + (w * 2 + (w_lo >= t_lo ? 0 : 1)) * 128;
-                    float2 a = *reinterpret_cast<const float2 *>(src + r * 8 + 2 * t);
-                    float2 q = *reinterpret_cast<const float2 *>(src + (r + 8) * 8 + 2 * t);
-                    v[0] += a.x; v[1] += a.y; v[2] += q.x; v[3] += q.y;
-                }
-                store = true;
-            }
-        } else if (!store) {
-            // The tile is cut by a block boundary: the warps first .. last (numbered through the
-            // grid, every block of a multi-block grid runs all its warps), this one number `mine`,
-            // leave their 16 x 8 partials in scratch; the one that arrives last adds them in run
-            // order (so the result does not depend on arrival order) and rearms the counter.
-            const int first = (int)(c1 * QMV_WARPS + w1), last = (int)(c2 * QMV_WARPS + w2);
-            const int mine = (int)blockIdx.x * QMV_WARPS + warp - first, count = last - first + 1;
             const int64_t slot = b * tiles + done_tile;
-            float *part = p.partials + slot * p.max_parts * 128;
-            __stcg(reinterpret_cast<float2 *>(part + mine * 128 + r * 8 + 2 * t), make_float2(v[0], v[1]));
-            __stcg(reinterpret_cast<float2 *>(part + mine * 128 + (r + 8) * 8 + 2 * t), make_float2(v[2], v[3]));
-            __threadfence();
-            __syncwarp();
-            uint32_t arrived = 0;
-            if (lane == 0) arrived = atomicAdd(p.counters + slot, 1u);
-            arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
-            if (arrived == (uint32_t)count - 1) {
-                __threadfence();
-                v[0] = v[1] = v[2] = v[3] = 0.f;
-                for (int s2 = 0; s2 < count; s2++) {
-                    float2 a = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + r * 8 + 2 * t));
-                    float2 q = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + (r + 8) * 8 + 2 * t));
-                    v[0] += a.x; v[1] += a.y; v[2] += q.x; v[3] += q.y;
-                }
-                if (lane == 0) p.counters[slot] = 0u;
-                store = true;
-            }
+            QmvCut c;
+            c.lo = lo; c.hi = hi; c.blk_lo = blk_lo; c.blk_len = blk_len; c.wq = wq; c.wr = wr;
+            c.blk_q = blk_q; c.blk_r = blk_r; c.t_lo = t_lo; c.t_hi = t_hi;
+            c.warp = warp; c.lane = lane; c.first_tile = done_tile == tile0 ? 1 : 0;
+            c.max_parts = p.max_parts; c.lpart = lpart; c.lcount = lcount;
+            c.part = p.partials + slot * p.max_parts * 128;
+            c.counter = p.counters + slot;
+            float4 vv = make_float4(v[0], v[1], v[2], v[3]);
+            store = qmv_meet_partials(c, vv);
+            v[0] = vv.x; v[1] = vv.y; v[2] = vv.z; v[3] = vv.w;
         }
         if (store && U::FP) {
 #pragma unroll
@@ -918,13 +1116,13 @@ int qmv_kind(int32_t mode, int32_t bits) {
     return 0;
 }
 
-// Words per lane per iteration: the widest vector load whose 4-lane span divides K.  Eight words
-// (two 16-byte copies) execute fewer instructions per weight but issue slower on the B200 than
-// four; they stay selectable with NUVEC_QMV_MAX_WPL=8.
+// Words per lane per iteration: the widest vector load, up to four words, whose 4-lane span divides
+// K.  (Eight words, two 16-byte copies, execute fewer instructions per weight but were measured to
+// issue slower on the B200 than four.)
 static int wpl_for(int bits, int gs, int64_t K) {
     if (bits != 2 && bits != 3 && bits != 4 && bits != 6 && bits != 8 && !kind_fp(bits)) return 0;
     const int codes = codes_per_word(bits);
-    static const int cap = [] { const char *e = getenv("NUVEC_QMV_MAX_WPL"); return e && *e ? atoi(e) : 4; }();
+    const int cap = 4;
     const int span = bits == 41 ? 2 * gs : gs;   // nvfp4 lanes may hold two groups of 16
     for (int wpl = bits == 3 ? 1 : bits == 2 || bits == 6 ? 2 : kind_fp(bits) ? 4 : 8; wpl >= 1; wpl >>= 1) {
         if (wpl > cap) continue;
@@ -936,7 +1134,7 @@ static int wpl_for(int bits, int gs, int64_t K) {
 
 static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
     const int codes = codes_per_word(bits), xw = codes / 2, lw = wpl * unit_words(bits);
-    return (size_t)(M * (K / codes * xw + 16) + 64 + QMV_WARPS * (2 * 16 * QMV_SPITCH) +
+    return (size_t)(M * (K / codes * xw + 16) + qmv_zero_words(wpl, xw) + QMV_WARPS * (QMV_SCALE_AREA / 4) +
                     qmv_stages(wpl) * 2 * QMV_THREADS * lw + QMV_WARPS * 2 * 128 + QMV_WARPS + 4) * 4 + 16;
 }
 
@@ -957,13 +1155,23 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
     return qmv_smem((int)M, K, bits, wpl) <= 220 * 1024;  // all activations are staged in shared memory
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of each kernel
+// instantiation: the largest size set so far is kept per device ordinal.
+constexpr int QMV_MAX_DEVICES = 64;
+static std::mutex g_qmv_cfg_mu;
+
 template <int BITS, int WPL>
 static int32_t launch_qmv_cfg(nvc_device *dev, QmvParams &p, dim3 grid, size_t smem) {
     auto kernel = qmv_affine_kernel<BITS, WPL>;
-    static size_t configured = 0;  // largest dynamic shared memory size set so far (per instantiation)
-    if (smem > 48 * 1024 && smem > configured) {
-        NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+    static size_t configured[QMV_MAX_DEVICES] = {};
+    if (dev->ordinal < 0 || dev->ordinal >= QMV_MAX_DEVICES)
+        return set_error(NVC_ERR_UNSUPPORTED, "qmv: device ordinal %d", dev->ordinal);
+    if (smem > 48 * 1024) {
+        std::lock_guard<std::mutex> g(g_qmv_cfg_mu);
+        if (smem > configured[dev->ordinal]) {
+            NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured[dev->ordinal] = smem;
+        }
     }
     // Launched with programmatic stream serialization: the kernel may start while its predecessor
     // drains and synchronises with it on the device (griddepcontrol.wait) before it reads
@@ -979,13 +1187,11 @@ static int32_t launch_qmv_cfg(nvc_device *dev, QmvParams &p, dim3 grid, size_t s
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    // On a stream adopted from the caller the kernel before this one may be anybody's, including one
+    // that produces these weights: nothing is read ahead of it there.
+    p.early_weights = dev->stream == dev->own_stream ? 1 : 0;
     NVC_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return check_launch(dev, "qmv_affine_kernel");
-}
-
-static int64_t env_int(const char *name, int64_t fallback) {
-    const char *e = getenv(name);
-    return e && *e ? atoll(e) : fallback;
 }
 
 int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t batch, const QmvScratch *fixed) {
@@ -1012,7 +1218,7 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
         const int64_t rg = p.K / p.gs, cg = chunk / p.gs;
         const uintptr_t al = (uintptr_t)p.scales | (uintptr_t)p.biases;
         if (kind_fp(bits)) p.s_vec = (al % 4 == 0 && p.s_batch_stride % 4 == 0 && rg % 4 == 0 && cg % 4 == 0) ? 4 : 0;
-        else if (al % 16 == 0 && p.s_batch_stride % 8 == 0 && rg % 8 == 0 && cg % 8 == 0) p.s_vec = 16;
+        else if (al % 16 == 0 && p.s_batch_stride % 8 == 0 && rg % 8 == 0 && cg % 8 == 0) p.s_vec = cg == 16 ? 32 : 16;
         else if (al % 4 == 0 && p.s_batch_stride % 2 == 0 && rg % 2 == 0 && cg % 2 == 0) p.s_vec = 4;
         else p.s_vec = 0;
     }
@@ -1023,14 +1229,11 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(smem + 1024);
     if (per_sm > QMV_BLOCKS_PER_SM) per_sm = QMV_BLOCKS_PER_SM;
     if (per_sm < 1) per_sm = 1;
-    per_sm = env_int("NUVEC_QMV_PER_SM", per_sm);
     int64_t blocks = per_sm * dev->prop.multiProcessorCount / batch;
-    const int64_t min_iters = env_int("NUVEC_QMV_MIN_ITERS", 4);
+    const int64_t min_iters = 4;
     const int64_t useful = (total + QMV_WARPS * min_iters - 1) / (QMV_WARPS * min_iters);
     if (blocks > useful) blocks = useful;
-    const int64_t env_blocks = env_int("NUVEC_QMV_BLOCKS", 0);
-    if (env_blocks > 0) blocks = env_blocks;
-    else if (env_int("NUVEC_QMV_ALIGN", 1) != 0 && blocks > 1) {
+    if (blocks > 1) {
         // A tile cut by a block boundary costs its warps a round trip through scratch; one cut between
         // warps of a block is settled in shared memory.  So, while blocks hold only a few tiles,
         // prefer a block count that divides the tiles if one lies within two fifths of the
@@ -1050,6 +1253,15 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     p.max_parts = (int32_t)(ipt / run + 2);
     p.blk_q = (uint32_t)(total / blocks);
     p.blk_r = (uint32_t)(total % blocks);
+    p.row_groups = (int32_t)(p.K / p.gs);
+    p.row_words = (uint32_t)(p.K * code_bits(bits) / 32);
+    p.ipt = (int32_t)ipt;
+    p.ci = (int32_t)(chunk / ik);
+    p.chunk_groups = (int32_t)(chunk / p.gs);
+    p.tiles = (int32_t)tiles;
+    p.rounds = (ipt % 4 == 0 && p.ci % 4 == 0) ? 1 : 0;
+    p.xs_pitch = (int32_t)(p.K / codes * (codes / 2) + 16);
+    if (!p.rhs) p.experts = p.x_batches = 0;
     const size_t partial_bytes = (size_t)tiles * batch * p.max_parts * 128 * sizeof(float);
     if (fixed) {
         // Scratch of fixed capacity provided by the caller of this function: nothing is allocated.

@@ -21,6 +21,7 @@ struct GenericParams {
     const void *scales, *biases;
     const float *global;
     const uint32_t *lhs, *rhs;  // gathered batches (rhs == nullptr: plain batches)
+    uint32_t experts, x_batches;  // what rhs / lhs may address; an index past the end selects the last one
     int64_t M, N, K, ldx, batch;
     int64_t x_batch_stride, w_batch_stride, s_batch_stride;  // elements (w: uint32 words)
     void *y;
@@ -40,6 +41,21 @@ struct QmvParams {
     int64_t x_batch_stride, w_batch_stride, s_batch_stride;
     int32_t M, gs, gs_shift, chunk_k, max_parts, x_vec, s_vec;
     uint32_t blk_q, blk_r;  // iterations per block: blk_q, one more in the first blk_r blocks
+    // Derived by the launch so that the kernel never divides on its hot paths:
+    int32_t row_groups;     // K / group size
+    uint32_t row_words;     // K * bits / 32
+    int32_t ipt;            // iterations per 16-row tile
+    int32_t ci;             // iterations per k-chunk
+    int32_t chunk_groups;   // groups per k-chunk
+    int32_t tiles;          // 16-row tiles of one product
+    int32_t rounds;         // 1: tiles and k-chunks are whole multiples of four iterations
+    int32_t xs_pitch;       // words between staged activation rows
+    // Gathers: number of weight batches and activation batches the index lists may address; an index
+    // past the end selects the last one (the reference's `take` clamps).  0 - 1 = no limit.
+    uint32_t experts, x_batches;
+    // 1: weights, scales and biases may be read before the previous kernel of the stream has
+    // finished (they are constants of the stream's work); 0: nothing is read before it has.
+    int32_t early_weights;
     const float *global;       // nvfp4 global scale(s) or nullptr
     int32_t expert_global;     // one value per expert (indexed like the weights' batch)
     // Fused gather (nullptr: plain product).  The result goes to every rank's region instead of y.
