@@ -43,6 +43,10 @@ PROJECTIONS = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096),
 LAYERS = 36
 GS, BITS = 64, 4
 PREFILL = (2048, 12288, 4096)  # M, N, K
+# DRAM bytes (read + write) of one launch of the few-row kernel on each projection at M = 1, from an
+# ncu capture of three launches per shape on distinct weight copies (profiles/qmv_dram_traffic_decode.md):
+# within 0.6 % of the algorithmic bytes, i.e. every weight byte crosses HBM once.
+NCU_DRAM_BYTES = {"qkv": 14.23e6, "o": 9.51e6, "gate_up": 56.70e6, "down": 28.41e6}
 
 
 def qmv_bytes(M, N, K, bits=BITS, gs=GS, s=4):
@@ -140,16 +144,25 @@ def cpu_layer_inputs(seed=0):
     return out
 
 
-def time_cpu_layer(inputs, reps):
-    """Seconds per layer (4 projections, M = 1) through the oracle's quantized_matmul, with the
-    reference's serial dequantize (kernels.rs:852-856) and parallel few-row product."""
+def use_all_host_threads():
+    """The CPU arm runs on every core of this host, whatever OMP_NUM_THREADS the launcher exported
+    (torchrun sets it to 1); returns the thread count used."""
+    import oracle
+    oracle.set_threads(os.cpu_count() or 1)
+    return oracle.threads()
+
+
+def time_cpu_layer(inputs, reps, parallel_dequant=False):
+    """Seconds per layer (4 projections, M = 1) through the oracle's quantized_matmul: the
+    reference's serial dequantize (kernels.rs:852-856) by default, all threads with
+    `parallel_dequant`; the few-row product runs over all threads either way."""
     import oracle
     best = float("inf")
     for _ in range(reps):
         t0 = time.perf_counter()
         for _, _, _, x, codes, scales, biases in inputs:
             oracle.quantized_matmul(x, codes, scales, biases, oracle.BF16, oracle.AFFINE, GS, BITS, True,
-                                    parallel_dequant=False)
+                                    parallel_dequant=parallel_dequant)
         best = min(best, time.perf_counter() - t0)
     return best
 
@@ -159,9 +172,12 @@ def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import oracle
+    threads = use_all_host_threads()
     inputs = cpu_layer_inputs()
     layer_bytes = sum(qmv_bytes(1, N, K) for _, N, K in PROJECTIONS)
+    # A step of this arm is the bounded sample it really runs: one layer of the token (a whole token
+    # is 36 such layers and would take minutes on the CPU).  `ms_per_step` is the measured time of
+    # that sample; `value` is a rate, so it compares with the GPU arm's directly.
     for _ in range(max(args.warmup, 0)):
         time_cpu_layer(inputs, 1)
     t0 = time.perf_counter()
@@ -169,13 +185,18 @@ def reference_arm(args):
         time_cpu_layer(inputs, 1)
     dt = (time.perf_counter() - t0) / max(args.steps, 1)
     value = layer_bytes / dt / 1e9
-    sample = "one layer (qkv, o, gate+up, down at M=1) per step; a full token is 36 such layers"
+    par = layer_bytes / time_cpu_layer(inputs, 1, parallel_dequant=True) / 1e9
+    sample = ("one layer (qkv, o, gate+up, down at M=1) per step: 1/36 of the GPU arm's step; serial dequantize as "
+              "the reference (kernels.rs:852-856), few-row product over all threads")
+    config = dict(workload_config(args.gpus), sample=sample)
     line = {"impl": "reference", "metric": "quantized_matmul weight GB/s (M=1)", "value": value, "unit": "GB/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * LAYERS,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(args.gpus),
-            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": oracle.threads(), "kind": "port",
-                             "sample": sample},
+            "config": config,
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample,
+                             "host_cores": os.cpu_count(), "value_parallel_dequantize": par,
+                             "note": "value_parallel_dequantize: the same layer with the dequantize spread over all "
+                                     "threads, which the reference does not do"},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
@@ -187,6 +208,55 @@ def workload_config(gpus):
             "parallelism": f"N-sharded x{gpus} + all_gather" if gpus > 1 else "single GPU",
             "l2": "inputs larger than L2 (3.9 GB of weights per step, 108 MB per layer)",
             "weights": "one seeded layer (W ~ N(0, 0.02) -> bf16 -> nuvec quantize) replicated into 36 distinct buffers"}
+
+
+# ── parity of what is timed, checked on the bench's own arrays before any timing ────────────
+def product_error(got, want):
+    """Worst |got - want| / (1e-2 * ||row||_inf) over the rows of a bfloat16 product (<= 1 passes)."""
+    import oracle
+    g = oracle.to_f32(got, oracle.BF16).astype(np.float64)
+    w = oracle.to_f32(want, oracle.BF16).astype(np.float64)
+    bound = 1e-2 * np.abs(w).max(axis=1, keepdims=True) + 1e-30
+    return float((np.abs(g - w) / bound).max())
+
+
+def check_products(nv, lib, dev, qc, cases, what):
+    """Every case (name, M, q, x): random rows against the oracle's product within the stated
+    1e-2 * ||row||_inf, on all output rows when M <= 8 and on a subset otherwise, and unit-vector
+    rows bit for bit against the oracle's dequantize.  Raises SystemExit on the first difference."""
+    import oracle
+    rng = np.random.default_rng(4242)
+    worst = 0.0
+    for name, M, q, x in cases:
+        n, K = q.weight.shape[0], x.shape[-1]
+        c = q.weight.to_numpy()
+        s = q.scales.to_numpy().view(np.uint16)
+        b = q.biases.to_numpy().view(np.uint16)
+        xh = x.to_numpy().view(np.uint16).reshape(M, K)
+        y = dev.empty((M, n), nv.BF16)
+
+        def run(xa):
+            rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, xa.ptr, q.weight.ptr, q.scales.ptr,
+                                          q.biases.ptr, None, M, n, K, K, 1, 0, 0, 0, y.ptr)
+            assert rc == 0
+            return y.to_numpy().view(np.uint16).reshape(M, n)
+
+        got = run(x)
+        rows = np.arange(n) if M <= 8 else np.sort(rng.permutation(n)[:128])
+        want = oracle.quantized_matmul(xh, c[rows], s[rows], b[rows], oracle.BF16, oracle.AFFINE, GS, BITS)
+        err = product_error(got[:, rows], want)
+        worst = max(worst, err)
+        if not err <= 1.0:
+            raise SystemExit(f"parity check failed: {what} {name}: error {err:.3f} x the bound 1e-2*||row||_inf")
+        ks = rng.integers(0, K, M)
+        xu = np.zeros((M, K), np.float32)
+        xu[np.arange(M), ks] = 1.0
+        got = run(dev.array(nv.f32_to_bf16(xu), nv.BF16))
+        rows = np.sort(rng.permutation(n)[:min(n, 512)])
+        dense = oracle.dequantize(c[rows], s[rows], b[rows], oracle.BF16, oracle.AFFINE, GS, BITS)
+        if not np.array_equal(got[:, rows], dense[:, ks].T):
+            raise SystemExit(f"parity check failed: {what} {name}: unit-vector rows differ from the oracle's dequantize")
+    return worst
 
 
 # ── GPU arm ────────────────────────────────────────────────────────────────────────────────
@@ -201,6 +271,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the parity check that precedes the timing")
     ap.add_argument("--sweep", action="store_true", help="time every single-GPU configuration of the benchmark definition and print one JSON object")
     ap.add_argument("--no-graph", action="store_true", help="launch every product from the host instead of replaying a recorded step")
     args = ap.parse_args()
@@ -260,6 +331,15 @@ def main():
         layers.append(projs)
     dev.synchronize()
 
+    qc = quant._c()
+    # What the timed region runs, checked first (rank 0's slices): abort instead of timing wrong results.
+    parity = None
+    if rank == 0 and not args.no_check:
+        worst = check_products(nv, lib, dev, qc, [(name, M, q, x) for name, N, K, n_local, q, x in base], "decode")
+        parity = {"status": "ok", "worst_error_over_bound": worst,
+                  "what": "the step's four products on this rank's arrays: all rows against the oracle within "
+                          "1e-2*||row||_inf, unit-vector rows bit for bit against the oracle's dequantize"}
+
     comm = None
     if world > 1:
         import torch
@@ -273,8 +353,6 @@ def main():
         h = C.c_void_p()
         assert lib.nvc_comm_init(dev._h, rank, world, idb, C.byref(h)) == 0, _ffi.last_error()
         comm = h
-
-    qc = quant._c()
 
     # ── fused product + gather over peer stores (the multi-GPU headline; NCCL stays as the check) ──
     fused = None
@@ -408,8 +486,15 @@ def main():
     launch_bytes = step_bytes / world / n_kernels
     launch_s = (ms_kernel_only / args.steps) * 1e-3 / n_kernels
     achieved = launch_bytes / launch_s / 1e9
+    # ncu's DRAM bytes per launch, averaged over the step's four shapes; a rank of an N-sharded step
+    # streams 1/N of every matrix (traffic is proportional to the rows a launch covers)
+    traffic = sum(NCU_DRAM_BYTES.values()) / len(NCU_DRAM_BYTES) / world if M == 1 else None
     roofline = {"kernel": "qmv_affine_kernel", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
+                "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture per shape "
+                                "(profiles/qmv_dram_traffic_decode.md), averaged over the four shapes" +
+                                ("" if world == 1 else f", scaled by 1/{world} for this rank's row slice"),
+                "peak_source": peaks["source"],
                 "avg_launch_us": launch_s * 1e6, "algorithmic_bytes_per_launch": launch_bytes}
 
     line = {"metric": "quantized_matmul weight GB/s (M=1)", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -417,6 +502,9 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload_config(world), launch="recorded step replayed (CUDA graph)" if graph is not None else "host launches"),
             "roofline": roofline, "gpu_launches": launches, "clocks": clocks}
+    if parity is not None:
+        line["parity_check"] = parity["status"]
+        line["parity"] = parity
     if world > 1:
         line["kernel_only"] = {"value": step_bytes / (ms_kernel_only / args.steps * 1e-3) / 1e9, "unit": "GB/s",
                                "note": "same step without any gather after the products"}
@@ -464,18 +552,22 @@ def main():
 
     # ── prefill product on tcgen05 (rank 0's view; N-sharded like the decode products) ───────
     if not args.no_prefill:
-        line["also"] = [prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier)]
+        line["also"] = [prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier, not args.no_check)]
 
     # ── CPU baseline on this host's cores (rank 0, bounded sample) ───────────────────────────
     if rank == 0 and world == 1 and not args.no_cpu:
-        import oracle
+        threads = use_all_host_threads()
         inputs = cpu_layer_inputs()
         secs = time_cpu_layer(inputs, 3)
+        secs_par = time_cpu_layer(inputs, 2, parallel_dequant=True)
         layer_bytes = sum(qmv_bytes(1, N, K) for _, N, K in PROJECTIONS)
-        line["cpu_baseline"] = {"value": layer_bytes / secs / 1e9, "unit": "GB/s", "cores": oracle.threads(),
+        line["cpu_baseline"] = {"value": layer_bytes / secs / 1e9, "unit": "GB/s", "cores": threads,
                                 "kind": "port", "host_cores": os.cpu_count(),
                                 "sample": "one layer (4 products, M=1), best of 3; serial dequantize as the reference, "
-                                          "few-row product over all threads", "seconds_per_layer": secs}
+                                          "few-row product over all threads", "seconds_per_layer": secs,
+                                "value_parallel_dequantize": layer_bytes / secs_par / 1e9,
+                                "note": "value_parallel_dequantize: the same layer with the dequantize spread over all "
+                                        "threads, which the reference does not do"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     # Multi-rank runs leave without tearing down: the ranks meet at a barrier and exit.  (Destroying
@@ -568,7 +660,7 @@ def config_sweep(nv, _ffi, dev, peaks):
 
     a4 = nv.Quant.affine(GS, BITS)
     dense("C1 qmv", 1, 4096, 4096, a4, 64, 20)
-    for bits in (2, 3, 6, 8):  # 3- and 6-bit codes straddle words: generic kernel
+    for bits in (2, 3, 6, 8):  # 3- and 6-bit codes straddle words: three-word units in the few-row kernel
         dense(f"C1 qmv b{bits}", 1, 4096, 4096, nv.Quant.affine(GS, bits), 64, 10)
     for M in (1, 4, 8):
         for name, N, K in PROJECTIONS:
@@ -611,7 +703,7 @@ def config_sweep(nv, _ffi, dev, peaks):
 
 
 
-def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier):
+def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier, check=True):
     M, N, K = PREFILL
     n_local = N // world
     rng = np.random.default_rng(1)
@@ -636,6 +728,13 @@ def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier):
                                           q.biases.ptr, None, M, n_local, K, K, 1, 0, 0, 0, y.ptr)
             assert rc == 0, _ffi.last_error()
 
+    if rank == 0 and check:
+        worst = check_products(nv, lib, dev, qc, [("prefill", M, qs[0][0], qs[0][1])], "prefill")
+        checked = {"status": "ok", "worst_error_over_bound": worst,
+                   "what": "128 output columns against the oracle within 1e-2*||row||_inf, 2048 unit-vector rows bit for "
+                           "bit against the oracle's dequantize on 512 weight rows"}
+    else:
+        checked = None
     for _ in range(3):
         step()
     steps = 10
@@ -645,6 +744,7 @@ def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier):
     per_launch = 2.0 * M * n_local * K / ((ms / steps) * 1e-3 / copies) / 1e12
     return {"workload": f"prefill qmm M={M} K={K} N={N} affine 4-bit g64", "metric": "quantized_matmul TFLOP/s (M=2048)",
             "value": tf, "unit": "TFLOP/s", "ms_per_product": ms / steps / copies, "gpu_launches": launches,
+            "parity_check": None if checked is None else checked["status"], "parity": checked,
             "roofline": {"kernel": "qmm kernel", "bound": "tensor", "achieved": per_launch, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": per_launch / peaks["bf16_tflops"], "traffic": None,
                          "peak_source": peaks["source"] + " (burst)"}}

@@ -191,3 +191,8 @@ def gather_qmm(x, codes, scales, biases, lhs, rhs, dtype, mode=AFFINE, group_siz
 
 def threads() -> int:
     return int(lib().orc_threads())
+
+
+def set_threads(n: int) -> None:
+    """Threads for the parallel parts from now on (overrides an inherited OMP_NUM_THREADS)."""
+    lib().orc_set_threads(int(n))

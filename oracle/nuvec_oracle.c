@@ -33,6 +33,16 @@ int orc_threads(void) {
 #endif
 }
 
+/* Threads the parallel parts use from now on (launchers such as torchrun export OMP_NUM_THREADS=1;
+ * the timed CPU arm asks for the host's cores explicitly, as the reference's rayon pool would take them). */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ── scalar conversions ─────────────────────────────────────────────────────────────── */
 
 static inline uint32_t f32_bits(float x) {

@@ -89,6 +89,7 @@ int orc_gather_qmm(int mode, int group_size, int bits, int dtype, int transpose,
 void orc_matmul_nt_f32(const float *x, const float *w, size_t M, size_t N, size_t K, float *y);
 
 int orc_threads(void);
+void orc_set_threads(int n);
 
 #ifdef __cplusplus
 }
