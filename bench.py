@@ -364,8 +364,17 @@ def main():
                 row = []
                 for name, N, K, n_local, q, x, y in projs:
                     row.append(at)
-                    at += (world * M * n_local * 2 + 255) // 256 * 256
+                    at += lib.nvc_gather_footprint(world, M, n_local)
                 offsets.append(row)
+            # packet areas of the K-sharded products of the paired layout (o and down), one pair per layer
+            sum_offsets = []
+            for projs in layers:
+                row = {}
+                for name, N, K, n_local, q, x, y in projs:
+                    if name in ("o", "down"):
+                        row[name] = at
+                        at += lib.nvc_all_sum_footprint(world, M, N)
+                sum_offsets.append(row)
             region, handle = C.c_void_p(), (C.c_uint8 * 64)()
             assert lib.nvc_symm_alloc(dev._h, at, C.byref(region), handle) == 0, _ffi.last_error()
             handles = [None] * world
@@ -380,12 +389,52 @@ def main():
                     assert lib.nvc_symm_open(dev._h, hb, C.byref(ptr)) == 0, _ffi.last_error()
                     bases[r] = ptr.value
             group = C.c_void_p()
-            assert lib.nvc_peer_group_create(dev._h, rank, world, bases, C.byref(group)) == 0, _ffi.last_error()
-            fused = {"region": region, "group": group, "offsets": offsets, "bytes": at}
+            assert lib.nvc_peer_group_create(dev._h, rank, world, bases, at, C.byref(group)) == 0, _ffi.last_error()
+            fused = {"region": region, "group": group, "offsets": offsets, "sum_offsets": sum_offsets, "bytes": at}
         except Exception as e:  # no peer access on this box: the NCCL path still runs
             fused = None
             if rank == 0:
                 print(f"fused gather unavailable: {e}", file=sys.stderr)
+
+    # Paired layout (the reference's own tensor-parallel pairing, crates/nuvec-nn/src/sharded.rs:84-202,
+    # crates/nuvec-lm/src/model/shard.rs:108-145): qkv and gate+up stay N-sharded and feed K-sharded o and down,
+    # whose partial products are summed across ranks -- two collectives per layer instead of four.
+    paired = None
+    if fused is not None:
+        prng = np.random.default_rng(0)
+        pbase = {}
+        for name, N, K in PROJECTIONS:
+            wfull = prng.standard_normal((N, K), dtype=np.float32) * 0.02
+            prng.standard_normal((M, K), dtype=np.float32)  # keep the stream aligned with the weights drawn above
+            if name in ("o", "down"):
+                kl = K // world
+                qk = nv.quantize(dev.array(nv.f32_to_bf16(np.ascontiguousarray(wfull[:, rank * kl:(rank + 1) * kl])), nv.BF16), quant)
+                xk = dev.array(nv.f32_to_bf16(prng.standard_normal((M, kl), dtype=np.float32)), nv.BF16)
+                pbase[name] = (qk, xk, kl)
+        paired = []
+        for layer in range(args.layers):
+            row = {}
+            for name, (qk, xk, kl) in pbase.items():
+                ql = nv.Quantized(dev.empty(qk.weight.shape, nv.U32), dev.empty(qk.scales.shape, nv.BF16),
+                                  dev.empty(qk.biases.shape, nv.BF16), quant)
+                ql.weight.copy_from(qk.weight), ql.scales.copy_from(qk.scales), ql.biases.copy_from(qk.biases)
+                N = qk.weight.shape[0]
+                row[name] = (ql, xk, kl, dev.empty((M, N), nv.BF16))
+            paired.append(row)
+        dev.synchronize()
+
+    def step_paired():
+        for projs, sums, row in zip(layers, fused["sum_offsets"], paired):
+            for name, N, K, n_local, q, x, y in projs:
+                if name in row:
+                    ql, xk, kl, yk = row[name]
+                    rc = lib.nvc_quantized_matmul_all_sum(dev._h, fused["group"], C.byref(qc), xk.ptr, ql.weight.ptr, ql.scales.ptr,
+                                                          ql.biases.ptr, M, N, kl, yk.ptr, sums[name])
+                else:  # N-sharded, its slice stays on this rank
+                    slot = C.c_void_p(y.ptr.value + rank * M * n_local * 2)
+                    rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, q.weight.ptr, q.scales.ptr,
+                                                  q.biases.ptr, None, M, n_local, K, K, 1, 0, 0, 0, slot)
+                assert rc == 0, _ffi.last_error()
 
     def step_fused():
         for projs, offs in zip(layers, fused["offsets"]):
@@ -464,6 +513,31 @@ def main():
         sampler.start()
     ms, launches = timed(run, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    paired_ms = paired_check = None
+    if paired is not None:
+        step_paired()
+        dev.synchronize()
+        # every rank must hold the same bits, and they must be the sum of the ranks' partial products
+        bad = 0
+        for name, (ql, xk, kl, yk) in paired[-1].items():
+            mine = yk.to_numpy().view(np.uint16).astype(np.int64)
+            t = torch.tensor(mine, device="cuda")
+            lo, hi = t.clone(), t.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            bad += int((lo != hi).sum().item())
+            part = nv.quantized_matmul(xk, ql)  # this rank's partial product, rounded to bfloat16
+            pf = torch.tensor(nv.bf16_to_f32(part.to_numpy()), device="cuda")
+            dist.all_reduce(pf)
+            got = torch.tensor(nv.bf16_to_f32(yk.to_numpy()), device="cuda")
+            tol = 2e-2 * pf.abs().max()  # partials rounded to bfloat16 before this check's own sum
+            bad += int(((got - pf).abs() > tol).sum().item())
+        paired_check = "ok" if bad == 0 else f"{bad} elements differ"
+        graph_p = dev.record(step_paired) if not args.no_graph else None
+        run_p = graph_p.launch if graph_p is not None else step_paired
+        for _ in range(args.warmup):
+            run_p()
+        paired_ms, _ = timed(run_p, args.steps)
     if world > 1:
         step(gather=False)
         graph_k = dev.record(lambda: step(gather=False)) if not args.no_graph else None
@@ -517,6 +591,12 @@ def main():
                                     "note": "nvc_quantized_matmul_gather: peer stores + flags inside the product kernel"}
             line["nccl_gather"] = {"value": step_bytes / (nccl_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
                                    "note": "nvc_quantized_matmul followed by ncclAllGather"}
+            line["config"]["value_is"] = "the faster of fused_gather and nccl_gather (both all-gather layouts, timed over the same steps)"
+        if paired_ms is not None:
+            line["paired_layout"] = {"value": step_bytes / (paired_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                                     "ms_per_step": paired_ms / args.steps, "check": paired_check,
+                                     "note": "the reference's tensor-parallel pairing: N-sharded qkv and gate+up feed K-sharded "
+                                             "o and down (nvc_quantized_matmul_all_sum): 72 collectives per step instead of 144"}
 
     # ── end to end through the host-operand entry point (rank-local x in, y out) ─────────────
     if not args.no_e2e:

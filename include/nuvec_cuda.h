@@ -253,20 +253,33 @@ int32_t nvc_comm_health(nvc_comm *comm);
 int32_t nvc_comm_abort(nvc_comm *comm);
 int32_t nvc_comm_destroy(nvc_comm *comm);
 
-/* ── the sharded product fused with its gather ─────────────────────────────────────────────
+/* ── sharded few-row products fused with their collective ──────────────────────────────────
  *
- * Replaces the pair "quantized_matmul on this rank's rows of W, then Communicator::all_gather"
- * (crates/nuvec-core/src/distributed.rs:52, 695-700) for few-row products: the kernel stores
- * its [M, N_local] slice straight into slot `rank` of every rank's gathered buffer over NVLink
- * peer stores, and when the last block of the kernel is done it raises this rank's flag in every
- * rank's flag array.  The next product of the group waits on the device for all flags of the
- * previous one before it reads its activations.  No collective library is involved.
+ * Replace the pairs "quantized_matmul on this rank's rows of W, then Communicator::all_gather"
+ * (crates/nuvec-core/src/distributed.rs:52, 695-700; the sharded logits of
+ * crates/nuvec-lm/src/model.rs:3336-3346) and "quantized_matmul on this rank's columns of W, then
+ * all_sum" (ShardedToAllLinear::forward, crates/nuvec-nn/src/sharded.rs:195-202) for few-row products.
+ * The product kernel itself sends every result to the other ranks over NVLink peer stores as
+ * 8-byte packets {value, sequence number}; at its end the same kernel collects the packets the other
+ * ranks sent to this one (a reader that sees the product's sequence number has the value with it:
+ * no fence, no flag, no collective library).  When the kernel ends the result is complete on this
+ * rank, so the next kernel of the stream needs no wait of its own.
  *
- * Set-up, once: every rank allocates a symmetric region (nvc_symm_alloc), the caller's bootstrap
- * carries the 64-byte handles to the other ranks, every rank opens the others' regions
- * (nvc_symm_open) and builds a group from the table of base addresses (its own included, at
- * index `rank`).  A region starts zeroed; its first 4 KiB belong to the group (flags, sequence
- * counter), the caller's buffers live behind NVC_SYMM_RESERVED. */
+ * Set-up, once: every rank allocates a symmetric region of the same size (nvc_symm_alloc), the
+ * caller's bootstrap carries the 64-byte handles to the other ranks, every rank opens the others'
+ * regions (nvc_symm_open) and builds a group from the table of base addresses (its own included,
+ * at index `rank`).  A region starts zeroed; its first 4 KiB belong to the group (sequence
+ * counters), the products' buffers live behind NVC_SYMM_RESERVED at offsets that are multiples of
+ * 256 and the same on every rank.
+ *
+ * Rules: every rank of the group issues the same sequence of fused products.  A product's buffers
+ * inside the regions (its footprint) may be reused by a later product; the packet areas alternate
+ * between two halves, so a rank that runs ahead by one product never lands on packets still being
+ * read, and it cannot run ahead by two (it needs the slower rank's packets of the product between).
+ * Only this rank's own kernel writes this rank's gathered buffer (the other ranks write packets,
+ * never results), so reading a gathered buffer as the activations of a later product is safe in
+ * stream order.  A wait that gives up (about a second) sets the device's error word:
+ * nvc_synchronize reports it, and the device stays usable. */
 #define NVC_SYMM_RESERVED 4096
 typedef struct { uint8_t bytes[64]; } nvc_ipc_handle;
 typedef struct nvc_peer_group nvc_peer_group; /* opaque: the ranks' region addresses on this device */
@@ -275,17 +288,29 @@ int32_t nvc_symm_alloc(nvc_device *dev, size_t bytes, void **out_ptr, nvc_ipc_ha
 int32_t nvc_symm_open(nvc_device *dev, const nvc_ipc_handle *handle, void **out_peer_ptr);
 int32_t nvc_symm_close(nvc_device *dev, void *peer_ptr);
 int32_t nvc_symm_free(nvc_device *dev, void *ptr);
+/* region_bytes: the size every rank allocated; products whose footprint would pass it are refused. */
 int32_t nvc_peer_group_create(nvc_device *dev, int32_t rank, int32_t size, void *const *region_bases,
-                              nvc_peer_group **out);
+                              size_t region_bytes, nvc_peer_group **out);
 int32_t nvc_peer_group_destroy(nvc_peer_group *group);
-/* y of rank r lands at byte offset out_offset + r * M * N_local * 2 of every rank's region
- * (out_offset >= NVC_SYMM_RESERVED, the same on all ranks): the [size, M, N_local] layout of
- * all_gather.  Operands as nvc_quantized_matmul_noalloc (bfloat16, affine 2/3/4/6/8 bits, M <= 8).
- * Every rank of the group must issue the same sequence of these calls.  A wait that gives up
- * (about a second) sets the device's error word: nvc_synchronize reports it. */
+/* Bytes a fused product occupies in every region from its offset on (a multiple of 256): the
+ * gathered [size, M, N_local] bfloat16 buffer followed by the packet areas / the packet areas alone. */
+size_t nvc_gather_footprint(int32_t size, int64_t M, int64_t N_local);
+size_t nvc_all_sum_footprint(int32_t size, int64_t M, int64_t N);
+/* N-sharded product + all_gather.  This rank multiplies its rows of W (w, scales, biases: [N_local, ..]);
+ * the gathered result, bfloat16 [size, M, N_local] (rank r's slice at index r: the layout of
+ * all_gather along axis 0), ends up at byte offset out_offset of THIS rank's region on every rank.
+ * Operands as nvc_quantized_matmul_noalloc (bfloat16, affine 2/3/4/6/8 bits, M <= 8). */
 int32_t nvc_quantized_matmul_gather(nvc_device *dev, nvc_peer_group *group, const nvc_quant *q, const void *x,
                                     const uint32_t *w, const void *scales, const void *biases, int64_t M,
                                     int64_t N_local, int64_t K, size_t out_offset);
+/* K-sharded product + all_sum.  This rank multiplies its K_local columns of W (w: [N, K_local * bits / 32],
+ * scales / biases: [N, K_local / group_size]) by its K_local columns of the activations (x: [M, K_local]);
+ * y (device memory, bfloat16 [M, N]) receives the sum of all ranks' float32 partial products, added in
+ * rank order and rounded once, bit-identical on every rank.  The packet areas occupy
+ * nvc_all_sum_footprint bytes at scratch_offset of every region. */
+int32_t nvc_quantized_matmul_all_sum(nvc_device *dev, nvc_peer_group *group, const nvc_quant *q, const void *x,
+                                     const uint32_t *w, const void *scales, const void *biases, int64_t M,
+                                     int64_t N, int64_t K_local, void *y, size_t scratch_offset);
 
 #ifdef __cplusplus
 }

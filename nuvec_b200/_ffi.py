@@ -90,9 +90,12 @@ SIGNATURES = {
     "nvc_symm_open": (I32T, [P, P, PP]),
     "nvc_symm_close": (I32T, [P, P]),
     "nvc_symm_free": (I32T, [P, P]),
-    "nvc_peer_group_create": (I32T, [P, I32T, I32T, PP, PP]),
+    "nvc_peer_group_create": (I32T, [P, I32T, I32T, PP, SZ, PP]),
     "nvc_peer_group_destroy": (I32T, [P]),
+    "nvc_gather_footprint": (SZ, [I32T, I64T, I64T]),
+    "nvc_all_sum_footprint": (SZ, [I32T, I64T, I64T]),
     "nvc_quantized_matmul_gather": (I32T, [P, P, QP, P, P, P, P, I64T, I64T, I64T, SZ]),
+    "nvc_quantized_matmul_all_sum": (I32T, [P, P, QP, P, P, P, P, I64T, I64T, I64T, P, SZ]),
 }
 
 _lib = None

@@ -437,7 +437,8 @@ static_assert(2 * 16 * QMV_FPITCH <= QMV_SCALE_AREA, "the floating-point scale b
 //                                         (chunk, lane) so that a quarter-warp reads 128
 //                                         consecutive bytes
 //   lpart [QMV_WARPS][2][128] f32         partial sums of tiles cut between warps of this block
-//   lcount[QMV_WARPS + 4] u32             their arrival counters; word QMV_WARPS: "this block finished last" (fused gather)
+//   lcount[QMV_WARPS + 4 + 32] u32        their arrival counters; fused collectives: word QMV_WARPS + 1 the product's
+//                                         sequence number, words QMV_WARPS + 4 .. the ranks' region addresses
 // Shared-memory loads by 32-bit shared address plus a compile-time offset (the main loop keeps a
 // few base addresses in registers and reaches everything else through the offset field).
 template <int OFS> __device__ __forceinline__ uint4 lds128(uint32_t a) {
@@ -792,6 +793,13 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         }
         for (int i = tid; i < ZERO_WORDS; i += QMV_THREADS) zero[i] = 0u;
         if (tid < QMV_WARPS) lcount[tid] = 0u;
+        if (p.peer) {
+            // fused collectives: the ranks' region addresses and this product's sequence number (the
+            // count of fused products this rank has finished, plus one: every rank runs the same
+            // sequence of them, so the numbers agree across ranks without any exchange)
+            if (tid < 16) reinterpret_cast<void **>(lcount + QMV_WARPS + 4)[tid] = p.peer->base[tid];
+            if (tid == 0) lcount[QMV_WARPS + 1] = __ldcg(static_cast<const uint32_t *>(p.peer->base[p.peer_rank]) + 16) + 1u;
+        }
     }
     __syncthreads();  // activations staged
 
@@ -1026,76 +1034,95 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
                 if (col < p.M && row <= last_row) out[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
             }
         } else if (store) {
-            // fused gather: into slot `rank` of this rank's own gathered buffer; the block that
-            // finishes last sends the whole slice to the other ranks (end of the kernel)
-            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(p.peer->base[p.peer->rank]) + p.peer_out_offset) +
-                                 (int64_t)p.peer->rank * p.M * p.N;
+            // Fused collective.  Every result (gather: the rounded bfloat16; all-sum: this rank's float32
+            // partial sum) travels as one 8-byte packet {value, sequence number} into the same slot of
+            // every rank's packet area: an aligned 8-byte store arrives whole, so a reader that sees
+            // the product's sequence number has the value with it -- no fence, no flag, and nothing
+            // waits for this rank's other blocks.  Two areas alternate with the sequence number's
+            // parity, so the next product on the same offsets never lands on packets still being read.
+            const uint32_t seq = lcount[QMV_WARPS + 1];
+            char *const *bases = reinterpret_cast<char *const *>(lcount + QMV_WARPS + 4);
+            const size_t per = (size_t)p.M * p.N;  // values per rank
+            const size_t area = p.peer_ll_offset + (size_t)(seq & 1u) * ((size_t)p.peer_size * per * 8);
+            uint16_t *own_out = reinterpret_cast<uint16_t *>(bases[p.peer_rank] + p.peer_out_offset) + (size_t)p.peer_rank * per;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int row = n0 + r + (i >> 1) * 8, col = 2 * t + (i & 1);
-                if (col < p.M && row <= last_row) dst[(int64_t)col * p.N + row] = __float2bfloat16_rn(v[i]);
+                if (col < p.M && row <= last_row) {
+                    const size_t e = (size_t)col * p.N + row;
+                    uint32_t data;
+                    if (p.peer_mode == 1) {  // gather: this rank's own slot is written directly
+                        const __nv_bfloat16 h = __float2bfloat16_rn(v[i]);
+                        data = (uint32_t)__bfloat16_as_ushort(h);
+                        own_out[e] = (uint16_t)data;
+                    } else {
+                        data = __float_as_uint(v[i]);
+                    }
+                    const size_t slot = area + ((size_t)p.peer_rank * per + e) * 8;
+                    for (int rk = 0; rk < p.peer_size; rk++) {
+                        if (p.peer_mode == 1 && rk == p.peer_rank) continue;
+                        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(bases[rk] + slot), "r"(data), "r"(seq) : "memory");
+                    }
+                }
             }
         }
     }
     cp_async_wait<0>();
     if (p.peer) {
-        // The block that finishes last copies this rank's slice from its own gathered buffer into
-        // every other rank's (16-byte peer stores over NVLink by all its threads), makes them
-        // visible system-wide, raises this rank's flag in every region, and then waits until every
-        // rank's flag in its own region shows the same product finished: when this kernel ends, the
-        // gathered buffer is complete on this rank, and the next kernel of the stream needs no
-        // wait of its own.  Rank r has finished n fused products when flag r holds n; this rank's
-        // own count is at byte 64.  (Fences by thread 0 after a block barrier cover the whole
-        // block's stores: the barrier orders them before the fence, and a fence is cumulative.)
-        // The wait is bounded; when it gives up the error word says so.
-        __syncthreads();
-        uint32_t *own = static_cast<uint32_t *>(p.peer->base[p.peer->rank]);
-        if (tid == 0) {
-            __threadfence();
-            lcount[QMV_WARPS] = atomicAdd(own + 17, 1u) == gridDim.x * gridDim.z - 1 ? 1u : 0u;
-            __threadfence();
-        }
-        __syncthreads();
-        if (lcount[QMV_WARPS]) {
-            const size_t slice = (size_t)p.M * p.N * 2, at = p.peer_out_offset + (size_t)p.peer->rank * slice;
-            const char *src = static_cast<const char *>(p.peer->base[p.peer->rank]) + at;
-            // each piece is read once and stored to every peer (the reads are L2 round trips)
-            if (slice % 16 == 0 && at % 16 == 0) {
-                for (size_t i = (size_t)tid * 16; i < slice; i += (size_t)QMV_THREADS * 16) {
-                    const uint4 piece = __ldcg(reinterpret_cast<const uint4 *>(src + i));
-                    for (int rk = 0; rk < p.peer->size; rk++)
-                        if (rk != p.peer->rank) *reinterpret_cast<uint4 *>(static_cast<char *>(p.peer->base[rk]) + at + i) = piece;
-                }
-            } else {
-                for (size_t i = (size_t)tid * 2; i < slice; i += (size_t)QMV_THREADS * 2) {
-                    const uint16_t piece = __ldcg(reinterpret_cast<const uint16_t *>(src + i));
-                    for (int rk = 0; rk < p.peer->size; rk++)
-                        if (rk != p.peer->rank) *reinterpret_cast<uint16_t *>(static_cast<char *>(p.peer->base[rk]) + at + i) = piece;
-                }
+        // Second half of the fused collective: all threads of the grid share the packets this rank
+        // receives.  A thread waits (bounded: about a second, then the error word says so) until its
+        // packet carries this product's sequence number and consumes it -- gather: the value goes
+        // into the gathered buffer; all-sum: the ranks' partial sums of one result are added in rank
+        // order, rounded once and stored, identically on every rank.  When the kernel ends the
+        // result is complete on this rank, so the next kernel of the stream needs no wait of its own.
+        const uint32_t seq = lcount[QMV_WARPS + 1];
+        char *const *bases = reinterpret_cast<char *const *>(lcount + QMV_WARPS + 4);
+        char *own = bases[p.peer_rank];
+        const size_t per = (size_t)p.M * p.N;
+        const char *area = own + p.peer_ll_offset + (size_t)(seq & 1u) * ((size_t)p.peer_size * per * 8);
+        const size_t gtid = (size_t)blockIdx.x * QMV_THREADS + tid, gthreads = (size_t)gridDim.x * QMV_THREADS;
+        bool late = false;
+        auto packet = [&](size_t index, uint32_t &data) {
+            const char *at = area + index * 8;
+            uint32_t s2 = 0;
+            for (uint32_t spins = 0; spins < (1u << 20); spins++) {
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(data), "=r"(s2) : "l"(at) : "memory");
+                if (s2 == seq) return true;
             }
-            __syncthreads();
-            if (tid == 0) {
-                const uint32_t seq = __ldcg(own + 16) + 1u;
-                own[17] = 0u;
-                // one release fence for all flags (a releasing store per flag would fence each time)
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                for (int rk = 0; rk < p.peer->size; rk++) {
-                    uint32_t *flag = static_cast<uint32_t *>(p.peer->base[rk]) + p.peer->rank;
-                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+            return false;
+        };
+        if (p.peer_mode == 1) {
+            uint16_t *gathered = reinterpret_cast<uint16_t *>(own + p.peer_out_offset);
+            for (size_t i = gtid; i < (size_t)p.peer_size * per; i += gthreads) {
+                if (i / per == (size_t)p.peer_rank) continue;
+                uint32_t data;
+                if (packet(i, data)) gathered[i] = (uint16_t)data;
+                else late = true;
+            }
+        } else {
+            __nv_bfloat16 *y = (__nv_bfloat16 *)p.y;
+            for (size_t e = gtid; e < per; e += gthreads) {
+                float sum = 0.f;
+                bool ok = true;
+                for (int rk = 0; rk < p.peer_size; rk++) {
+                    uint32_t data;
+                    if (packet((size_t)rk * per + e, data)) sum += __uint_as_float(data);
+                    else ok = false;
                 }
-                __stcg(own + 16, seq);
-                // all flags are polled together (relaxed loads that overlap), one fence acquires
-                bool all = false;
-                for (uint32_t spins = 0; spins < (1u << 20) && !all; spins++) {  // about a second
-                    all = true;
-                    for (int rk = 0; rk < p.peer->size; rk++) {
-                        uint32_t seen;
-                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(own + rk) : "memory");
-                        all = all && seen >= seq;
-                    }
-                }
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                if (!all && p.error) *p.error = 2;
+                if (ok) y[e] = __float2bfloat16_rn(sum);
+                else late = true;
+            }
+        }
+        if (late && p.error) *p.error = 2;
+        // the count of finished fused products advances once the last block is through
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t *head = reinterpret_cast<uint32_t *>(own);
+            __threadfence();
+            if (atomicAdd(head + 17, 1u) == gridDim.x * gridDim.z - 1) {
+                head[17] = 0u;
+                __stcg(head + 16, seq);
+                __stcg(head + p.peer_rank, seq);
             }
         }
     }
@@ -1135,7 +1162,7 @@ static int wpl_for(int bits, int gs, int64_t K) {
 static size_t qmv_smem(int M, int64_t K, int bits, int wpl) {
     const int codes = codes_per_word(bits), xw = codes / 2, lw = wpl * unit_words(bits);
     return (size_t)(M * (K / codes * xw + 16) + qmv_zero_words(wpl, xw) + QMV_WARPS * (QMV_SCALE_AREA / 4) +
-                    qmv_stages(wpl) * 2 * QMV_THREADS * lw + QMV_WARPS * 2 * 128 + QMV_WARPS + 4) * 4 + 16;
+                    qmv_stages(wpl) * 2 * QMV_THREADS * lw + QMV_WARPS * 2 * 128 + QMV_WARPS + 4 + 32) * 4 + 16;
 }
 
 bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M,

@@ -5,8 +5,8 @@
 namespace nvc {
 
 // The ranks' symmetric regions as seen from this device (device memory, read by the kernel).
-// Region layout, first bytes: uint32 flags[16] (flag r is raised by rank r), at 64 the count of
-// fused products this rank has finished, at 68 the blocks of the running kernel that are done.
+// Region layout, first bytes: uint32 word `rank` and the word at byte 64 hold the count of fused
+// products this rank has finished, the word at byte 68 the blocks of the running kernel that are done.
 struct PeerTable {
     void *base[16];
     int32_t rank, size;
@@ -58,10 +58,13 @@ struct QmvParams {
     int32_t early_weights;
     const float *global;       // nvfp4 global scale(s) or nullptr
     int32_t expert_global;     // one value per expert (indexed like the weights' batch)
-    // Fused gather (nullptr: plain product).  The result goes to every rank's region instead of y.
+    // Fused collective (nullptr: plain product).
     const struct PeerTable *peer;
-    uint64_t peer_out_offset;  // byte offset of the [size, M, N] gathered buffer inside a region
-    int32_t *error;            // host-visible word: 2 when the wait for the peers' flags gave up
+    int32_t peer_rank, peer_size;
+    int32_t peer_mode;         // 1: gather of the ranks' [M, N] slices; 2: sum of the ranks' partial [M, N] products into y
+    uint64_t peer_out_offset;  // gather: byte offset of the [size, M, N] gathered buffer inside this rank's region
+    uint64_t peer_ll_offset;   // byte offset, inside every region, of the two packet areas of size * M * N * 8 bytes
+    int32_t *error;            // host-visible word: 2 when the wait for the peers' packets gave up
 };
 // Returns NVC_ERR_UNSUPPORTED (without setting an error message) when the shape is not one
 // the fast kernel takes; the caller then uses the generic kernel.
