@@ -601,15 +601,27 @@ def main():
     # ── end to end through the host-operand entry point (rank-local x in, y out) ─────────────
     if not args.no_e2e:
         hx = {K: np.ascontiguousarray(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32))) for _, _, K in PROJECTIONS}
-        hy = {n: np.empty((M, n), np.uint16) for n in {p[3] for p in base}}
+
+        hy = {(li, name): np.empty((M, n_local), np.uint16) for li, projs in enumerate(layers)
+              for name, N, K, n_local, q, x, y in projs}
+
+        items = (_ffi.HostProduct * (len(layers) * len(PROJECTIONS)))()
+        i = 0
+        for li, projs in enumerate(layers):
+            for name, N, K, n_local, q, x, y in projs:
+                it = items[i]
+                it.quant, it.dtype, it.transpose = qc, nv.BF16, 1
+                it.host_x, it.host_y = hx[K].ctypes.data, hy[(li, name)].ctypes.data
+                it.w, it.scales, it.biases, it.global_scale = q.weight.ptr.value, q.scales.ptr.value, q.biases.ptr.value, None
+                it.M, it.N, it.K = M, n_local, K
+                i += 1
 
         def step_host():
-            for projs in layers:
-                for name, N, K, n_local, q, x, y in projs:
-                    rc = lib.nvc_quantized_matmul_host(dev._h, C.byref(qc), nv.BF16, 1, hx[K].ctypes.data_as(C.c_void_p),
-                                                       q.weight.ptr, q.scales.ptr, q.biases.ptr, None, M, n_local, K,
-                                                       hy[n_local].ctypes.data_as(C.c_void_p))
-                    assert rc == 0, _ffi.last_error()
+            # the whole token through the host-operand call: every product's activations come from host
+            # memory and its result goes back to host memory; the step's products are issued as one
+            # list (what an evaluator walking the step's nodes does) and the step waits once
+            assert lib.nvc_quantized_matmul_host_batch(dev._h, items, len(items)) == 0, _ffi.last_error()
+            assert lib.nvc_synchronize(dev._h) == 0, _ffi.last_error()
 
         step_host()
         barrier()
@@ -628,7 +640,15 @@ def main():
                        "h2d_bytes_per_step": args.layers * sum(M * K * 2 for _, _, K in PROJECTIONS),
                        "d2h_bytes_per_step": args.layers * sum(M * (N // world) * 2 for _, N, _ in PROJECTIONS),
                        "ms_per_step": wall * 1e3,
-                       "note": "nvc_quantized_matmul_host per product: x through the pinned block and an H2D copy, kernel, y stored by the kernel into the pinned block over PCIe, wait; weights resident"}
+                       "note": "nvc_quantized_matmul_host_batch: the step's 144 products as one list of host-operand products (x from "
+                               "host memory through a pinned block and an H2D copy, y stored by the kernel into the pinned "
+                               "block over PCIe), one nvc_synchronize per step delivers the results into host memory; weights resident"}
+        # the results that came back through host memory are the ones the device-resident step computes
+        if rank == 0 and not args.no_check:
+            name, N, K, n_local, q, x, y = layers[0][0]
+            ref = nv.quantized_matmul(dev.array(hx[K], nv.BF16), q).to_numpy().view(np.uint16).reshape(M, n_local)
+            if not np.array_equal(ref, hy[(0, name)]):
+                raise SystemExit("parity check failed: host-operand result differs from the device-resident product")
 
     # ── prefill product on tcgen05 (rank 0's view; N-sharded like the decode products) ───────
     if not args.no_prefill:

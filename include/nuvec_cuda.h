@@ -212,6 +212,31 @@ int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q, int32_t d
                                   const float *global_scale, int64_t M, int64_t N, int64_t K,
                                   void *host_y);
 
+/* The asynchronous form: returns as soon as the copies and the kernel are on the stream.  The
+ * result is PENDING, as a GPU result is in the reference's evaluator until `flush`
+ * (crates/nuvec-core/src/gpu.rs:1772-1795): nvc_synchronize (or any call that synchronizes, e.g.
+ * nvc_memcpy_d2h) delivers it into host_y.  host_x may be reused when the call returns; host_y must
+ * stay valid until the synchronization.  A decode step issues its products back to back and waits once. */
+int32_t nvc_quantized_matmul_host_async(nvc_device *dev, const nvc_quant *q, int32_t dtype,
+                                        int32_t transpose, const void *host_x, const uint32_t *w,
+                                        const void *scales, const void *biases,
+                                        const float *global_scale, int64_t M, int64_t N, int64_t K,
+                                        void *host_y);
+
+/* A list of such products in one call (an evaluator walking the nodes of a step between two
+ * flushes); the fields are the arguments of nvc_quantized_matmul_host_async. */
+typedef struct {
+    nvc_quant quant;
+    int32_t dtype, transpose;
+    const void *host_x;
+    const uint32_t *w;
+    const void *scales, *biases;
+    const float *global_scale;
+    int64_t M, N, K;
+    void *host_y;
+} nvc_host_product;
+int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_host_product *items, size_t count);
+
 /* No counterpart in the reference.  The few-row product for callers that may not allocate device
  * memory while they run: code that executes between a memory reservation made up front and its
  * release (a serving loop under a fixed memory budget, a plugin hosted by a runtime that owns
@@ -240,14 +265,29 @@ int32_t nvc_quantized_matmul_noalloc(nvc_device *dev, const nvc_quant *q, const 
 int32_t nvc_comm_unique_id(uint8_t out_id[128]);
 int32_t nvc_comm_init(nvc_device *dev, int32_t rank, int32_t size, const uint8_t id[128],
                       nvc_comm **out);
+/* The same with a host-side time limit (milliseconds; 0 = the default): a rank that never joins
+ * ends the call with NVC_ERR_COMM after the limit instead of blocking for ever, and the
+ * half-built communicator is aborted.  nvc_comm_init uses NUVEC_DISTRIBUTED_TIMEOUT seconds (the
+ * reference's variable, crates/nuvec-distributed/src/backend.rs:44-59), 120 when it is unset. */
+int32_t nvc_comm_init_timeout(nvc_device *dev, int32_t rank, int32_t size, const uint8_t id[128],
+                              int64_t timeout_ms, nvc_comm **out);
 int32_t nvc_comm_rank(nvc_comm *comm);
 int32_t nvc_comm_size(nvc_comm *comm);
 /* Communicator::all_gather(&[u8], &mut [u8]) (distributed.rs:52; ring.rs:868-889): recv holds
  * size * bytes_per_rank bytes, rank r's block at offset r * bytes_per_rank.  In place when
  * send == recv + rank * bytes_per_rank. */
 int32_t nvc_all_gather(nvc_comm *comm, const void *send, void *recv, size_t bytes_per_rank);
-/* Communicator::all_reduce(op = sum, dtype, &mut [u8]) (distributed.rs:50). */
+/* Communicator::all_reduce(op, dtype, &mut [u8]) (distributed.rs:50), in place; op is one of
+ * AllReduce::{Sum, Max, Min} (distributed.rs:32-39). */
+#define NVC_REDUCE_SUM 0
+#define NVC_REDUCE_MAX 1
+#define NVC_REDUCE_MIN 2
+int32_t nvc_all_reduce(nvc_comm *comm, int32_t op, int32_t dtype, void *buf, size_t count);
 int32_t nvc_all_reduce_sum(nvc_comm *comm, int32_t dtype, void *buf, size_t count);
+/* Communicator::send / recv (distributed.rs:54-57): `bytes` bytes to / from rank `peer`, ordered on
+ * the device's stream; a send pairs with the peer's recv of the same size. */
+int32_t nvc_send(nvc_comm *comm, const void *buf, size_t bytes, int32_t peer);
+int32_t nvc_recv(nvc_comm *comm, void *buf, size_t bytes, int32_t peer);
 /* Communicator::health (distributed.rs:66-70): NVC_OK or NVC_ERR_COMM with the async error. */
 int32_t nvc_comm_health(nvc_comm *comm);
 int32_t nvc_comm_abort(nvc_comm *comm);

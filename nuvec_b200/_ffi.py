@@ -20,6 +20,13 @@ class Quant(C.Structure):
     _fields_ = [("mode", C.c_int32), ("group_size", C.c_int32), ("bits", C.c_int32)]
 
 
+class HostProduct(C.Structure):
+    """nvc_host_product: one entry of nvc_quantized_matmul_host_batch."""
+    _fields_ = [("quant", Quant), ("dtype", C.c_int32), ("transpose", C.c_int32), ("host_x", C.c_void_p),
+                ("w", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p), ("global_scale", C.c_void_p),
+                ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("host_y", C.c_void_p)]
+
+
 class Info(C.Structure):
     _fields_ = [("name", C.c_char * 128), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
                 ("multiprocessors", C.c_int32), ("driver_version", C.c_int32),
@@ -76,9 +83,15 @@ SIGNATURES = {
     "nvc_gather_qmm": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, P, P, P, I32T, I64T, I64T, I64T, I64T,
                               I64T, I64T, P]),
     "nvc_quantized_matmul_host": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, P]),
+    "nvc_quantized_matmul_host_async": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, P]),
+    "nvc_quantized_matmul_host_batch": (I32T, [P, C.POINTER(HostProduct), SZ]),
     "nvc_quantized_matmul_noalloc": (I32T, [P, QP, P, P, P, P, I64T, I64T, I64T, P]),
     "nvc_comm_unique_id": (I32T, [P]),
     "nvc_comm_init": (I32T, [P, I32T, I32T, P, C.POINTER(P)]),
+    "nvc_comm_init_timeout": (I32T, [P, I32T, I32T, P, I64T, C.POINTER(P)]),
+    "nvc_all_reduce": (I32T, [P, I32T, I32T, P, SZ]),
+    "nvc_send": (I32T, [P, P, SZ, I32T]),
+    "nvc_recv": (I32T, [P, P, SZ, I32T]),
     "nvc_comm_rank": (I32T, [P]),
     "nvc_comm_size": (I32T, [P]),
     "nvc_all_gather": (I32T, [P, P, P, SZ]),

@@ -84,6 +84,14 @@ struct nvc_device {
     size_t qmm_counters_len = 0;
     // Host-mapped word a kernel sets when one of its bounded waits gives up; read at synchronisation.
     int32_t *error_word = nullptr, *error_word_dev = nullptr;
+    // Asynchronous host-operand products: a pinned block (mapped into the device) and a device block
+    // handed out front to back, and the results that wait in the pinned block for nvc_synchronize
+    // to deliver them to the caller's memory.
+    struct PendingResult { const void *pinned; void *host; size_t bytes; };
+    std::mutex host_mu;
+    std::vector<PendingResult> pending;
+    char *ring_host = nullptr, *ring_host_dev = nullptr, *ring_dev = nullptr;  // (ring_host_dev: the pinned block as the device sees it)
+    size_t ring_bytes = 0, ring_at = 0;
 };
 
 struct nvc_graph {
@@ -104,6 +112,7 @@ int32_t ensure_scratch(nvc_device *dev, size_t bytes, void **out);
 int32_t ensure_counters(nvc_device *dev, size_t count, uint32_t **out);
 int32_t check_quant(const char *op, const nvc_quant *q);
 int32_t check_launch(nvc_device *dev, const char *kernel);
+int32_t deliver_pending(nvc_device *dev);    // copies finished host-operand results out (the stream must be idle)
 int32_t ensure_error_word(nvc_device *dev);  // the host-mapped word kernels report a bounded wait's failure in
 
 inline size_t dtype_size(int32_t dtype) { return dtype == NVC_F32 ? 4 : 2; }

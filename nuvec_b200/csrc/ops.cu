@@ -288,3 +288,130 @@ extern "C" int32_t nvc_quantized_matmul_host(nvc_device *dev, const nvc_quant *q
     memcpy(host_y, hp + yoff, yb);
     return NVC_OK;
 }
+
+// The asynchronous form of the host-operand product: nothing waits.  The activations are copied
+// into a pinned block and from there to the device on the stream, the kernel follows, and the
+// result stays pending -- stored by the kernel straight into the pinned block through its device
+// mapping when it is small, copied back on the stream otherwise -- until nvc_synchronize (or any
+// call that synchronizes, such as nvc_memcpy_d2h) delivers it into host_y.  This is how the
+// reference's evaluator treats GPU results: pending until flush
+// (crates/nuvec-core/src/gpu.rs:1772-1795).  host_x may be reused as soon as the call returns;
+// host_y must stay valid until the synchronization.
+extern "C" int32_t nvc_quantized_matmul_host_async(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32_t transpose,
+                                                   const void *host_x, const uint32_t *w, const void *scales,
+                                                   const void *biases, const float *global_scale, int64_t M, int64_t N,
+                                                   int64_t K, void *host_y) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_product("quantized_matmul", q, dtype, transpose, biases, global_scale, M, N, K));
+    if (M == 0 || N == 0) return NVC_OK;
+    if (!host_x || !host_y) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul: null host operand");
+    if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (host operands): not inside a recorded step");
+    const size_t xb = (size_t)(M * K) * dtype_size(dtype), yb = (size_t)(M * N) * dtype_size(dtype);
+    const size_t xpad = (xb + 255) / 256 * 256, ypad = (yb + 255) / 256 * 256;
+    constexpr size_t RING = (size_t)64 << 20;
+    if (xpad + ypad > RING)  // too large to stage beside other pending work: the synchronous form
+        return nvc_quantized_matmul_host(dev, q, dtype, transpose, host_x, w, scales, biases, global_scale, M, N, K, host_y);
+    if (!dev->ring_host) {
+        NVC_CUDA(cudaHostAlloc((void **)&dev->ring_host, RING, cudaHostAllocMapped));
+        NVC_CUDA(cudaHostGetDevicePointer((void **)&dev->ring_host_dev, dev->ring_host, 0));
+        void *d = nullptr;
+        NVC_TRY(dev->pool.alloc(RING, &d));
+        dev->ring_dev = static_cast<char *>(d);
+        dev->ring_bytes = RING;
+    }
+    if (dev->ring_at + xpad + ypad > dev->ring_bytes) NVC_TRY(nvc_synchronize(dev));  // delivers what is pending, rewinds the blocks
+    size_t at;
+    {
+        std::lock_guard<std::mutex> g(dev->host_mu);
+        at = dev->ring_at;
+        dev->ring_at += xpad + ypad;
+    }
+    char *hx = dev->ring_host + at, *hy = hx + xpad, *dx = dev->ring_dev + at, *dy = dx + xpad;
+    memcpy(hx, host_x, xb);
+    // The activations go to device memory first: every block of the product reads all of them, which
+    // over PCIe (reading the pinned block in place) was measured 15 times slower than one copy.
+    const void *xdev = dx;
+    NVC_CUDA(cudaMemcpyAsync(dx, hx, xb, cudaMemcpyHostToDevice, dev->stream));
+    void *ydev = dy;
+    const bool direct = yb <= 256 * 1024;
+    if (direct) ydev = dev->ring_host_dev + at + xpad;
+    NVC_TRY(nvc_quantized_matmul(dev, q, dtype, transpose, xdev, w, scales, biases, global_scale, M, N, K, K, 1, 0, 0, 0, ydev));
+    if (!direct) NVC_CUDA(cudaMemcpyAsync(hy, dy, yb, cudaMemcpyDeviceToHost, dev->stream));
+    std::lock_guard<std::mutex> g(dev->host_mu);
+    dev->pending.push_back({hy, host_y, yb});
+    return NVC_OK;
+}
+
+// A list of asynchronous host-operand products in one call: what an evaluator that walks a step's
+// nodes issues between two flushes.  All activations of the list are packed into the pinned block
+// and reach the device in ONE copy (a copy command per product costs more than a decode product
+// itself), then the kernels follow back to back; every result is stored by its kernel into the
+// pinned block (or copied back when large) and stays pending until the synchronization.  A list
+// that does not fit the staging blocks is issued product by product.
+extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_host_product *items, size_t count) {
+    if (count && !items) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul (host batch): null list");
+    if (count == 0) return NVC_OK;
+    NVC_TRY(make_current(dev));
+    if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (host operands): not inside a recorded step");
+    constexpr size_t RING = (size_t)64 << 20;
+    auto pad = [](size_t n) { return (n + 255) / 256 * 256; };
+    size_t xtotal = 0, ytotal = 0;
+    for (size_t i = 0; i < count; i++) {
+        const nvc_host_product &it = items[i];
+        NVC_TRY(check_product("quantized_matmul", &it.quant, it.dtype, it.transpose, it.biases, it.global_scale, it.M, it.N, it.K));
+        if ((it.M != 0 && it.N != 0) && (!it.host_x || !it.host_y))
+            return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul (host batch): null host operand in product %zu", i);
+        xtotal += pad((size_t)(it.M * it.K) * dtype_size(it.dtype));
+        ytotal += pad((size_t)(it.M * it.N) * dtype_size(it.dtype));
+    }
+    if (xtotal + ytotal > RING) {
+        for (size_t i = 0; i < count; i++) {
+            const nvc_host_product &it = items[i];
+            NVC_TRY(nvc_quantized_matmul_host_async(dev, &it.quant, it.dtype, it.transpose, it.host_x, it.w, it.scales, it.biases,
+                                                    it.global_scale, it.M, it.N, it.K, it.host_y));
+        }
+        return NVC_OK;
+    }
+    if (!dev->ring_host) {
+        NVC_CUDA(cudaHostAlloc((void **)&dev->ring_host, RING, cudaHostAllocMapped));
+        NVC_CUDA(cudaHostGetDevicePointer((void **)&dev->ring_host_dev, dev->ring_host, 0));
+        void *d = nullptr;
+        NVC_TRY(dev->pool.alloc(RING, &d));
+        dev->ring_dev = static_cast<char *>(d);
+        dev->ring_bytes = RING;
+    }
+    if (dev->ring_at + xtotal + ytotal > dev->ring_bytes) NVC_TRY(nvc_synchronize(dev));
+    size_t at;
+    {
+        std::lock_guard<std::mutex> g(dev->host_mu);
+        at = dev->ring_at;
+        dev->ring_at += xtotal + ytotal;
+    }
+    // activations: packed front to back, one copy
+    size_t xo = at;
+    for (size_t i = 0; i < count; i++) {
+        const size_t xb = (size_t)(items[i].M * items[i].K) * dtype_size(items[i].dtype);
+        if (xb) memcpy(dev->ring_host + xo, items[i].host_x, xb);
+        xo += pad(xb);
+    }
+    if (xtotal) NVC_CUDA(cudaMemcpyAsync(dev->ring_dev + at, dev->ring_host + at, xtotal, cudaMemcpyHostToDevice, dev->stream));
+    xo = at;
+    size_t yo = at + xtotal;
+    for (size_t i = 0; i < count; i++) {
+        const nvc_host_product &it = items[i];
+        const size_t xb = (size_t)(it.M * it.K) * dtype_size(it.dtype), yb = (size_t)(it.M * it.N) * dtype_size(it.dtype);
+        if (it.M != 0 && it.N != 0) {
+            const bool direct = yb <= 256 * 1024;
+            void *ydev = direct ? (void *)(dev->ring_host_dev + yo) : (void *)(dev->ring_dev + yo);
+            int32_t rc = nvc_quantized_matmul(dev, &it.quant, it.dtype, it.transpose, dev->ring_dev + xo, it.w, it.scales, it.biases,
+                                              it.global_scale, it.M, it.N, it.K, it.K, 1, 0, 0, 0, ydev);
+            if (rc != NVC_OK) return rc;
+            if (!direct) NVC_CUDA(cudaMemcpyAsync(dev->ring_host + yo, dev->ring_dev + yo, yb, cudaMemcpyDeviceToHost, dev->stream));
+            std::lock_guard<std::mutex> g(dev->host_mu);
+            dev->pending.push_back({dev->ring_host + yo, it.host_y, yb});
+        }
+        xo += pad(xb);
+        yo += pad(yb);
+    }
+    return NVC_OK;
+}

@@ -41,6 +41,14 @@ int32_t check_launch(nvc_device *dev, const char *kernel) {
     return NVC_OK;
 }
 
+int32_t deliver_pending(nvc_device *dev) {
+    std::lock_guard<std::mutex> g(dev->host_mu);
+    for (const auto &r : dev->pending) std::memcpy(r.host, r.pinned, r.bytes);
+    dev->pending.clear();
+    dev->ring_at = 0;
+    return NVC_OK;
+}
+
 int32_t ensure_error_word(nvc_device *dev) {
     if (!dev->error_word) {
         NVC_CUDA(cudaHostAlloc((void **)&dev->error_word, sizeof(int32_t), cudaHostAllocMapped));
@@ -255,6 +263,8 @@ int32_t nvc_device_close(nvc_device *dev) {
     if (dev->qmm_partials) dev->pool.free(dev->qmm_partials);
     if (dev->qmm_counters) dev->pool.free(dev->qmm_counters);
     if (dev->counters) dev->pool.free(dev->counters);
+    if (dev->ring_dev) dev->pool.free(dev->ring_dev);
+    if (dev->ring_host) cudaFreeHost(dev->ring_host);
     if (dev->staging) dev->pool.free(dev->staging);
     if (dev->pinned) cudaFreeHost(dev->pinned);
     if (dev->error_word) cudaFreeHost(dev->error_word);
@@ -282,6 +292,7 @@ int32_t nvc_device_info(nvc_device *dev, nvc_info *out) {
 int32_t nvc_synchronize(nvc_device *dev) {
     NVC_TRY(make_current(dev));
     NVC_CUDA(cudaStreamSynchronize(dev->stream));
+    deliver_pending(dev);
     if (dev->error_word && *dev->error_word != 0) {
         *dev->error_word = 0;
         // A kernel that gave up may have left arrival counters half-counted: rearm them, so that

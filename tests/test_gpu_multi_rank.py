@@ -137,3 +137,92 @@ def test_two_ranks_gather_and_all_sum_against_the_oracle():
             pr.join(30)
             if pr.is_alive():
                 pr.kill()
+
+
+def _comm_child(rank, world, conn):
+    try:
+        import nuvec_b200 as nv
+        from nuvec_b200 import _ffi
+        lib = _ffi.lib()
+        dev = nv.Device.shared(rank)
+        if rank == 0:
+            ident = (C.c_uint8 * 128)()
+            assert lib.nvc_comm_unique_id(ident) == 0, _ffi.last_error()
+            conn.send(bytes(ident))
+        ident = (C.c_uint8 * 128).from_buffer_copy(conn.recv())
+        comm = C.c_void_p()
+        assert lib.nvc_comm_init_timeout(dev._h, rank, world, ident, 120000, C.byref(comm)) == 0, _ffi.last_error()
+        assert lib.nvc_comm_rank(comm) == rank and lib.nvc_comm_size(comm) == world
+        base = np.arange(1000, dtype=np.float32) * (1 if rank == 0 else -1) + rank
+        out = {}
+        for name, op in (("sum", 0), ("max", 1), ("min", 2)):
+            buf = dev.array(base.copy(), nv.F32)
+            assert lib.nvc_all_reduce(comm, op, nv.F32, buf.ptr, base.size) == 0, _ffi.last_error()
+            out[name] = buf.to_numpy()
+        # ring exchange: send to the next rank, receive from the previous one
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        src = dev.array(np.full(4096, rank + 1, np.uint8), nv.U8)
+        dst = dev.array(np.zeros(4096, np.uint8), nv.U8)
+        if rank % 2 == 0:
+            assert lib.nvc_send(comm, src.ptr, 4096, nxt) == 0, _ffi.last_error()
+            assert lib.nvc_recv(comm, dst.ptr, 4096, prv) == 0, _ffi.last_error()
+        else:
+            assert lib.nvc_recv(comm, dst.ptr, 4096, prv) == 0, _ffi.last_error()
+            assert lib.nvc_send(comm, src.ptr, 4096, nxt) == 0, _ffi.last_error()
+        out["recv"] = dst.to_numpy()
+        gathered = dev.array(np.zeros(world * 8, np.uint8), nv.U8)
+        mine = dev.array(np.full(8, 10 + rank, np.uint8), nv.U8)
+        assert lib.nvc_all_gather(comm, mine.ptr, gathered.ptr, 8) == 0, _ffi.last_error()
+        out["gather"] = gathered.to_numpy()
+        assert lib.nvc_comm_health(comm) == 0, _ffi.last_error()
+        conn.send(("ok", out))
+        conn.recv()
+        lib.nvc_comm_destroy(comm)
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+        conn.send(("error", traceback.format_exc()))
+
+
+def test_two_ranks_nccl_communicator_reduce_ops_send_recv():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    pipes, procs = [], []
+    for r in range(world):
+        parent, child = ctx.Pipe()
+        pr = ctx.Process(target=_comm_child, args=(r, world, child))
+        pr.start()
+        pipes.append(parent)
+        procs.append(pr)
+    try:
+        assert pipes[0].poll(120)
+        ident = pipes[0].recv()
+        assert isinstance(ident, bytes), ident
+        for p in pipes:
+            p.send(ident)
+        results = []
+        for p in pipes:
+            assert p.poll(180), "a rank did not finish"
+            status, payload = p.recv()
+            assert status == "ok", payload
+            results.append(payload)
+        a = np.arange(1000, dtype=np.float32)
+        b = -a + 1
+        for r in range(world):
+            assert np.array_equal(results[r]["sum"], a + b)
+            assert np.array_equal(results[r]["max"], np.maximum(a, b))
+            assert np.array_equal(results[r]["min"], np.minimum(a, b))
+            assert np.all(results[r]["recv"] == ((r - 1) % world) + 1)
+            assert results[r]["gather"].tolist() == [10] * 8 + [11] * 8
+    finally:
+        for p in pipes:
+            try:
+                p.send("bye")
+            except Exception:
+                pass
+        for pr in procs:
+            pr.join(30)
+            if pr.is_alive():
+                pr.kill()

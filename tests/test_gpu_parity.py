@@ -443,3 +443,56 @@ def test_host_operand_entry_point_matches_the_device_one(be, M, N, K):
         assert rc == 0, _ffi.last_error()
         assert np.array_equal(got, want.view(np.uint16).reshape(M, N))
         got[:] = 0
+
+
+def test_asynchronous_host_entry_point_delivers_at_synchronize(be):
+    # nvc_quantized_matmul_host_async: products are issued back to back, nothing waits, and one
+    # nvc_synchronize delivers every pending result -- the same bits as the device-resident call
+    import ctypes as C
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+    lib = _ffi.lib()
+    rng = np.random.default_rng(31)
+    dev = nv.Device.shared(0)
+    quant = nv.Quant.affine(64, 4)
+    qc = quant._c()
+    cases = []
+    for M, N, K in [(1, 4096, 4096), (8, 512, 1024), (1, 24576, 4096), (300, 512, 1024), (1, 64, 128)]:
+        q = nv.quantize(dev.array(rand(rng, (N, K), oracle.BF16, 0.02), nv.BF16), quant)
+        xh = np.ascontiguousarray(rand(rng, (M, K), oracle.BF16))
+        want = nv.quantized_matmul(dev.array(xh, nv.BF16), q).to_numpy().view(np.uint16).reshape(M, N)
+        cases.append((M, N, K, q, xh, want, np.zeros((M, N), np.uint16)))
+    for rounds in range(3):
+        for M, N, K, q, xh, want, got in cases:
+            got[:] = 0
+            x_call = xh.copy()
+            rc = lib.nvc_quantized_matmul_host_async(dev._h, C.byref(qc), nv.BF16, 1, x_call.ctypes.data_as(C.c_void_p),
+                                                     q.weight.ptr, q.scales.ptr, q.biases.ptr, None, M, N, K,
+                                                     got.ctypes.data_as(C.c_void_p))
+            assert rc == 0, _ffi.last_error()
+            x_call[:] = 0  # the activations may be reused as soon as the call returns
+        dev.synchronize()
+        for M, N, K, q, xh, want, got in cases:
+            assert np.array_equal(got, want), (M, N, K)
+    # the same products as one list (nvc_quantized_matmul_host_batch)
+    items = (_ffi.HostProduct * len(cases))()
+    for it, (M, N, K, q, xh, want, got) in zip(items, cases):
+        got[:] = 0
+        it.quant, it.dtype, it.transpose = qc, nv.BF16, 1
+        it.host_x, it.host_y = xh.ctypes.data, got.ctypes.data
+        it.w, it.scales, it.biases, it.global_scale = q.weight.ptr.value, q.scales.ptr.value, q.biases.ptr.value, None
+        it.M, it.N, it.K = M, N, K
+    assert lib.nvc_quantized_matmul_host_batch(dev._h, items, len(items)) == 0, _ffi.last_error()
+    dev.synchronize()
+    for M, N, K, q, xh, want, got in cases:
+        assert np.array_equal(got, want), (M, N, K)
+    # more pending work than the staging blocks hold: the call flushes by itself
+    M, N, K, q, xh, want, _ = cases[2]
+    outs = [np.zeros((M, N), np.uint16) for _ in range(40)]
+    big = [np.zeros((300, 512), np.uint16) for _ in range(200)]
+    Mb, Nb, Kb, qb, xb, wantb, _ = cases[3]
+    for o in big:
+        assert lib.nvc_quantized_matmul_host_async(dev._h, C.byref(qc), nv.BF16, 1, xb.ctypes.data_as(C.c_void_p), qb.weight.ptr,
+                                                   qb.scales.ptr, qb.biases.ptr, None, Mb, Nb, Kb, o.ctypes.data_as(C.c_void_p)) == 0
+    dev.synchronize()
+    assert all(np.array_equal(o, wantb) for o in big)
