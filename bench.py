@@ -31,6 +31,7 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 from pathlib import Path
 
 import numpy as np
@@ -40,6 +41,9 @@ sys.path.insert(0, str(ROOT))
 
 # Qwen3-8B projection shapes (N out, K in): qkv, o, gate+up, down.
 PROJECTIONS = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288)]
+# Rows of the fused projections' segments (q | k | v with 32 query and 8 key/value heads of 128; gate | up):
+# a rank of an N-sharded step holds its share of every segment (nuvec_b200.shard.parts).
+SEGMENTS = {"qkv": [4096, 1024, 1024], "o": [4096], "gate_up": [12288, 12288], "down": [4096]}
 LAYERS = 36
 GS, BITS = 64, 4
 PREFILL = (2048, 12288, 4096)  # M, N, K
@@ -205,7 +209,7 @@ def reference_arm(args):
 def workload_config(gpus):
     return {"workload": "qwen3-8b decode projections, M=1, affine 4-bit g64, 36 layers x (qkv 4096->6144, o 4096->4096, "
                         "gate+up 4096->24576, down 12288->4096)",
-            "parallelism": f"N-sharded x{gpus} + all_gather" if gpus > 1 else "single GPU",
+            "parallelism": f"N-sharded x{gpus} (each rank its share of every q|k|v and gate|up segment) + all_gather" if gpus > 1 else "single GPU",
             "l2": "inputs larger than L2 (3.9 GB of weights per step, 108 MB per layer)",
             "weights": "one seeded layer (W ~ N(0, 0.02) -> bf16 -> nuvec quantize) replicated into 36 distinct buffers"}
 
@@ -274,6 +278,8 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the parity check that precedes the timing")
     ap.add_argument("--sweep", action="store_true", help="time every single-GPU configuration of the benchmark definition and print one JSON object")
     ap.add_argument("--no-graph", action="store_true", help="launch every product from the host instead of replaying a recorded step")
+    ap.add_argument("--workload", default="decode", choices=["decode", "moe"],
+                    help="moe: the expert-sharded mixture-of-experts products (gather_qmm) on --gpus ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -285,7 +291,7 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
 
     import nuvec_b200 as nv
-    from nuvec_b200 import _ffi
+    from nuvec_b200 import _ffi, shard
 
     dist = None
     if world > 1:
@@ -301,6 +307,8 @@ def main():
             raise SystemExit("--sweep runs on one GPU")
         print(json.dumps({"sweep": config_sweep(nv, _ffi, dev, peaks), "peaks": peaks}))
         return
+    if args.workload == "moe":
+        return moe_bench(args, nv, _ffi, shard, dev, dist, rank, world, peaks)
     M = args.rows
 
     # ── weights: one seeded layer, quantized on the device, replicated into distinct buffers ──
@@ -311,7 +319,7 @@ def main():
     for name, N, K in PROJECTIONS:
         assert N % world == 0
         n_local = N // world
-        w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02)[rank * n_local:(rank + 1) * n_local]
+        w = shard.shard_rows(rng.standard_normal((N, K), dtype=np.float32) * 0.02, world, rank, SEGMENTS[name])
         q = nv.quantize(dev.array(nv.f32_to_bf16(w), nv.BF16), quant)
         x = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
         base.append((name, N, K, n_local, q, x))
@@ -356,7 +364,7 @@ def main():
 
     # ── fused product + gather over peer stores (the multi-GPU headline; NCCL stays as the check) ──
     fused = None
-    if world > 1 and not os.environ.get("NUVEC_BENCH_NO_FUSED"):
+    if world > 1:
         try:
             RES = 4096
             offsets, at = [], RES
@@ -678,6 +686,152 @@ def main():
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
+        os._exit(0)
+
+
+# ── expert-sharded mixture of experts (gather_qmm), --workload moe ───────────────────────────
+MOE_CONFIGS = [
+    # name, experts, top-k, tokens, (projection, N, K) list, quantization
+    ("qwen3-30b-a3b", 128, 8, (1, 512), [("gate_up", 1536, 2048), ("down", 2048, 768)], ("affine", 64, 4)),
+    ("gpt-oss-20b mxfp4", 32, 4, (1, 1024), [("gate_up", 5760, 2880), ("down", 2880, 2880)], ("mxfp4", 32, 4)),
+    ("gpt-oss-20b nvfp4", 32, 4, (1, 1024), [("gate_up", 5760, 2880), ("down", 2880, 2880)], ("nvfp4", 16, 4)),
+]
+
+
+def moe_bench(args, nv, _ffi, shard, dev, dist, rank, world, peaks):
+    """Every rank owns experts [r E/g, (r+1) E/g) and, the gathered rows being sorted by expert, a
+    contiguous slice of them (from the sorted offsets); it multiplies that slice with its own experts
+    (nvc_gather_qmm) and the ranks' disjoint row ranges are joined by a padded all_gather.  Before any
+    timing, rank 0 multiplies the whole list with all experts on its own GPU and the joined result
+    must agree with it row for row (same kernel, same operands: bit for bit unless a tile is cut
+    along K differently, in which case within one output rounding)."""
+    lib = _ffi.lib()
+    comm = None
+    if world > 1:
+        import torch
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            assert lib.nvc_comm_unique_id(buf) == 0, _ffi.last_error()
+            ident = torch.tensor(list(buf), dtype=torch.uint8, device="cuda")
+        dist.broadcast(ident, 0)
+        idb = (C.c_uint8 * 128)(*ident.cpu().tolist())
+        comm = C.c_void_p()
+        assert lib.nvc_comm_init(dev._h, rank, world, idb, C.byref(comm)) == 0, _ffi.last_error()
+    rows_out = []
+    for cname, E, topk, tokens, projs, (mode, gs, bits) in MOE_CONFIGS:
+        quant = nv.Quant(nv.QuantMode(mode), gs, bits)
+        lo, hi = shard.expert_range(E, world, rank)
+        for pname, N, K in projs:
+            rng = np.random.default_rng(zlib.crc32(f"{cname}/{pname}".encode()))
+            # random codes with scales in the range quantizing N(0, 0.02) weights gives; every rank
+            # draws the same experts, keeps its own (rank 0 keeps all of them for the check)
+            words = K * bits // 32
+            codes = rng.integers(0, 2 ** 32, (E, N, words), dtype=np.uint32)
+            if mode == "affine":
+                sc = nv.f32_to_bf16((rng.random((E, N, K // gs), dtype=np.float32) * 0.06 + 0.03) / 15.0)
+                bi = nv.f32_to_bf16(-(rng.random((E, N, K // gs), dtype=np.float32) * 0.04 + 0.02))
+                sdt = nv.BF16
+            else:
+                sc = rng.integers(117, 123, (E, N, K // gs), dtype=np.uint8) if mode == "mxfp4" else \
+                    rng.integers(0x08, 0x30, (E, N, K // gs), dtype=np.uint8)
+                bi, sdt = None, nv.U8
+
+            def on_device(e0, e1):
+                return nv.Quantized(dev.array(np.ascontiguousarray(codes[e0:e1]), nv.U32), dev.array(np.ascontiguousarray(sc[e0:e1]), sdt),
+                                    None if bi is None else dev.array(np.ascontiguousarray(bi[e0:e1]), nv.BF16), quant)
+            mine = on_device(lo, hi)
+            copies = [mine]
+            per_rank_bytes = (hi - lo) * N * (words * 4 + (K // gs) * (4 if mode == "affine" else 1))
+            while len(copies) * per_rank_bytes < 300e6 and len(copies) < 16:  # distinct copies: more than L2 per rank
+                copies.append(on_device(lo, hi))
+            full = on_device(0, E) if rank == 0 and world > 1 else None
+            for T in tokens:
+                ids = np.concatenate([rng.permutation(E)[:topk] for _ in range(T)]).astype(np.uint32)
+                order = np.argsort(ids, kind="stable")
+                sid = ids[order]
+                xh = nv.f32_to_bf16(rng.standard_normal((T, K), dtype=np.float32))
+                xs = np.ascontiguousarray(xh[order // topk]).reshape(T * topk, 1, K)
+                bounds = [shard.expert_rows(sid, E, world, r) for r in range(world)]
+                first, last = bounds[rank]
+                mrows = max(1, max(b - a for a, b in bounds))
+                x_local = dev.array(np.ascontiguousarray(xs[first:last]) if last > first else np.zeros((1, 1, K), np.uint16), nv.BF16)
+                rhs_local = dev.array((sid[first:last] - lo).astype(np.uint32) if last > first else np.zeros(1, np.uint32), nv.U32)
+                n_local = last - first
+                gathered = dev.empty((world, mrows, N), nv.BF16)
+                lib.nvc_memset(dev._h, gathered.ptr, 0, gathered.nbytes)
+                slot = C.c_void_p(gathered.ptr.value + rank * mrows * N * 2)
+                qc = quant._c()
+                opts = nv.GatherQmm(transpose=True, sorted_indices=True)
+                state = {"i": 0}
+
+                def product():
+                    q = copies[state["i"] % len(copies)]
+                    state["i"] += 1
+                    if n_local > 0:
+                        rc = lib.nvc_gather_qmm(dev._h, C.byref(qc), nv.BF16, 1, x_local.ptr, q.weight.ptr, q.scales.ptr,
+                                                None if q.biases is None else q.biases.ptr, None, None, rhs_local.ptr, None, 1,
+                                                n_local, n_local, 1, N, K, hi - lo, slot)
+                        assert rc == 0, _ffi.last_error()
+                    if comm is not None:
+                        assert lib.nvc_all_gather(comm, slot, gathered.ptr, mrows * N * 2) == 0, _ffi.last_error()
+
+                product()
+                dev.synchronize()
+                check = None
+                if world > 1:
+                    got = gathered.to_numpy().view(np.uint16)
+                    joined = np.concatenate([got[r, :b - a] for r, (a, b) in enumerate(bounds)], axis=0)
+                    if rank == 0:
+                        want = nv.gather_qmm(dev.array(xs, nv.BF16), full, None, dev.array(sid, nv.U32), opts).to_numpy()
+                        want = want.view(np.uint16).reshape(T * topk, N)
+                        if np.array_equal(joined, want):
+                            check = "ok (bit for bit)"
+                        else:
+                            g32, w32 = nv.bf16_to_f32(joined).astype(np.float64), nv.bf16_to_f32(want).astype(np.float64)
+                            lim = 2.0 ** -7 * np.abs(w32) + 2e-5 * np.abs(w32).max(axis=1, keepdims=True)
+                            check = "ok (within one output rounding)" if np.all(np.abs(g32 - w32) <= lim) else "FAILED"
+                        if check == "FAILED":
+                            raise SystemExit(f"parity check failed: expert-sharded {cname} {pname} T={T} differs from the single-GPU product")
+                reps = 5 if T > 1 else 20
+
+                def step():
+                    for _ in range(len(copies)):
+                        product()
+                step()
+                g = dev.record(step)
+                for _ in range(3):
+                    g.launch()
+                dev.synchronize()
+                if dist is not None:
+                    dist.barrier()
+                e0, e1 = dev.event(), dev.event()
+                e0.record()
+                for _ in range(reps):
+                    g.launch()
+                e1.record()
+                e1.synchronize()
+                us = e0.elapsed_ms(e1) * 1e3 / reps / len(copies)
+                if dist is not None:
+                    import torch
+                    t = torch.tensor([us], device="cuda")
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    us = float(t.item())
+                touched = len(np.unique(ids))
+                wbytes = touched * N * (words * 4 + (K // gs) * (4 if mode == "affine" else 1))
+                flops = 2.0 * T * topk * N * K
+                rows_out.append({"config": cname, "projection": pname, "tokens": T, "rows": T * topk, "experts": E, "N": N, "K": K,
+                                 "quant": f"{mode} b{bits} g{gs}", "n_gpus": world, "experts_per_gpu": hi - lo,
+                                 "rows_per_rank": [b - a for a, b in bounds], "us_per_product": us,
+                                 "weight_GB/s": wbytes / us / 1e3, "TFLOP/s": flops / us / 1e6, "check": check,
+                                 "includes": "gather_qmm on the rank's row slice" + (" + padded ncclAllGather of the row slices" if world > 1 else "")})
+    if rank == 0:
+        print(json.dumps({"workload": "moe", "metric": "gather_qmm, expert-sharded", "n_gpus": world, "data": "synthetic",
+                          "scaling": "strong", "rows": rows_out, "peaks": peaks}), flush=True)
+    dev.synchronize()
+    if world > 1:
+        dist.barrier()
+        sys.stdout.flush()
         os._exit(0)
 
 

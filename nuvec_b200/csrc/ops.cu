@@ -33,19 +33,6 @@ static int32_t check_product(const char *op, const nvc_quant *q, int32_t dtype, 
 // per expert on average.
 static bool grouped(int64_t rows, int64_t experts) { return rows >= 16 && rows / (experts > 0 ? experts : 1) >= 4; }
 
-// Rows from which a plain product goes to the tensor-core kernel.  Affine weights with up to 8
-// rows stream once through the few-row kernel when it takes the shape (it stages every activation
-// row in shared memory); everything else the tensor-core kernel is eligible for goes there, with
-// its smallest token tile for few rows: 9 to 16 rows, and few-row products the few-row kernel refused.
-// NUVEC_QMM_MIN_ROWS raises the bar (products below it fall through to the generic kernel).
-static int64_t qmm_threshold() {
-    static int64_t v = [] {
-        const char *e = getenv("NUVEC_QMM_MIN_ROWS");
-        return e ? atoll(e) : 1;
-    }();
-    return v;
-}
-
 __global__ void sorted_offsets_kernel(const uint32_t *__restrict__ idx, int64_t rows, int64_t groups,
                                       int32_t *__restrict__ out) {
     int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -106,7 +93,7 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
         p.global = global_scale; p.expert_global = 0;
         return launch_qmv_affine(dev, qmv_kind(q->mode, q->bits), p, batch);
     }
-    if (M >= qmm_threshold() && qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
+    if (qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
         for (int64_t b = 0; b < batch; b++) {
             QmmParams p{};
             p.mode = q->mode; p.gs = q->group_size; p.bits = q->bits;

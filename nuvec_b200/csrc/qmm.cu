@@ -72,18 +72,6 @@ struct QmmKernelParams {
 };
 
 
-// Optional role timing (probe builds only: -DNUVEC_QMM_TIMING): cycles block 0 spends in each phase.
-#ifdef NUVEC_QMM_TIMING
-__device__ long long g_qmm_timing[16];
-#define QMM_T0() long long tacc[4] = {0, 0, 0, 0}; long long t__ = clock64()
-#define QMM_ACC(slot) do { long long n__ = clock64(); tacc[slot] += n__ - t__; t__ = n__; } while (0)
-#define QMM_DUMP(base) do { if (blockIdx.x == 0 && lane == 0) for (int i__ = 0; i__ < 4; i__++) atomicAdd((unsigned long long *)&g_qmm_timing[base + i__], (unsigned long long)tacc[i__]); } while (0)
-#else
-#define QMM_T0() do {} while (0)
-#define QMM_ACC(slot) do {} while (0)
-#define QMM_DUMP(base) do {} while (0)
-#endif
-
 // ── PTX wrappers ───────────────────────────────────────────────────────────────────────────
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -113,9 +101,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 // Bounded wait.  Returns false when it gave up (after QMM_WAIT_LIMIT_NS) or another thread of the
-// block already did.  The SLEEP_NS parameter is kept for call sites that used to back off between
-// polls; parking makes it unnecessary.
-template <int SLEEP_NS = 0>
+// block already did.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
@@ -134,24 +120,8 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// Non-blocking test of two barriers; true when both phases are complete.  (A successful
-// mbarrier.try_wait was measured at ~200 cycles on an idle SM: it parks and wakes the warp.  The
-// MMA thread, whose inputs are normally ready long before it asks, tests first and only falls
-// back to the parking wait when it really has to wait.)
-__device__ __forceinline__ bool mbar_test2(uint32_t bar_a, uint32_t bar_b, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %3;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q, [%2], %3;\n\t"
-        "and.pred p, p, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar_a), "r"(bar_b), "r"(parity) : "memory");
-    return done != 0;
-}
 // Hardware named barriers between the watcher warp and the MMA warp (64 threads).
 __device__ __forceinline__ void named_sync(uint32_t id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 __device__ __forceinline__ void named_sync_n(uint32_t id, uint32_t threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
@@ -182,14 +152,6 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32])
           "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, f32 accumulate.
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -546,7 +508,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
                 for (int kb = item.kb0; kb < item.kb1 && ok; kb += KPS, wit++) {
                     const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
-                    ok = mbar_wait<200>(wempty + s, ph ^ 1, abort_flag);
+                    ok = mbar_wait(wempty + s, ph ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(wfull + s, QMM_W_BYTES);
                     tma_load_2d(ws + s * QMM_W_BYTES, &tmap_w, (kb / KPS) * 128, ti.wrow0, wfull + s);
@@ -564,7 +526,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         uint32_t tcount = 0, s = 0;
         const uint32_t empty0 = smem_u32(empty);
         const uint64_t bd0 = umma_desc(smem_u32(xs));
-        QMM_T0();
         for (int j = 0;; j++) {
             Item item;
             if (!qmm_item<KPS>(p, kblocks, j, item)) break;
@@ -573,9 +534,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint32_t buf = tcount % ACC_BUFS;
             const uint32_t d = tmem_base + buf * BT;
             for (int kb = item.kb0; kb < item.kb1; kb++) {
-                QMM_ACC(2);
                 named_sync(1 + s);  // stage s is full (and, for kb = 0, the accumulator is drained)
-                QMM_ACC(1);
                 if (lane == 0) {
                     tc_fence_after();
                     const uint32_t at = tmem_base + A_COL0 + s * 32;
@@ -583,50 +542,40 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 #pragma unroll
                     for (int k = 0; k < QMM_BK / 16; k++)  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
                         tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
-                    QMM_ACC(3);
                     tc_commit_addr(empty0 + 8 * s);  // frees both halves of the stage once these MMAs have read them
                 }
                 __syncwarp();
-                QMM_ACC(0);
                 if (++s == STAGES) s = 0;
             }
             if (lane == 0) tc_commit(accfull + buf);
             __syncwarp();
             tcount++;
         }
-        QMM_DUMP(0);
     } else if (warp == QMM_WATCH_WARP) {
         // ── watcher: the MMA warp's eyes.  It arrives on the named barrier of every stage exactly
         //    once per k-block whatever happens (after a wait gave up it stops waiting, not
         //    arriving), so the MMA warp can never be left behind in a barrier. ──
         uint32_t tcount = 0, s = 0, ph = 0;
         bool ok = true;
-        QMM_T0();
         for (int j = 0;; j++) {
             Item item;
             if (!qmm_item<KPS>(p, kblocks, j, item)) break;
             TileInfo ti;
             if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
-            QMM_ACC(3);
-            if (lane == 0 && ok) ok = mbar_wait<100>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
-            QMM_ACC(0);
+            if (lane == 0 && ok) ok = mbar_wait(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
             for (int kb = item.kb0; kb < item.kb1; kb++) {
                 if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
-                QMM_ACC(1);
                 if (lane == 0 && ok) ok = mbar_wait(afull + s, ph, abort_flag);
-                QMM_ACC(2);
                 __syncwarp();
                 named_arrive(1 + s);
                 if (++s == STAGES) {
                     s = 0;
                     ph ^= 1;
                 }
-                QMM_ACC(3);
             }
             tcount++;
         }
-        QMM_DUMP(12);
     } else if (warp >= 7 && warp < QMM_WATCH_WARP) {
         // ── dequantizers ─────────────────────────────────────────────────────────────────
         // Four groups of 4 warps take k-blocks in turn.  Thread = weight row = tensor-memory lane
@@ -638,7 +587,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
         uint32_t it_base = 0, wit = 0;
         bool ok = true;
-        QMM_T0();
         // scale / bias codes of one block: [half] for 32-value halves (equal when the group is larger)
         auto load_consts = [&](const uint16_t *sc, const uint16_t *bi, const uint8_t *fsc, int kb, uint32_t (&sv)[2], uint32_t (&bv)[2]) {
 #pragma unroll
@@ -673,12 +621,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     if ((int)((it_base + kb - item.kb0) % QMM_DQ_GROUPS) != group) continue;
                     const uint32_t s_cur[2] = {s_next[0], s_next[1]}, b_cur[2] = {b_next[0], b_next[1]};
                     if (kb + QMM_DQ_GROUPS < item.kb1) load_consts(sc, bi, fsc, kb + QMM_DQ_GROUPS, s_next, b_next);  // prefetch
-                    QMM_ACC(2);
                     if (!have) {
                         ok = mbar_wait(wfull + wsi, wph, abort_flag);
                         have = true;
                     }
-                    QMM_ACC(0);
                     const uint8_t *wrow = ws + wsi * QMM_W_BYTES + row * 128;
                     uint32_t v[32];  // 64 bfloat16: column c of the stage holds k = 2c, 2c + 1
                     if (ok) {
@@ -732,9 +678,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                         }
                     }
                     const uint32_t it = it_base + (uint32_t)(kb - item.kb0), sa = it % STAGES, pha = (it / STAGES) & 1;
-                    QMM_ACC(2);
                     ok = ok && mbar_wait(empty + sa, pha ^ 1, abort_flag);  // the MMAs that read this stage are done
-                    QMM_ACC(1);
                     if (!ok) break;
                     tc_fence_after();
                     tc_st32(tmem_base + lane_base + A_COL0 + sa * 32, v);
@@ -742,7 +686,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     tc_fence_before();  // the stores are ordered before the arrive the MMA thread waits on
                     __syncwarp();
                     if (lane == 0) mbar_arrive(afull + sa);
-                    QMM_ACC(3);
                 }
                 // A warp none of whose blocks lay in this slab still waits for the slab before it
                 // releases it: otherwise it could run ahead and its arrival for a later slab would
@@ -753,8 +696,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             }
             it_base += (uint32_t)(item.kb1 - item.kb0);
         }
-        if (warp == 7) QMM_DUMP(4);
-        if (warp == 19) QMM_DUMP(8);
     } else {
         // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
         uint32_t tcount = 0;
@@ -767,7 +708,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             // After a wait gave up the warp keeps walking the items without touching data: the
             // named barriers of K-split tiles below must still see all four epilogue warps.
-            if (ok) ok = mbar_wait<500>(accfull + buf, aph, abort_flag);
+            if (ok) ok = mbar_wait(accfull + buf, aph, abort_flag);
             tc_fence_after();
             const int r = warp * 32 + lane;  // row of the tile
             const int n = ti.n0 + r;
@@ -868,17 +809,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     }
 }
 
-#ifdef NUVEC_QMM_TIMING
-extern "C" int nvc_debug_qmm_timing(long long *out, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_qmm_timing, sizeof(long long) * 16);
-    if (reset) {
-        long long z[16] = {0};
-        cudaMemcpyToSymbol(g_qmm_timing, z, sizeof z);
-    }
-    return 0;
-}
-#endif
 
 // ── host side ──────────────────────────────────────────────────────────────────────────────
 
@@ -914,7 +844,8 @@ static int32_t make_map(CUtensorMap *map, CUtensorMapDataType type, const void *
 bool qmm_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t transpose, int64_t M, int64_t N,
                   int64_t K, const void *x, int64_t ldx, const uint32_t *w) {
     (void)gs;
-    if (getenv("NUVEC_QMM_DISABLE")) return false;
+    static const bool disabled = getenv("NUVEC_QMM_DISABLE") != nullptr;  // read once: products then take the other kernels
+    if (disabled) return false;
     if (dtype != NVC_BF16 || !transpose) return false;
     if (mode == NVC_AFFINE) {
         if (bits != 2 && bits != 4 && bits != 8) return false;
@@ -966,10 +897,16 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     // alignment slack, activation stages, packed-weight slabs, 1 KB of barriers and flags, the grouped products' tables
     constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1);
     auto kernel = qmm_kernel<BITS, BT, STAGES, MODE>;
-    static bool configured = false;
-    if (!configured) {
-        NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
+    // the opt-in to this much dynamic shared memory is a per-device attribute of the instantiation
+    static bool configured[64] = {};
+    static std::mutex configured_mu;
+    if (dev->ordinal < 0 || dev->ordinal >= 64) return set_error(NVC_ERR_UNSUPPORTED, "qmm: device ordinal %d", dev->ordinal);
+    {
+        std::lock_guard<std::mutex> g(configured_mu);
+        if (!configured[dev->ordinal]) {
+            NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured[dev->ordinal] = true;
+        }
     }
     // The schedule (see Item): whole tiles wave by wave, then the left-over tiles cut along K.
     QmmKernelParams k = kp;
@@ -984,7 +921,7 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
         k.full_waves = 0;
         k.tail_tiles = total_tiles;
     }
-    if (k.tail_tiles > 0 && !getenv("NUVEC_QMM_NO_KSPLIT")) {
+    if (k.tail_tiles > 0) {
         // Parts per tile: whatever makes the left-over tiles finish soonest when the parts are dealt
         // over the multiprocessors in one or two rounds (time ~ rounds / parts, plus a little for
         // the partial sums); at least two slabs of weights per part, at most 16 parts.
@@ -1039,10 +976,6 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     // measured: 8-bit weights at 2048 rows run 294 us with 192-token tiles and 333-356 us with 256
     if (p.bits == 8 && per > 192 && per <= 4096) bt = 192;
     if (p.offsets) bt = per > 170 ? 256 : per > 128 ? 192 : per > 85 ? 192 : per > 42 ? 128 : per > 21 ? 64 : 32;
-    if (const char *e = getenv("NUVEC_QMM_BT")) {
-        int v = atoi(e);
-        if (v == 32 || v == 64 || v == 128 || v == 192 || v == 256) bt = v;
-    }
     const int n_tiles = (int)((p.N + QMM_BN - 1) / QMM_BN);
     int64_t token_tiles;
     if (p.offsets) token_tiles = (p.rows + bt - 1) / bt + experts;  // upper bound: one partial tile per expert

@@ -74,6 +74,65 @@ def test_n_sharded_product_equals_the_unsharded_one():
     assert sorted(results) == [(0, True), (1, True)]
 
 
+def test_segment_aware_split_keeps_every_rank_in_every_segment():
+    # q|k|v of a Qwen3-8B layer: 4096 + 1024 + 1024 rows; the reference gives every rank its share of
+    # each segment (shard.rs:34-45), not a flat slice of the fused matrix
+    from nuvec_b200 import shard
+    import oracle
+    segs = [4096, 1024, 1024]
+    assert shard.parts(segs, 8, 3) == [(1536, 2048), (4096 + 384, 4096 + 512), (5120 + 384, 5120 + 512)]
+    assert shard.parts([12288, 12288], 2, 1) == [(6144, 12288), (18432, 24576)]
+    with pytest.raises(ValueError):
+        shard.parts([10, 6], 4, 0)
+    rng = np.random.default_rng(1)
+    segs, K, M, g = [64, 32, 32], 256, 2, 4
+    N = sum(segs)
+    w = oracle.from_f32((rng.standard_normal((N, K)) * 0.02).astype(np.float32), oracle.BF16)
+    c, s, b = oracle.quantize(w, oracle.BF16, oracle.AFFINE, 64, 4)
+    x = oracle.from_f32(rng.standard_normal((M, K)).astype(np.float32), oracle.BF16)
+    full = oracle.quantized_matmul(x, c, s, b, oracle.BF16)
+    slots = np.stack([oracle.quantized_matmul(x, shard.shard_rows(c, g, r, segs), shard.shard_rows(s, g, r, segs),
+                                              shard.shard_rows(b, g, r, segs), oracle.BF16) for r in range(g)])
+    assert np.array_equal(shard.unshard(slots, segs), full)
+    assert not np.array_equal(shard.unshard(slots), full)   # a flat reading of the slots mixes the segments
+
+
+def test_column_shards_sum_to_the_whole_product():
+    from nuvec_b200 import shard
+    import oracle
+    rng = np.random.default_rng(2)
+    N, K, M, g = 48, 512, 3, 4
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    c, s, b = oracle.quantize(w, oracle.F32, oracle.AFFINE, 64, 4)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    full = oracle.quantized_matmul(x, c, s, b, oracle.F32)
+    total = np.zeros_like(full, dtype=np.float64)
+    for r in range(g):
+        lo, hi = shard.col_range(K, 64, g, r)
+        cr, sr, br = shard.shard_cols(c, s, b, 4, 64, g, r)
+        total += oracle.quantized_matmul(np.ascontiguousarray(x[:, lo:hi]), cr, sr, br, oracle.F32)
+    assert np.allclose(total, full, rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        shard.col_range(192, 64, 2, 0)   # 96 columns per rank are not whole groups of 64
+
+
+def test_expert_rows_partition_the_sorted_list():
+    from nuvec_b200 import shard
+    import oracle
+    rng = np.random.default_rng(3)
+    E, g = 128, 8
+    ids = np.sort(np.concatenate([rng.permutation(E)[:8] for _ in range(512)])).astype(np.uint32)
+    offs = oracle.sorted_offsets(ids, E)
+    at = 0
+    for r in range(g):
+        first, last = shard.expert_rows(ids, E, g, r)
+        lo, hi = shard.expert_range(E, g, r)
+        assert first == at and first == int(offs[lo]) and last == (int(offs[hi]) if hi < E else len(ids))
+        assert np.all((ids[first:last] >= lo) & (ids[first:last] < hi))
+        at = last
+    assert at == len(ids)
+
+
 def test_row_ranges():
     from nuvec_b200 import shard
     assert [shard.row_range(24576, 8, r) for r in (0, 7)] == [(0, 3072), (21504, 24576)]
