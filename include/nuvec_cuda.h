@@ -202,6 +202,20 @@ int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32
                        const int32_t *offsets, int32_t sorted, int64_t rows, int64_t x_batches,
                        int64_t M, int64_t N, int64_t K, int64_t experts, void *y);
 
+/* fast::moe_route (crates/nuvec-core/src/fast/imp.rs:2652-2672; kernel crates/nuvec-kernels/src/metal/moe.metal):
+ * per row of `experts` router probabilities (float dtype, dense [rows, experts]) the indices
+ * (uint32 [rows, k]) of the k largest in the stable ascending order of a sort with NaN last, and
+ * those probabilities ([rows, k], same dtype), divided by their sum when `normalize` is set.  At
+ * most 1024 experts.  The results are the bits of the reference's CPU composition
+ * (argpartition, take_along_axis, sum, divide). */
+int32_t nvc_moe_route(nvc_device *dev, int32_t dtype, const void *probs, int64_t rows, int64_t experts,
+                      int64_t k, int32_t normalize, uint32_t *out_indices, void *out_scores);
+/* fast::weighted_sum (fast/imp.rs:2731-2747): out[r, :] = sum over j of x[r, j, :] * w[r, j] for
+ * x [rows, k, d] and w [rows, k] of one float dtype; products rounded to the dtype, the sum taken in
+ * float64 in order and rounded once, as the reference's CPU composition does. */
+int32_t nvc_weighted_sum(nvc_device *dev, int32_t dtype, const void *x, const void *w, int64_t rows,
+                         int64_t k, int64_t d, void *out);
+
 /* The same product with HOST operands for the activations and the result: copies x in,
  * multiplies, copies y out and waits.  This is what an evaluator whose arrays live in host
  * memory calls per step (the reference's CPU arrays, buffer.rs:17-27); the weights stay

@@ -82,6 +82,8 @@ SIGNATURES = {
     "nvc_sorted_offsets": (I32T, [P, P, I64T, I64T, P]),
     "nvc_gather_qmm": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, P, P, P, I32T, I64T, I64T, I64T, I64T,
                               I64T, I64T, P]),
+    "nvc_moe_route": (I32T, [P, I32T, P, I64T, I64T, I64T, I32T, P, P]),
+    "nvc_weighted_sum": (I32T, [P, I32T, P, P, I64T, I64T, I64T, P]),
     "nvc_quantized_matmul_host": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, P]),
     "nvc_quantized_matmul_host_async": (I32T, [P, QP, I32T, I32T, P, P, P, P, P, I64T, I64T, I64T, P]),
     "nvc_quantized_matmul_host_batch": (I32T, [P, C.POINTER(HostProduct), SZ]),

@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -524,6 +524,35 @@ def sorted_offsets(indices: Array, groups: int) -> Array:
         raise InvalidArgument("sorted_offsets: indices must be uint32")
     out = indices.dev.empty((groups,), I32)
     _check(_ffi.lib().nvc_sorted_offsets(indices.dev._h, indices.ptr, indices.size, groups, out.ptr))
+    return out
+
+
+def moe_route(probs: Array, k: int, normalize: bool = True):
+    """fast::moe_route (fast/imp.rs:2652-2672): (indices uint32 [..., k], scores [..., k]) of the k
+    largest probabilities along the last axis, in the stable ascending order of a sort."""
+    if probs.dtype not in _FLOATS:
+        raise InvalidArgument(f"moe_route: probabilities must be floating point, got {DTYPE_NAMES.get(probs.dtype, probs.dtype)}")
+    e = probs.shape[-1] if probs.ndim else 0
+    if not 1 <= k <= e:
+        raise InvalidArgument(f"moe_route: k must be in 1..={e} for probabilities of shape {list(probs.shape)}")
+    rows = probs.size // e
+    lead = tuple(probs.shape[:-1])
+    idx = probs.dev.empty(lead + (k,), U32)
+    scores = probs.dev.empty(lead + (k,), probs.dtype)
+    _check(_ffi.lib().nvc_moe_route(probs.dev._h, probs.dtype, probs.ptr, rows, e, k, int(normalize), idx.ptr, scores.ptr))
+    return idx, scores
+
+
+def weighted_sum(x: Array, w: Array) -> Array:
+    """fast::weighted_sum (fast/imp.rs:2731-2747): x [..., k, D] times w [..., k], summed over k."""
+    if x.ndim < 2 or tuple(w.shape) != tuple(x.shape[:-1]):
+        raise InvalidArgument(f"weighted_sum: x must be [..., k, D] and w [..., k], got {list(x.shape)} and {list(w.shape)}")
+    if x.dtype not in _FLOATS or w.dtype != x.dtype:
+        raise UnsupportedError("weighted_sum: x and w must share one floating-point dtype")
+    k, d = x.shape[-2], x.shape[-1]
+    rows = x.size // (k * d) if k * d else 0
+    out = x.dev.empty(tuple(x.shape[:-2]) + (d,), x.dtype)
+    _check(_ffi.lib().nvc_weighted_sum(x.dev._h, x.dtype, x.ptr, w.ptr, rows, k, d, out.ptr))
     return out
 
 

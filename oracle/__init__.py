@@ -189,6 +189,27 @@ def gather_qmm(x, codes, scales, biases, lhs, rhs, dtype, mode=AFFINE, group_siz
     return y
 
 
+def moe_route(probs, dtype, k, normalize=True):
+    """probs [..., E] stored as `dtype` -> (indices uint32 [..., k], scores [..., k])."""
+    probs = _c(probs)
+    e = probs.shape[-1]
+    rows = probs.size // e if e else 0
+    idx = np.zeros(probs.shape[:-1] + (k,), np.uint32)
+    scores = np.zeros(probs.shape[:-1] + (k,), store_dtype(dtype))
+    _check(lib().orc_moe_route(dtype, _ptr(probs), _sz(rows), _sz(e), _sz(k), int(normalize), _ptr(idx), _ptr(scores)))
+    return idx, scores
+
+
+def weighted_sum(x, w, dtype):
+    """x [..., k, D], w [..., k] -> [..., D]."""
+    x, w = _c(x), _c(w)
+    k, d = x.shape[-2], x.shape[-1]
+    rows = x.size // (k * d) if k * d else 0
+    out = np.zeros(x.shape[:-2] + (d,), store_dtype(dtype))
+    _check(lib().orc_weighted_sum(dtype, _ptr(x), _ptr(w), _sz(rows), _sz(k), _sz(d), _ptr(out)))
+    return out
+
+
 def threads() -> int:
     return int(lib().orc_threads())
 

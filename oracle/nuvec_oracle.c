@@ -614,3 +614,83 @@ int orc_gather_qmm(int mode, int gs, int bits, int dtype, int transpose, const v
     free(dense), free(x32), free(out);
     return rc;
 }
+
+/* ── mixture-of-experts glue (fast/imp.rs:2652-2672, 2731-2747; the compositions they stand for:
+ *    fast/imp.rs:1586-1600) ────────────────────────────────────────────────────────────────
+ *
+ * moe_route = argpartition(e - k) -> the last k indices (kernels.rs:231-273: the CPU argpartition
+ * is a stable ascending argsort, NaN last), the probabilities at those indices, and with
+ * `normalize` those divided by their sum: the sum in float64 over 8 lanes combined by a fixed tree
+ * (kernels.rs:609-621, 626-645), rounded to the array's type, then an element-wise divide in that
+ * type (f16 / bf16 divide in float32 and round, kernels.rs:1581). */
+
+static int route_less(float x, float y) {
+    int xn = x != x, yn = y != y;
+    if (!xn && !yn) return x < y;
+    return !xn && yn;
+}
+
+static double lane_sum(const float *xs, size_t n) {
+    double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (size_t i = 0; i < n; i++) acc[i % 8] += (double)xs[i];
+    return ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+}
+
+int orc_moe_route(int dtype, const void *probs, size_t rows, size_t experts, size_t k, int normalize,
+                  uint32_t *out_indices, void *out_scores) {
+    if (k < 1 || k > experts) return fail("moe_route: k = %ld must be in 1..=%ld", (long)k, (long)experts);
+    float *p = (float *)malloc(sizeof(float) * (experts + k));
+    uint32_t *order = (uint32_t *)malloc(sizeof(uint32_t) * experts);
+    if (!p || !order) return fail("moe_route: out of memory (%ld experts, %ld)", (long)experts, 0);
+    float *top = p + experts;
+    for (size_t r = 0; r < rows; r++) {
+        for (size_t e = 0; e < experts; e++) p[e] = load_f32(probs, r * experts + e, dtype);
+        /* stable ascending order: position of e = number of experts sorting before it */
+        for (size_t e = 0; e < experts; e++) {
+            size_t rank = 0;
+            for (size_t j = 0; j < experts; j++)
+                rank += (route_less(p[j], p[e]) || (!route_less(p[e], p[j]) && j < e)) ? 1 : 0;
+            order[rank] = (uint32_t)e;
+        }
+        for (size_t j = 0; j < k; j++) {
+            out_indices[r * k + j] = order[experts - k + j];
+            top[j] = p[order[experts - k + j]];
+        }
+        if (normalize) {
+            float total;
+            { /* the sum, rounded to the array's type */
+                uint32_t cell[1];
+                store_round(cell, 0, dtype, 0.0 + lane_sum(top, k));
+                total = load_f32(cell, 0, dtype);
+            }
+            for (size_t j = 0; j < k; j++) {
+                float q = top[j] / total;
+                store_round(out_scores, r * k + j, dtype, (double)q);
+            }
+        } else {
+            for (size_t j = 0; j < k; j++) store_round(out_scores, r * k + j, dtype, (double)top[j]);
+        }
+    }
+    free(p);
+    free(order);
+    return 0;
+}
+
+/* weighted_sum = sum(x * w[..., None], -2): the element-wise product rounded to the array's type
+ * (kernels.rs:1191-1195: f16 / bf16 multiply in float32 and round), summed over the k axis in
+ * float64 in order and rounded once (kernels.rs:626-645; the reduced axis is not the innermost
+ * one, so the sum is element by element). */
+int orc_weighted_sum(int dtype, const void *x, const void *w, size_t rows, size_t k, size_t d, void *out) {
+    for (size_t r = 0; r < rows; r++)
+        for (size_t c = 0; c < d; c++) {
+            double s = 0.0;
+            for (size_t j = 0; j < k; j++) {
+                float prod = load_f32(x, (r * k + j) * d + c, dtype) * load_f32(w, r * k + j, dtype);
+                uint32_t cell[1];
+                store_round(cell, 0, dtype, (double)prod);
+                s += (double)load_f32(cell, 0, dtype);
+            }
+            store_round(out, r * d + c, dtype, s);
+        }
+    return 0;
+}

@@ -88,6 +88,12 @@ int orc_gather_qmm(int mode, int group_size, int bits, int dtype, int transpose,
 /* The f32 product alone (x [M,K] row-major, w [N,K] row-major): few_rows order for M <= 16. */
 void orc_matmul_nt_f32(const float *x, const float *w, size_t M, size_t N, size_t K, float *y);
 
+/* fast::moe_route / fast::weighted_sum (crates/nuvec-core/src/fast/imp.rs:2652-2672, 2731-2747) as their
+ * CPU compositions compute them.  probs [rows, experts] -> indices u32 [rows, k] (ascending by
+ * probability, stable), scores [rows, k];  x [rows, k, d], w [rows, k] -> out [rows, d]. */
+int orc_moe_route(int dtype, const void *probs, size_t rows, size_t experts, size_t k, int normalize,
+                  uint32_t *out_indices, void *out_scores);
+int orc_weighted_sum(int dtype, const void *x, const void *w, size_t rows, size_t k, size_t d, void *out);
 int orc_threads(void);
 void orc_set_threads(int n);
 

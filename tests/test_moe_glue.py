@@ -1,0 +1,113 @@
+"""The router's top-k selection and the weighted expert sum: the CPU oracle against a plain numpy
+statement of the compositions (CPU), and the CUDA kernels against the oracle bit for bit (GPU).
+Cases follow the reference's own test (crates/nuvec-core/tests/fast.rs:841-925): router
+probabilities with and without ties, k from 1 to all experts, every float dtype, NaN last."""
+import numpy as np
+import pytest
+
+import oracle
+
+DT = {"f32": oracle.F32, "f16": oracle.F16, "bf16": oracle.BF16}
+CASES = [(3, 8, (1, 2, 8)), (5, 60, (4, 8)), (4, 128, (1, 8, 10, 128)), (2, 512, (8, 22))]
+
+
+def probabilities(rng, rows, e, dtype, ties):
+    z = rng.standard_normal((rows, e)).astype(np.float32)
+    p = np.exp(z - z.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    if ties:  # a few values (none 0) repeated across experts
+        levels = 4.0 * e
+        p = (np.floor(p * levels) + 1.0) / levels
+    return oracle.from_f32(p.astype(np.float32), dtype)
+
+
+@pytest.mark.parametrize("dt", list(DT))
+def test_oracle_moe_route_is_a_stable_sort_take_and_renormalisation(dt):
+    dtype = DT[dt]
+    rng = np.random.default_rng(0x72)
+    for rows, e, ks in CASES:
+        for ties in (False, True):
+            p = probabilities(rng, rows, e, dtype, ties)
+            pf = oracle.to_f32(p, dtype)
+            order = np.argsort(pf, axis=-1, kind="stable")
+            for k in ks:
+                idx, scores = oracle.moe_route(p, dtype, k, False)
+                assert np.array_equal(idx, order[:, e - k:])
+                assert np.array_equal(scores, np.take_along_axis(p, order[:, e - k:], -1))
+                idx, scores = oracle.moe_route(p, dtype, k, True)
+                assert np.array_equal(idx, order[:, e - k:])
+                top = np.take_along_axis(pf, order[:, e - k:], -1).astype(np.float64)
+                total = oracle.to_f32(oracle.from_f32(top.sum(-1, keepdims=True).astype(np.float32), dtype), dtype)
+                want = oracle.from_f32((top.astype(np.float32) / total).astype(np.float32), dtype)
+                got = oracle.to_f32(scores, dtype)
+                # (the float64 sum of at most 128 such values is exact; so is its one rounding)
+                assert np.allclose(got, oracle.to_f32(want, dtype), rtol=2.0 ** -7 if dt == "bf16" else 2.0 ** -10, atol=0)
+    # NaN sorts last
+    p = np.array([[0.1, np.nan, 0.3, 0.2]], np.float32)
+    idx, _ = oracle.moe_route(p, oracle.F32, 2, False)
+    assert idx.tolist() == [[2, 1]]
+    with pytest.raises(oracle.OracleError):
+        oracle.moe_route(p, oracle.F32, 5, False)
+
+
+@pytest.mark.parametrize("dt", list(DT))
+def test_oracle_weighted_sum(dt):
+    dtype = DT[dt]
+    rng = np.random.default_rng(5)
+    for rows, k, d in [(3, 8, 16), (7, 4, 1), (2, 1, 5), (4, 10, 33)]:
+        x = oracle.from_f32(rng.standard_normal((rows, k, d)).astype(np.float32), dtype)
+        w = oracle.from_f32(rng.random((rows, k)).astype(np.float32), dtype)
+        got = oracle.to_f32(oracle.weighted_sum(x, w, dtype), dtype)
+        prod = oracle.to_f32(oracle.from_f32(oracle.to_f32(x, dtype) * oracle.to_f32(w, dtype)[..., None], dtype), dtype)
+        want = oracle.to_f32(oracle.from_f32(prod.astype(np.float64).sum(-2).astype(np.float32), dtype), dtype)
+        tol = {"f32": 1e-6, "f16": 2.0 ** -10, "bf16": 2.0 ** -7}[dt]
+        assert np.allclose(got, want, rtol=tol, atol=tol * 1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", list(DT))
+def test_cuda_moe_route_matches_the_oracle_bit_for_bit(dt):
+    import nuvec_b200 as nv
+    dtype = DT[dt]
+    code = {"f32": nv.F32, "f16": nv.F16, "bf16": nv.BF16}[dt]
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(0x73)
+    up = lambda a: dev.array(a.view(np.float16) if dt == "f16" else a, code)
+    bits = lambda a: a.to_numpy().view(np.uint16 if dt != "f32" else np.uint32)
+    for rows, e, ks in CASES + [(512, 128, (8,)), (1024, 32, (4,)), (2, 1024, (64,))]:
+        for ties in (False, True):
+            p = probabilities(rng, rows, e, dtype, ties)
+            for k in ks:
+                for normalize in (False, True):
+                    want_idx, want_scores = oracle.moe_route(p, dtype, k, normalize)
+                    idx, scores = nv.moe_route(up(p), k, normalize)
+                    assert np.array_equal(idx.to_numpy(), want_idx), (rows, e, k, ties, normalize)
+                    assert np.array_equal(bits(scores), want_scores.view(bits(scores).dtype)), (rows, e, k, ties, normalize)
+    p = np.array([[0.1, np.nan, 0.3, 0.2]], np.float32)
+    idx, _ = nv.moe_route(dev.array(p, nv.F32), 2, False)
+    assert idx.to_numpy().tolist() == [[2, 1]]
+    # batched leading axes, as a model's [B, L, E]
+    p = probabilities(rng, 6, 16, dtype, False).reshape(2, 3, 16)
+    idx, scores = nv.moe_route(up(p), 4, True)
+    assert idx.shape == (2, 3, 4) and np.array_equal(idx.to_numpy(), oracle.moe_route(p, dtype, 4, True)[0])
+    with pytest.raises(nv.InvalidArgument):
+        nv.moe_route(up(p), 17, True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", list(DT))
+def test_cuda_weighted_sum_matches_the_oracle_bit_for_bit(dt):
+    import nuvec_b200 as nv
+    dtype = DT[dt]
+    code = {"f32": nv.F32, "f16": nv.F16, "bf16": nv.BF16}[dt]
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(9)
+    up = lambda a: dev.array(a.view(np.float16) if dt == "f16" else a, code)
+    for rows, k, d in [(3, 8, 16), (7, 4, 1), (2, 1, 5), (4, 10, 33), (512, 8, 2048), (1024, 4, 2880)]:
+        x = oracle.from_f32(rng.standard_normal((rows, k, d)).astype(np.float32), dtype)
+        w = oracle.from_f32(rng.random((rows, k)).astype(np.float32), dtype)
+        want = oracle.weighted_sum(x, w, dtype)
+        got = nv.weighted_sum(up(x), up(w)).to_numpy()
+        assert np.array_equal(got.view(want.dtype) if dt != "f16" else got.view(np.uint16), want), (rows, k, d)
+    with pytest.raises(nv.InvalidArgument):
+        nv.weighted_sum(up(x), up(w[:, :2]))
