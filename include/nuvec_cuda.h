@@ -262,7 +262,10 @@ int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_host_product 
  *   x: bfloat16 [M, K] dense, 1 <= M <= 8;  w: affine 2-, 3-, 4-, 6- or 8-bit, [N, K*bits/32], K a multiple
  *   of 32 values per vector-load step (any K the fast kernel of nvc_quantized_matmul takes);
  *   scales/biases bfloat16 [N, K/gs];  y: bfloat16 [M, N].  Results equal nvc_quantized_matmul's.
- * Limits: N <= 262144 and partial sums <= 4 MiB - 64 KiB, else NVC_ERR_UNSUPPORTED with the sizes
+ * Limit: the partial sums of tiles that block boundaries cut (one slot per block of the launch, each
+ * of as many 512-byte partial tiles as a tile can be cut into) must fit 4 MiB - 64 KiB: every decode
+ * projection does, by three orders of magnitude; a product of few rows and a very long K spread over
+ * all multiprocessors (say N = 304, K = 65536) does not and gets NVC_ERR_UNSUPPORTED with the sizes
  * in the message.  The first call on a device looks up the array's device address; make that
  * call before any stream capture.  All calls share the one array: it keeps the last call's
  * contents (the counters are cleared on the stream at the start of each call), and two calls

@@ -496,8 +496,9 @@ struct QmvCut {
     int32_t max_parts;
     float *lpart;
     uint32_t *lcount;
-    float *part;                // the tile's slots in global scratch
-    uint32_t *counter;          // the tile's arrival counter in global scratch
+    float *partials;            // global scratch: [batch * blocks][max_parts][128] float32
+    uint32_t *counters;         // global scratch: [batch * blocks] arrival counters
+    int64_t slot0;              // batch * blocks: a tile cut by block boundaries uses the slot of its first block
 };
 __device__ __noinline__ bool qmv_meet_partials(const QmvCut c, float4 &v) {
     const int lane = c.lane, r = lane >> 2, t = lane & 3, warp = c.warp;
@@ -545,21 +546,26 @@ __device__ __noinline__ bool qmv_meet_partials(const QmvCut c, float4 &v) {
     // block of a multi-block grid runs all its warps), this one number `mine`, leave their 16 x 8
     // partials in scratch; the one that arrives last adds them in run order (so the result does not
     // depend on arrival order) and rearms the counter.
-    auto owner = [&](uint32_t i) {  // number, through the grid, of the warp whose run holds iteration i
-        const uint32_t cta = part_of(i, c.blk_q, c.blk_r);
+    auto owner = [&](uint32_t i, uint32_t &cta) {  // number, through the grid, of the warp whose run holds iteration i
+        cta = part_of(i, c.blk_q, c.blk_r);
         const uint32_t l = part_lo(cta, c.blk_q, c.blk_r), len = c.blk_q + (cta < c.blk_r ? 1u : 0u);
         const uint32_t w = len >= QMV_WARPS ? part_of(i - l, len / QMV_WARPS, len % QMV_WARPS) : i - l;
         return (int)(cta * QMV_WARPS + w);
     };
-    const int first = owner(c.t_lo), last = owner(c.t_hi - 1);
+    uint32_t cta_first = 0, cta_last = 0;
+    const int first = owner(c.t_lo, cta_first), last = owner(c.t_hi - 1, cta_last);
     const int mine = (int)blockIdx.x * QMV_WARPS + warp - first, count = last - first + 1;
-    float *part = c.part;
+    // The tile's first block is the first block of no other tile cut by a block boundary (the tile
+    // before it, if cut, starts in an earlier block): its number names the tile's slot.
+    const int64_t slot = c.slot0 + cta_first;
+    float *part = c.partials + slot * c.max_parts * 128;
+    uint32_t *counter = c.counters + slot;
     __stcg(reinterpret_cast<float2 *>(part + mine * 128 + r * 8 + 2 * t), make_float2(v.x, v.y));
     __stcg(reinterpret_cast<float2 *>(part + mine * 128 + (r + 8) * 8 + 2 * t), make_float2(v.z, v.w));
     __threadfence();
     __syncwarp();
     uint32_t arrived = 0;
-    if (lane == 0) arrived = atomicAdd(c.counter, 1u);
+    if (lane == 0) arrived = atomicAdd(counter, 1u);
     arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
     if (arrived != (uint32_t)count - 1) return false;
     __threadfence();
@@ -569,7 +575,7 @@ __device__ __noinline__ bool qmv_meet_partials(const QmvCut c, float4 &v) {
         float2 q = __ldcg(reinterpret_cast<const float2 *>(part + s2 * 128 + (r + 8) * 8 + 2 * t));
         v.x += a.x; v.y += a.y; v.z += q.x; v.w += q.y;
     }
-    if (lane == 0) *c.counter = 0u;
+    if (lane == 0) *counter = 0u;
     return true;
 }
 
@@ -1011,14 +1017,12 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         const uint32_t t_lo = (uint32_t)done_tile * (uint32_t)ipt, t_hi = t_lo + (uint32_t)ipt;
         bool store = lo <= t_lo && hi >= t_hi;  // the whole tile was this warp's
         if (!store) {
-            const int64_t slot = b * tiles + done_tile;
             QmvCut c;
             c.lo = lo; c.hi = hi; c.blk_lo = blk_lo; c.blk_len = blk_len; c.wq = wq; c.wr = wr;
             c.blk_q = blk_q; c.blk_r = blk_r; c.t_lo = t_lo; c.t_hi = t_hi;
             c.warp = warp; c.lane = lane; c.first_tile = done_tile == tile0 ? 1 : 0;
             c.max_parts = p.max_parts; c.lpart = lpart; c.lcount = lcount;
-            c.part = p.partials + slot * p.max_parts * 128;
-            c.counter = p.counters + slot;
+            c.partials = p.partials; c.counters = p.counters; c.slot0 = b * gridDim.x;
             float4 vv = make_float4(v[0], v[1], v[2], v[3]);
             store = qmv_meet_partials(c, vv);
             v[0] = vv.x; v[1] = vv.y; v[2] = vv.z; v[3] = vv.w;
@@ -1289,13 +1293,15 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     p.rounds = (ipt % 4 == 0 && p.ci % 4 == 0) ? 1 : 0;
     p.xs_pitch = (int32_t)(p.K / codes * (codes / 2) + 16);
     if (!p.rhs) p.experts = p.x_batches = 0;
-    const size_t partial_bytes = (size_t)tiles * batch * p.max_parts * 128 * sizeof(float);
+    // Only tiles cut by a block boundary use global scratch, and such a tile is named by its first
+    // block: one slot of max_parts partial tiles and one counter per (batch, block).
+    const size_t partial_bytes = (size_t)blocks * batch * p.max_parts * 128 * sizeof(float);
     if (fixed) {
         // Scratch of fixed capacity provided by the caller of this function: nothing is allocated.
-        if (partial_bytes > fixed->partial_bytes || (size_t)(tiles * batch) > fixed->counters_len)
+        if (partial_bytes > fixed->partial_bytes || (size_t)(blocks * batch) > fixed->counters_len)
             return set_error(NVC_ERR_UNSUPPORTED,
                              "qmv: this product needs %zu bytes of partial sums and %lld counters; the fixed scratch holds "
-                             "%zu bytes and %zu counters", partial_bytes, (long long)(tiles * batch), fixed->partial_bytes,
+                             "%zu bytes and %zu counters", partial_bytes, (long long)(blocks * batch), fixed->partial_bytes,
                              fixed->counters_len);
         p.partials = fixed->partials;
         p.counters = fixed->counters;
@@ -1303,7 +1309,7 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
         void *scratch = nullptr;
         NVC_TRY(ensure_scratch(dev, partial_bytes, &scratch));
         p.partials = (float *)scratch;
-        NVC_TRY(ensure_counters(dev, (size_t)(tiles * batch), &p.counters));
+        NVC_TRY(ensure_counters(dev, (size_t)(blocks * batch), &p.counters));
     }
     dim3 grid((unsigned)blocks, 1, (unsigned)batch);
 #define NVC_QMV(B, W) if (bits == B && wpl == W) return launch_qmv_cfg<B, W>(dev, p, grid, smem);
@@ -1323,7 +1329,7 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
 // arrival counters.
 namespace {
 constexpr size_t NOALLOC_SCRATCH_BYTES = 4u << 20;
-constexpr size_t NOALLOC_COUNTERS = 16384;  // one per 16-row tile: N up to 262144
+constexpr size_t NOALLOC_COUNTERS = 16384;  // one per block of a launch (at most two blocks per multiprocessor)
 constexpr size_t NOALLOC_PARTIAL_BYTES = NOALLOC_SCRATCH_BYTES - NOALLOC_COUNTERS * sizeof(uint32_t);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
 
@@ -1369,12 +1375,13 @@ extern "C" int32_t nvc_quantized_matmul_noalloc(nvc_device *dev, const nvc_quant
     fixed.partial_bytes = NOALLOC_PARTIAL_BYTES;
     fixed.counters = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(base) + NOALLOC_PARTIAL_BYTES);
     fixed.counters_len = NOALLOC_COUNTERS;
-    const int64_t tiles = (N + 15) / 16;
-    if ((size_t)tiles > NOALLOC_COUNTERS)
-        return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (no-alloc): N = %lld exceeds the fixed scratch (at most %zu rows)",
-                         (long long)N, NOALLOC_COUNTERS * 16);
-    // The array keeps whatever the last call left; the counters must start at zero.
-    NVC_CUDA(cudaMemsetAsync(fixed.counters, 0, (size_t)tiles * sizeof(uint32_t), dev->stream));
+    // The array keeps whatever the last call left; the counters must start at zero.  One counter per
+    // block of the launch, and a grid never has more than two blocks per multiprocessor.
+    const size_t used = (size_t)2 * dev->prop.multiProcessorCount;
+    if (used > NOALLOC_COUNTERS)
+        return set_error(NVC_ERR_UNSUPPORTED, "quantized_matmul (no-alloc): %d multiprocessors exceed the fixed scratch",
+                         dev->prop.multiProcessorCount);
+    NVC_CUDA(cudaMemsetAsync(fixed.counters, 0, used * sizeof(uint32_t), dev->stream));
     QmvParams p{};
     p.x = x; p.w = w; p.scales = scales; p.biases = biases; p.lhs = nullptr; p.rhs = nullptr; p.y = y;
     p.N = N; p.K = K; p.ldx = K;
