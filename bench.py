@@ -278,6 +278,9 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the parity check that precedes the timing")
     ap.add_argument("--sweep", action="store_true", help="time every single-GPU configuration of the benchmark definition and print one JSON object")
     ap.add_argument("--no-graph", action="store_true", help="launch every product from the host instead of replaying a recorded step")
+    ap.add_argument("--one", default=None, metavar="M,N,K,BITS,COPIES",
+                    help="profiling driver: one product shape on COPIES distinct weight sets, each launched twice "
+                         "(prints the device time per launch); what the ncu commands under profiles/ run")
     ap.add_argument("--workload", default="decode", choices=["decode", "moe"],
                     help="moe: the expert-sharded mixture-of-experts products (gather_qmm) on --gpus ranks")
     args = ap.parse_args()
@@ -307,6 +310,8 @@ def main():
             raise SystemExit("--sweep runs on one GPU")
         print(json.dumps({"sweep": config_sweep(nv, _ffi, dev, peaks), "peaks": peaks}))
         return
+    if args.one:
+        return one_shape(args, nv, _ffi, dev)
     if args.workload == "moe":
         return moe_bench(args, nv, _ffi, shard, dev, dist, rank, world, peaks)
     M = args.rows
@@ -687,6 +692,36 @@ def main():
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
+
+
+# ── profiling driver (--one) ─────────────────────────────────────────────────────────────────
+def one_shape(args, nv, _ffi, dev):
+    """One product shape on several distinct weight sets (random codes, scales and biases in the range
+    quantizing N(0, 0.02) weights gives), every set launched twice: launches COPIES + 1 .. 2 COPIES run
+    on weights that left L2 long ago.  Used under ncu with -k / -s / -c."""
+    M, N, K, bits, copies = (int(v) for v in args.one.split(","))
+    lib = _ffi.lib()
+    rng = np.random.default_rng(0)
+    quant = nv.Quant.affine(GS, bits)
+    qc = quant._c()
+    codes = rng.integers(0, 2 ** 32, (N, K * bits // 32), dtype=np.uint32)
+    sc = nv.f32_to_bf16((rng.random((N, K // GS), dtype=np.float32) * 0.06 + 0.03) / float(2 ** bits - 1))
+    bi = nv.f32_to_bf16(-(rng.random((N, K // GS), dtype=np.float32) * 0.04 + 0.02))
+    x = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
+    sets = [(dev.array(codes, nv.U32), dev.array(sc, nv.BF16), dev.array(bi, nv.BF16), dev.empty((M, N), nv.BF16))
+            for _ in range(copies)]
+    dev.synchronize()
+    e0, e1 = dev.event(), dev.event()
+    for rnd in range(2):
+        if rnd == 1:
+            e0.record()
+        for c, s, b, y in sets:
+            rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, c.ptr, s.ptr, b.ptr, None, M, N, K, K, 1, 0, 0, 0, y.ptr)
+            assert rc == 0, _ffi.last_error()
+    e1.record()
+    e1.synchronize()
+    print(json.dumps({"one": args.one, "launches": 2 * copies, "us_per_launch": e0.elapsed_ms(e1) * 1e3 / copies,
+                      "bytes_per_launch": qmv_bytes(M, N, K, bits)}))
 
 
 # ── expert-sharded mixture of experts (gather_qmm), --workload moe ───────────────────────────
