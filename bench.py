@@ -281,6 +281,9 @@ def main():
     ap.add_argument("--one", default=None, metavar="M,N,K,BITS,COPIES",
                     help="profiling driver: one product shape on COPIES distinct weight sets, each launched twice "
                          "(prints the device time per launch); what the ncu commands under profiles/ run")
+    ap.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
+                    help="diagnostic: replay a recorded decode step of LAYERS layers on the timeline build of the "
+                         "library (python -m nuvec_b200.build --timeline) and print where each product's time goes")
     ap.add_argument("--workload", default="decode", choices=["decode", "moe"],
                     help="moe: the expert-sharded mixture-of-experts products (gather_qmm) on --gpus ranks")
     args = ap.parse_args()
@@ -295,6 +298,11 @@ def main():
 
     import nuvec_b200 as nv
     from nuvec_b200 import _ffi, shard
+    if args.timeline:
+        from nuvec_b200 import build as nvbuild
+        if not nvbuild.TIMELINE_LIB.exists():
+            raise SystemExit("build the timeline library first: python -m nuvec_b200.build --timeline")
+        _ffi.LIB_PATH = nvbuild.TIMELINE_LIB
 
     dist = None
     if world > 1:
@@ -312,6 +320,8 @@ def main():
         return
     if args.one:
         return one_shape(args, nv, _ffi, dev)
+    if args.timeline:
+        return timeline(args, nv, _ffi, dev)
     if args.workload == "moe":
         return moe_bench(args, nv, _ffi, shard, dev, dist, rank, world, peaks)
     M = args.rows
@@ -722,6 +732,68 @@ def one_shape(args, nv, _ffi, dev):
     e1.synchronize()
     print(json.dumps({"one": args.one, "launches": 2 * copies, "us_per_launch": e0.elapsed_ms(e1) * 1e3 / copies,
                       "bytes_per_launch": qmv_bytes(M, N, K, bits)}))
+
+
+# ── where a decode product's time goes (--timeline) ──────────────────────────────────────────
+def timeline(args, nv, _ffi, dev):
+    """Replays a recorded step of args.timeline layers on the library built with -DNUVEC_TIMELINE,
+    whose few-row kernel records %globaltimer (minimum and maximum over its blocks) at: block start,
+    before / after the dependency wait, activations staged, a warp's last iteration, block end.  All
+    figures are relative to the end of the previous product's last block.  The stamps themselves cost
+    time (the products run ~30 % longer than in the plain build): read proportions, not absolutes."""
+    lib = _ffi.lib()
+    lib.nvc_debug_timeline_read.restype = C.c_int32
+    lib.nvc_debug_timeline_read.argtypes = [C.c_void_p, C.c_int32]
+    lib.nvc_debug_timeline_reset.restype = C.c_int32
+    rng = np.random.default_rng(0)
+    quant = nv.Quant.affine(GS, BITS)
+    qc = quant._c()
+    M = args.rows
+    prods = []
+    for _ in range(args.timeline):
+        for name, N, K in PROJECTIONS:
+            codes = dev.array(rng.integers(0, 2 ** 32, (N, K * BITS // 32), dtype=np.uint32), nv.U32)
+            sc = dev.array(nv.f32_to_bf16(rng.random((N, K // GS), dtype=np.float32) * 0.004 + 0.001), nv.BF16)
+            bi = dev.array(nv.f32_to_bf16(-rng.random((N, K // GS), dtype=np.float32) * 0.04), nv.BF16)
+            x = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
+            prods.append((name, N, K, codes, sc, bi, x, dev.empty((M, N), nv.BF16)))
+
+    def step():
+        for name, N, K, c, s, b, x, y in prods:
+            rc = lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, c.ptr, s.ptr, b.ptr, None, M, N, K, K, 1, 0, 0, 0, y.ptr)
+            assert rc == 0, _ffi.last_error()
+    step()
+    graph = dev.record(step)
+    for _ in range(3):
+        graph.launch()
+    dev.synchronize()
+    assert lib.nvc_debug_timeline_reset() == 0
+    graph.launch()
+    dev.synchronize()
+    n = len(prods)
+    buf = (C.c_ulonglong * (12 * n))()
+    got = lib.nvc_debug_timeline_read(buf, n)
+    assert got == n, f"{got} launches recorded, {n} expected"
+    a = np.frombuffer(buf, dtype=np.uint64).reshape(n, 12).astype(np.int64) / 1000.0   # microseconds
+    per = {}
+    for i in range(1, n):
+        start, _, pre_wait_max, wait_ret_max, staged_max, loop_first, loop_last, end_last = \
+            a[i, 0], a[i, 1], a[i, 3], a[i, 5], a[i, 7], a[i, 8], a[i, 9], a[i, 11]
+        prev_end = a[i - 1, 11]
+        per.setdefault(prods[i][0], []).append([
+            start - prev_end,            # first block starts (negative: while the previous product runs)
+            pre_wait_max - prev_end,     # last block has issued its first weight copies and reaches the wait
+            wait_ret_max - prev_end,     # last block's wait returns
+            staged_max - wait_ret_max,   # activations staged
+            loop_first - staged_max,     # first warp finishes its iterations
+            loop_last - staged_max,      # last warp finishes its iterations
+            end_last - loop_last,        # partial sums met, results stored
+            end_last - prev_end])        # the product's share of the step
+    keys = ["first_block_start", "last_block_at_wait", "last_wait_returns", "stage_activations",
+            "first_warp_done", "last_warp_done", "tail", "period"]
+    out = {name: {k: round(float(v), 2) for k, v in zip(keys, np.median(np.array(rows), axis=0))} for name, rows in per.items()}
+    print(json.dumps({"timeline_us": out, "layers": args.timeline, "rows": M,
+                      "relative_to": "end of the previous product's last block (median over layers)"}))
 
 
 # ── expert-sharded mixture of experts (gather_qmm), --workload moe ───────────────────────────

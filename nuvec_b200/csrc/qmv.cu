@@ -27,6 +27,48 @@
 
 namespace nvc {
 
+// ── optional timeline of the few-row kernel (diagnostic builds only: -DNUVEC_TIMELINE) ─────────
+// Every launch of qmv_affine_kernel records %globaltimer at six points -- block start, before and
+// after the dependency wait, activations staged, a warp's last iteration done, block end -- as the
+// minimum and maximum over its blocks (warps for the fifth).  The last block to finish moves on to
+// the next record.  nvc_debug_timeline_reset / _read (end of this file) clear and fetch the records.
+#ifdef NUVEC_TIMELINE
+constexpr int TIMELINE_RECORDS = 4096, TIMELINE_POINTS = 6;
+__device__ unsigned long long g_timeline[TIMELINE_RECORDS][2 * TIMELINE_POINTS];
+__device__ unsigned int g_timeline_at, g_timeline_done;
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void timeline_put(unsigned int rec, int point, unsigned long long t) {
+    atomicMin(&g_timeline[rec][2 * point], t);
+    atomicMax(&g_timeline[rec][2 * point + 1], t);
+}
+#define QMV_TIMELINE_BEGIN unsigned long long tl_[4]; tl_[0] = global_timer();
+#define QMV_TIMELINE_MARK(k) tl_[k] = global_timer();
+#define QMV_TIMELINE_END(worked)                                                                         \
+    {                                                                                                    \
+        const unsigned int rec_ = *(volatile unsigned int *)&g_timeline_at % TIMELINE_RECORDS;           \
+        if ((threadIdx.x & 31) == 0 && (worked)) timeline_put(rec_, 4, global_timer());                  \
+        __syncthreads();                                                                                 \
+        if (threadIdx.x == 0) {                                                                          \
+            for (int k_ = 0; k_ < 4; k_++) timeline_put(rec_, k_, tl_[k_]);                              \
+            timeline_put(rec_, 5, global_timer());                                                       \
+            __threadfence();                                                                             \
+            if (atomicAdd(&g_timeline_done, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) {              \
+                g_timeline_done = 0;                                                                     \
+                __threadfence();                                                                         \
+                g_timeline_at = g_timeline_at + 1;                                                       \
+            }                                                                                            \
+        }                                                                                                \
+    }
+#else
+#define QMV_TIMELINE_BEGIN
+#define QMV_TIMELINE_MARK(k)
+#define QMV_TIMELINE_END(worked)
+#endif
+
 // ── generic kernels ────────────────────────────────────────────────────────────────────
 
 template <typename T>
@@ -591,6 +633,7 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     constexpr int CPL = UW == 3 ? LW : WPL == 8 ? 2 : 1;
     constexpr int CW = LW / CPL;               // words per copy
     extern __shared__ __align__(16) uint32_t smem[];
+    QMV_TIMELINE_BEGIN
 
     const int tid = threadIdx.x, lane = tid & 31;
     // the warp index read from lane 0: the compiler then knows that everything derived from it (run
@@ -752,8 +795,10 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     }
 #pragma unroll
     for (int st = 0; st < QMV_STAGES; st++) prefetch(ring_s + ((first_stage + st) % QMV_STAGES) * STAGE_BYTES);
+    QMV_TIMELINE_MARK(1)
     if (p.early_weights)
         asm volatile("griddepcontrol.wait;" ::: "memory");  // activations, scratch and output belong to this kernel from here
+    QMV_TIMELINE_MARK(2)
     // ── stage the activations once per block (the first weight copies are already in flight) ──
     {
         const uint16_t *x = (const uint16_t *)p.x + xb * p.x_batch_stride;
@@ -808,6 +853,7 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         }
     }
     __syncthreads();  // activations staged
+    QMV_TIMELINE_MARK(3)
 
     const bool xrow = r < p.M;
     const uint32_t x_it_bytes = xrow ? X_IT_WORDS * 4 : 0;  // bytes per iteration in xs (0: stay on the zero page)
@@ -1071,6 +1117,7 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
             }
         }
     }
+    QMV_TIMELINE_END(lo < hi)
     cp_async_wait<0>();
     if (p.peer) {
         // Second half of the fused collective: all threads of the grid share the packets this rank
@@ -1390,3 +1437,29 @@ extern "C" int32_t nvc_quantized_matmul_noalloc(nvc_device *dev, const nvc_quant
     p.x_vec = ((uintptr_t)x % 16 == 0) && (K % 8 == 0);
     return launch_qmv_affine(dev, q->bits, p, 1, &fixed);
 }
+
+#ifdef NUVEC_TIMELINE
+// Diagnostic build only.  Reset: every minimum to the largest value, every maximum to 0, record 0 next.
+extern "C" int32_t nvc_debug_timeline_reset(void) {
+    static unsigned long long init[nvc::TIMELINE_RECORDS][2 * nvc::TIMELINE_POINTS];
+    for (auto &rec : init)
+        for (int k = 0; k < 2 * nvc::TIMELINE_POINTS; k++) rec[k] = (k & 1) ? 0ull : ~0ull;
+    const unsigned int zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpyToSymbol(nvc::g_timeline, init, sizeof init) != cudaSuccess ||
+        cudaMemcpyToSymbol(nvc::g_timeline_at, &zero, sizeof zero) != cudaSuccess ||
+        cudaMemcpyToSymbol(nvc::g_timeline_done, &zero, sizeof zero) != cudaSuccess)
+        return NVC_ERR_DRIVER;
+    return cudaDeviceSynchronize() == cudaSuccess ? NVC_OK : NVC_ERR_DRIVER;
+}
+// Copies the first `records` records ({min, max} nanoseconds of the six points each) to `out` and
+// returns how many launches have been recorded since the reset (negative on error).
+extern "C" int32_t nvc_debug_timeline_read(unsigned long long *out, int32_t records) {
+    unsigned int launches = 0;
+    if (records > nvc::TIMELINE_RECORDS) records = nvc::TIMELINE_RECORDS;
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpyFromSymbol(&launches, nvc::g_timeline_at, sizeof launches) != cudaSuccess ||
+        cudaMemcpyFromSymbol(out, nvc::g_timeline, sizeof(unsigned long long) * 2 * nvc::TIMELINE_POINTS * (size_t)records) != cudaSuccess)
+        return -1;
+    return (int32_t)launches;
+}
+#endif

@@ -277,7 +277,7 @@ int32_t nvc_device_close(nvc_device *dev) {
 int32_t nvc_device_info(nvc_device *dev, nvc_info *out) {
     if (!dev || !out) return set_error(NVC_ERR_INVALID_ARGUMENT, "nvc_device_info: null argument");
     memset(out, 0, sizeof *out);
-    strncpy(out->name, dev->prop.name, sizeof out->name - 1);
+    memcpy(out->name, dev->prop.name, sizeof out->name - 1);  // zeroed above: always terminated
     out->cc_major = dev->prop.major;
     out->cc_minor = dev->prop.minor;
     out->multiprocessors = dev->prop.multiProcessorCount;
