@@ -809,13 +809,26 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
             if (CODES == 8 && p.x_vec) {
                 // eight values per unit (4-bit codes): the pairs (x0,x4) (x1,x5) (x2,x6) (x3,x7) come out
                 // of one 16-byte load with four byte permutations and go back as one 16-byte store
-                for (int blk = tid; blk < blocks_per_row; blk += QMV_THREADS) {
-                    const uint4 in = __ldcg(reinterpret_cast<const uint4 *>(xrow_src) + blk);
-                    uint4 o;
-                    o.x = __byte_perm(in.x, in.z, 0x5410); o.y = __byte_perm(in.x, in.z, 0x7632);
-                    o.z = __byte_perm(in.y, in.w, 0x5410); o.w = __byte_perm(in.y, in.w, 0x7632);
-                    const int it = blk / (4 * WPL), tt = (blk / WPL) & 3, j = blk % WPL;
-                    *reinterpret_cast<uint4 *>(xrow_dst + (size_t)(((it * WPL + j) * 4 + tt) * XW)) = o;
+                // (the loads of up to four units per thread are issued together: the block pays one
+                // round trip to L2 for a row of 8192 values instead of four)
+                constexpr int XB = 4;
+                for (int blk0 = tid; blk0 < blocks_per_row; blk0 += XB * QMV_THREADS) {
+                    uint4 in[XB];
+#pragma unroll
+                    for (int u = 0; u < XB; u++)
+                        if (blk0 + u * QMV_THREADS < blocks_per_row)
+                            in[u] = __ldcg(reinterpret_cast<const uint4 *>(xrow_src) + blk0 + u * QMV_THREADS);
+#pragma unroll
+                    for (int u = 0; u < XB; u++) {
+                        const int blk = blk0 + u * QMV_THREADS;
+                        if (blk < blocks_per_row) {
+                            uint4 o;
+                            o.x = __byte_perm(in[u].x, in[u].z, 0x5410); o.y = __byte_perm(in[u].x, in[u].z, 0x7632);
+                            o.z = __byte_perm(in[u].y, in[u].w, 0x5410); o.w = __byte_perm(in[u].y, in[u].w, 0x7632);
+                            const int it = blk / (4 * WPL), tt = (blk / WPL) & 3, j = blk % WPL;
+                            *reinterpret_cast<uint4 *>(xrow_dst + (size_t)(((it * WPL + j) * 4 + tt) * XW)) = o;
+                        }
+                    }
                 }
                 continue;
             }
