@@ -238,7 +238,11 @@ int32_t nvc_quantized_matmul_host_async(nvc_device *dev, const nvc_quant *q, int
                                         void *host_y);
 
 /* A list of such products in one call (an evaluator walking the nodes of a step between two
- * flushes); the fields are the arguments of nvc_quantized_matmul_host_async. */
+ * flushes); the fields are the arguments of nvc_quantized_matmul_host_async.  All activations travel
+ * in one copy.  A list that arrives again unchanged after a synchronization (the same weights, sizes
+ * and host buffers: a decode loop) is recorded the second time and replayed from then on, so the
+ * step costs one copy and one graph launch; the contents of the host buffers are read anew at every
+ * call.  Any other list drops the recording. */
 typedef struct {
     nvc_quant quant;
     int32_t dtype, transpose;

@@ -92,6 +92,14 @@ struct nvc_device {
     std::vector<PendingResult> pending;
     char *ring_host = nullptr, *ring_host_dev = nullptr, *ring_dev = nullptr;  // (ring_host_dev: the pinned block as the device sees it)
     size_t ring_bytes = 0, ring_at = 0;
+    // The last list given to nvc_quantized_matmul_host_batch: the second time the same list arrives
+    // (same operands, sizes and host buffers, same place in the ring) its copy and kernels are
+    // recorded, from the third on the recording is replayed.
+    std::vector<unsigned char> batch_key;
+    size_t batch_at = 0;
+    cudaGraphExec_t batch_exec = nullptr;
+    uint64_t batch_kernels = 0;
+    std::vector<PendingResult> batch_results;
 };
 
 struct nvc_graph {

@@ -381,7 +381,70 @@ extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_ho
         if (xb) memcpy(dev->ring_host + xo, items[i].host_x, xb);
         xo += pad(xb);
     }
-    if (xtotal) NVC_CUDA(cudaMemcpyAsync(dev->ring_dev + at, dev->ring_host + at, xtotal, cudaMemcpyHostToDevice, dev->stream));
+    // A decode loop sends the same list step after step (same weights, same host buffers).  The
+    // second time a list arrives its copy and kernels are recorded (the first, unrecorded run has
+    // sized every scratch buffer, so nothing allocates while recording); after that one replay
+    // stands for the whole list.
+    const unsigned char *key = reinterpret_cast<const unsigned char *>(items);
+    const size_t key_bytes = count * sizeof(nvc_host_product);
+    const bool same = dev->batch_key.size() == key_bytes && dev->batch_at == at && memcmp(dev->batch_key.data(), key, key_bytes) == 0;
+    if (same && dev->batch_exec) {
+        NVC_CUDA(cudaGraphLaunch(dev->batch_exec, dev->stream));
+        dev->launches += dev->batch_kernels;
+        std::lock_guard<std::mutex> g(dev->host_mu);
+        dev->pending.insert(dev->pending.end(), dev->batch_results.begin(), dev->batch_results.end());
+        return NVC_OK;
+    }
+    if (dev->batch_exec) {  // a different list: the old recording is of no use any more
+        cudaGraphExecDestroy(dev->batch_exec);
+        dev->batch_exec = nullptr;
+    }
+    const bool record = same && dev->stream == dev->own_stream;
+    if (!same) {
+        dev->batch_key.assign(key, key + key_bytes);
+        dev->batch_at = at;
+    }
+    const size_t pending_before = dev->pending.size();
+    if (record) {
+        NVC_CUDA(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+        dev->capturing = true;
+        dev->captured = 0;
+    }
+    // (leaves the recording, if one is open, before an error is returned)
+    auto finish = [&](int32_t rc) -> int32_t {
+        if (!record) return rc;
+        dev->capturing = false;
+        cudaGraph_t graph = nullptr;
+        cudaError_t err = cudaStreamEndCapture(dev->stream, &graph);
+        if (rc != NVC_OK || err != cudaSuccess) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            dev->batch_key.clear();
+            std::lock_guard<std::mutex> g(dev->host_mu);
+            dev->pending.resize(pending_before);
+            return rc != NVC_OK ? rc : cuda_error("cudaStreamEndCapture", err);
+        }
+        err = cudaGraphInstantiate(&dev->batch_exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (err != cudaSuccess) {
+            dev->batch_exec = nullptr;
+            dev->batch_key.clear();
+            std::lock_guard<std::mutex> g(dev->host_mu);
+            dev->pending.resize(pending_before);
+            return cuda_error("cudaGraphInstantiate", err);
+        }
+        dev->batch_kernels = dev->captured;
+        {
+            std::lock_guard<std::mutex> g(dev->host_mu);
+            dev->batch_results.assign(dev->pending.begin() + pending_before, dev->pending.end());
+        }
+        NVC_CUDA(cudaGraphLaunch(dev->batch_exec, dev->stream));
+        return NVC_OK;
+    };
+    if (xtotal) {
+        cudaError_t err = cudaMemcpyAsync(dev->ring_dev + at, dev->ring_host + at, xtotal, cudaMemcpyHostToDevice, dev->stream);
+        if (err != cudaSuccess) return finish(cuda_error("cudaMemcpyAsync", err));
+    }
     xo = at;
     size_t yo = at + xtotal;
     for (size_t i = 0; i < count; i++) {
@@ -392,13 +455,16 @@ extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_ho
             void *ydev = direct ? (void *)(dev->ring_host_dev + yo) : (void *)(dev->ring_dev + yo);
             int32_t rc = nvc_quantized_matmul(dev, &it.quant, it.dtype, it.transpose, dev->ring_dev + xo, it.w, it.scales, it.biases,
                                               it.global_scale, it.M, it.N, it.K, it.K, 1, 0, 0, 0, ydev);
-            if (rc != NVC_OK) return rc;
-            if (!direct) NVC_CUDA(cudaMemcpyAsync(dev->ring_host + yo, dev->ring_dev + yo, yb, cudaMemcpyDeviceToHost, dev->stream));
+            if (rc != NVC_OK) return finish(rc);
+            if (!direct) {
+                cudaError_t err = cudaMemcpyAsync(dev->ring_host + yo, dev->ring_dev + yo, yb, cudaMemcpyDeviceToHost, dev->stream);
+                if (err != cudaSuccess) return finish(cuda_error("cudaMemcpyAsync", err));
+            }
             std::lock_guard<std::mutex> g(dev->host_mu);
             dev->pending.push_back({dev->ring_host + yo, it.host_y, yb});
         }
         xo += pad(xb);
         yo += pad(yb);
     }
-    return NVC_OK;
+    return finish(NVC_OK);
 }

@@ -95,6 +95,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(QMM_PARK_NS) : "memory");
     return done != 0;
 }
+// The same attempt with cluster-scope acquire: for barriers that threads of the other block of a
+// pair arrive on.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(QMM_PARK_NS) : "memory");
+    return done != 0;
+}
+// Block pairs (clusters of two): rank in the pair, the pair's barrier, and an arrival on the
+// barrier at the same shared-memory offset in the pair's first block.
+__device__ __forceinline__ uint32_t pair_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void pair_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t *bar) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(0));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -102,11 +128,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Bounded wait.  Returns false when it gave up (after QMM_WAIT_LIMIT_NS) or another thread of the
 // block already did.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t spin = 0;; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if ((spin & 7u) == 7u) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > QMM_WAIT_LIMIT_NS) break;
@@ -139,6 +166,21 @@ __device__ __forceinline__ void tc_mma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a,
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The pair's form: one instruction drives the tensor cores of both multiprocessors; each multiplies
+// its own 128 weight rows (its tensor memory) by all the activation rows, of which each block's
+// shared memory holds half.
+__device__ __forceinline__ void tc_mma_bf16_ta_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, once the pair's earlier MMAs are complete, on the barrier at this address in both blocks.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 // Thread i of the warp writes 32 consecutive columns of lane (base lane + i).
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
@@ -177,8 +219,8 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return d;
 }
 // Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(QMM_BN >> 4) << 24);
+__host__ __device__ constexpr uint32_t umma_idesc(int n, int m = QMM_BN) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 __device__ __forceinline__ uint32_t q_lop3(uint32_t a, uint32_t mask, uint32_t orv) {
@@ -312,10 +354,12 @@ struct GroupTable {
     const int *tiles;  // [experts + 1] token tiles before each expert, then the total
 };
 
+// `half`: -1, or the block's rank in a pair, whose tiles are 2 x 128 weight rows (ungrouped products only).
 template <int BT>
-__device__ __forceinline__ bool tile_info(const QmmKernelParams &p, const GroupTable &gt, int tile, int n_tiles, TileInfo &ti) {
+__device__ __forceinline__ bool tile_info(const QmmKernelParams &p, const GroupTable &gt, int tile, int n_tiles, TileInfo &ti,
+                                          int half = -1) {
     const int nt = tile % n_tiles, j = tile / n_tiles;
-    ti.n0 = nt * QMM_BN;
+    ti.n0 = half < 0 ? nt * QMM_BN : (2 * nt + half) * QMM_BN;
     if (!p.offsets) {
         ti.expert = 0;
         ti.wrow0 = ti.n0;
@@ -363,17 +407,17 @@ struct Item {
     int part, parts, slot;
     int round;           // which of the block's (at most two) parts of left-over tiles this is
 };
+// `worker` of `grid` workers: a block of the grid, or a pair of blocks.
 template <int KPS>
-__device__ __forceinline__ bool qmm_item(const QmmKernelParams &p, int kblocks, int j, Item &it) {
-    const int grid = (int)gridDim.x;
+__device__ __forceinline__ bool qmm_item(const QmmKernelParams &p, int kblocks, int j, Item &it, int worker, int grid) {
     if (j < p.full_waves) {
-        it.tile = (int)blockIdx.x + j * grid;
+        it.tile = worker + j * grid;
         it.kb0 = 0; it.kb1 = kblocks; it.part = 0; it.parts = 1; it.slot = 0; it.round = 0;
         return true;
     }
     // the parts of the left-over tiles are dealt round-robin, at most tail_rounds per block
     it.round = j - p.full_waves;
-    const int pi = (int)blockIdx.x + it.round * grid;
+    const int pi = worker + it.round * grid;
     if (it.round >= p.tail_rounds || pi >= p.tail_tiles * p.splits) return false;
     it.slot = pi / p.splits;
     it.part = pi % p.splits;
@@ -387,30 +431,42 @@ __device__ __forceinline__ bool qmm_item(const QmmKernelParams &p, int kblocks, 
 
 // Stages of the dequantized-weight ring in tensor memory: 32 columns each, in what the two
 // accumulators leave of the 512 columns.
-template <int BT> struct QmmTmem {
+// PAIR: two blocks of a cluster share a tile of 2 x 128 weight rows x BT tokens; each keeps half of
+// the tokens' activations in its shared memory (the stage is half as large) and one accumulator.
+template <int BT, bool PAIR = false> struct QmmTmem {
     // Two accumulators (the epilogue of one tile overlaps the main loop of the next) while they
     // leave 128 columns for the weight ring; the widest tile keeps a single one.
     static constexpr int ACC_BUFS = 2 * BT + 128 <= 512 ? 2 : 1;
+    static constexpr int XT = PAIR ? BT / 2 : BT;  // token rows of a stage in this block's shared memory
     static constexpr int ACC_COLS = ACC_BUFS * BT;
     static constexpr int A_COL0 = ACC_COLS;
     // ring depth: what the tensor-memory columns and the shared memory (activation stages beside
     // two packed-weight slabs) both allow, at most 8
     static constexpr int BY_TMEM = (512 - ACC_COLS) / 32;
-    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - 2 * 128 * 128) / (BT * 64 * 2);
+    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - 2 * 128 * 128) / (XT * 64 * 2);
     static constexpr int FIT = BY_TMEM < BY_SMEM ? (BY_TMEM < 8 ? BY_TMEM : 8) : (BY_SMEM < 8 ? BY_SMEM : 8);
     // a multiple of the dequantizer groups, so that a stage is always refilled by the same group
     static constexpr int STAGES = FIT / QMM_DQ_GROUPS * QMM_DQ_GROUPS;
     static_assert(STAGES >= QMM_DQ_GROUPS, "token tile too wide for the weight ring");
 };
 
-template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 3 nvfp4*/>
+template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 3 nvfp4*/, bool PAIR = false>
 __global__ void __launch_bounds__(QMM_THREADS, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, QmmKernelParams p,
            int total_tiles, int n_tiles) {
     constexpr int KPS = QmmBits<BITS>::KPS;
-    constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
-    constexpr int A_COL0 = QmmTmem<BT>::A_COL0, ACC_BUFS = QmmTmem<BT>::ACC_BUFS;
-    static_assert(STAGES == QmmTmem<BT>::STAGES, "activation stages in shared memory and weight stages in tensor memory form one ring");
+    using Ring = QmmTmem<BT, PAIR>;
+    constexpr int XT = Ring::XT;
+    constexpr uint32_t X_BYTES = XT * QMM_BK * 2;
+    constexpr int A_COL0 = Ring::A_COL0, ACC_BUFS = Ring::ACC_BUFS;
+    static_assert(STAGES == Ring::STAGES, "activation stages in shared memory and weight stages in tensor memory form one ring");
+    static_assert(!PAIR || ACC_BUFS == 1, "a pair keeps one accumulator");
+    // A pair works as one: both blocks walk the same items; `half` is the block's rank in the pair
+    // (its 128 of the tile's 256 weight rows, its half of the tile's tokens), -1 without pairs.
+    const int half = PAIR ? (int)pair_rank() : -1;
+    const bool leader = !PAIR || half == 0;
+    const int worker = PAIR ? (int)blockIdx.x >> 1 : (int)blockIdx.x;
+    const int workers = PAIR ? (int)gridDim.x >> 1 : (int)gridDim.x;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -422,7 +478,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     uint64_t *xfull = bars, *afull = xfull + STAGES, *empty = afull + STAGES;
     uint64_t *wfull = empty + STAGES, *wempty = wfull + QMM_W_STAGES;
     uint64_t *accfull = wempty + QMM_W_STAGES, *accempty = accfull + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accempty + 2);
+    // Pairs: afull, accempty and pxfull of the FIRST block are the ones waited on; the second block's
+    // dequantizers, epilogue and watcher arrive there (its activation stage has landed: pxfull).
+    uint64_t *pxfull = accempty + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pxfull + STAGES);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *last_flag = abort_flag + 1;  // epilogue: this block arrived last at a K-split tile
     int *table = reinterpret_cast<int *>(bars) + 256;  // behind the 1 KB of barriers and flags: 2 x (experts + 1) ints
@@ -433,8 +492,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(xfull + s, 1);
-            mbar_init(afull + s, QMM_DQ_WARPS / QMM_DQ_GROUPS);
+            mbar_init(afull + s, (PAIR ? 2 : 1) * QMM_DQ_WARPS / QMM_DQ_GROUPS);
             mbar_init(empty + s, 1);
+            mbar_init(pxfull + s, 1);
         }
         for (int s = 0; s < QMM_W_STAGES; s++) {
             mbar_init(wfull + s, 1);
@@ -442,15 +502,20 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(accfull + s, 1);
-            mbar_init(accempty + s, QMM_EPI_WARPS);
+            mbar_init(accempty + s, (PAIR ? 2 : 1) * QMM_EPI_WARPS);
         }
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {  // all of tensor memory: two accumulators and the dequantized-weight ring
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {  // the same warp of both blocks
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     GroupTable gt{nullptr, nullptr};
     const bool tabled = p.offsets && p.experts <= QMM_MAX_TABLE_EXPERTS;
@@ -459,6 +524,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) pair_sync();  // the other block's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (tabled) {
@@ -483,15 +549,15 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             bool ok = true;
             for (int j = 0; ok; j++) {
                 Item item;
-                if (!qmm_item<KPS>(p, kblocks, j, item)) break;
+                if (!qmm_item<KPS>(p, kblocks, j, item, worker, workers)) break;
                 TileInfo ti;
-                if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
+                if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
                 for (int kb = item.kb0; kb < item.kb1 && ok; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(xfull + s, X_BYTES);
-                    tma_load_2d(xs + s * X_BYTES, &tmap_x, kb * QMM_BK, ti.tok0, xfull + s);
+                    tma_load_2d(xs + s * X_BYTES, &tmap_x, kb * QMM_BK, ti.tok0 + (PAIR ? half * XT : 0), xfull + s);
                 }
             }
         }
@@ -503,9 +569,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             bool ok = true;
             for (int j = 0; ok; j++) {
                 Item item;
-                if (!qmm_item<KPS>(p, kblocks, j, item)) break;
+                if (!qmm_item<KPS>(p, kblocks, j, item, worker, workers)) break;
                 TileInfo ti;
-                if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
+                if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
                 for (int kb = item.kb0; kb < item.kb1 && ok; kb += KPS, wit++) {
                     const uint32_t s = wit % QMM_W_STAGES, ph = (wit / QMM_W_STAGES) & 1;
                     ok = mbar_wait(wempty + s, ph ^ 1, abort_flag);
@@ -522,15 +588,16 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         // a hardware named barrier costs ~30.  So this warp never reads shared memory: the watcher
         // warp waits on the mbarriers (stage full, accumulator drained) and passes each stage on
         // through named barrier 1 + stage.  All lanes walk the loop; lane 0 issues.
-        constexpr uint32_t idesc = umma_idesc(BT);
+        constexpr uint32_t idesc = umma_idesc(BT, PAIR ? 2 * QMM_BN : QMM_BN);
         uint32_t tcount = 0, s = 0;
         const uint32_t empty0 = smem_u32(empty);
         const uint64_t bd0 = umma_desc(smem_u32(xs));
-        for (int j = 0;; j++) {
+        // (pairs: the first block's warp issues for both; the second block's has nothing to do)
+        for (int j = 0; leader; j++) {
             Item item;
-            if (!qmm_item<KPS>(p, kblocks, j, item)) break;
+            if (!qmm_item<KPS>(p, kblocks, j, item, worker, workers)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
             const uint32_t buf = tcount % ACC_BUFS;
             const uint32_t d = tmem_base + buf * BT;
             for (int kb = item.kb0; kb < item.kb1; kb++) {
@@ -540,14 +607,21 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     const uint32_t at = tmem_base + A_COL0 + s * 32;
                     const uint64_t bd = bd0 + (uint64_t)(s * (X_BYTES >> 4));
 #pragma unroll
-                    for (int k = 0; k < QMM_BK / 16; k++)  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
-                        tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
-                    tc_commit_addr(empty0 + 8 * s);  // frees both halves of the stage once these MMAs have read them
+                    for (int k = 0; k < QMM_BK / 16; k++) {  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
+                        if (PAIR) tc_mma_bf16_ta_pair(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
+                        else tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
+                    }
+                    // frees both halves of the stage (in both blocks of a pair) once these MMAs have read them
+                    if (PAIR) tc_commit_pair(empty0 + 8 * s);
+                    else tc_commit_addr(empty0 + 8 * s);
                 }
                 __syncwarp();
                 if (++s == STAGES) s = 0;
             }
-            if (lane == 0) tc_commit(accfull + buf);
+            if (lane == 0) {
+                if (PAIR) tc_commit_pair(smem_u32(accfull + buf));
+                else tc_commit(accfull + buf);
+            }
             __syncwarp();
             tcount++;
         }
@@ -559,14 +633,29 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         bool ok = true;
         for (int j = 0;; j++) {
             Item item;
-            if (!qmm_item<KPS>(p, kblocks, j, item)) break;
+            if (!qmm_item<KPS>(p, kblocks, j, item, worker, workers)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
-            if (lane == 0 && ok) ok = mbar_wait(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
+            if (!leader) {
+                // second block of a pair: tells the first when this block's half of a stage has landed
+                for (int kb = item.kb0; kb < item.kb1; kb++) {
+                    if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
+                    if (lane == 0 && ok) mbar_arrive_leader(pxfull + s);
+                    __syncwarp();
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                tcount++;
+                continue;
+            }
+            if (lane == 0 && ok) ok = mbar_wait<PAIR>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
             for (int kb = item.kb0; kb < item.kb1; kb++) {
                 if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
-                if (lane == 0 && ok) ok = mbar_wait(afull + s, ph, abort_flag);
+                if (PAIR && lane == 0 && ok) ok = mbar_wait<true>(pxfull + s, ph, abort_flag);
+                if (lane == 0 && ok) ok = mbar_wait<PAIR>(afull + s, ph, abort_flag);
                 __syncwarp();
                 named_arrive(1 + s);
                 if (++s == STAGES) {
@@ -598,9 +687,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         };
         for (int j = 0; ok; j++) {
             Item item;
-            if (!qmm_item<KPS>(p, kblocks, j, item)) break;
+            if (!qmm_item<KPS>(p, kblocks, j, item, worker, workers)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
             // rows past N (last tile) read the last valid row's scales; their outputs are not stored
             const int wr = ti.wrow0 + min(row, p.N - 1 - ti.n0);
             const uint16_t *sc = p.scales + (size_t)wr * p.row_groups;
@@ -685,7 +774,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     tc_st_wait();
                     tc_fence_before();  // the stores are ordered before the arrive the MMA thread waits on
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(afull + sa);
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_leader(afull + sa);
+                        else mbar_arrive(afull + sa);
+                    }
                 }
                 // A warp none of whose blocks lay in this slab still waits for the slab before it
                 // releases it: otherwise it could run ahead and its arrival for a later slab would
@@ -702,9 +794,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         bool ok = true;
         for (int jj = 0; ok; jj++) {
             Item item;
-            if (!qmm_item<KPS>(p, kblocks, jj, item)) break;
+            if (!qmm_item<KPS>(p, kblocks, jj, item, worker, workers)) break;
             TileInfo ti;
-            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti)) continue;
+            if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             // After a wait gave up the warp keeps walking the items without touching data: the
             // named barriers of K-split tiles below must still see all four epilogue warps.
@@ -734,12 +826,16 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(accempty + buf);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_leader(accempty + buf);
+                    else mbar_arrive(accempty + buf);
+                }
             } else {
                 // One part of a tile cut along K: the float32 partial goes to scratch as
                 // [token][row] (a warp writes 128 consecutive bytes per token); the block that
                 // arrives last adds the parts in part order and rounds once.
-                float *mine = p.partials + ((size_t)item.slot * item.parts + item.part) * (size_t)(BT * QMM_BN);
+                const int pslot = PAIR ? 2 * item.slot + half : item.slot;  // each block of a pair keeps its own rows' parts
+                float *mine = p.partials + ((size_t)pslot * item.parts + item.part) * (size_t)(BT * QMM_BN);
 #pragma unroll 1
                 for (int c = 0; c < BT / 32 && ok; c++) {
                     uint32_t v[32];
@@ -751,15 +847,18 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(accempty + buf);  // the accumulator is free again
+                if (lane == 0) {  // the accumulator is free again
+                    if (PAIR) mbar_arrive_leader(accempty + buf);
+                    else mbar_arrive(accempty + buf);
+                }
                 __threadfence();
                 named_sync_n(QMM_EPI_BARRIER, QMM_EPI_WARPS * 32);
                 if (tid == 0) {
                     bool last = false;
                     if (ok) {
-                        const uint32_t arrived = atomicAdd(p.counters + item.slot, 1u);
+                        const uint32_t arrived = atomicAdd(p.counters + pslot, 1u);
                         last = arrived == (uint32_t)item.parts - 1;
-                        if (last) p.counters[item.slot] = 0u;  // rearmed for the next launch
+                        if (last) p.counters[pslot] = 0u;  // rearmed for the next launch
                     }
                     // K-split parts are a block's last items: the whole block adds the parts up
                     // after its roles have finished (below).
@@ -780,11 +879,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         // part order (the sum does not depend on who arrived when), round once and store.
         Item item;
         TileInfo ti;
-        if (qmm_item<KPS>(p, kblocks, p.full_waves + round, item) && tile_info<BT>(p, gt, item.tile, n_tiles, ti)) {
+        if (qmm_item<KPS>(p, kblocks, p.full_waves + round, item, worker, workers) && tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) {
             __threadfence();
             float gmul = 1.0f;
             if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
-            const float4 *base = reinterpret_cast<const float4 *>(p.partials + (size_t)item.slot * item.parts * (size_t)(BT * QMM_BN));
+            const int pslot = PAIR ? 2 * item.slot + half : item.slot;
+            const float4 *base = reinterpret_cast<const float4 *>(p.partials + (size_t)pslot * item.parts * (size_t)(BT * QMM_BN));
             constexpr int TILE4 = BT * QMM_BN / 4;  // float4 per part
             const int tokens = min(BT, ti.tok_end - ti.tok0);
             for (int idx = tid; idx < tokens * (QMM_BN / 4); idx += QMM_THREADS) {
@@ -803,9 +903,15 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             }
         }
     }
+    if (PAIR) {
+        // neither block leaves (or frees the pair's tensor memory) while the other may still arrive on its barriers
+        tc_fence_before();
+        pair_sync();
+    }
     if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
     }
 }
 
@@ -887,16 +993,18 @@ static int32_t ensure_qmm_scratch(nvc_device *dev, size_t bytes, size_t counters
     return NVC_OK;
 }
 
-template <int BITS, int BT, int MODE>
+// PAIR: the grid is made of clusters of two blocks that work on tiles of 256 weight rows as one
+// (`total_tiles`, `n_tiles` then count such tiles and `sms` below counts pairs).
+template <int BITS, int BT, int MODE, bool PAIR = false>
 static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
                           int total_tiles, int n_tiles) {
-    constexpr uint32_t X_BYTES = BT * QMM_BK * 2;
+    constexpr uint32_t X_BYTES = QmmTmem<BT, PAIR>::XT * QMM_BK * 2;
     // one ring: activation stages in shared memory, weight stages in tensor memory
-    constexpr int STAGES = QmmTmem<BT>::STAGES;
+    constexpr int STAGES = QmmTmem<BT, PAIR>::STAGES;
     static_assert(1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1) <= 227 * 1024, "not enough shared memory for the pipeline");
     // alignment slack, activation stages, packed-weight slabs, 1 KB of barriers and flags, the grouped products' tables
     constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1);
-    auto kernel = qmm_kernel<BITS, BT, STAGES, MODE>;
+    auto kernel = qmm_kernel<BITS, BT, STAGES, MODE, PAIR>;
     // the opt-in to this much dynamic shared memory is a per-device attribute of the instantiation
     static bool configured[64] = {};
     static std::mutex configured_mu;
@@ -910,7 +1018,29 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     }
     // The schedule (see Item): whole tiles wave by wave, then the left-over tiles cut along K.
     QmmKernelParams k = kp;
-    const int sms = dev->prop.multiProcessorCount;
+    int sms = dev->prop.multiProcessorCount;
+    if (PAIR) {
+        // pairs that can be resident together (a pair needs two multiprocessors of one cluster-capable group)
+        static int pairs[64] = {};
+        std::lock_guard<std::mutex> g(configured_mu);
+        if (pairs[dev->ordinal] == 0) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(2 * (unsigned)sms);
+            probe.blockDim = dim3(QMM_THREADS);
+            probe.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2;
+            attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
+            probe.attrs = &attr;
+            probe.numAttrs = 1;
+            int n = 0;
+            NVC_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &probe));
+            if (n < 1) return set_error(NVC_ERR_DRIVER, "qmm: no cluster of two blocks fits the device");
+            pairs[dev->ordinal] = n < sms / 2 ? n : sms / 2;
+        }
+        sms = pairs[dev->ordinal];
+    }
     const int kblocks = k.K / QMM_BK, slabs = (kblocks + QmmBits<BITS>::KPS - 1) / QmmBits<BITS>::KPS;
     int grid = sms < total_tiles ? sms : total_tiles;
     k.full_waves = total_tiles / grid;
@@ -941,18 +1071,35 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     }
     if (k.full_waves == 0) grid = k.tail_tiles * k.splits < sms ? k.tail_tiles * k.splits : sms;
     if (k.splits > 1) {
-        const size_t need = (size_t)k.tail_tiles * k.splits * BT * QMM_BN * sizeof(float);
-        NVC_TRY(ensure_qmm_scratch(dev, need, (size_t)k.tail_tiles));
+        const size_t blocks_per_tile = PAIR ? 2 : 1;  // each block of a pair keeps the parts of its own rows
+        const size_t need = blocks_per_tile * k.tail_tiles * k.splits * BT * QMM_BN * sizeof(float);
+        NVC_TRY(ensure_qmm_scratch(dev, need, blocks_per_tile * k.tail_tiles));
         k.partials = (float *)dev->qmm_partials;
         k.counters = dev->qmm_counters;
     }
-    kernel<<<grid, QMM_THREADS, smem, dev->stream>>>(mx, mw, k, total_tiles, n_tiles);
+    if (PAIR) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)grid);
+        cfg.blockDim = dim3(QMM_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = dev->stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        NVC_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, mw, k, total_tiles, n_tiles));
+    } else {
+        kernel<<<grid, QMM_THREADS, smem, dev->stream>>>(mx, mw, k, total_tiles, n_tiles);
+    }
     return check_launch(dev, "qmm_kernel");
 }
 
 template <int BITS, int MODE>
-static int32_t launch_bt(nvc_device *dev, int bt, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
+static int32_t launch_bt(nvc_device *dev, int bt, bool pair, const CUtensorMap &mx, const CUtensorMap &mw, const QmmKernelParams &kp,
                          int total_tiles, int n_tiles) {
+    if (pair) return launch_cfg<BITS, 256, MODE, true>(dev, mx, mw, kp, total_tiles, n_tiles);
     switch (bt) {
     case 32: return launch_cfg<BITS, 32, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
     case 64: return launch_cfg<BITS, 64, MODE>(dev, mx, mw, kp, total_tiles, n_tiles);
@@ -976,7 +1123,12 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     // measured: 8-bit weights at 2048 rows run 294 us with 192-token tiles and 333-356 us with 256
     if (p.bits == 8 && per > 192 && per <= 4096) bt = 192;
     if (p.offsets) bt = per > 170 ? 256 : per > 128 ? 192 : per > 85 ? 192 : per > 42 ? 128 : per > 21 ? 64 : 32;
-    const int n_tiles = (int)((p.N + QMM_BN - 1) / QMM_BN);
+    // Pairs of blocks on tiles of 256 weight rows: ungrouped products of 256-token tiles whose rows
+    // split evenly, with enough tiles to occupy the pairs.
+    static const bool no_pairs = getenv("NUVEC_QMM_NO_PAIRS") != nullptr;
+    const bool pair = !no_pairs && !p.offsets && bt == 256 && p.N % (2 * QMM_BN) == 0 &&
+                      (p.N / (2 * QMM_BN)) * ((p.rows + bt - 1) / bt) >= dev->prop.multiProcessorCount / 2;
+    const int n_tiles = pair ? (int)(p.N / (2 * QMM_BN)) : (int)((p.N + QMM_BN - 1) / QMM_BN);
     int64_t token_tiles;
     if (p.offsets) token_tiles = (p.rows + bt - 1) / bt + experts;  // upper bound: one partial tile per expert
     else token_tiles = (p.rows + bt - 1) / bt;
@@ -985,7 +1137,7 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
 
     CUtensorMap mx, mw;
     NVC_TRY(make_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.x, (uint64_t)p.K, (uint64_t)p.rows, (uint64_t)p.ldx * 2,
-                     QMM_BK, (uint32_t)bt));
+                     QMM_BK, (uint32_t)(pair ? bt / 2 : bt)));
     const uint64_t wrow_bytes = (uint64_t)p.K * p.bits / 8;
     NVC_TRY(make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.w, wrow_bytes, (uint64_t)(experts * p.N), wrow_bytes, 128, 128));
 
@@ -1010,13 +1162,13 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     const int tt = (int)total;
     if (affine) {
         switch (p.bits) {
-        case 4: return launch_bt<4, 0>(dev, bt, mx, mw, kp, tt, n_tiles);
-        case 8: return launch_bt<8, 0>(dev, bt, mx, mw, kp, tt, n_tiles);
-        default: return launch_bt<2, 0>(dev, bt, mx, mw, kp, tt, n_tiles);
+        case 4: return launch_bt<4, 0>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
+        case 8: return launch_bt<8, 0>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
+        default: return launch_bt<2, 0>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
         }
     }
-    if (p.mode == NVC_MXFP4) return launch_bt<4, 1>(dev, bt, mx, mw, kp, tt, n_tiles);
-    return launch_bt<4, 3>(dev, bt, mx, mw, kp, tt, n_tiles);
+    if (p.mode == NVC_MXFP4) return launch_bt<4, 1>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
+    return launch_bt<4, 3>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
 }
 
 }  // namespace nvc

@@ -264,6 +264,7 @@ int32_t nvc_device_close(nvc_device *dev) {
     if (dev->qmm_counters) dev->pool.free(dev->qmm_counters);
     if (dev->counters) dev->pool.free(dev->counters);
     if (dev->ring_dev) dev->pool.free(dev->ring_dev);
+    if (dev->batch_exec) cudaGraphExecDestroy(dev->batch_exec);
     if (dev->ring_host) cudaFreeHost(dev->ring_host);
     if (dev->staging) dev->pool.free(dev->staging);
     if (dev->pinned) cudaFreeHost(dev->pinned);

@@ -486,6 +486,28 @@ def test_asynchronous_host_entry_point_delivers_at_synchronize(be):
     dev.synchronize()
     for M, N, K, q, xh, want, got in cases:
         assert np.array_equal(got, want), (M, N, K)
+    # The same list again and again, as a decode loop sends it: the second call records its copy and
+    # kernels, later calls replay the recording.  New activations in the same host buffers every
+    # time; every result must be the product of the activations of ITS call.
+    originals = [xh.copy() for _, _, _, _, xh, _, _ in cases]
+    for step in range(4):
+        fresh = []
+        for M, N, K, q, xh, want, got in cases:
+            xh[:] = rand(rng, (M, K), oracle.BF16)
+            fresh.append(nv.quantized_matmul(dev.array(xh, nv.BF16), q).to_numpy().view(np.uint16).reshape(M, N))
+            got[:] = 0
+        dev.synchronize()
+        assert lib.nvc_quantized_matmul_host_batch(dev._h, items, len(items)) == 0, _ffi.last_error()
+        dev.synchronize()
+        for (M, N, K, q, xh, want, got), ref in zip(cases, fresh):
+            assert np.array_equal(got, ref), (step, M, N, K)
+    # a different list afterwards drops the recording
+    assert lib.nvc_quantized_matmul_host_batch(dev._h, items, len(items) - 1) == 0, _ffi.last_error()
+    dev.synchronize()
+    for (M, N, K, q, xh, want, got), ref in zip(cases[:-1], fresh[:-1]):
+        assert np.array_equal(got, ref), (M, N, K)
+    for (M, N, K, q, xh, want, got), x0 in zip(cases, originals):
+        xh[:] = x0  # the rest of the test uses the first activations and their products again
     # more pending work than the staging blocks hold: the call flushes by itself
     M, N, K, q, xh, want, _ = cases[2]
     outs = [np.zeros((M, N), np.uint16) for _ in range(40)]
