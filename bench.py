@@ -50,7 +50,7 @@ PREFILL = (2048, 12288, 4096)  # M, N, K
 # DRAM bytes (read + write) of one launch of the few-row kernel on each projection at M = 1, from an
 # ncu capture of three launches per shape on distinct weight copies (profiles/qmv_dram_traffic_decode.md):
 # within 0.6 % of the algorithmic bytes, i.e. every weight byte crosses HBM once.
-NCU_DRAM_BYTES = {"qkv": 14.23e6, "o": 9.51e6, "gate_up": 56.70e6, "down": 28.41e6}
+NCU_DRAM_BYTES = {"qkv": 14.24e6, "o": 9.52e6, "gate_up": 56.84e6, "down": 28.41e6}
 
 
 def qmv_bytes(M, N, K, bits=BITS, gs=GS, s=4):
@@ -730,8 +730,19 @@ def one_shape(args, nv, _ffi, dev):
             assert rc == 0, _ffi.last_error()
     e1.record()
     e1.synchronize()
-    print(json.dumps({"one": args.one, "launches": 2 * copies, "us_per_launch": e0.elapsed_ms(e1) * 1e3 / copies,
-                      "bytes_per_launch": qmv_bytes(M, N, K, bits)}))
+    out = {"one": args.one, "launches": 2 * copies, "us_per_launch": e0.elapsed_ms(e1) * 1e3 / copies,
+           "bytes_per_launch": qmv_bytes(M, N, K, bits)}
+    if args.timeline and M > 8:
+        # the timeline build of the tensor-core kernel: cycles per role of blocks 0 and 1 in the last launch
+        # (total, then the role's waits in program order)
+        buf = (C.c_longlong * (2 * 8 * 6))()
+        lib.nvc_debug_qmm_timing.restype = C.c_int32
+        assert lib.nvc_debug_qmm_timing(buf) == 0
+        t = np.frombuffer(buf, dtype=np.int64).reshape(2, 8, 6)
+        roles = ["activation producer", "mma issuer", "watcher", "dequantizers 0", "dequantizers 1", "dequantizers 2",
+                 "dequantizers 3", "epilogue"]
+        out["role_cycles"] = {f"block {b}": {r: t[b, i].tolist() for i, r in enumerate(roles)} for b in range(2)}
+    print(json.dumps(out))
 
 
 # ── where a decode product's time goes (--timeline) ──────────────────────────────────────────

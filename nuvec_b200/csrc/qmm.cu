@@ -46,6 +46,25 @@
 
 namespace nvc {
 
+// ── optional role timing (diagnostic builds only: -DNUVEC_TIMELINE) ─────────────────────────
+// Every role of blocks 0 and 1 adds up the clock cycles it spends inside each of its waits (and
+// in total); nvc_debug_qmm_timing (end of this file) fetches the sums of the last launch.
+#ifdef NUVEC_TIMELINE
+constexpr int QT_ROLES = 8, QT_SLOTS = 6;
+__device__ long long g_qmm_timing[2][QT_ROLES][QT_SLOTS];
+#define QT_BEGIN long long qt_[QT_SLOTS] = {0, 0, 0, 0, 0, 0}; const long long qt_start_ = clock64();
+#define QT(k, ...) { const long long qt_t_ = clock64(); __VA_ARGS__; qt_[k] += clock64() - qt_t_; }
+#define QT_END(role, writer)                                                        \
+    if (blockIdx.x < 2 && (writer)) {                                               \
+        qt_[0] = clock64() - qt_start_;                                             \
+        for (int q_ = 0; q_ < QT_SLOTS; q_++) g_qmm_timing[blockIdx.x][role][q_] = qt_[q_]; \
+    }
+#else
+#define QT_BEGIN
+#define QT(k, ...) { __VA_ARGS__; }
+#define QT_END(role, writer)
+#endif
+
 constexpr int QMM_BN = 128;  // weight rows per tile (UMMA M)
 constexpr int QMM_BK = 64;   // k-values per block: one 128-byte swizzle row of bfloat16
 constexpr int QMM_EPI_WARPS = 4, QMM_DQ_WARPS = 16, QMM_DQ_GROUPS = 4;  // dequantizers: groups of 4 warps
@@ -56,6 +75,8 @@ constexpr int QMM_W_STAGES = 2;          // packed-weight slabs in flight
 constexpr uint32_t QMM_W_BYTES = 128 * 128;  // one slab: 128 rows x 128 bytes
 constexpr unsigned long long QMM_WAIT_LIMIT_NS = 2000000000ull;  // a wait gives up after two seconds
 constexpr uint32_t QMM_PARK_NS = 20000;  // how long one try_wait may keep the warp parked
+constexpr int QMM_TABLE_BYTES = 4112;        // the grouped products' tables: 2 x (512 + 1) ints, rounded up to 16 bytes
+constexpr int QMM_EPI_STAGE_BYTES = 4 * 2048;  // epilogue: 32 tokens x 32 weight rows of bfloat16 per warp
 
 struct QmmKernelParams {
     const uint16_t *scales, *biases;  // bfloat16 [weight rows, K / gs]
@@ -95,17 +116,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(QMM_PARK_NS) : "memory");
     return done != 0;
 }
-// The same attempt with cluster-scope acquire: for barriers that threads of the other block of a
-// pair arrive on.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(QMM_PARK_NS) : "memory");
-    return done != 0;
-}
 // Block pairs (clusters of two): rank in the pair, the pair's barrier, and an arrival on the
 // barrier at the same shared-memory offset in the pair's first block.
 __device__ __forceinline__ uint32_t pair_rank() {
@@ -119,7 +129,11 @@ __device__ __forceinline__ void pair_sync() {
 __device__ __forceinline__ void mbar_arrive_leader(uint64_t *bar) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(0));
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+    // What the arrival announces -- tensor-memory stores, a landed TMA tile, a drained accumulator -- is
+    // read by the tensor cores, not by the waiting thread, and is complete before this instruction
+    // (tcgen05.wait, tcgen05.fence, the TMA's own barrier); so neither this arrival nor the wait for it
+    // asks for cluster-wide ordering, which was measured to cost more than the MMAs of a k-block.
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -128,12 +142,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Bounded wait.  Returns false when it gave up (after QMM_WAIT_LIMIT_NS) or another thread of the
 // block already did.
-template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t spin = 0;; spin++) {
-        if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 7u) == 7u) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > QMM_WAIT_LIMIT_NS) break;
@@ -443,7 +456,7 @@ template <int BT, bool PAIR = false> struct QmmTmem {
     // ring depth: what the tensor-memory columns and the shared memory (activation stages beside
     // two packed-weight slabs) both allow, at most 8
     static constexpr int BY_TMEM = (512 - ACC_COLS) / 32;
-    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - 2 * 128 * 128) / (XT * 64 * 2);
+    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - QMM_EPI_STAGE_BYTES - 2 * 128 * 128) / (XT * 64 * 2);
     static constexpr int FIT = BY_TMEM < BY_SMEM ? (BY_TMEM < 8 ? BY_TMEM : 8) : (BY_SMEM < 8 ? BY_SMEM : 8);
     // a multiple of the dequantizer groups, so that a stage is always refilled by the same group
     static constexpr int STAGES = FIT / QMM_DQ_GROUPS * QMM_DQ_GROUPS;
@@ -485,6 +498,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *last_flag = abort_flag + 1;  // epilogue: this block arrived last at a K-split tile
     int *table = reinterpret_cast<int *>(bars) + 256;  // behind the 1 KB of barriers and flags: 2 x (experts + 1) ints
+    uint8_t *epi_stage = reinterpret_cast<uint8_t *>(bars) + 1024 + QMM_TABLE_BYTES;  // [epilogue warp][32 tokens][32 rows] bfloat16
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kblocks = p.K / QMM_BK;
@@ -545,6 +559,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     if (warp == 4) {
         // ── TMA producer, activations: one 64-k x BT tile per stage ─────────────────────────
         if (lane == 0) {
+            QT_BEGIN
             uint32_t it = 0;  // k-blocks issued so far
             bool ok = true;
             for (int j = 0; ok; j++) {
@@ -554,12 +569,13 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 if (!tile_info<BT>(p, gt, item.tile, n_tiles, ti, half)) continue;
                 for (int kb = item.kb0; kb < item.kb1 && ok; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
+                    QT(1, ok = mbar_wait(empty + s, ph ^ 1, abort_flag))
                     if (!ok) break;
                     mbar_expect_tx(xfull + s, X_BYTES);
                     tma_load_2d(xs + s * X_BYTES, &tmap_x, kb * QMM_BK, ti.tok0 + (PAIR ? half * XT : 0), xfull + s);
                 }
             }
+            QT_END(0, true)
         }
     } else if (warp == 6) {
         // ── TMA producer, packed weights: runs ahead on its own ring, so a slab's latency is
@@ -589,6 +605,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         // warp waits on the mbarriers (stage full, accumulator drained) and passes each stage on
         // through named barrier 1 + stage.  All lanes walk the loop; lane 0 issues.
         constexpr uint32_t idesc = umma_idesc(BT, PAIR ? 2 * QMM_BN : QMM_BN);
+        QT_BEGIN
         uint32_t tcount = 0, s = 0;
         const uint32_t empty0 = smem_u32(empty);
         const uint64_t bd0 = umma_desc(smem_u32(xs));
@@ -601,8 +618,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint32_t buf = tcount % ACC_BUFS;
             const uint32_t d = tmem_base + buf * BT;
             for (int kb = item.kb0; kb < item.kb1; kb++) {
-                named_sync(1 + s);  // stage s is full (and, for kb = 0, the accumulator is drained)
-                if (lane == 0) {
+                QT(1, named_sync(1 + s))  // stage s is full (and, for kb = 0, the accumulator is drained)
+                QT(2, if (lane == 0) {
                     tc_fence_after();
                     const uint32_t at = tmem_base + A_COL0 + s * 32;
                     const uint64_t bd = bd0 + (uint64_t)(s * (X_BYTES >> 4));
@@ -614,7 +631,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     // frees both halves of the stage (in both blocks of a pair) once these MMAs have read them
                     if (PAIR) tc_commit_pair(empty0 + 8 * s);
                     else tc_commit_addr(empty0 + 8 * s);
-                }
+                })
                 __syncwarp();
                 if (++s == STAGES) s = 0;
             }
@@ -625,12 +642,14 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             __syncwarp();
             tcount++;
         }
+        QT_END(1, lane == 0)
     } else if (warp == QMM_WATCH_WARP) {
         // ── watcher: the MMA warp's eyes.  It arrives on the named barrier of every stage exactly
         //    once per k-block whatever happens (after a wait gave up it stops waiting, not
         //    arriving), so the MMA warp can never be left behind in a barrier. ──
         uint32_t tcount = 0, s = 0, ph = 0;
         bool ok = true;
+        QT_BEGIN
         for (int j = 0;; j++) {
             Item item;
             if (!qmm_item<KPS>(p, kblocks, j, item, worker, workers)) break;
@@ -640,8 +659,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             if (!leader) {
                 // second block of a pair: tells the first when this block's half of a stage has landed
                 for (int kb = item.kb0; kb < item.kb1; kb++) {
-                    if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
-                    if (lane == 0 && ok) mbar_arrive_leader(pxfull + s);
+                    QT(1, if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag))
+                    QT(2, if (lane == 0 && ok) mbar_arrive_leader(pxfull + s))
                     __syncwarp();
                     if (++s == STAGES) {
                         s = 0;
@@ -651,13 +670,13 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 tcount++;
                 continue;
             }
-            if (lane == 0 && ok) ok = mbar_wait<PAIR>(accempty + buf, aph ^ 1, abort_flag);  // the epilogue has drained this buffer
+            QT(4, if (lane == 0 && ok) ok = mbar_wait(accempty + buf, aph ^ 1, abort_flag))  // the epilogue has drained this buffer
             for (int kb = item.kb0; kb < item.kb1; kb++) {
-                if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag);
-                if (PAIR && lane == 0 && ok) ok = mbar_wait<true>(pxfull + s, ph, abort_flag);
-                if (lane == 0 && ok) ok = mbar_wait<PAIR>(afull + s, ph, abort_flag);
+                QT(1, if (lane == 0 && ok) ok = mbar_wait(xfull + s, ph, abort_flag))
+                QT(2, if (PAIR && lane == 0 && ok) ok = mbar_wait(pxfull + s, ph, abort_flag))
+                QT(3, if (lane == 0 && ok) ok = mbar_wait(afull + s, ph, abort_flag))
                 __syncwarp();
-                named_arrive(1 + s);
+                QT(5, named_arrive(1 + s))
                 if (++s == STAGES) {
                     s = 0;
                     ph ^= 1;
@@ -665,6 +684,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             }
             tcount++;
         }
+        QT_END(2, lane == 0)
     } else if (warp >= 7 && warp < QMM_WATCH_WARP) {
         // ── dequantizers ─────────────────────────────────────────────────────────────────
         // Four groups of 4 warps take k-blocks in turn.  Thread = weight row = tensor-memory lane
@@ -676,6 +696,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
         uint32_t it_base = 0, wit = 0;
         bool ok = true;
+        QT_BEGIN
         // scale / bias codes of one block: [half] for 32-value halves (equal when the group is larger)
         auto load_consts = [&](const uint16_t *sc, const uint16_t *bi, const uint8_t *fsc, int kb, uint32_t (&sv)[2], uint32_t (&bv)[2]) {
 #pragma unroll
@@ -711,7 +732,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     const uint32_t s_cur[2] = {s_next[0], s_next[1]}, b_cur[2] = {b_next[0], b_next[1]};
                     if (kb + QMM_DQ_GROUPS < item.kb1) load_consts(sc, bi, fsc, kb + QMM_DQ_GROUPS, s_next, b_next);  // prefetch
                     if (!have) {
-                        ok = mbar_wait(wfull + wsi, wph, abort_flag);
+                        QT(1, ok = mbar_wait(wfull + wsi, wph, abort_flag))
                         have = true;
                     }
                     const uint8_t *wrow = ws + wsi * QMM_W_BYTES + row * 128;
@@ -767,17 +788,17 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                         }
                     }
                     const uint32_t it = it_base + (uint32_t)(kb - item.kb0), sa = it % STAGES, pha = (it / STAGES) & 1;
-                    ok = ok && mbar_wait(empty + sa, pha ^ 1, abort_flag);  // the MMAs that read this stage are done
+                    QT(2, ok = ok && mbar_wait(empty + sa, pha ^ 1, abort_flag))  // the MMAs that read this stage are done
                     if (!ok) break;
-                    tc_fence_after();
+                    QT(3, tc_fence_after();
                     tc_st32(tmem_base + lane_base + A_COL0 + sa * 32, v);
                     tc_st_wait();
                     tc_fence_before();  // the stores are ordered before the arrive the MMA thread waits on
-                    __syncwarp();
-                    if (lane == 0) {
+                    __syncwarp())
+                    QT(4, if (lane == 0) {
                         if (PAIR) mbar_arrive_leader(afull + sa);
                         else mbar_arrive(afull + sa);
-                    }
+                    })
                 }
                 // A warp none of whose blocks lay in this slab still waits for the slab before it
                 // releases it: otherwise it could run ahead and its arrival for a later slab would
@@ -788,10 +809,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             }
             it_base += (uint32_t)(item.kb1 - item.kb0);
         }
+        QT_END(3 + group, (warp & 3) == 3 && lane == 0)
     } else {
         // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
         uint32_t tcount = 0;
         bool ok = true;
+        QT_BEGIN
         for (int jj = 0; ok; jj++) {
             Item item;
             if (!qmm_item<KPS>(p, kblocks, jj, item, worker, workers)) break;
@@ -800,19 +823,44 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint32_t buf = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
             // After a wait gave up the warp keeps walking the items without touching data: the
             // named barriers of K-split tiles below must still see all four epilogue warps.
-            if (ok) ok = mbar_wait(accfull + buf, aph, abort_flag);
+            QT(1, if (ok) ok = mbar_wait(accfull + buf, aph, abort_flag))
             tc_fence_after();
             const int r = warp * 32 + lane;  // row of the tile
             const int n = ti.n0 + r;
             float gmul = 1.0f;
             if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
             if (item.parts == 1) {
+                // Thread = weight row, registers = 32 tokens, but y is [token][row]: the warp turns each
+                // 32 x 32 piece around in shared memory ([token][row], 64 bytes per token) and stores it
+                // as 16-byte pieces of 8 rows -- 4 store instructions per piece instead of 32.  Rows in
+                // whole groups of 8 (N a multiple of 8 and y aligned): otherwise element by element.
+                const bool wide = (p.N & 7) == 0 && ((uintptr_t)p.y & 15) == 0;
+                uint8_t *mine = epi_stage + warp * 2048;
+                const int t8 = lane >> 2, g8 = lane & 3;  // this lane's token (of 8 per pass) and group of 8 rows
 #pragma unroll 1
                 for (int c = 0; c < BT / 32 && ok; c++) {
                     uint32_t v[32];
                     tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
                     tc_ld_wait();
-                    if (n < p.N) {
+                    if (wide) {
+                        if (ti.tok0 + c * 32 >= ti.tok_end) continue;  // (the whole warp: nothing of this piece is stored)
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            float f = __uint_as_float(v[j]);
+                            if (MODE != 0) f *= gmul;
+                            *reinterpret_cast<uint16_t *>(mine + j * 64 + lane * 2) = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                        }
+                        __syncwarp();
+                        const int ng = ti.n0 + warp * 32 + g8 * 8;
+                        uint16_t *dst = p.y + (size_t)(ti.tok0 + c * 32 + t8) * p.N + ng;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint4 q = *reinterpret_cast<const uint4 *>(mine + (i * 8 + t8) * 64 + g8 * 16);
+                            if (ng < p.N && ti.tok0 + c * 32 + i * 8 + t8 < ti.tok_end)
+                                *reinterpret_cast<uint4 *>(dst + (size_t)(i * 8) * p.N) = q;
+                        }
+                        __syncwarp();  // the piece has been read before the next one overwrites it
+                    } else if (n < p.N) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
                             const int tok = ti.tok0 + c * 32 + j;
@@ -867,6 +915,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             }
             tcount++;
         }
+        QT_END(7, warp == 0 && lane == 0)
     }
 
     // ── teardown ────────────────────────────────────────────────────────────────────────
@@ -1001,9 +1050,11 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     constexpr uint32_t X_BYTES = QmmTmem<BT, PAIR>::XT * QMM_BK * 2;
     // one ring: activation stages in shared memory, weight stages in tensor memory
     constexpr int STAGES = QmmTmem<BT, PAIR>::STAGES;
-    static_assert(1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1) <= 227 * 1024, "not enough shared memory for the pipeline");
-    // alignment slack, activation stages, packed-weight slabs, 1 KB of barriers and flags, the grouped products' tables
-    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + 8 * (QMM_MAX_TABLE_EXPERTS + 1);
+    static_assert(8 * (QMM_MAX_TABLE_EXPERTS + 1) <= QMM_TABLE_BYTES, "the tables' area");
+    // alignment slack, activation stages, packed-weight slabs, 1 KB of barriers and flags, the grouped products' tables,
+    // the epilogue's staging area
+    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + QMM_TABLE_BYTES + QMM_EPI_STAGE_BYTES;
+    static_assert(smem <= 227 * 1024, "not enough shared memory for the pipeline");
     auto kernel = qmm_kernel<BITS, BT, STAGES, MODE, PAIR>;
     // the opt-in to this much dynamic shared memory is a per-device attribute of the instantiation
     static bool configured[64] = {};
@@ -1125,8 +1176,10 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
     if (p.offsets) bt = per > 170 ? 256 : per > 128 ? 192 : per > 85 ? 192 : per > 42 ? 128 : per > 21 ? 64 : 32;
     // Pairs of blocks on tiles of 256 weight rows: ungrouped products of 256-token tiles whose rows
     // split evenly, with enough tiles to occupy the pairs.
-    static const bool no_pairs = getenv("NUVEC_QMM_NO_PAIRS") != nullptr;
-    const bool pair = !no_pairs && !p.offsets && bt == 256 && p.N % (2 * QMM_BN) == 0 &&
+    // Off unless NUVEC_QMM_PAIRS is set: measured 10-15 % slower than single blocks (the pair's
+    // cross-block arrivals and its third wait per k-block cost more than the halved operand traffic gains).
+    static const bool pairs_on = getenv("NUVEC_QMM_PAIRS") != nullptr;
+    const bool pair = pairs_on && !p.offsets && bt == 256 && p.N % (2 * QMM_BN) == 0 &&
                       (p.N / (2 * QMM_BN)) * ((p.rows + bt - 1) / bt) >= dev->prop.multiProcessorCount / 2;
     const int n_tiles = pair ? (int)(p.N / (2 * QMM_BN)) : (int)((p.N + QMM_BN - 1) / QMM_BN);
     int64_t token_tiles;
@@ -1172,3 +1225,15 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
 }
 
 }  // namespace nvc
+
+#ifdef NUVEC_TIMELINE
+// Diagnostic build only: cycles per role of blocks 0 and 1 in the last launch of the tensor-core
+// kernel.  out[block][role][slot]: roles 0 activation producer, 1 MMA issuer, 2 watcher, 3-6 the
+// dequantizer groups, 7 epilogue; slot 0 the role's total, the others its waits in program order.
+extern "C" int32_t nvc_debug_qmm_timing(long long *out) {
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpyFromSymbol(out, nvc::g_qmm_timing, sizeof(long long) * 2 * nvc::QT_ROLES * nvc::QT_SLOTS) != cudaSuccess)
+        return NVC_ERR_DRIVER;
+    return NVC_OK;
+}
+#endif
