@@ -623,7 +623,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     tc_fence_after();
                     const uint32_t at = tmem_base + A_COL0 + s * 32;
                     const uint64_t bd = bd0 + (uint64_t)(s * (X_BYTES >> 4));
-#pragma unroll
+_Pragma("unroll")
                     for (int k = 0; k < QMM_BK / 16; k++) {  // 16 k-values: 8 columns of A, 32 bytes of the swizzle row of B
                         if (PAIR) tc_mma_bf16_ta_pair(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
                         else tc_mma_bf16_ta(d, at + 8 * k, bd + (uint64_t)(2 * k), idesc, kb != item.kb0 || k != 0);
@@ -840,26 +840,26 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 #pragma unroll 1
                 for (int c = 0; c < BT / 32 && ok; c++) {
                     uint32_t v[32];
-                    tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
-                    tc_ld_wait();
+                    QT(2, tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
+                    tc_ld_wait())
                     if (wide) {
                         if (ti.tok0 + c * 32 >= ti.tok_end) continue;  // (the whole warp: nothing of this piece is stored)
-#pragma unroll
+                        QT(3, _Pragma("unroll")
                         for (int j = 0; j < 32; j++) {
                             float f = __uint_as_float(v[j]);
                             if (MODE != 0) f *= gmul;
                             *reinterpret_cast<uint16_t *>(mine + j * 64 + lane * 2) = __bfloat16_as_ushort(__float2bfloat16_rn(f));
                         }
-                        __syncwarp();
+                        __syncwarp())
                         const int ng = ti.n0 + warp * 32 + g8 * 8;
                         uint16_t *dst = p.y + (size_t)(ti.tok0 + c * 32 + t8) * p.N + ng;
-#pragma unroll
+                        QT(4, _Pragma("unroll")
                         for (int i = 0; i < 4; i++) {
                             const uint4 q = *reinterpret_cast<const uint4 *>(mine + (i * 8 + t8) * 64 + g8 * 16);
                             if (ng < p.N && ti.tok0 + c * 32 + i * 8 + t8 < ti.tok_end)
                                 *reinterpret_cast<uint4 *>(dst + (size_t)(i * 8) * p.N) = q;
                         }
-                        __syncwarp();  // the piece has been read before the next one overwrites it
+                        __syncwarp())  // the piece has been read before the next one overwrites it
                     } else if (n < p.N) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {

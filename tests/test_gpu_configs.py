@@ -204,3 +204,19 @@ def test_gather_indices_past_the_end_select_the_last_batch(be):
     want = oracle.gather_qmm(xf, c, sf, bf, np.minimum(lhs, 4), np.minimum(rhs, E - 1), oracle.F32)
     got = be.gather_qmm(xf, c, sf, bf, lhs, rhs, oracle.F32, oracle.AFFINE, 64, 4, True, None, False)
     assert_product_close(got, want, oracle.F32)
+
+
+def test_block_pairs_switched_on():
+    # The tensor-core kernel's block pairs (tcgen05.mma.cta_group::2) are off by default and the
+    # switch is read once per process: the prefill and persistent-run cases of this file run again
+    # in a child process with NUVEC_QMM_PAIRS=1.
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, NUVEC_QMM_PAIRS="1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_configs.py"), "-x", "-q", "-m", "gpu",
+                          "-k", "prefill or persistent"], env=env, cwd=os.path.dirname(here), capture_output=True, text=True,
+                         timeout=1200)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert " passed" in out.stdout, out.stdout[-500:]
