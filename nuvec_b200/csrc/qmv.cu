@@ -629,9 +629,15 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     constexpr int IK = 4 * WPL * CODES;
     constexpr int XW = AREGS;  // activation words per unit (AREGS bf16 pairs)
     constexpr int QMV_STAGES = qmv_stages(WPL);
-    // copies per lane and row half: 3-word units are only 4-byte aligned and go word by word
-    constexpr int CPL = UW == 3 ? LW : WPL == 8 ? 2 : 1;
-    constexpr int CW = LW / CPL;               // words per copy
+    // 3-word units (3- and 6-bit codes): a lane's words are only 4-byte aligned, so the copies do not
+    // follow the lanes.  A stage holds the tile's 16 row pieces one after the other (ROWB bytes each, a
+    // multiple of 48), two lanes copy a row piece in 16-byte parts, and lane 4 r + t finds its LW words
+    // at r * ROWB + t * LW * 4: the lanes' words lie back to back, LW words per lane.
+    constexpr bool ROWMAJOR = UW == 3;
+    constexpr int ROWB = 4 * LW * 4;           // bytes of one row piece
+    // copies per lane and row half (other formats)
+    constexpr int CPL = WPL == 8 ? 2 : 1;
+    constexpr int CW = ROWMAJOR ? LW : LW / CPL;  // words per copy (3-word units: words per lane)
     extern __shared__ __align__(16) uint32_t smem[];
     QMV_TIMELINE_BEGIN
 
@@ -667,6 +673,11 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     uint16_t *braw = sraw + 16 * QMV_SPITCH;
     uint32_t *ring = zero + ZERO_WORDS + QMV_WARPS * (QMV_SCALE_AREA / 4) + (size_t)warp * (QMV_STAGES * 2 * 32 * LW);
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring + lane * CW);
+    // 3-word units: where this lane's copies go (row piece lane / 2, its first or second half)
+    constexpr int HB = ROWB / 2 / 16 * 16;     // where the second lane of a row piece starts: 16 (3 words) or 48 (6 words)
+    constexpr int PARTS = LW == 3 ? 1 : 3;     // 16-byte parts every lane copies; with 3 words the first lane of a
+    const bool extra_part = LW == 3 && (lane & 1) == 0;  // row piece copies one more, 32 bytes on
+    const uint32_t copy_s = (uint32_t)__cvta_generic_to_shared(ring) + (uint32_t)((lane >> 1) * ROWB + (lane & 1) * HB);
     const uint32_t sraw_s = (uint32_t)__cvta_generic_to_shared(sraw);
     float *lpart = reinterpret_cast<float *>(ring + (size_t)(QMV_WARPS - warp) * (QMV_STAGES * 2 * 32 * LW));
     uint32_t *lcount = reinterpret_cast<uint32_t *>(lpart + QMV_WARPS * 2 * 128);
@@ -751,18 +762,38 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
     int pf_wrap = ipt - it_first;    // iterations until the cursor enters the next tile
     const uint32_t *pf_a = nullptr, *pf_q = nullptr;
     auto pf_rows = [&](int it) {
+        if constexpr (ROWMAJOR) {  // one pointer: this lane's half of row piece lane / 2
+            pf_a = p.w + wb * p.w_batch_stride + (size_t)min(pf_tile * 16 + (lane >> 1), last_row) * row_words +
+                   it * (4 * LW) + (lane & 1) * (HB / 4);
+            return;
+        }
         pf_a = wbase + (size_t)min(pf_tile * 16 + r, last_row) * row_words + it * (4 * LW);
         pf_q = wbase + (size_t)min(pf_tile * 16 + r + 8, last_row) * row_words + it * (4 * LW);
+    };
+    // The 16-byte copies of a 3-word-unit iteration: destination `dst` (this lane's place in the stage),
+    // source pf_a + GOFS bytes.
+    auto copy_row_parts = [&](uint32_t dst, auto sofs_c, auto gofs_c) {
+        constexpr int SOFS = decltype(sofs_c)::value, GOFS = decltype(gofs_c)::value;
+        static_for<PARTS>([&](auto k_) {
+            constexpr int k = decltype(k_)::value;
+            cp_async_at<16, SOFS + 16 * k, GOFS + 16 * k>(dst, pf_a);
+        });
+        if (extra_part) cp_async_at<16, SOFS + 32, GOFS + 32>(dst, pf_a);
     };
     // Issues the copies of one iteration into the stage at shared address `slot` and always commits
     // one group, so the group count seen by wait_group is the same for every lane and iteration.
     auto prefetch = [&](uint32_t slot) {
         if (pf_left != 0u) {
-            static_for<CPL>([&](auto c_) {
-                constexpr int c = decltype(c_)::value;
-                cp_async_at<CW * 4, c * (32 * CW * 4), c * CW * 4>(slot, pf_a);
-                cp_async_at<CW * 4, HALF_BYTES + c * (32 * CW * 4), c * CW * 4>(slot, pf_q);
-            });
+            if constexpr (ROWMAJOR) {
+                // (`slot` is this lane's place for reading; its place for copying lies copy_s - ring_s further)
+                copy_row_parts(slot + (copy_s - ring_s), std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
+            } else {
+                static_for<CPL>([&](auto c_) {
+                    constexpr int c = decltype(c_)::value;
+                    cp_async_at<CW * 4, c * (32 * CW * 4), c * CW * 4>(slot, pf_a);
+                    cp_async_at<CW * 4, HALF_BYTES + c * (32 * CW * 4), c * CW * 4>(slot, pf_q);
+                });
+            }
             pf_a += 4 * LW;
             pf_q += 4 * LW;
             pf_left--;
@@ -896,11 +927,18 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         const uint32_t sb = FIX ? ring_s : rs;
         cp_async_wait<QMV_STAGES - 1>();  // the oldest group, this iteration's words, has landed
         uint32_t wa_[LW], wq_[LW];
-        if constexpr (UW == 3) {
-            static_for<LW>([&](auto c_) {
+        if constexpr (LW == 3) {  // lane 4 r + t: words 3 (4 r + t) .. + 2 of the half, conflict-free word by word
+            static_for<3>([&](auto c_) {
                 constexpr int c = decltype(c_)::value;
-                wa_[c] = lds32<SO + c * 128>(sb);
-                wq_[c] = lds32<SO + (int)HALF_BYTES + c * 128>(sb);
+                wa_[c] = lds32<SO + c * 4>(sb);
+                wq_[c] = lds32<SO + (int)HALF_BYTES + c * 4>(sb);
+            });
+        } else if constexpr (LW == 6 && UW == 3) {  // 24 bytes per lane: three 8-byte loads
+            static_for<3>([&](auto c_) {
+                constexpr int c = decltype(c_)::value;
+                const uint2 a = lds64<SO + c * 8>(sb), q = lds64<SO + (int)HALF_BYTES + c * 8>(sb);
+                wa_[2 * c] = a.x; wa_[2 * c + 1] = a.y;
+                wq_[2 * c] = q.x; wq_[2 * c + 1] = q.y;
             });
         } else if constexpr (WPL == 8) {
             static_for<2>([&](auto c_) {
@@ -969,7 +1007,9 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
         });
         // Refill the slot just consumed (its words are in registers and already used).
         if constexpr (FIX) {
-            if constexpr (COPY) {
+            if constexpr (COPY && ROWMAJOR) {
+                copy_row_parts(copy_s, std::integral_constant<int, SO>{}, std::integral_constant<int, J * 4 * LW * 4>{});
+            } else if constexpr (COPY) {
                 static_for<CPL>([&](auto c_) {
                     constexpr int c = decltype(c_)::value;
                     cp_async_at<CW * 4, SO + c * (32 * CW * 4), (J * 4 * LW + c * CW) * 4>(ring_s, pf_a);
@@ -1240,7 +1280,7 @@ bool qmv_affine_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, 
     int wpl = wpl_for(bits, gs, K);
     if (wpl == 0) return false;
     int64_t row_words = K * code_bits(bits) / 32;
-    const int cw = unit_words(bits) == 3 ? 1 : wpl == 8 ? 4 : wpl;  // words per asynchronous copy
+    const int cw = unit_words(bits) == 3 ? 4 : wpl == 8 ? 4 : wpl;  // words per asynchronous copy (3-word units: 16-byte parts of a row)
     if (row_words % cw != 0 || w_batch_stride % cw != 0 || ((uintptr_t)w % (4 * cw)) != 0) return false;
     if (((N + 15) / 16) * (K / (4 * wpl * codes_per_word(bits))) >= (int64_t)1 << 30) return false;  // 32-bit iteration counts
     return qmv_smem((int)M, K, bits, wpl) <= 220 * 1024;  // all activations are staged in shared memory
