@@ -76,6 +76,7 @@ constexpr uint32_t QMM_W_BYTES = 128 * 128;  // one slab: 128 rows x 128 bytes
 constexpr unsigned long long QMM_WAIT_LIMIT_NS = 2000000000ull;  // a wait gives up after two seconds
 constexpr uint32_t QMM_PARK_NS = 20000;  // how long one try_wait may keep the warp parked
 constexpr int QMM_TABLE_BYTES = 4112;        // the grouped products' tables: 2 x (512 + 1) ints, rounded up to 16 bytes
+constexpr int QMM_EPI_STAGE_BYTES = 4 * 2048;  // epilogue: 32 tokens x 32 weight rows of bfloat16 per warp
 
 struct QmmKernelParams {
     const uint16_t *scales, *biases;  // bfloat16 [weight rows, K / gs]
@@ -450,17 +451,12 @@ template <int BT, bool PAIR = false> struct QmmTmem {
     // leave 128 columns for the weight ring; the widest tile keeps a single one.
     static constexpr int ACC_BUFS = 2 * BT + 128 <= 512 ? 2 : 1;
     static constexpr int XT = PAIR ? BT / 2 : BT;  // token rows of a stage in this block's shared memory
-    // With a single accumulator the MMAs of the next tile wait for the epilogue, so the dequantizer
-    // warps help to drain it (each warp reaches the tensor-memory lanes of its rank in the warpgroup).
-    static constexpr bool HELP = ACC_BUFS == 1;
-    static constexpr int DRAIN_WARPS = HELP ? QMM_EPI_WARPS + QMM_DQ_WARPS : QMM_EPI_WARPS;
-    static constexpr int EPI_BYTES = DRAIN_WARPS * 2048;  // a staging piece of 32 tokens x 32 rows of bfloat16 per draining warp
     static constexpr int ACC_COLS = ACC_BUFS * BT;
     static constexpr int A_COL0 = ACC_COLS;
     // ring depth: what the tensor-memory columns and the shared memory (activation stages beside
     // two packed-weight slabs) both allow, at most 8
     static constexpr int BY_TMEM = (512 - ACC_COLS) / 32;
-    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - EPI_BYTES - 2 * 128 * 128) / (XT * 64 * 2);
+    static constexpr int BY_SMEM = (227 * 1024 - 2048 - 8192 - QMM_EPI_STAGE_BYTES - 2 * 128 * 128) / (XT * 64 * 2);
     static constexpr int FIT = BY_TMEM < BY_SMEM ? (BY_TMEM < 8 ? BY_TMEM : 8) : (BY_SMEM < 8 ? BY_SMEM : 8);
     // a multiple of the dequantizer groups, so that a stage is always refilled by the same group
     static constexpr int STAGES = FIT / QMM_DQ_GROUPS * QMM_DQ_GROUPS;
@@ -478,8 +474,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     constexpr int A_COL0 = Ring::A_COL0, ACC_BUFS = Ring::ACC_BUFS;
     static_assert(STAGES == Ring::STAGES, "activation stages in shared memory and weight stages in tensor memory form one ring");
     static_assert(!PAIR || ACC_BUFS == 1, "a pair keeps one accumulator");
-    constexpr bool HELP = Ring::HELP;
-    constexpr int DRAIN_STRIDE = HELP ? 1 + QMM_DQ_GROUPS : 1;  // warps that share a quarter's pieces
     // A pair works as one: both blocks walk the same items; `half` is the block's rank in the pair
     // (its 128 of the tile's 256 weight rows, its half of the tile's tokens), -1 without pairs.
     const int half = PAIR ? (int)pair_rank() : -1;
@@ -522,7 +516,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(accfull + s, 1);
-            mbar_init(accempty + s, (PAIR ? 2 : 1) * Ring::DRAIN_WARPS);
+            mbar_init(accempty + s, (PAIR ? 2 : 1) * QMM_EPI_WARPS);
         }
         *abort_flag = 0;
         *last_flag = 0;
@@ -561,57 +555,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         gt.off = table;
         gt.tiles = tiles;
     }
-
-    // One 32-token piece of a warp's 32 rows of the accumulator, out of tensor memory and into y.
-    // Thread = weight row, registers = 32 tokens, but y is [token][row]: the warp turns the piece
-    // around in shared memory ([token][row], 64 bytes per token) and stores it as 16-byte pieces of
-    // 8 rows -- 4 store instructions per piece instead of 32.  Rows in whole groups of 8 (N a
-    // multiple of 8 and y aligned): otherwise element by element.  `quarter`: the warp's rank in
-    // its warpgroup (the tensor-memory lanes it reaches), `slot`: its staging piece.
-    const bool y_wide = (p.N & 7) == 0 && ((uintptr_t)p.y & 15) == 0;
-    auto drain_piece = [&](int quarter, int slot, uint32_t buf, int c, const TileInfo &ti, float gmul) {
-        uint32_t v[32];
-        tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BT + c * 32, v);
-        tc_ld_wait();
-        if (y_wide) {
-            if (ti.tok0 + c * 32 >= ti.tok_end) return;  // (the whole warp: nothing of this piece is stored)
-            uint8_t *mine = epi_stage + slot * 2048;
-            const int t8 = lane >> 2, g8 = lane & 3;  // this lane's token (of 8 per pass) and group of 8 rows
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                float f = __uint_as_float(v[j]);
-                if (MODE != 0) f *= gmul;
-                *reinterpret_cast<uint16_t *>(mine + j * 64 + lane * 2) = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-            }
-            __syncwarp();
-            const int ng = ti.n0 + quarter * 32 + g8 * 8;
-            uint16_t *dst = p.y + (size_t)(ti.tok0 + c * 32 + t8) * p.N + ng;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint4 q = *reinterpret_cast<const uint4 *>(mine + (i * 8 + t8) * 64 + g8 * 16);
-                if (ng < p.N && ti.tok0 + c * 32 + i * 8 + t8 < ti.tok_end)
-                    *reinterpret_cast<uint4 *>(dst + (size_t)(i * 8) * p.N) = q;
-            }
-            __syncwarp();  // the piece has been read before the next one overwrites it
-        } else {
-            const int n = ti.n0 + quarter * 32 + lane;
-            if (n < p.N) {
-#pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const int tok = ti.tok0 + c * 32 + j;
-                    if (tok < ti.tok_end) {
-                        float f = __uint_as_float(v[j]);
-                        if (MODE != 0) f *= gmul;
-                        p.y[(size_t)tok * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-                    }
-                }
-            }
-        }
-    };
-    auto tile_gmul = [&](const TileInfo &ti) {
-        if (MODE != 0 && p.global) return (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
-        return 1.0f;
-    };
 
     if (warp == 4) {
         // ── TMA producer, activations: one 64-k x BT tile per stage ─────────────────────────
@@ -754,36 +697,6 @@ _Pragma("unroll")
         uint32_t it_base = 0, wit = 0;
         bool ok = true;
         QT_BEGIN
-        // Helping to drain the single accumulator: when this warp has finished a tile's blocks it goes
-        // on to its first block of the next tile (so the MMAs can start as soon as the accumulator is
-        // free), then takes its share of the finished tile's pieces and arrives on `accempty`, which
-        // counts every draining warp.  A tile cut along K is drained by the epilogue warps alone;
-        // this warp then only arrives.
-        // (the owed tile's coordinates wait in shared memory, 16 bytes per warp behind the barriers, so
-        // that they take no registers from the dequantization; the accumulator is always number 0 here)
-        uint32_t tiles_seen = 0;  // bit 31: a share is owed, bit 30: the owed tile is whole (not one part of a K split)
-        int *owed_info = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(bars) + 512) + (warp - 7) * 4;
-        auto settle = [&]() {
-            if (!HELP || !(tiles_seen & 0x80000000u)) return;
-            if (tiles_seen & 0x40000000u) {
-                const uint32_t phase = ((tiles_seen & 0x3FFFFFFFu) - 1u) & 1u;
-                QT(5, if (ok) ok = mbar_wait(accfull, phase, abort_flag))
-                tc_fence_after();
-                TileInfo ot;
-                ot.n0 = owed_info[0]; ot.tok0 = owed_info[1]; ot.tok_end = owed_info[2]; ot.expert = owed_info[3];
-                ot.wrow0 = 0;
-                const float gmul = tile_gmul(ot);
-                for (int c = 1 + group; c < BT / 32 && ok; c += DRAIN_STRIDE)
-                    drain_piece(warp & 3, QMM_EPI_WARPS + (warp - 7), 0u, c, ot, gmul);
-                tc_fence_before();
-            }
-            tiles_seen &= 0x3FFFFFFFu;
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR) mbar_arrive_leader(accempty);
-                else mbar_arrive(accempty);
-            }
-        };
         // scale / bias codes of one block: [half] for 32-value halves (equal when the group is larger)
         auto load_consts = [&](const uint16_t *sc, const uint16_t *bi, const uint8_t *fsc, int kb, uint32_t (&sv)[2], uint32_t (&bv)[2]) {
 #pragma unroll
@@ -886,7 +799,6 @@ _Pragma("unroll")
                         if (PAIR) mbar_arrive_leader(afull + sa);
                         else mbar_arrive(afull + sa);
                     })
-                    settle();  // (the previous tile's share, after this tile's first block is on its way)
                 }
                 // A warp none of whose blocks lay in this slab still waits for the slab before it
                 // releases it: otherwise it could run ahead and its arrival for a later slab would
@@ -896,16 +808,7 @@ _Pragma("unroll")
                 if (lane == 0) mbar_arrive(wempty + wsi);
             }
             it_base += (uint32_t)(item.kb1 - item.kb0);
-            if (HELP) {
-                settle();  // (no block of this tile was this warp's)
-                if (lane == 0) {
-                    owed_info[0] = ti.n0; owed_info[1] = ti.tok0; owed_info[2] = ti.tok_end; owed_info[3] = ti.expert;
-                }
-                __syncwarp();
-                tiles_seen = (tiles_seen + 1u) | 0x80000000u | (item.parts == 1 ? 0x40000000u : 0u);
-            }
         }
-        settle();
         QT_END(3 + group, (warp & 3) == 3 && lane == 0)
     } else {
         // ── epilogue: warp q owns tensor-memory lanes 32q .. 32q+31 = weight rows n0 + 32q + lane ──
@@ -924,12 +827,50 @@ _Pragma("unroll")
             tc_fence_after();
             const int r = warp * 32 + lane;  // row of the tile
             const int n = ti.n0 + r;
-            const float gmul = tile_gmul(ti);
+            float gmul = 1.0f;
+            if (MODE != 0 && p.global) gmul = (p.expert_global ? p.global[ti.expert] : p.global[0]) / (448.0f * 6.0f);
             if (item.parts == 1) {
-                // (with a single accumulator the dequantizer warps of this quarter take the other pieces)
+                // Thread = weight row, registers = 32 tokens, but y is [token][row]: the warp turns each
+                // 32 x 32 piece around in shared memory ([token][row], 64 bytes per token) and stores it
+                // as 16-byte pieces of 8 rows -- 4 store instructions per piece instead of 32.  Rows in
+                // whole groups of 8 (N a multiple of 8 and y aligned): otherwise element by element.
+                const bool wide = (p.N & 7) == 0 && ((uintptr_t)p.y & 15) == 0;
+                uint8_t *mine = epi_stage + warp * 2048;
+                const int t8 = lane >> 2, g8 = lane & 3;  // this lane's token (of 8 per pass) and group of 8 rows
 #pragma unroll 1
-                for (int c = 0; c < BT / 32 && ok; c += DRAIN_STRIDE) {
-                    QT(2, drain_piece(warp, warp, buf, c, ti, gmul))
+                for (int c = 0; c < BT / 32 && ok; c++) {
+                    uint32_t v[32];
+                    QT(2, tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BT + c * 32, v);
+                    tc_ld_wait())
+                    if (wide) {
+                        if (ti.tok0 + c * 32 >= ti.tok_end) continue;  // (the whole warp: nothing of this piece is stored)
+                        QT(3, _Pragma("unroll")
+                        for (int j = 0; j < 32; j++) {
+                            float f = __uint_as_float(v[j]);
+                            if (MODE != 0) f *= gmul;
+                            *reinterpret_cast<uint16_t *>(mine + j * 64 + lane * 2) = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                        }
+                        __syncwarp())
+                        const int ng = ti.n0 + warp * 32 + g8 * 8;
+                        uint16_t *dst = p.y + (size_t)(ti.tok0 + c * 32 + t8) * p.N + ng;
+                        QT(4, _Pragma("unroll")
+                        for (int i = 0; i < 4; i++) {
+                            const uint4 q = *reinterpret_cast<const uint4 *>(mine + (i * 8 + t8) * 64 + g8 * 16);
+                            if (ng < p.N && ti.tok0 + c * 32 + i * 8 + t8 < ti.tok_end)
+                                *reinterpret_cast<uint4 *>(dst + (size_t)(i * 8) * p.N) = q;
+                        }
+                        __syncwarp())  // the piece has been read before the next one overwrites it
+                    } else if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int tok = ti.tok0 + c * 32 + j;
+                            if (tok < ti.tok_end) {
+                                float f = __uint_as_float(v[j]);
+                                if (MODE != 0) f *= gmul;
+                                p.y[(size_t)tok * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                            }
+                        }
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -1112,7 +1053,7 @@ static int32_t launch_cfg(nvc_device *dev, const CUtensorMap &mx, const CUtensor
     static_assert(8 * (QMM_MAX_TABLE_EXPERTS + 1) <= QMM_TABLE_BYTES, "the tables' area");
     // alignment slack, activation stages, packed-weight slabs, 1 KB of barriers and flags, the grouped products' tables,
     // the epilogue's staging area
-    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + QMM_TABLE_BYTES + QmmTmem<BT, PAIR>::EPI_BYTES;
+    constexpr size_t smem = 1024 + STAGES * X_BYTES + QMM_W_STAGES * QMM_W_BYTES + 1024 + QMM_TABLE_BYTES + QMM_EPI_STAGE_BYTES;
     static_assert(smem <= 227 * 1024, "not enough shared memory for the pipeline");
     auto kernel = qmm_kernel<BITS, BT, STAGES, MODE, PAIR>;
     // the opt-in to this much dynamic shared memory is a per-device attribute of the instantiation
