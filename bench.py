@@ -816,6 +816,53 @@ MOE_CONFIGS = [
 ]
 
 
+def moe_glue_rows(nv, dev):
+    """The layer's glue around the expert products at the same configurations (one GPU): router top-k,
+    the sort's bookkeeping, the two row gathers, the experts' bias, the weighted sum.  Device time per
+    call (CUDA events over a recorded run of 20 calls) and the bytes each call has to move."""
+    rng = np.random.default_rng(3)
+    out = []
+    for cname, E, topk, tokens, projs, _ in MOE_CONFIGS[:2]:
+        D = projs[0][2]  # the model width: K of the first projection
+        T = tokens[1]
+        probs = rng.random((T, E), dtype=np.float32)
+        probs /= probs.sum(-1, keepdims=True)
+        p = dev.array(nv.f32_to_bf16(probs), nv.BF16)
+        idx, scores = nv.moe_route(p, topk, True)
+        order, restore, toks, srt, offsets = nv.moe_sort(idx, E)
+        x = dev.array(nv.f32_to_bf16(rng.standard_normal((T, D), dtype=np.float32)), nv.BF16)
+        rows = nv.take_rows(x, toks)
+        bias = dev.array(nv.f32_to_bf16(rng.standard_normal((E, D), dtype=np.float32)), nv.BF16)
+        y4 = dev.array(nv.f32_to_bf16(rng.standard_normal((T, topk, D), dtype=np.float32)), nv.BF16)
+        calls = [
+            ("moe_route", lambda: nv.moe_route(p, topk, True), T * E * 2 + T * topk * 6),
+            ("moe_sort", lambda: nv.moe_sort(idx, E), T * topk * 4 * 5 + E * 4),
+            ("take_rows (activations by sorted pair)", lambda: nv.take_rows(x, toks), T * topk * D * 2 * 2),
+            ("expert_bias_add", lambda: nv.expert_bias_add(rows, bias, srt), T * topk * D * 2 * 3),
+            ("take_rows (results back into pair order)", lambda: nv.take_rows(rows, restore), T * topk * D * 2 * 2),
+            ("weighted_sum", lambda: nv.weighted_sum(y4, scores), T * topk * D * 2 + T * D * 2 + T * topk * 2),
+        ]
+        for name, call, nbytes in calls:
+            call()
+            dev.synchronize()
+
+            def run():
+                for _ in range(20):
+                    call()
+            g = dev.record(run)
+            g.launch()
+            dev.synchronize()
+            e0, e1 = dev.event(), dev.event()
+            e0.record()
+            for _ in range(3):
+                g.launch()
+            e1.record()
+            e1.synchronize()
+            us = e0.elapsed_ms(e1) * 1e3 / 60
+            out.append({"config": cname, "tokens": T, "kernel": name, "us": us, "GB/s": nbytes / us / 1e3})
+    return out
+
+
 def moe_bench(args, nv, _ffi, shard, dev, dist, rank, world, peaks):
     """Every rank owns experts [r E/g, (r+1) E/g) and, the gathered rows being sorted by expert, a
     contiguous slice of them (from the sorted offsets); it multiplies that slice with its own experts
@@ -943,9 +990,10 @@ def moe_bench(args, nv, _ffi, shard, dev, dist, rank, world, peaks):
                                  "rows_per_rank": [b - a for a, b in bounds], "us_per_product": us,
                                  "weight_GB/s": wbytes / us / 1e3, "TFLOP/s": flops / us / 1e6, "check": check,
                                  "includes": "gather_qmm on the rank's row slice" + (" + padded ncclAllGather of the row slices" if world > 1 else "")})
+    glue = moe_glue_rows(nv, dev) if world == 1 else None
     if rank == 0:
         print(json.dumps({"workload": "moe", "metric": "gather_qmm, expert-sharded", "n_gpus": world, "data": "synthetic",
-                          "scaling": "strong", "rows": rows_out, "peaks": peaks}), flush=True)
+                          "scaling": "strong", "rows": rows_out, "glue": glue, "peaks": peaks}), flush=True)
     dev.synchronize()
     if world > 1:
         dist.barrier()

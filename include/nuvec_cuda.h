@@ -215,6 +215,29 @@ int32_t nvc_moe_route(nvc_device *dev, int32_t dtype, const void *probs, int64_t
  * float64 in order and rounded once, as the reference's CPU composition does. */
 int32_t nvc_weighted_sum(nvc_device *dev, int32_t dtype, const void *x, const void *w, int64_t rows,
                          int64_t k, int64_t d, void *out);
+/* The bias of SwitchProjection::forward (crates/nuvec-lm/src/model.rs:2139-2143: `y.add(bias.take(indices, 0))`
+ * after gather_qmm): y[r, :] += bias[indices[r], :] in place, for y [rows, n] and bias [experts, n] of one
+ * float dtype and uint32 indices [rows]; float32 arithmetic and one rounding for the halves; an index past
+ * the end takes the last expert's bias, as `take` clamps (crates/nuvec-core/src/kernels.rs:120-133). */
+int32_t nvc_expert_bias_add(nvc_device *dev, int32_t dtype, void *y, const void *bias, const uint32_t *indices,
+                            int64_t rows, int64_t n, int64_t experts);
+
+/* The bookkeeping of SwitchGlu::forward for many rows (crates/nuvec-lm/src/model.rs:2199-2210), all uint32 [pairs]:
+ *   out_order    the stable ascending argsort of the flattened expert indices (pairs = tokens x k;
+ *                crates/nuvec-core/src/kernels.rs:231-266),
+ *   out_restore  its inverse (the argsort of out_order): where each pair went,
+ *   out_tokens   each sorted pair's token, out_order / k (may be NULL),
+ *   out_sorted   each sorted pair's expert (may be NULL),
+ *   out_offsets  int32 [experts]: the experts' first rows, what nvc_sorted_offsets gives for out_sorted (may be NULL).
+ * Indices must be smaller than `experts` (at most 1024). */
+int32_t nvc_moe_sort(nvc_device *dev, const uint32_t *indices, int64_t pairs, int64_t k, int64_t experts,
+                     uint32_t *out_order, uint32_t *out_restore, uint32_t *out_tokens, uint32_t *out_sorted,
+                     int32_t *out_offsets);
+/* take(src, indices, 0) of whole rows (the activations by token before the experts, the results back into
+ * pair order after them): out[i, :] = src[indices[i], :] for rows of row_bytes bytes; an index past the
+ * end takes the last row (kernels.rs:120-133). */
+int32_t nvc_take_rows(nvc_device *dev, const void *src, int64_t src_rows, int64_t row_bytes, const uint32_t *indices,
+                      int64_t n, void *out);
 
 /* The same product with HOST operands for the activations and the result: copies x in,
  * multiplies, copies y out and waits.  This is what an evaluator whose arrays live in host

@@ -98,6 +98,7 @@ struct nvc_device {
     std::vector<unsigned char> batch_key;
     size_t batch_at = 0;
     cudaGraphExec_t batch_exec = nullptr;
+    bool batch_norecord = false;  // this list failed to record once: it runs unrecorded
     uint64_t batch_kernels = 0;
     std::vector<PendingResult> batch_results;
 };

@@ -10,7 +10,17 @@
 //               float64 over 8 lanes combined by a fixed tree, rounded to the array's type, the
 //               divide element-wise in that type (float32 arithmetic for the halves);
 //   weighted_sum  the products x * w rounded to the array's type, summed over k in float64 in
-//               order, rounded once.
+//               order, rounded once;
+//   moe_sort    SwitchGlu::forward's bookkeeping for many rows (crates/nuvec-lm/src/model.rs:2199-2210): the
+//               stable ascending argsort of the flattened expert indices (kernels.rs:231-266), its inverse
+//               (the argsort of the argsort), each sorted pair's token (pair / k) and expert, and the
+//               experts' first rows (sorted_offsets); integers throughout;
+//   take_rows   `take(.., 0)` of whole rows (the activations by token, the results back into pair order),
+//               indices past the end clamped (kernels.rs:120-133);
+//   expert_bias_add  SwitchProjection::forward's `y.add(bias.take(indices, 0))`
+//               (crates/nuvec-lm/src/model.rs:2139-2143): every gathered row plus its expert's bias,
+//               float32 arithmetic for the halves, one rounding; an index past the end selects the
+//               last expert (kernels.rs:120-133).
 #include "common.cuh"
 
 namespace nvc {
@@ -133,6 +143,99 @@ extern "C" int32_t nvc_moe_route(nvc_device *dev, int32_t dtype, const void *pro
     return check_launch(dev, "moe_route_kernel");
 }
 
+// Stable sort of `pairs` expert indices by one block.  A histogram and its exclusive scan give every
+// expert its first place.  Then the pairs are taken 1024 at a time, one per thread: the lanes of a warp
+// that hold the same expert rank themselves (__match_any_sync) and leave their number in a
+// [warp][expert] table; a pair's place is its expert's next place, plus the table's entries of the
+// warps before its own, plus its rank.  Warps and lanes follow the pairs' order, so an expert's pairs
+// keep theirs: the reference's stable sort.  At most MOE_ROUTE_MAX experts.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const uint32_t *__restrict__ indices, int64_t pairs, uint32_t k, uint32_t experts,
+                                                        uint32_t *__restrict__ order, uint32_t *__restrict__ restore,
+                                                        uint32_t *__restrict__ tokens, uint32_t *__restrict__ sorted,
+                                                        int32_t *__restrict__ offsets) {
+    __shared__ uint32_t next[MOE_ROUTE_MAX];          // expert -> its next place
+    __shared__ uint8_t in_warp[32 * MOE_ROUTE_MAX];   // [warp][expert] (pitch `experts`): the expert's pairs among the warp's 32
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t c = tid; c < experts; c += 1024u) next[c] = 0u;
+    __syncthreads();
+    for (int64_t i = tid; i < pairs; i += 1024) atomicAdd(&next[min(indices[i], experts - 1u)], 1u);
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t at = 0;
+        for (uint32_t c = 0; c < experts; c++) {
+            const uint32_t n = next[c];
+            next[c] = at;
+            if (offsets) offsets[c] = (int32_t)at;
+            at += n;
+        }
+    }
+    for (int64_t base = 0; base < pairs; base += 1024) {
+        for (uint32_t c = tid; c < 32u * experts; c += 1024u) in_warp[c] = 0;
+        __syncthreads();  // (also: the scan above, the previous round's update of `next`)
+        const int64_t i = base + tid;
+        const bool have = i < pairs;
+        const uint32_t e = have ? min(indices[i], experts - 1u) : 0xFFFFFFFFu;
+        const uint32_t peers = __match_any_sync(0xFFFFFFFFu, e);
+        const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+        if (have && before == 0u) in_warp[warp * experts + e] = (uint8_t)__popc(peers);
+        __syncthreads();
+        if (have) {
+            uint32_t pos = next[e] + before;
+            for (uint32_t w = 0; w < warp; w++) pos += in_warp[w * experts + e];
+            order[pos] = (uint32_t)i;
+            restore[i] = pos;
+            if (tokens) tokens[pos] = (uint32_t)(i / k);
+            if (sorted) sorted[pos] = e;
+        }
+        __syncthreads();
+        for (uint32_t c = tid; c < experts; c += 1024u) {
+            uint32_t total = 0;
+            for (uint32_t w = 0; w < 32u; w++) total += in_warp[w * experts + c];
+            next[c] += total;
+        }
+        __syncthreads();
+    }
+}
+
+// out[i, :] = src[min(idx[i], src_rows - 1), :], rows of row_bytes bytes; 16-byte pieces when everything is aligned.
+__global__ void __launch_bounds__(256) take_rows_kernel(const uint8_t *__restrict__ src, int64_t src_rows, int64_t row_bytes,
+                                                        const uint32_t *__restrict__ idx, uint8_t *__restrict__ out, int wide) {
+    const int64_t i = blockIdx.x;
+    const int64_t from = min((int64_t)idx[i], src_rows - 1);
+    const uint8_t *a = src + from * row_bytes;
+    uint8_t *b = out + i * row_bytes;
+    if (wide) {
+        for (int64_t c = threadIdx.x; c < row_bytes / 16; c += 256)
+            reinterpret_cast<uint4 *>(b)[c] = reinterpret_cast<const uint4 *>(a)[c];
+    } else {
+        for (int64_t c = threadIdx.x; c < row_bytes; c += 256) b[c] = a[c];
+    }
+}
+
+// y[r, c] += bias[indices[r], c]: one block per row; 16-byte pieces when the rows allow it.
+template <typename T>
+__global__ void __launch_bounds__(256) expert_bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias,
+                                                              const uint32_t *__restrict__ indices, int64_t n, uint32_t experts, int wide) {
+    const int64_t r = blockIdx.x;
+    const uint32_t e = min(indices[r], experts - 1u);
+    T *row = y + r * n;
+    const T *b = bias + (size_t)e * n;
+    constexpr int PER = 16 / sizeof(T);
+    if (wide) {
+        for (int64_t c = threadIdx.x; c < n / PER; c += 256) {
+            uint4 a = reinterpret_cast<uint4 *>(row)[c];
+            const uint4 q = reinterpret_cast<const uint4 *>(b)[c];
+            T *av = reinterpret_cast<T *>(&a);
+            const T *qv = reinterpret_cast<const T *>(&q);
+#pragma unroll
+            for (int v = 0; v < PER; v++) av[v] = Glue<T>::from_f32(Glue<T>::widen(av[v]) + Glue<T>::widen(qv[v]));
+            reinterpret_cast<uint4 *>(row)[c] = a;
+        }
+    } else {
+        for (int64_t c = threadIdx.x; c < n; c += 256) row[c] = Glue<T>::from_f32(Glue<T>::widen(row[c]) + Glue<T>::load(b, c));
+    }
+}
+
 extern "C" int32_t nvc_weighted_sum(nvc_device *dev, int32_t dtype, const void *x, const void *w, int64_t rows, int64_t k, int64_t d,
                                     void *out) {
     NVC_TRY(make_current(dev));
@@ -154,4 +257,54 @@ extern "C" int32_t nvc_weighted_sum(nvc_device *dev, int32_t dtype, const void *
                                                                                      (__nv_bfloat16 *)out, rows, (int)k, d);
     }
     return check_launch(dev, "weighted_sum_kernel");
+}
+
+extern "C" int32_t nvc_expert_bias_add(nvc_device *dev, int32_t dtype, void *y, const void *bias, const uint32_t *indices, int64_t rows,
+                                       int64_t n, int64_t experts) {
+    NVC_TRY(make_current(dev));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_INVALID_ARGUMENT, "expert_bias_add: y must be floating point (dtype %d)", dtype);
+    if (rows < 0 || n < 0 || experts < 0 || experts > 0xFFFFFFFFll) return set_error(NVC_ERR_INVALID_ARGUMENT, "expert_bias_add: invalid shape");
+    if (rows * n == 0) return NVC_OK;
+    if (experts == 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "expert_bias_add: no experts to take a bias from");
+    if (!y || !bias || !indices) return set_error(NVC_ERR_INVALID_ARGUMENT, "expert_bias_add: null operand");
+    if (rows > 0x7FFFFFFFll) return set_error(NVC_ERR_UNSUPPORTED, "expert_bias_add: %lld rows exceed the grid limit", (long long)rows);
+    const size_t item = dtype == NVC_F32 ? 4 : 2;
+    const int wide = (n * item) % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)bias % 16 == 0;
+    switch (dtype) {
+    case NVC_F32:
+        expert_bias_add_kernel<float><<<(unsigned)rows, 256, 0, dev->stream>>>((float *)y, (const float *)bias, indices, n, (uint32_t)experts, wide);
+        break;
+    case NVC_F16:
+        expert_bias_add_kernel<__half><<<(unsigned)rows, 256, 0, dev->stream>>>((__half *)y, (const __half *)bias, indices, n, (uint32_t)experts, wide);
+        break;
+    default:
+        expert_bias_add_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, dev->stream>>>((__nv_bfloat16 *)y, (const __nv_bfloat16 *)bias, indices, n,
+                                                                                     (uint32_t)experts, wide);
+    }
+    return check_launch(dev, "expert_bias_add_kernel");
+}
+
+extern "C" int32_t nvc_moe_sort(nvc_device *dev, const uint32_t *indices, int64_t pairs, int64_t k, int64_t experts, uint32_t *out_order,
+                                uint32_t *out_restore, uint32_t *out_tokens, uint32_t *out_sorted, int32_t *out_offsets) {
+    NVC_TRY(make_current(dev));
+    if (pairs < 0 || k < 1 || experts < 0 || pairs > 0x7FFFFFFFll) return set_error(NVC_ERR_INVALID_ARGUMENT, "moe_sort: invalid shape");
+    if (experts > MOE_ROUTE_MAX) return set_error(NVC_ERR_UNSUPPORTED, "moe_sort: %lld experts (at most %d)", (long long)experts, MOE_ROUTE_MAX);
+    if (pairs > 0 && experts == 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "moe_sort: pairs without experts");
+    if (pairs == 0 && experts == 0) return NVC_OK;
+    if ((pairs > 0 && (!indices || !out_order || !out_restore))) return set_error(NVC_ERR_INVALID_ARGUMENT, "moe_sort: null operand");
+    moe_sort_kernel<<<1, 1024, 0, dev->stream>>>(indices, pairs, (uint32_t)k, (uint32_t)experts, out_order, out_restore, out_tokens, out_sorted,
+                                                 out_offsets);
+    return check_launch(dev, "moe_sort_kernel");
+}
+
+extern "C" int32_t nvc_take_rows(nvc_device *dev, const void *src, int64_t src_rows, int64_t row_bytes, const uint32_t *indices, int64_t n,
+                                 void *out) {
+    NVC_TRY(make_current(dev));
+    if (src_rows < 0 || row_bytes < 0 || n < 0 || n > 0x7FFFFFFFll) return set_error(NVC_ERR_INVALID_ARGUMENT, "take_rows: invalid shape");
+    if (n * row_bytes == 0) return NVC_OK;
+    if (src_rows == 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "take_rows: rows taken from an empty array");
+    if (!src || !indices || !out) return set_error(NVC_ERR_INVALID_ARGUMENT, "take_rows: null operand");
+    const int wide = row_bytes % 16 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)out % 16 == 0;
+    take_rows_kernel<<<(unsigned)n, 256, 0, dev->stream>>>((const uint8_t *)src, src_rows, row_bytes, indices, (uint8_t *)out, wide);
+    return check_launch(dev, "take_rows_kernel");
 }

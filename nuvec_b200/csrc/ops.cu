@@ -335,7 +335,10 @@ extern "C" int32_t nvc_quantized_matmul_host_async(nvc_device *dev, const nvc_qu
 // itself), then the kernels follow back to back; every result is stored by its kernel into the
 // pinned block (or copied back when large) and stays pending until the synchronization.  A list
 // that does not fit the staging blocks is issued product by product.
-extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_host_product *items, size_t count) {
+// (internal) the list could not be recorded: it has been marked and the call runs once more, unrecorded
+static constexpr int32_t HOST_BATCH_AGAIN = 1;
+
+static int32_t host_batch(nvc_device *dev, const nvc_host_product *items, size_t count) {
     if (count && !items) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_matmul (host batch): null list");
     if (count == 0) return NVC_OK;
     NVC_TRY(make_current(dev));
@@ -387,7 +390,9 @@ extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_ho
     // stands for the whole list.
     const unsigned char *key = reinterpret_cast<const unsigned char *>(items);
     const size_t key_bytes = count * sizeof(nvc_host_product);
-    const bool same = dev->batch_key.size() == key_bytes && dev->batch_at == at && memcmp(dev->batch_key.data(), key, key_bytes) == 0;
+    const bool same_list = dev->batch_key.size() == key_bytes && memcmp(dev->batch_key.data(), key, key_bytes) == 0;
+    const bool same = same_list && dev->batch_at == at;
+    if (!same_list) dev->batch_norecord = false;
     if (same && dev->batch_exec) {
         NVC_CUDA(cudaGraphLaunch(dev->batch_exec, dev->stream));
         dev->launches += dev->batch_kernels;
@@ -399,7 +404,7 @@ extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_ho
         cudaGraphExecDestroy(dev->batch_exec);
         dev->batch_exec = nullptr;
     }
-    const bool record = same && dev->stream == dev->own_stream;
+    const bool record = same && !dev->batch_norecord && dev->stream == dev->own_stream;
     if (!same) {
         dev->batch_key.assign(key, key + key_bytes);
         dev->batch_at = at;
@@ -416,22 +421,20 @@ extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_ho
         dev->capturing = false;
         cudaGraph_t graph = nullptr;
         cudaError_t err = cudaStreamEndCapture(dev->stream, &graph);
-        if (rc != NVC_OK || err != cudaSuccess) {
-            if (graph) cudaGraphDestroy(graph);
-            cudaGetLastError();
-            dev->batch_key.clear();
-            std::lock_guard<std::mutex> g(dev->host_mu);
-            dev->pending.resize(pending_before);
-            return rc != NVC_OK ? rc : cuda_error("cudaStreamEndCapture", err);
+        if (rc == NVC_OK && err == cudaSuccess) {
+            err = cudaGraphInstantiate(&dev->batch_exec, graph, 0);
+            if (err != cudaSuccess) dev->batch_exec = nullptr;
         }
-        err = cudaGraphInstantiate(&dev->batch_exec, graph, 0);
-        cudaGraphDestroy(graph);
-        if (err != cudaSuccess) {
-            dev->batch_exec = nullptr;
-            dev->batch_key.clear();
+        if (graph) cudaGraphDestroy(graph);
+        if (rc != NVC_OK || err != cudaSuccess) {
+            // Something in this list does not record (a product that has to grow a scratch buffer,
+            // say).  Nothing has run: forget what was queued and let the caller run the list the
+            // plain way, now and from now on.
+            cudaGetLastError();
+            dev->batch_norecord = true;
             std::lock_guard<std::mutex> g(dev->host_mu);
             dev->pending.resize(pending_before);
-            return cuda_error("cudaGraphInstantiate", err);
+            return HOST_BATCH_AGAIN;
         }
         dev->batch_kernels = dev->captured;
         {
@@ -467,4 +470,10 @@ extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_ho
         yo += pad(yb);
     }
     return finish(NVC_OK);
+}
+
+extern "C" int32_t nvc_quantized_matmul_host_batch(nvc_device *dev, const nvc_host_product *items, size_t count) {
+    int32_t rc = host_batch(dev, items, count);
+    if (rc == HOST_BATCH_AGAIN) rc = host_batch(dev, items, count);
+    return rc;
 }

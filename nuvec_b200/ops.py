@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -553,6 +553,50 @@ def weighted_sum(x: Array, w: Array) -> Array:
     rows = x.size // (k * d) if k * d else 0
     out = x.dev.empty(tuple(x.shape[:-2]) + (d,), x.dtype)
     _check(_ffi.lib().nvc_weighted_sum(x.dev._h, x.dtype, x.ptr, w.ptr, rows, k, d, out.ptr))
+    return out
+
+
+def expert_bias_add(y: Array, bias: Array, indices: Array) -> Array:
+    """The bias of SwitchProjection::forward (crates/nuvec-lm/src/model.rs:2139-2143): y [rows, ..., n] plus
+    bias[indices] ([experts, n], uint32 indices [rows]), in place; returns y."""
+    if bias.ndim != 2 or y.ndim < 2 or y.shape[-1] != bias.shape[1]:
+        raise InvalidArgument(f"expert_bias_add: y [..., n] and bias [experts, n] expected, got {list(y.shape)} and {list(bias.shape)}")
+    if y.dtype not in _FLOATS or bias.dtype != y.dtype:
+        raise UnsupportedError("expert_bias_add: y and bias must share one floating-point dtype")
+    n = y.shape[-1]
+    rows = y.size // n if n else 0
+    if indices.dtype != U32 or indices.size != rows:
+        raise InvalidArgument(f"expert_bias_add: {rows} uint32 indices expected, got {indices.size}")
+    _check(_ffi.lib().nvc_expert_bias_add(y.dev._h, y.dtype, y.ptr, bias.ptr, indices.ptr, rows, n, bias.shape[0]))
+    return y
+
+
+def moe_sort(indices: Array, experts: int):
+    """The bookkeeping of SwitchGlu::forward (crates/nuvec-lm/src/model.rs:2199-2210) for expert indices
+    [..., k] (uint32): (order, restore, tokens, sorted, offsets) -- the stable argsort of the flattened
+    indices, its inverse, each sorted pair's token and expert (uint32 [pairs]) and the experts' first
+    rows (int32 [experts])."""
+    if indices.dtype != U32 or indices.ndim < 1:
+        raise InvalidArgument("moe_sort: uint32 indices [..., k] expected")
+    k = indices.shape[-1]
+    pairs = indices.size
+    if k < 1:
+        raise InvalidArgument("moe_sort: k must be at least 1")
+    dev = indices.dev
+    order, restore, tokens, srt = (dev.empty((pairs,), U32) for _ in range(4))
+    offsets = dev.empty((experts,), I32)
+    _check(_ffi.lib().nvc_moe_sort(dev._h, indices.ptr, pairs, k, experts, order.ptr, restore.ptr, tokens.ptr, srt.ptr, offsets.ptr))
+    return order, restore, tokens, srt, offsets
+
+
+def take_rows(src: Array, indices: Array) -> Array:
+    """take(src, indices, 0) of whole rows: out[i] = src[indices[i]] (indices past the end take the last row)."""
+    if src.ndim < 1 or indices.dtype != U32:
+        raise InvalidArgument("take_rows: an array of rows and uint32 indices expected")
+    rows = src.shape[0]
+    row_bytes = (src.size // rows if rows else 0) * src.itemsize
+    out = src.dev.empty((indices.size,) + tuple(src.shape[1:]), src.dtype)
+    _check(_ffi.lib().nvc_take_rows(src.dev._h, src.ptr, rows, row_bytes, indices.ptr, indices.size, out.ptr))
     return out
 
 

@@ -210,6 +210,28 @@ def weighted_sum(x, w, dtype):
     return out
 
 
+def expert_bias_add(y, bias, indices, dtype):
+    """y [rows, n] + bias[indices] ([experts, n]); returns a new array."""
+    out = np.array(_c(y), copy=True)
+    bias, idx = _c(bias), _c(indices, np.uint32).reshape(-1)
+    n = out.shape[-1]
+    rows = out.size // n if n else 0
+    _check(lib().orc_expert_bias_add(dtype, _ptr(out), _ptr(bias), _ptr(idx), _sz(rows), _sz(n), _sz(bias.shape[0])))
+    return out
+
+
+def moe_sort(indices, experts):
+    """indices [..., k] -> (order, restore, tokens, sorted) uint32 [pairs] and offsets int32 [experts]."""
+    idx = _c(indices, np.uint32)
+    k = idx.shape[-1]
+    flat = idx.reshape(-1)
+    n = flat.size
+    order, restore, tokens, srt = (np.zeros(n, np.uint32) for _ in range(4))
+    offsets = np.zeros(experts, np.int32)
+    _check(lib().orc_moe_sort(_ptr(flat), _sz(n), _sz(k), _sz(experts), _ptr(order), _ptr(restore), _ptr(tokens), _ptr(srt), _ptr(offsets)))
+    return order, restore, tokens, srt, offsets
+
+
 def threads() -> int:
     return int(lib().orc_threads())
 

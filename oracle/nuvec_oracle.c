@@ -694,3 +694,45 @@ int orc_weighted_sum(int dtype, const void *x, const void *w, size_t rows, size_
         }
     return 0;
 }
+
+/* SwitchProjection::forward's bias (crates/nuvec-lm/src/model.rs:2139-2143): y + bias.take(indices, 0), in
+ * place.  Element-wise add in the array's type (kernels.rs:1191-1195: f16 / bf16 add in float32 and
+ * round); `take` clamps an index past the end to the last row (kernels.rs:120-133). */
+int orc_expert_bias_add(int dtype, void *y, const void *bias, const uint32_t *indices, size_t rows, size_t n, size_t experts) {
+    if (rows * n == 0) return 0;
+    if (experts == 0) return -1;
+    for (size_t r = 0; r < rows; r++) {
+        size_t e = indices[r] < experts ? indices[r] : experts - 1;
+        for (size_t c = 0; c < n; c++) {
+            float sum = load_f32(y, r * n + c, dtype) + load_f32(bias, e * n + c, dtype);
+            store_round(y, r * n + c, dtype, (double)sum);
+        }
+    }
+    return 0;
+}
+
+/* The bookkeeping of SwitchGlu::forward (crates/nuvec-lm/src/model.rs:2199-2210): order = argsort(flat)
+ * (stable, ascending: kernels.rs:231-266), restore = argsort(order), tokens = (pair / k).take(order),
+ * sorted = flat.take(order), offsets = sorted_offsets(sorted) (kernels.rs:875-892).  Plain insertion of
+ * every pair behind the pairs of smaller or equal experts that came before it. */
+int orc_moe_sort(const uint32_t *indices, size_t pairs, size_t k, size_t experts, uint32_t *order, uint32_t *restore,
+                 uint32_t *tokens, uint32_t *sorted, int32_t *offsets) {
+    if (k == 0) return -1;
+    size_t *next = (size_t *)calloc(experts + 1, sizeof(size_t));
+    if (!next) return -1;
+    for (size_t i = 0; i < pairs; i++) {
+        if (indices[i] >= experts) { free(next); return -1; }
+        next[indices[i] + 1]++;
+    }
+    for (size_t e = 0; e < experts; e++) next[e + 1] += next[e];
+    for (size_t e = 0; e < experts; e++) offsets[e] = (int32_t)next[e];
+    for (size_t i = 0; i < pairs; i++) {
+        size_t pos = next[indices[i]]++;
+        order[pos] = (uint32_t)i;
+        restore[i] = (uint32_t)pos;
+        tokens[pos] = (uint32_t)(i / k);
+        sorted[pos] = indices[i];
+    }
+    free(next);
+    return 0;
+}

@@ -94,6 +94,9 @@ void orc_matmul_nt_f32(const float *x, const float *w, size_t M, size_t N, size_
 int orc_moe_route(int dtype, const void *probs, size_t rows, size_t experts, size_t k, int normalize,
                   uint32_t *out_indices, void *out_scores);
 int orc_weighted_sum(int dtype, const void *x, const void *w, size_t rows, size_t k, size_t d, void *out);
+int orc_expert_bias_add(int dtype, void *y, const void *bias, const uint32_t *indices, size_t rows, size_t n, size_t experts);
+int orc_moe_sort(const uint32_t *indices, size_t pairs, size_t k, size_t experts, uint32_t *order, uint32_t *restore,
+                 uint32_t *tokens, uint32_t *sorted, int32_t *offsets);
 int orc_threads(void);
 void orc_set_threads(int n);
 

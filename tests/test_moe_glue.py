@@ -111,3 +111,87 @@ def test_cuda_weighted_sum_matches_the_oracle_bit_for_bit(dt):
         assert np.array_equal(got.view(want.dtype) if dt != "f16" else got.view(np.uint16), want), (rows, k, d)
     with pytest.raises(nv.InvalidArgument):
         nv.weighted_sum(up(x), up(w[:, :2]))
+
+
+@pytest.mark.parametrize("dt", list(DT))
+def test_oracle_expert_bias_add(dt):
+    # y + bias.take(indices, 0): the add in the array's type (float32 arithmetic, one rounding),
+    # indices past the end clamped to the last expert
+    dtype = DT[dt]
+    rng = np.random.default_rng(11)
+    for rows, n, e in [(5, 16, 4), (9, 33, 7), (1, 1, 1)]:
+        y = oracle.from_f32(rng.standard_normal((rows, n)).astype(np.float32), dtype)
+        b = oracle.from_f32(rng.standard_normal((e, n)).astype(np.float32), dtype)
+        idx = rng.integers(0, e + 2, rows).astype(np.uint32)
+        got = oracle.expert_bias_add(y, b, idx, dtype)
+        want = oracle.from_f32(oracle.to_f32(y, dtype) + oracle.to_f32(b, dtype)[np.minimum(idx, e - 1)], dtype)
+        assert np.array_equal(got.view(want.dtype), want), (rows, n, e)
+        assert np.array_equal(y.view(want.dtype), oracle.from_f32(oracle.to_f32(y, dtype), dtype).view(want.dtype))  # the input is left alone
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", list(DT))
+def test_cuda_expert_bias_add_matches_the_oracle_bit_for_bit(dt):
+    import nuvec_b200 as nv
+    dtype = DT[dt]
+    code = {"f32": nv.F32, "f16": nv.F16, "bf16": nv.BF16}[dt]
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(12)
+    up = lambda a: dev.array(a.view(np.float16) if dt == "f16" else a, code)
+    # the expert products' own shapes: 4096 gathered rows of 2880 (32 experts) and of 2048 (128 experts)
+    for rows, n, e in [(5, 16, 4), (9, 33, 7), (4096, 2880, 32), (4096, 2048, 128), (8, 1536, 128)]:
+        y = oracle.from_f32(rng.standard_normal((rows, n)).astype(np.float32), dtype)
+        b = oracle.from_f32(rng.standard_normal((e, n)).astype(np.float32), dtype)
+        idx = np.sort(rng.integers(0, e + (2 if rows < 100 else 0), rows)).astype(np.uint32)
+        want = oracle.expert_bias_add(y, b, idx, dtype)
+        got = nv.expert_bias_add(up(y), up(b), dev.array(idx, nv.U32)).to_numpy()
+        assert np.array_equal(got.view(np.uint16) if dt != "f32" else got.view(np.uint32),
+                              want.view(np.uint16) if dt != "f32" else want.view(np.uint32)), (rows, n, e)
+    with pytest.raises(nv.InvalidArgument):
+        nv.expert_bias_add(up(y), up(b[:, :5]), dev.array(idx, nv.U32))
+
+
+def expert_choices(rng, tokens, experts, k):
+    """k distinct experts per token, as a router's top-k gives them."""
+    return np.stack([rng.permutation(experts)[:k] for _ in range(tokens)]).astype(np.uint32)
+
+
+def test_oracle_moe_sort_is_the_stable_argsort_and_its_inverse():
+    rng = np.random.default_rng(21)
+    for tokens, experts, k in [(1, 8, 2), (7, 16, 4), (512, 128, 8), (1024, 32, 4), (3, 5, 5)]:
+        idx = expert_choices(rng, tokens, experts, k)
+        order, restore, toks, srt, offsets = oracle.moe_sort(idx, experts)
+        flat = idx.reshape(-1)
+        want = np.argsort(flat, kind="stable").astype(np.uint32)
+        assert np.array_equal(order, want)
+        assert np.array_equal(restore, np.argsort(want, kind="stable").astype(np.uint32))
+        assert np.array_equal(toks, want // k) and np.array_equal(srt, flat[want])
+        assert np.array_equal(offsets, oracle.sorted_offsets(srt, experts))
+    with pytest.raises(oracle.OracleError):
+        oracle.moe_sort(np.array([[9]], np.uint32), 4)
+
+
+@pytest.mark.gpu
+def test_cuda_moe_sort_and_take_rows_match_the_oracle():
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(22)
+    for tokens, experts, k in [(1, 8, 2), (7, 16, 4), (512, 128, 8), (1024, 32, 4), (3, 5, 5), (8192, 128, 8), (300, 1024, 3)]:
+        idx = expert_choices(rng, tokens, experts, k)
+        want = oracle.moe_sort(idx, experts)
+        got = nv.moe_sort(dev.array(idx, nv.U32), experts)
+        for name, g, w in zip(("order", "restore", "tokens", "sorted", "offsets"), got, want):
+            assert np.array_equal(g.to_numpy(), w), (name, tokens, experts, k)
+        # the layer's two row gathers: activations by sorted pair, results back into pair order
+        d = 96
+        x = oracle.from_f32(rng.standard_normal((tokens, d)).astype(np.float32), oracle.BF16)
+        rows = nv.take_rows(dev.array(x, nv.BF16), got[2]).to_numpy().view(np.uint16)
+        assert np.array_equal(rows, x[want[2]])
+        back = nv.take_rows(dev.array(rows, nv.BF16), got[1]).to_numpy().view(np.uint16)
+        assert np.array_equal(back, x[np.arange(tokens * k) // k])
+    # rows of a width that is no multiple of 16 bytes, and an index past the end
+    src = rng.integers(0, 255, (5, 7), dtype=np.uint8)
+    out = nv.take_rows(dev.array(src, nv.U8), dev.array(np.array([4, 0, 9, 2], np.uint32), nv.U32)).to_numpy()
+    assert np.array_equal(out, src[[4, 0, 4, 2]])
+    with pytest.raises(nv.UnsupportedError):
+        nv.moe_sort(dev.array(np.zeros((2, 2), np.uint32), nv.U32), 2000)
