@@ -834,10 +834,15 @@ def moe_glue_rows(nv, dev):
         rows = nv.take_rows(x, toks)
         bias = dev.array(nv.f32_to_bf16(rng.standard_normal((E, D), dtype=np.float32)), nv.BF16)
         y4 = dev.array(nv.f32_to_bf16(rng.standard_normal((T, topk, D), dtype=np.float32)), nv.BF16)
+        inter = projs[1][2]  # the experts' intermediate width: K of the down projection
+        gate = dev.array(nv.f32_to_bf16(rng.standard_normal((T * topk, inter), dtype=np.float32)), nv.BF16)
+        upp = dev.array(nv.f32_to_bf16(rng.standard_normal((T * topk, inter), dtype=np.float32)), nv.BF16)
+        glu = (lambda: nv.swiglu_oai(gate, upp)) if "gpt-oss" in cname else (lambda: nv.swiglu(gate, upp))
         calls = [
             ("moe_route", lambda: nv.moe_route(p, topk, True), T * E * 2 + T * topk * 6),
             ("moe_sort", lambda: nv.moe_sort(idx, E), T * topk * 4 * 5 + E * 4),
             ("take_rows (activations by sorted pair)", lambda: nv.take_rows(x, toks), T * topk * D * 2 * 2),
+            ("swiglu_oai" if "gpt-oss" in cname else "swiglu", glu, T * topk * inter * 2 * 3),
             ("expert_bias_add", lambda: nv.expert_bias_add(rows, bias, srt), T * topk * D * 2 * 3),
             ("take_rows (results back into pair order)", lambda: nv.take_rows(rows, restore), T * topk * D * 2 * 2),
             ("weighted_sum", lambda: nv.weighted_sum(y4, scores), T * topk * D * 2 + T * D * 2 + T * topk * 2),

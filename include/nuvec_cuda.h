@@ -238,6 +238,17 @@ int32_t nvc_moe_sort(nvc_device *dev, const uint32_t *indices, int64_t pairs, in
  * end takes the last row (kernels.rs:120-133). */
 int32_t nvc_take_rows(nvc_device *dev, const void *src, int64_t src_rows, int64_t row_bytes, const uint32_t *indices,
                       int64_t n, void *out);
+/* The activation between the up / gate and the down products (SwitchGlu::through,
+ * crates/nuvec-lm/src/model.rs:2160-2171): nuvec_nn::swiglu = silu(gate) * up and gpt-oss's clamped
+ * nuvec_nn::swiglu_oai = (clip(up, -limit, limit) + 1) * g * sigmoid(alpha * g) with g = min(gate, limit)
+ * (crates/nuvec-nn/src/lib.rs:513-579), over n elements of one float dtype.  The arithmetic is the reference's
+ * CPU evaluation of the compiled function -- its operations one by one, each rounded to the dtype
+ * (crates/nuvec-core/src/fused.rs:214-217), MLX's sigmoid in float32 (kernels.rs:1538-1543), alpha and limit
+ * rounded to the dtype first.  The exponential is the one step that is not an IEEE operation: where the
+ * device's and the host's differ in their last bit, a result can differ by a unit or two in the last place. */
+int32_t nvc_swiglu(nvc_device *dev, int32_t dtype, const void *gate, const void *up, int64_t n, void *out);
+int32_t nvc_swiglu_oai(nvc_device *dev, int32_t dtype, const void *gate, const void *up, float alpha, float limit,
+                       int64_t n, void *out);
 
 /* The same product with HOST operands for the activations and the result: copies x in,
  * multiplies, copies y out and waits.  This is what an evaluator whose arrays live in host

@@ -17,6 +17,12 @@
 //               experts' first rows (sorted_offsets); integers throughout;
 //   take_rows   `take(.., 0)` of whole rows (the activations by token, the results back into pair order),
 //               indices past the end clamped (kernels.rs:120-133);
+//   swiglu / swiglu_oai  the activation between the up/gate and the down products
+//               (crates/nuvec-nn/src/lib.rs:513-579; SwitchGlu::through, model.rs:2160-2171): on the CPU the
+//               compiled function is its operations one by one (crates/nuvec-core/src/fused.rs:214-217), each
+//               rounded to the array's type, the sigmoid as MLX's (kernels.rs:1538-1543) in float32.  The
+//               only step that is not an IEEE operation is the exponential: where the device's expf and the
+//               host's differ in their last bit a result can differ by a unit or two in the last place;
 //   expert_bias_add  SwitchProjection::forward's `y.add(bias.take(indices, 0))`
 //               (crates/nuvec-lm/src/model.rs:2139-2143): every gathered row plus its expert's bias,
 //               float32 arithmetic for the halves, one rounding; an index past the end selects the
@@ -212,6 +218,39 @@ __global__ void __launch_bounds__(256) take_rows_kernel(const uint8_t *__restric
     }
 }
 
+// MLX's Sigmoid in float32 (kernels.rs:1538-1543): y = 1 / (1 + exp(|x|)), then x < 0 ? y : 1 - y.
+__device__ __forceinline__ float sigmoid_f32(float x) {
+    const float a = x < 0.0f ? -x : x;
+    const float y = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(a)));
+    return x < 0.0f ? y : __fsub_rn(1.0f, y);
+}
+// minimum / maximum that propagate NaN (kernels.rs:1366-1367)
+__device__ __forceinline__ float min_nan(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7FC00000) : fminf(a, b); }
+__device__ __forceinline__ float max_nan(float a, float b) { return (a != a || b != b) ? __int_as_float(0x7FC00000) : fmaxf(a, b); }
+
+// out = silu(gate) * up, op by op: s = sigmoid(g), t = g * s, out = t * up, each rounded to T.
+// OAI form (alpha, limit already rounded to T): g = min(gate, limit), x = min(max(up, -limit), limit),
+// out = (x + 1) * (g * sigmoid(alpha * g)), each operation rounded to T.
+template <typename T, bool OAI>
+__global__ void __launch_bounds__(256) swiglu_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ out, int64_t n,
+                                                     float alpha, float limit) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    auto r = [](float v) { return Glue<T>::widen(Glue<T>::from_f32(v)); };  // one rounding to T
+    float g = Glue<T>::load(gate, i), x = Glue<T>::load(up, i);
+    if (OAI) {
+        g = min_nan(g, limit);
+        x = min_nan(max_nan(x, -limit), limit);
+        const float s = r(sigmoid_f32(r(__fmul_rn(alpha, g))));
+        const float gs = r(__fmul_rn(g, s));
+        out[i] = Glue<T>::from_f32(__fmul_rn(r(__fadd_rn(x, 1.0f)), gs));
+    } else {
+        const float s = r(sigmoid_f32(g));
+        const float t = r(__fmul_rn(g, s));
+        out[i] = Glue<T>::from_f32(__fmul_rn(t, x));
+    }
+}
+
 // y[r, c] += bias[indices[r], c]: one block per row; 16-byte pieces when the rows allow it.
 template <typename T>
 __global__ void __launch_bounds__(256) expert_bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias,
@@ -307,4 +346,40 @@ extern "C" int32_t nvc_take_rows(nvc_device *dev, const void *src, int64_t src_r
     const int wide = row_bytes % 16 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)out % 16 == 0;
     take_rows_kernel<<<(unsigned)n, 256, 0, dev->stream>>>((const uint8_t *)src, src_rows, row_bytes, indices, (uint8_t *)out, wide);
     return check_launch(dev, "take_rows_kernel");
+}
+
+template <bool OAI>
+static int32_t launch_swiglu(nvc_device *dev, const char *op, int32_t dtype, const void *gate, const void *up, int64_t n, float alpha,
+                             float limit, void *out) {
+    NVC_TRY(make_current(dev));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: operands must be floating point (dtype %d)", op, dtype);
+    if (n < 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: invalid size", op);
+    if (n == 0) return NVC_OK;
+    if (!gate || !up || !out) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: null operand", op);
+    const int64_t blocks = (n + 255) / 256;
+    if (blocks > 0x7FFFFFFFll) return set_error(NVC_ERR_UNSUPPORTED, "%s: %lld elements exceed the grid limit", op, (long long)n);
+    switch (dtype) {
+    case NVC_F32:
+        swiglu_kernel<float, OAI><<<(unsigned)blocks, 256, 0, dev->stream>>>((const float *)gate, (const float *)up, (float *)out, n, alpha, limit);
+        break;
+    case NVC_F16:
+        // (the scalars are weak: rounded to the arrays' type, crates/nuvec-nn/src/lib.rs:504-507)
+        swiglu_kernel<__half, OAI><<<(unsigned)blocks, 256, 0, dev->stream>>>((const __half *)gate, (const __half *)up, (__half *)out, n,
+                                                                             __half2float(__float2half_rn(alpha)), __half2float(__float2half_rn(limit)));
+        break;
+    default:
+        swiglu_kernel<__nv_bfloat16, OAI><<<(unsigned)blocks, 256, 0, dev->stream>>>(
+            (const __nv_bfloat16 *)gate, (const __nv_bfloat16 *)up, (__nv_bfloat16 *)out, n, __bfloat162float(__float2bfloat16_rn(alpha)),
+            __bfloat162float(__float2bfloat16_rn(limit)));
+    }
+    return check_launch(dev, "swiglu_kernel");
+}
+
+extern "C" int32_t nvc_swiglu(nvc_device *dev, int32_t dtype, const void *gate, const void *up, int64_t n, void *out) {
+    return launch_swiglu<false>(dev, "swiglu", dtype, gate, up, n, 0.0f, 0.0f, out);
+}
+
+extern "C" int32_t nvc_swiglu_oai(nvc_device *dev, int32_t dtype, const void *gate, const void *up, float alpha, float limit, int64_t n,
+                                  void *out) {
+    return launch_swiglu<true>(dev, "swiglu_oai", dtype, gate, up, n, alpha, limit, out);
 }

@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -598,6 +598,25 @@ def take_rows(src: Array, indices: Array) -> Array:
     out = src.dev.empty((indices.size,) + tuple(src.shape[1:]), src.dtype)
     _check(_ffi.lib().nvc_take_rows(src.dev._h, src.ptr, rows, row_bytes, indices.ptr, indices.size, out.ptr))
     return out
+
+
+def _glu(name, gate: Array, up: Array, call):
+    if tuple(gate.shape) != tuple(up.shape) or gate.dtype not in _FLOATS or up.dtype != gate.dtype:
+        raise InvalidArgument(f"{name}: gate and up must share one shape and one floating-point dtype")
+    out = gate.dev.empty(tuple(gate.shape), gate.dtype)
+    _check(call(out))
+    return out
+
+
+def swiglu(gate: Array, up: Array) -> Array:
+    """nuvec_nn::swiglu (crates/nuvec-nn/src/lib.rs:513): silu(gate) * up."""
+    return _glu("swiglu", gate, up, lambda out: _ffi.lib().nvc_swiglu(gate.dev._h, gate.dtype, gate.ptr, up.ptr, gate.size, out.ptr))
+
+
+def swiglu_oai(gate: Array, up: Array, alpha: float = 1.702, limit: float = 7.0) -> Array:
+    """nuvec_nn::swiglu_oai (crates/nuvec-nn/src/lib.rs:564): gpt-oss's clamped SwiGLU."""
+    return _glu("swiglu_oai", gate, up,
+                lambda out: _ffi.lib().nvc_swiglu_oai(gate.dev._h, gate.dtype, gate.ptr, up.ptr, alpha, limit, gate.size, out.ptr))
 
 
 def _promote(op: str, x: Array, q: Quantized):

@@ -232,6 +232,14 @@ def moe_sort(indices, experts):
     return order, restore, tokens, srt, offsets
 
 
+def swiglu(gate, up, dtype, oai=False, alpha=1.702, limit=7.0):
+    """silu(gate) * up, or gpt-oss's clamped form; arrays of one shape stored as `dtype`."""
+    gate, up = _c(gate), _c(up)
+    out = np.zeros(gate.shape, store_dtype(dtype))
+    _check(lib().orc_swiglu(dtype, int(oai), _ptr(gate), _ptr(up), ctypes.c_float(alpha), ctypes.c_float(limit), _sz(gate.size), _ptr(out)))
+    return out
+
+
 def threads() -> int:
     return int(lib().orc_threads())
 

@@ -736,3 +736,48 @@ int orc_moe_sort(const uint32_t *indices, size_t pairs, size_t k, size_t experts
     free(next);
     return 0;
 }
+
+/* MLX's Sigmoid as the reference computes it (crates/nuvec-core/src/kernels.rs:1538-1543), float32. */
+static float sigmoid_f32(float x) {
+    volatile float a = x < 0.0f ? -x : x;
+    volatile float e = expf(a);
+    volatile float d = 1.0f + e;
+    volatile float y = 1.0f / d;
+    return x < 0.0f ? y : 1.0f - y;
+}
+static float round_to(float v, int dtype) {
+    uint32_t cell[1];
+    store_round(cell, 0, dtype, (double)v);
+    return load_f32(cell, 0, dtype);
+}
+static float min_nan(float a, float b) { return (a != a || b != b) ? NAN : (a < b ? a : b); }
+static float max_nan(float a, float b) { return (a != a || b != b) ? NAN : (a > b ? a : b); }
+
+/* nuvec_nn::swiglu / swiglu_oai (crates/nuvec-nn/src/lib.rs:513-579) as the CPU evaluates the compiled
+ * function: its operations one by one (crates/nuvec-core/src/fused.rs:214-217), each rounded to the array's
+ * type (kernels.rs:1576-1590: f16 / bf16 compute in float32 and round); alpha and limit are weak scalars,
+ * rounded to the type first (lib.rs:504-507).  oai = 0: silu(gate) * up = (gate * sigmoid(gate)) * up. */
+int orc_swiglu(int dtype, int oai, const void *gate, const void *up, float alpha, float limit, size_t n, void *out) {
+    alpha = round_to(alpha, dtype);
+    limit = round_to(limit, dtype);
+    for (size_t i = 0; i < n; i++) {
+        float g = load_f32(gate, i, dtype), x = load_f32(up, i, dtype);
+        volatile float r;
+        if (oai) {
+            g = min_nan(g, limit);
+            x = min_nan(max_nan(x, -limit), limit);
+            volatile float ag = alpha * g;
+            float s = round_to(sigmoid_f32(round_to(ag, dtype)), dtype);
+            volatile float gs0 = g * s;
+            float gs = round_to(gs0, dtype);
+            volatile float x1 = x + 1.0f;
+            r = round_to(x1, dtype) * gs;
+        } else {
+            float s = round_to(sigmoid_f32(g), dtype);
+            volatile float t0 = g * s;
+            r = round_to(t0, dtype) * x;
+        }
+        store_round(out, i, dtype, (double)r);
+    }
+    return 0;
+}

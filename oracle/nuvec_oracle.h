@@ -97,6 +97,7 @@ int orc_weighted_sum(int dtype, const void *x, const void *w, size_t rows, size_
 int orc_expert_bias_add(int dtype, void *y, const void *bias, const uint32_t *indices, size_t rows, size_t n, size_t experts);
 int orc_moe_sort(const uint32_t *indices, size_t pairs, size_t k, size_t experts, uint32_t *order, uint32_t *restore,
                  uint32_t *tokens, uint32_t *sorted, int32_t *offsets);
+int orc_swiglu(int dtype, int oai, const void *gate, const void *up, float alpha, float limit, size_t n, void *out);
 int orc_threads(void);
 void orc_set_threads(int n);
 

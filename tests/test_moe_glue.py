@@ -195,3 +195,68 @@ def test_cuda_moe_sort_and_take_rows_match_the_oracle():
     assert np.array_equal(out, src[[4, 0, 4, 2]])
     with pytest.raises(nv.UnsupportedError):
         nv.moe_sort(dev.array(np.zeros((2, 2), np.uint32), nv.U32), 2000)
+
+
+def glu_inputs(rng, n, dtype):
+    gate = rng.standard_normal(n).astype(np.float32) * 3.0
+    up = rng.standard_normal(n).astype(np.float32) * 3.0
+    gate[:8] = [0.0, -0.0, 20.0, -20.0, 90.0, -90.0, 7.0, np.nan]
+    up[:8] = [1.0, 1.0, 9.0, -9.0, 1.0, 1.0, np.nan, 1.0]
+    return oracle.from_f32(gate, dtype), oracle.from_f32(up, dtype)
+
+
+@pytest.mark.parametrize("dt", list(DT))
+def test_oracle_swiglu_is_the_composition_op_by_op(dt):
+    dtype = DT[dt]
+    rng = np.random.default_rng(31)
+    gate, up = glu_inputs(rng, 4096, dtype)
+    g, x = oracle.to_f32(gate, dtype), oracle.to_f32(up, dtype)
+    rnd = lambda v: oracle.to_f32(oracle.from_f32(v.astype(np.float32), dtype), dtype)
+    with np.errstate(over="ignore", invalid="ignore"):
+        def sigmoid(v):
+            y = (np.float32(1) / (np.float32(1) + np.exp(np.abs(v), dtype=np.float32))).astype(np.float32)
+            return np.where(v < 0, y, np.float32(1) - y).astype(np.float32)
+        want = rnd(rnd(g * rnd(sigmoid(g))) * x)
+        got = oracle.to_f32(oracle.swiglu(gate, up, dtype), dtype)
+        tol = {"f32": 1e-6, "f16": 2.0 ** -10, "bf16": 2.0 ** -7}[dt]
+        assert np.allclose(got, want, rtol=tol, atol=1e-30, equal_nan=True)
+        # the clamped form: limits reached on both sides, NaN kept
+        alpha, limit = rnd(np.float32(1.702)), rnd(np.float32(7.0))
+        gc = np.where(np.isnan(g), np.nan, np.minimum(g, limit)).astype(np.float32)
+        xc = np.where(np.isnan(x), np.nan, np.clip(x, -limit, limit)).astype(np.float32)
+        want = rnd(rnd(xc + np.float32(1)) * rnd(gc * rnd(sigmoid(rnd(alpha * gc)))))
+        got = oracle.to_f32(oracle.swiglu(gate, up, dtype, oai=True), dtype)
+        assert np.allclose(got, want, rtol=tol, atol=1e-30, equal_nan=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", list(DT))
+def test_cuda_swiglu_matches_the_oracle(dt):
+    # every step but the exponential is an IEEE operation: results equal the oracle's bit for bit
+    # except where the device's and the host's expf differ in their last bit AND the sigmoid's
+    # rounding to the array's type falls the other way -- the sigmoid is then one unit in the last
+    # place off, and the two roundings behind it can make that two (measured: 2 of 3.1 M float16
+    # elements); float32 shows the exponentials' difference directly (a few units)
+    import nuvec_b200 as nv
+    dtype = DT[dt]
+    code = {"f32": nv.F32, "f16": nv.F16, "bf16": nv.BF16}[dt]
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(32)
+    up_ = lambda a: dev.array(a.view(np.float16) if dt == "f16" else a, code)
+    for n in (4096 * 768, 1000):
+        gate, up = glu_inputs(rng, n, dtype)
+        for oai in (False, True):
+            want = oracle.swiglu(gate, up, dtype, oai=oai)
+            got = (nv.swiglu_oai(up_(gate), up_(up)) if oai else nv.swiglu(up_(gate), up_(up))).to_numpy()
+            g32, w32 = oracle.to_f32(got.view(want.dtype) if dt != "f16" else got.view(np.uint16), dtype), oracle.to_f32(want, dtype)
+            same = (g32 == w32) | (np.isnan(g32) & np.isnan(w32))
+            if dt == "f32":
+                assert np.allclose(g32, w32, rtol=4e-7, atol=1e-37, equal_nan=True), (n, oai)
+            else:
+                assert same.mean() > 0.9995, (n, oai, float(same.mean()))
+                # (units in the last place: relative for normal numbers, 2^-24 among float16's subnormals)
+                ulp = np.maximum(np.abs(w32) * (2.0 ** -10 if dt == "f16" else 2.0 ** -7), 2.0 ** -24 if dt == "f16" else 2.0 ** -133)
+                bad = ~(same | (np.abs(g32 - w32) <= 2.0 * ulp))
+                assert not bad.any(), (n, oai, int(bad.sum()), g32[bad][:4], w32[bad][:4])
+    with pytest.raises(nv.InvalidArgument):
+        nv.swiglu(up_(gate), up_(up[:5]))
