@@ -238,6 +238,14 @@ int32_t nvc_moe_sort(nvc_device *dev, const uint32_t *indices, int64_t pairs, in
  * end takes the last row (kernels.rs:120-133). */
 int32_t nvc_take_rows(nvc_device *dev, const void *src, int64_t src_rows, int64_t row_bytes, const uint32_t *indices,
                       int64_t n, void *out);
+/* QuantizedEmbedding::forward (crates/nuvec-nn/src/layers.rs:246-255): the rows of a quantized table
+ * (codes [vocab, cols * bits / 32], scales and biases [vocab, cols / group_size]) picked by uint32 ids
+ * [count] and dequantized with nvc_dequantize's arithmetic into out [count, cols] of `dtype` (the scales'
+ * dtype for affine tables); an id past the end takes the last row, as `take` clamps
+ * (crates/nuvec-core/src/kernels.rs:120-133). */
+int32_t nvc_quantized_embedding(nvc_device *dev, const nvc_quant *q, int32_t dtype, const uint32_t *codes,
+                                const void *scales, const void *biases, int64_t vocab, int64_t cols,
+                                const uint32_t *ids, int64_t count, void *out);
 /* The activation between the up / gate and the down products (SwitchGlu::through,
  * crates/nuvec-lm/src/model.rs:2160-2171): nuvec_nn::swiglu = silu(gate) * up and gpt-oss's clamped
  * nuvec_nn::swiglu_oai = (clip(up, -limit, limit) + 1) * g * sigmoid(alpha * g) with g = min(gate, limit)

@@ -11,20 +11,36 @@ namespace nvc {
 
 // ── dequantize ─────────────────────────────────────────────────────────────────────────
 
+// Rows picked by index (an embedding look-up: QuantizedEmbedding::forward takes the ids' rows of
+// the packed table, its scales and biases, then dequantizes them, crates/nuvec-nn/src/layers.rs:246-255):
+// pack i of the output is pack `p` of source row ids[r]; an id past the end takes the last row, as
+// `take` clamps (crates/nuvec-core/src/kernels.rs:120-133).  Without ids the source pack is i itself.
+struct RowPick {
+    const uint32_t *ids;   // nullptr: rows as they are
+    size_t packs_per_row;  // cols / 8
+    uint32_t rows;         // rows of the table
+    __device__ __forceinline__ size_t source(size_t i) const {
+        if (!ids) return i;
+        const size_t r = i / packs_per_row, p = i - r * packs_per_row;
+        return (size_t)min(ids[r], rows - 1u) * packs_per_row + p;
+    }
+};
+
 // One thread decodes 8 consecutive values (8 * bits bits = `bits` whole bytes), which never
 // straddle a group because every group size is a multiple of 8.
 template <typename T, int BITS, bool FUSED>
 __global__ void __launch_bounds__(256)
 dequantize_affine_kernel(const uint8_t *__restrict__ codes, const T *__restrict__ scales,
-                         const T *__restrict__ biases, T *__restrict__ out, size_t packs, int gs) {
+                         const T *__restrict__ biases, T *__restrict__ out, size_t packs, int gs, RowPick pick) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= packs) return;
-    const uint8_t *src = codes + i * BITS;
+    const size_t si = pick.source(i);
+    const uint8_t *src = codes + si * BITS;
     uint64_t stream = 0;
 #pragma unroll
     for (int b = 0; b < BITS; b++) stream |= (uint64_t)src[b] << (8 * b);
     size_t first = i * 8;
-    size_t g = first / (size_t)gs;
+    size_t g = si * 8 / (size_t)gs;
     float s = DT<T>::load(scales, g), bias = DT<T>::load(biases, g);
     float vals[8];
 #pragma unroll
@@ -46,11 +62,12 @@ dequantize_affine_kernel(const uint8_t *__restrict__ codes, const T *__restrict_
 template <typename T, int BITS>
 __global__ void __launch_bounds__(256)
 dequantize_fp_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales,
-                     const float *__restrict__ global, T *__restrict__ out, size_t packs, int gs) {
+                     const float *__restrict__ global, T *__restrict__ out, size_t packs, int gs, RowPick pick) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= packs) return;
     size_t first = i * 8;
-    uint32_t sc = scales[first / (size_t)gs];
+    const size_t sfirst = pick.source(i) * 8;
+    uint32_t sc = scales[sfirst / (size_t)gs];
     float scale = ftz(gs == 32 ? e8m0_to_f32(sc) : e4m3_to_f32(sc));
     if (global) {
         float inv = ftz(__fdiv_rn(*global, 448.0f * 6.0f));
@@ -59,20 +76,20 @@ dequantize_fp_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restric
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         float v;
-        if (BITS == 8) v = e4m3_to_f32(codes[first + j]);
-        else v = e2m1_to_f32((codes[(first + j) >> 1] >> (4 * (j & 1))) & 0xFu);
+        if (BITS == 8) v = e4m3_to_f32(codes[sfirst + j]);
+        else v = e2m1_to_f32((codes[(sfirst + j) >> 1] >> (4 * (j & 1))) & 0xFu);
         DT<T>::store(out, first + j, canonical(ftz(__fmul_rn(scale, v))));
     }
 }
 
 template <typename T, bool FUSED>
 static int32_t launch_dequantize_affine(nvc_device *dev, int bits, const uint8_t *codes, const void *scales,
-                                        const void *biases, void *out, size_t packs, int gs) {
+                                        const void *biases, void *out, size_t packs, int gs, RowPick pick) {
     unsigned blocks = (unsigned)((packs + 255) / 256);
 #define NVC_CASE(B)                                                                               \
     case B:                                                                                       \
         dequantize_affine_kernel<T, B, FUSED><<<blocks, 256, 0, dev->stream>>>(                   \
-            codes, (const T *)scales, (const T *)biases, (T *)out, packs, gs);                    \
+            codes, (const T *)scales, (const T *)biases, (T *)out, packs, gs, pick);              \
         break;
     switch (bits) {
         NVC_CASE(1) NVC_CASE(2) NVC_CASE(3) NVC_CASE(4) NVC_CASE(5) NVC_CASE(6) NVC_CASE(8)
@@ -239,18 +256,19 @@ static int32_t quantize_typed(nvc_device *dev, const nvc_quant *q, const void *w
 
 template <typename T>
 static int32_t dequantize_typed(nvc_device *dev, const nvc_quant *q, const uint32_t *codes, const void *scales,
-                                const void *biases, const float *global, size_t count, void *out, int fused) {
+                                const void *biases, const float *global, size_t count, void *out, int fused,
+                                RowPick pick = RowPick{nullptr, 0, 0}) {
     size_t packs = count / 8;
     const uint8_t *bytes = (const uint8_t *)codes;
     if (q->mode == NVC_AFFINE) {
-        return fused ? launch_dequantize_affine<T, true>(dev, q->bits, bytes, scales, biases, out, packs, q->group_size)
-                     : launch_dequantize_affine<T, false>(dev, q->bits, bytes, scales, biases, out, packs, q->group_size);
+        return fused ? launch_dequantize_affine<T, true>(dev, q->bits, bytes, scales, biases, out, packs, q->group_size, pick)
+                     : launch_dequantize_affine<T, false>(dev, q->bits, bytes, scales, biases, out, packs, q->group_size, pick);
     }
     unsigned blocks = (unsigned)((packs + 255) / 256);
     if (q->bits == 4)
-        dequantize_fp_kernel<T, 4><<<blocks, 256, 0, dev->stream>>>(bytes, (const uint8_t *)scales, global, (T *)out, packs, q->group_size);
+        dequantize_fp_kernel<T, 4><<<blocks, 256, 0, dev->stream>>>(bytes, (const uint8_t *)scales, global, (T *)out, packs, q->group_size, pick);
     else
-        dequantize_fp_kernel<T, 8><<<blocks, 256, 0, dev->stream>>>(bytes, (const uint8_t *)scales, global, (T *)out, packs, q->group_size);
+        dequantize_fp_kernel<T, 8><<<blocks, 256, 0, dev->stream>>>(bytes, (const uint8_t *)scales, global, (T *)out, packs, q->group_size, pick);
     return check_launch(dev, "dequantize_fp_kernel");
 }
 
@@ -303,5 +321,29 @@ extern "C" int32_t nvc_dequantize(nvc_device *dev, const nvc_quant *q, int32_t d
     case NVC_F32: return dequantize_typed<float>(dev, q, codes, scales, biases, global_scale, count, out, fused);
     case NVC_F16: return dequantize_typed<__half>(dev, q, codes, scales, biases, global_scale, count, out, fused);
     default: return dequantize_typed<__nv_bfloat16>(dev, q, codes, scales, biases, global_scale, count, out, fused);
+    }
+}
+
+extern "C" int32_t nvc_quantized_embedding(nvc_device *dev, const nvc_quant *q, int32_t dtype, const uint32_t *codes, const void *scales,
+                                           const void *biases, int64_t vocab, int64_t cols, const uint32_t *ids, int64_t count, void *out) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("quantized_embedding", q));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_UNSUPPORTED, "quantized_embedding: unsupported dtype %d", dtype);
+    if (q->mode == NVC_AFFINE && !biases)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_embedding: biases must be provided for affine quantization");
+    if (q->mode != NVC_AFFINE && biases)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_embedding: biases must be null for this quantization mode");
+    if (vocab < 0 || count < 0 || cols < 0 || cols % q->group_size != 0 || vocab > 0xFFFFFFFFll)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_embedding: invalid shape (%lld rows of %lld columns, group size %d)",
+                         (long long)vocab, (long long)cols, q->group_size);
+    const size_t total = (size_t)count * (size_t)cols;
+    if (total == 0) return NVC_OK;
+    if (vocab == 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_embedding: rows taken from an empty table");
+    if (!codes || !scales || !ids || !out) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_embedding: null operand");
+    const RowPick pick{ids, (size_t)cols / 8, (uint32_t)vocab};
+    switch (dtype) {
+    case NVC_F32: return dequantize_typed<float>(dev, q, codes, scales, biases, nullptr, total, out, 0, pick);
+    case NVC_F16: return dequantize_typed<__half>(dev, q, codes, scales, biases, nullptr, total, out, 0, pick);
+    default: return dequantize_typed<__nv_bfloat16>(dev, q, codes, scales, biases, nullptr, total, out, 0, pick);
     }
 }

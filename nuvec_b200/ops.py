@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -597,6 +597,27 @@ def take_rows(src: Array, indices: Array) -> Array:
     row_bytes = (src.size // rows if rows else 0) * src.itemsize
     out = src.dev.empty((indices.size,) + tuple(src.shape[1:]), src.dtype)
     _check(_ffi.lib().nvc_take_rows(src.dev._h, src.ptr, rows, row_bytes, indices.ptr, indices.size, out.ptr))
+    return out
+
+
+def quantized_embedding(q: Quantized, ids: Array) -> Array:
+    """QuantizedEmbedding::forward (crates/nuvec-nn/src/layers.rs:246-255): the ids' rows of a quantized table
+    [vocab, cols], dequantized: shape ids.shape + (cols,), the scales' dtype (bfloat16 for the fp modes)."""
+    quant = q.quant
+    quant.checked("quantized_embedding")
+    if q.weight.ndim != 2 or ids.dtype != U32:
+        raise InvalidArgument("quantized_embedding: a 2-D quantized table and uint32 ids expected")
+    if q.global_scale is not None:
+        raise UnsupportedError("quantized_embedding: tables with a global scale are not supported")
+    _check_groups("quantized_embedding", quant.mode, q.scales, q.biases)
+    cols = _columns("quantized_embedding", q.weight, q.scales, q.biases, quant)
+    affine = quant.mode == QuantMode.AFFINE
+    dtype = q.scales.dtype if affine else BF16
+    dev = q.weight.dev
+    out = dev.empty(tuple(ids.shape) + (cols,), dtype)
+    c = quant._c()
+    _check(_ffi.lib().nvc_quantized_embedding(dev._h, C.byref(c), dtype, q.weight.ptr, q.scales.ptr, _ptr(q.biases),
+                                              q.weight.shape[0], cols, ids.ptr, ids.size, out.ptr))
     return out
 
 

@@ -518,3 +518,33 @@ def test_asynchronous_host_entry_point_delivers_at_synchronize(be):
                                                    qb.scales.ptr, qb.biases.ptr, None, Mb, Nb, Kb, o.ctypes.data_as(C.c_void_p)) == 0
     dev.synchronize()
     assert all(np.array_equal(o, wantb) for o in big)
+
+
+def test_quantized_embedding_is_take_then_dequantize(be):
+    # QuantizedEmbedding::forward (crates/nuvec-nn/src/layers.rs:246-255): the ids' rows of the packed table,
+    # its scales and biases, dequantized -- bit for bit the oracle's dequantize of the rows numpy takes;
+    # ids past the end take the last row
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(77)
+    vocab, cols = 1000, 512
+    ids = rng.integers(0, vocab, (3, 37)).astype(np.uint32)
+    ids[0, :3] = [vocab - 1, vocab, vocab + 50]
+    picked = np.minimum(ids, vocab - 1)
+    for bits, gs in [(4, 64), (3, 32), (8, 128), (6, 64), (2, 64)]:
+        quant = nv.Quant.affine(gs, bits)
+        w = rand(rng, (vocab, cols), oracle.BF16, 0.05)
+        codes, scales, biases = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+        q = nv.Quantized(dev.array(codes, nv.U32), dev.array(scales, nv.BF16), dev.array(biases, nv.BF16), quant)
+        got = nv.quantized_embedding(q, dev.array(ids, nv.U32)).to_numpy().view(np.uint16)
+        want = oracle.dequantize(codes[picked], scales[picked], biases[picked], oracle.BF16, oracle.AFFINE, gs, bits)
+        assert got.shape == (3, 37, cols) and np.array_equal(got, want), (bits, gs)
+    for mode, name, gs in [(oracle.MXFP4, "mxfp4", 32), (oracle.NVFP4, "nvfp4", 16), (oracle.MXFP8, "mxfp8", 32)]:
+        bits = 8 if mode == oracle.MXFP8 else 4
+        quant = nv.Quant(nv.QuantMode(name), gs, bits)
+        w = rand(rng, (vocab, cols), oracle.BF16, 0.05)
+        codes, scales, _ = oracle.quantize(w, oracle.BF16, mode, gs, bits)
+        q = nv.Quantized(dev.array(codes, nv.U32), dev.array(scales, nv.U8), None, quant)
+        got = nv.quantized_embedding(q, dev.array(ids, nv.U32)).to_numpy().view(np.uint16)
+        want = oracle.dequantize(codes[picked], scales[picked], None, oracle.BF16, mode, gs, bits)
+        assert np.array_equal(got, want), name
