@@ -838,7 +838,9 @@ def moe_glue_rows(nv, dev):
         gate = dev.array(nv.f32_to_bf16(rng.standard_normal((T * topk, inter), dtype=np.float32)), nv.BF16)
         upp = dev.array(nv.f32_to_bf16(rng.standard_normal((T * topk, inter), dtype=np.float32)), nv.BF16)
         glu = (lambda: nv.swiglu_oai(gate, upp)) if "gpt-oss" in cname else (lambda: nv.swiglu(gate, upp))
+        wnorm = dev.array(nv.f32_to_bf16(rng.standard_normal(D, dtype=np.float32)), nv.BF16)
         calls = [
+            ("add_rms_norm (in front of the layer)", lambda: nv.add_rms_norm(x, x, wnorm, 1e-6), T * D * 2 * 4 + D * 2),
             ("moe_route", lambda: nv.moe_route(p, topk, True), T * E * 2 + T * topk * 6),
             ("moe_sort", lambda: nv.moe_sort(idx, E), T * topk * 4 * 5 + E * 4),
             ("take_rows (activations by sorted pair)", lambda: nv.take_rows(x, toks), T * topk * D * 2 * 2),

@@ -238,6 +238,17 @@ int32_t nvc_moe_sort(nvc_device *dev, const uint32_t *indices, int64_t pairs, in
  * end takes the last row (kernels.rs:120-133). */
 int32_t nvc_take_rows(nvc_device *dev, const void *src, int64_t src_rows, int64_t row_bytes, const uint32_t *indices,
                       int64_t n, void *out);
+/* fast::rms_norm and fast::add_rms_norm (crates/nuvec-core/src/fast/imp.rs:358-412), the normalisation in front
+ * of a layer's projections: y[r, :] = x[r, :] / sqrt(mean(x[r, :]^2) + eps) * weight over rows of d elements
+ * of one float dtype (weight [d] or NULL); add_rms_norm first stores out_sum = x + residual (rounded to the
+ * dtype) and normalises that.  The arithmetic is the CPU expansion's (fast/imp.rs:1367-1379): float32 squares,
+ * their sum in float64 over 8 lanes combined by a fixed tree (kernels.rs:611-624) and rounded to float32,
+ * times float32(1 / d), plus eps, 1 / sqrt, x times that rounded to the dtype, times the weight rounded
+ * again -- every step an IEEE operation in the reference's order, so the results are its bits. */
+int32_t nvc_rms_norm(nvc_device *dev, int32_t dtype, const void *x, const void *weight, float eps, int64_t rows,
+                     int64_t d, void *y);
+int32_t nvc_add_rms_norm(nvc_device *dev, int32_t dtype, const void *x, const void *residual, const void *weight,
+                         float eps, int64_t rows, int64_t d, void *out_sum, void *y);
 /* QuantizedEmbedding::forward (crates/nuvec-nn/src/layers.rs:246-255): the rows of a quantized table
  * (codes [vocab, cols * bits / 32], scales and biases [vocab, cols / group_size]) picked by uint32 ids
  * [count] and dequantized with nvc_dequantize's arithmetic into out [count, cols] of `dtype` (the scales'

@@ -23,6 +23,13 @@
 //               rounded to the array's type, the sigmoid as MLX's (kernels.rs:1538-1543) in float32.  The
 //               only step that is not an IEEE operation is the exponential: where the device's expf and the
 //               host's differ in their last bit a result can differ by a unit or two in the last place;
+//   rms_norm / add_rms_norm  fast::rms_norm and fast::add_rms_norm (fast/imp.rs:358-412), the normalisation in
+//               front of a layer's projections, with the arithmetic of their CPU expansion
+//               (fast/imp.rs:1367-1379): float32 squares, their sum in float64 over 8 lanes combined by a
+//               fixed tree (kernels.rs:611-624) and rounded to float32, times float32(1 / d), plus eps,
+//               1 / sqrt, x * that rounded to the array's type, times the weight rounded again; the sum
+//               x + residual of add_rms_norm rounded to the type first.  Every step is an IEEE operation
+//               performed in the reference's order: the results are its bits;
 //   expert_bias_add  SwitchProjection::forward's `y.add(bias.take(indices, 0))`
 //               (crates/nuvec-lm/src/model.rs:2139-2143): every gathered row plus its expert's bias,
 //               float32 arithmetic for the halves, one rounding; an index past the end selects the
@@ -251,6 +258,53 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T *__restrict__ gate,
     }
 }
 
+// One block per row.  The float64 lane sums must be taken in the reference's order (addition does
+// not associate): threads 0-7 each add their lane's squares one after the other from shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ residual, const T *__restrict__ weight,
+                                                       T *__restrict__ sum_out, T *__restrict__ y, int64_t d, float eps, float inv_count) {
+    extern __shared__ float squares[];  // [d], then 8 lane sums (float64) and the scale
+    double *lanes = reinterpret_cast<double *>(squares + ((d + 1) & ~(int64_t)1));
+    float *scale = reinterpret_cast<float *>(lanes + 8);
+    const int tid = threadIdx.x;
+    const T *xr = x + (size_t)blockIdx.x * d;
+    const T *rr = residual ? residual + (size_t)blockIdx.x * d : nullptr;
+    T *hr = sum_out ? sum_out + (size_t)blockIdx.x * d : nullptr;
+    T *yr = y + (size_t)blockIdx.x * d;
+    for (int64_t j = tid; j < d; j += 256) {
+        float v = Glue<T>::load(xr, j);
+        if (rr) {
+            const T h = Glue<T>::from_f32(__fadd_rn(v, Glue<T>::load(rr, j)));  // x + residual, rounded to T
+            hr[j] = h;
+            v = Glue<T>::widen(h);
+        }
+        squares[j] = __fmul_rn(v, v);
+    }
+    __syncthreads();
+    if (tid < 8) {
+        double acc = 0.0;
+        const int64_t whole = d & ~(int64_t)7;
+        for (int64_t j = tid; j < whole; j += 8) acc = __dadd_rn(acc, (double)squares[j]);
+        if (tid < d - whole) acc = __dadd_rn(acc, (double)squares[whole + tid]);
+        lanes[tid] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const double total = __dadd_rn(__dadd_rn(__dadd_rn(lanes[0], lanes[4]), __dadd_rn(lanes[1], lanes[5])),
+                                       __dadd_rn(__dadd_rn(lanes[2], lanes[6]), __dadd_rn(lanes[3], lanes[7])));
+        const float mean = __fmul_rn(__double2float_rn(total), inv_count);
+        *scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    }
+    __syncthreads();
+    const float n = *scale;
+    for (int64_t j = tid; j < d; j += 256) {
+        const float v = rr ? Glue<T>::widen(hr[j]) : Glue<T>::load(xr, j);
+        T out = Glue<T>::from_f32(__fmul_rn(v, n));
+        if (weight) out = Glue<T>::from_f32(__fmul_rn(Glue<T>::widen(out), Glue<T>::load(weight, j)));
+        yr[j] = out;
+    }
+}
+
 // y[r, c] += bias[indices[r], c]: one block per row; 16-byte pieces when the rows allow it.
 template <typename T>
 __global__ void __launch_bounds__(256) expert_bias_add_kernel(T *__restrict__ y, const T *__restrict__ bias,
@@ -382,4 +436,44 @@ extern "C" int32_t nvc_swiglu(nvc_device *dev, int32_t dtype, const void *gate, 
 extern "C" int32_t nvc_swiglu_oai(nvc_device *dev, int32_t dtype, const void *gate, const void *up, float alpha, float limit, int64_t n,
                                   void *out) {
     return launch_swiglu<true>(dev, "swiglu_oai", dtype, gate, up, n, alpha, limit, out);
+}
+
+static int32_t launch_rms_norm(nvc_device *dev, const char *op, int32_t dtype, const void *x, const void *residual, const void *weight, float eps,
+                               int64_t rows, int64_t d, void *sum_out, void *y) {
+    NVC_TRY(make_current(dev));
+    if (!is_float_dtype(dtype)) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: the input must be floating point (dtype %d)", op, dtype);
+    if (rows < 0 || d < 0 || rows > 0x7FFFFFFFll) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: invalid shape", op);
+    if (rows * d == 0) return NVC_OK;
+    if (!x || !y || (residual && !sum_out)) return set_error(NVC_ERR_INVALID_ARGUMENT, "%s: null operand", op);
+    const size_t smem = (size_t)((d + 1) & ~(int64_t)1) * sizeof(float) + 8 * sizeof(double) + 16;
+    if (smem > 200 * 1024) return set_error(NVC_ERR_UNSUPPORTED, "%s: rows of %lld elements do not fit shared memory", op, (long long)d);
+    const float inv_count = (float)(1.0 / (double)d);
+#define NVC_RMS(T)                                                                                                              \
+    {                                                                                                                           \
+        auto kernel = rms_norm_kernel<T>;                                                                                       \
+        static bool configured[64] = {};                                                                                        \
+        if (smem > 48 * 1024 && dev->ordinal >= 0 && dev->ordinal < 64 && !configured[dev->ordinal]) {                          \
+            NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));                    \
+            configured[dev->ordinal] = true;                                                                                    \
+        }                                                                                                                       \
+        kernel<<<(unsigned)rows, 256, smem, dev->stream>>>((const T *)x, (const T *)residual, (const T *)weight, (T *)sum_out, (T *)y, d, eps, \
+                                                           inv_count);                                                          \
+    }
+    switch (dtype) {
+    case NVC_F32: NVC_RMS(float) break;
+    case NVC_F16: NVC_RMS(__half) break;
+    default: NVC_RMS(__nv_bfloat16)
+    }
+#undef NVC_RMS
+    return check_launch(dev, "rms_norm_kernel");
+}
+
+extern "C" int32_t nvc_rms_norm(nvc_device *dev, int32_t dtype, const void *x, const void *weight, float eps, int64_t rows, int64_t d, void *y) {
+    return launch_rms_norm(dev, "rms_norm", dtype, x, nullptr, weight, eps, rows, d, nullptr, y);
+}
+
+extern "C" int32_t nvc_add_rms_norm(nvc_device *dev, int32_t dtype, const void *x, const void *residual, const void *weight, float eps,
+                                    int64_t rows, int64_t d, void *out_sum, void *y) {
+    if (!residual) return set_error(NVC_ERR_INVALID_ARGUMENT, "add_rms_norm: null residual");
+    return launch_rms_norm(dev, "add_rms_norm", dtype, x, residual, weight, eps, rows, d, out_sum, y);
 }

@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -619,6 +619,33 @@ def quantized_embedding(q: Quantized, ids: Array) -> Array:
     _check(_ffi.lib().nvc_quantized_embedding(dev._h, C.byref(c), dtype, q.weight.ptr, q.scales.ptr, _ptr(q.biases),
                                               q.weight.shape[0], cols, ids.ptr, ids.size, out.ptr))
     return out
+
+
+def _norm_args(name, x: Array, weight):
+    if x.ndim < 1 or x.dtype not in _FLOATS:
+        raise InvalidArgument(f"{name}: a floating-point input with at least one dimension expected")
+    d = x.shape[-1]
+    if weight is not None and (weight.dtype != x.dtype or tuple(weight.shape) != (d,)):
+        raise InvalidArgument(f"{name}: the weight must be [{d}] of the input's dtype")
+    return d, (x.size // d if d else 0)
+
+
+def rms_norm(x: Array, weight: Optional[Array] = None, eps: float = 1e-5) -> Array:
+    """fast::rms_norm (crates/nuvec-core/src/fast/imp.rs:358-378) over the last axis."""
+    d, rows = _norm_args("rms_norm", x, weight)
+    y = x.dev.empty(tuple(x.shape), x.dtype)
+    _check(_ffi.lib().nvc_rms_norm(x.dev._h, x.dtype, x.ptr, _ptr(weight), eps, rows, d, y.ptr))
+    return y
+
+
+def add_rms_norm(x: Array, residual: Array, weight: Optional[Array] = None, eps: float = 1e-5):
+    """fast::add_rms_norm (fast/imp.rs:381-412): (x + residual, rms_norm of that)."""
+    d, rows = _norm_args("add_rms_norm", x, weight)
+    if tuple(residual.shape) != tuple(x.shape) or residual.dtype != x.dtype:
+        raise InvalidArgument("add_rms_norm: x and the residual must share shape and dtype")
+    h, y = x.dev.empty(tuple(x.shape), x.dtype), x.dev.empty(tuple(x.shape), x.dtype)
+    _check(_ffi.lib().nvc_add_rms_norm(x.dev._h, x.dtype, x.ptr, residual.ptr, _ptr(weight), eps, rows, d, h.ptr, y.ptr))
+    return h, y
 
 
 def _glu(name, gate: Array, up: Array, call):

@@ -240,6 +240,19 @@ def swiglu(gate, up, dtype, oai=False, alpha=1.702, limit=7.0):
     return out
 
 
+def rms_norm(x, dtype, weight=None, eps=1e-5, residual=None):
+    """rms_norm over the last axis; with `residual` returns (x + residual, its rms_norm)."""
+    x = _c(x)
+    d = x.shape[-1]
+    rows = x.size // d if d else 0
+    y = np.zeros(x.shape, store_dtype(dtype))
+    h = np.zeros(x.shape, store_dtype(dtype)) if residual is not None else None
+    res = None if residual is None else _c(residual)
+    w = None if weight is None else _c(weight)
+    _check(lib().orc_rms_norm(dtype, _ptr(x), _ptr(res), _ptr(w), ctypes.c_float(eps), _sz(rows), _sz(d), _ptr(h), _ptr(y)))
+    return y if residual is None else (h, y)
+
+
 def threads() -> int:
     return int(lib().orc_threads())
 

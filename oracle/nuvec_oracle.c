@@ -781,3 +781,56 @@ int orc_swiglu(int dtype, int oai, const void *gate, const void *up, float alpha
     }
     return 0;
 }
+
+/* fast::rms_norm / fast::add_rms_norm as their CPU expansion computes them
+ * (crates/nuvec-core/src/fast/imp.rs:1367-1379 over ops/imp.rs:546-555 and kernels.rs:611-645, 1418):
+ *   xf = float32(x) (x + residual first, rounded to the array's type, for add_rms_norm);
+ *   s  = float32(lane_sum(xf * xf))        -- float64 over 8 lanes, fixed tree;
+ *   n  = 1 / sqrt(s * float32(1 / d) + eps)  -- float32 throughout;
+ *   y  = T(xf * n), then T(y * weight) when there is a weight.
+ * residual, weight and sum_out may be NULL. */
+int orc_rms_norm(int dtype, const void *x, const void *residual, const void *weight, float eps, size_t rows, size_t d, void *sum_out,
+                 void *y) {
+    float *xf = (float *)malloc((d ? d : 1) * sizeof(float));
+    if (!xf) return -1;
+    volatile float inv_count = (float)(1.0 / (double)d);
+    for (size_t r = 0; r < rows; r++) {
+        double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (size_t j = 0; j < d; j++) {
+            float v = load_f32(x, r * d + j, dtype);
+            if (residual) {
+                volatile float h = v + load_f32(residual, r * d + j, dtype);
+                v = round_to(h, dtype);
+                if (sum_out) store_round(sum_out, r * d + j, dtype, (double)v);
+            }
+            xf[j] = v;
+        }
+        size_t whole = d / 8 * 8;
+        for (size_t j = 0; j < whole; j += 8)
+            for (size_t l = 0; l < 8; l++) {
+                volatile float sq = xf[j + l] * xf[j + l];
+                acc[l] += (double)sq;
+            }
+        for (size_t l = 0; l < d - whole; l++) {
+            volatile float sq = xf[whole + l] * xf[whole + l];
+            acc[l] += (double)sq;
+        }
+        volatile double total = ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+        volatile float s = (float)total;
+        volatile float mean = s * inv_count;
+        volatile float v = mean + eps;
+        volatile float root = sqrtf(v);
+        volatile float n = 1.0f / root;
+        for (size_t j = 0; j < d; j++) {
+            volatile float scaled = xf[j] * n;
+            float out = round_to(scaled, dtype);
+            if (weight) {
+                volatile float ww = out * load_f32(weight, j, dtype);
+                out = round_to(ww, dtype);
+            }
+            store_round(y, r * d + j, dtype, (double)out);
+        }
+    }
+    free(xf);
+    return 0;
+}

@@ -98,6 +98,8 @@ int orc_expert_bias_add(int dtype, void *y, const void *bias, const uint32_t *in
 int orc_moe_sort(const uint32_t *indices, size_t pairs, size_t k, size_t experts, uint32_t *order, uint32_t *restore,
                  uint32_t *tokens, uint32_t *sorted, int32_t *offsets);
 int orc_swiglu(int dtype, int oai, const void *gate, const void *up, float alpha, float limit, size_t n, void *out);
+int orc_rms_norm(int dtype, const void *x, const void *residual, const void *weight, float eps, size_t rows, size_t d, void *sum_out,
+                 void *y);
 int orc_threads(void);
 void orc_set_threads(int n);
 

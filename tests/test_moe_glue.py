@@ -260,3 +260,54 @@ def test_cuda_swiglu_matches_the_oracle(dt):
                 assert not bad.any(), (n, oai, int(bad.sum()), g32[bad][:4], w32[bad][:4])
     with pytest.raises(nv.InvalidArgument):
         nv.swiglu(up_(gate), up_(up[:5]))
+
+
+@pytest.mark.parametrize("dt", list(DT))
+def test_oracle_rms_norm(dt):
+    dtype = DT[dt]
+    rng = np.random.default_rng(41)
+    for rows, d in [(3, 64), (2, 4096), (5, 37), (1, 8), (4, 5)]:
+        x = oracle.from_f32(rng.standard_normal((rows, d)).astype(np.float32) * 2.0, dtype)
+        w = oracle.from_f32(rng.standard_normal(d).astype(np.float32), dtype)
+        res = oracle.from_f32(rng.standard_normal((rows, d)).astype(np.float32), dtype)
+        xf = oracle.to_f32(x, dtype)
+        rnd = lambda v: oracle.to_f32(oracle.from_f32(v.astype(np.float32), dtype), dtype)
+        def norm(v):
+            n = np.float32(1) / np.sqrt((v.astype(np.float64) ** 2).mean(-1, keepdims=True).astype(np.float32) + np.float32(1e-5))
+            return rnd(rnd(v * n.astype(np.float32)) * oracle.to_f32(w, dtype))
+        tol = {"f32": 2e-6, "f16": 2.0 ** -9, "bf16": 2.0 ** -6}[dt]
+        got = oracle.to_f32(oracle.rms_norm(x, dtype, w), dtype)
+        assert np.allclose(got, norm(xf), rtol=tol, atol=tol * 1e-2), (rows, d)
+        h, y = oracle.rms_norm(x, dtype, w, residual=res)
+        hf = rnd(xf + oracle.to_f32(res, dtype))
+        assert np.array_equal(oracle.to_f32(h, dtype), hf)
+        assert np.allclose(oracle.to_f32(y, dtype), norm(hf), rtol=tol, atol=tol * 1e-2), (rows, d)
+        # without a weight: the scaled input, rounded once
+        got = oracle.to_f32(oracle.rms_norm(x, dtype), dtype)
+        n = np.float32(1) / np.sqrt((xf.astype(np.float64) ** 2).mean(-1, keepdims=True).astype(np.float32) + np.float32(1e-5))
+        assert np.allclose(got, rnd(xf * n), rtol=tol, atol=tol * 1e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", list(DT))
+def test_cuda_rms_norm_matches_the_oracle_bit_for_bit(dt):
+    import nuvec_b200 as nv
+    dtype = DT[dt]
+    code = {"f32": nv.F32, "f16": nv.F16, "bf16": nv.BF16}[dt]
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(42)
+    up_ = lambda a: dev.array(a.view(np.float16) if dt == "f16" else a, code)
+    bits = lambda a: a.view(np.uint32) if dt == "f32" else a.view(np.uint16)
+    for rows, d in [(3, 64), (1, 4096), (5, 37), (1, 8), (4, 5), (512, 2048), (64, 12288), (2, 40000)]:
+        x = oracle.from_f32(rng.standard_normal((rows, d)).astype(np.float32) * 2.0, dtype)
+        w = oracle.from_f32(rng.standard_normal(d).astype(np.float32), dtype)
+        res = oracle.from_f32(rng.standard_normal((rows, d)).astype(np.float32), dtype)
+        want = oracle.rms_norm(x, dtype, w, eps=1e-6)
+        got = nv.rms_norm(up_(x), up_(w), 1e-6).to_numpy()
+        assert np.array_equal(bits(got), bits(want)), (rows, d)
+        assert np.array_equal(bits(nv.rms_norm(up_(x)).to_numpy()), bits(oracle.rms_norm(x, dtype))), (rows, d)
+        wh, wy = oracle.rms_norm(x, dtype, w, eps=1e-6, residual=res)
+        gh, gy = nv.add_rms_norm(up_(x), up_(res), up_(w), 1e-6)
+        assert np.array_equal(bits(gh.to_numpy()), bits(wh)) and np.array_equal(bits(gy.to_numpy()), bits(wy)), (rows, d)
+    with pytest.raises(nv.UnsupportedError):
+        nv.rms_norm(dev.empty((1, 60000), code))
