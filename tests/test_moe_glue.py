@@ -311,3 +311,57 @@ def test_cuda_rms_norm_matches_the_oracle_bit_for_bit(dt):
         assert np.array_equal(bits(gh.to_numpy()), bits(wh)) and np.array_equal(bits(gy.to_numpy()), bits(wy)), (rows, d)
     with pytest.raises(nv.UnsupportedError):
         nv.rms_norm(dev.empty((1, 60000), code))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens", [3, 96])
+def test_a_mixture_of_experts_layer_end_to_end(tokens):
+    # The layer as nuvec-lm runs it (MoeMlp / SwitchGlu::forward, crates/nuvec-lm/src/model.rs:2160-2210):
+    # router top-k, sort by expert, the activations by sorted pair, gate and up products, SwiGLU, down
+    # product, the experts' biases, back into pair order, weighted sum -- every step on the device, against
+    # the same steps through the oracle.  3 tokens take the per-row gather, 96 the sorted, grouped one.
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(50 + tokens)
+    E, k, D, I, gs, bits = 8, 2, 128, 192, 64, 4
+    quant = nv.Quant.affine(gs, bits)
+    bf = lambda a: oracle.from_f32(np.asarray(a, np.float32), oracle.BF16)
+    x = bf(rng.standard_normal((tokens, D)))
+    logits = rng.standard_normal((tokens, E)).astype(np.float32)
+    probs = np.exp(logits - logits.max(-1, keepdims=True))
+    probs = bf(probs / probs.sum(-1, keepdims=True))
+    experts = {}
+    for name, n_out, n_in in (("gate", I, D), ("up", I, D), ("down", D, I)):
+        w = bf(rng.standard_normal((E, n_out, n_in)) * 0.05)
+        experts[name] = oracle.quantize(w, oracle.BF16, oracle.AFFINE, gs, bits)
+    bias = bf(rng.standard_normal((E, D)) * 0.1)
+
+    # the oracle's layer
+    idx, scores = oracle.moe_route(probs, oracle.BF16, k, True)
+    order, restore, toks, srt, offsets = oracle.moe_sort(idx, E)
+    rows = x[toks][:, None, :]                                  # [pairs, 1, D]
+    lhs = np.arange(tokens * k, dtype=np.uint32)
+    prod = lambda name, a: oracle.gather_qmm(a, *experts[name], lhs, srt, oracle.BF16, oracle.AFFINE, gs, bits)
+    h = oracle.swiglu(prod("gate", rows), prod("up", rows), oracle.BF16)
+    y = oracle.expert_bias_add(prod("down", h).reshape(tokens * k, D), bias, srt, oracle.BF16)
+    want = oracle.weighted_sum(y[restore].reshape(tokens, k, D), scores, oracle.BF16)
+
+    # the same on the device
+    up = lambda a, code=nv.BF16: dev.array(a, code)
+    q = {name: nv.Quantized(up(c, nv.U32), up(s), up(b), quant) for name, (c, s, b) in experts.items()}
+    d_idx, d_scores = nv.moe_route(up(probs), k, True)
+    d_order, d_restore, d_toks, d_srt, d_offsets = nv.moe_sort(d_idx, E)
+    assert np.array_equal(d_srt.to_numpy(), srt) and np.array_equal(d_restore.to_numpy(), restore)
+    d_rows = nv.take_rows(up(x), d_toks).reshape((tokens * k, 1, D))
+    opts = nv.GatherQmm().with_sorted_indices(True)
+    dprod = lambda name, a: nv.gather_qmm(a, q[name], None, d_srt, opts, d_offsets)
+    d_h = nv.swiglu(dprod("gate", d_rows), dprod("up", d_rows))
+    d_y = nv.expert_bias_add(dprod("down", d_h).reshape((tokens * k, D)), up(bias), d_srt)
+    got = nv.weighted_sum(nv.take_rows(d_y, d_restore).reshape((tokens, k, D)), d_scores).to_numpy().view(np.uint16)
+
+    g32, w32 = oracle.to_f32(got, oracle.BF16), oracle.to_f32(want, oracle.BF16)
+    # products agree within one output rounding; three of them in a row, an activation and a
+    # weighted sum in between: a few bfloat16 units of the row's largest magnitude
+    bound = 4.0 * 2.0 ** -7 * np.abs(w32).max(-1, keepdims=True)
+    assert np.all(np.abs(g32 - w32) <= bound), float((np.abs(g32 - w32) / bound).max())
+    assert (g32 == w32).mean() > 0.5
