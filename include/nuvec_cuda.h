@@ -202,6 +202,18 @@ int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32
                        const int32_t *offsets, int32_t sorted, int64_t rows, int64_t x_batches,
                        int64_t M, int64_t N, int64_t K, int64_t experts, void *y);
 
+/* qqmm (crates/nuvec-core/src/products.rs:337-352: MLX's qqmm): y = q(x) * w^T with BOTH operands quantized
+ * in the weight's mode -- x (bfloat16 [M, K]) goes through its own quantization first (fake_quant, :317-324:
+ * the values the codes represent), then the ordinary quantized product.  NVFP4 weights without global
+ * scales ([N, K / 8] codes, [N, K / 16] E4M3 scales); K a multiple of 64.  This is the product that the
+ * tensor cores' native block-scaled instruction computes (tcgen05.mma.kind::mxf4nvf4.block_scale: both
+ * operands as 4-bit codes with their scale factors in tensor memory): within a block of 16 the products and
+ * their scaled sum are exact in float32, so only the order of the blocks' addition differs from the
+ * reference's float32 product of the dequantized operands.  Takes scratch from the pool (the quantized
+ * activations and the two scale arrays in the tensor core's layout): not inside a recorded step. */
+int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w,
+                 const void *w_scales, int64_t M, int64_t N, int64_t K, void *y);
+
 /* fast::moe_route (crates/nuvec-core/src/fast/imp.rs:2652-2672; kernel crates/nuvec-kernels/src/metal/moe.metal):
  * per row of `experts` router probabilities (float dtype, dense [rows, experts]) the indices
  * (uint32 [rows, k]) of the k largest in the stable ascending order of a sort with NaN last, and

@@ -1,0 +1,322 @@
+// qqmm: the product of two operands that are BOTH quantized to NVFP4 (4-bit E2M1 codes, one E4M3
+// scale per 16 values) on the tensor cores' native block-scaled path,
+//
+//     y[tok, n] = sum_k q(x)[tok, k] * w[n, k]
+//
+// where q(x) is x through its NVFP4 quantization (the reference's qqmm: fake_quant(x) followed by
+// the ordinary quantized product, crates/nuvec-core/src/products.rs:337-352, 317-324).  Both
+// operands reach the MMA as packed 4-bit codes with their scale factors:
+//
+//   tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16  D(tmem), A(smem), B(smem), SFA(tmem), SFB(tmem)
+//
+// A block of 16 codes times 16 codes sums exactly in float32 (products of two 2-bit significands),
+// and so does the block sum times the two E4M3 scales (8 more significant bits); only the order in
+// which the blocks are added differs from the reference's float32 product of the dequantized
+// operands, so the results agree within one output rounding -- unlike a product of bfloat16
+// activations forced onto this path, which the reference does not define.
+//
+// Pipeline per call: quantize x (the kernel of quantize.cu, the reference's bits), lay the two scale
+// arrays out the way the tensor core reads them (below), then the product kernel: one block per
+// 128 weight rows x BN tokens, a TMA producer thread, an MMA thread and four epilogue warps.
+//
+// Scale-factor layout.  For one MMA (128 rows, 64 k-values = 4 scales per row) the tensor core reads
+// 512 bytes placed by tcgen05.cp.32x128b.warpx4: byte (r % 32) * 16 + (r / 32) * 4 + s holds the
+// scale of row r, k-block s.  The arrays of the reference ([rows, K / 16], one byte per scale) are
+// re-laid-out into such 512-byte pieces, [row tile of 128][k-block of 256][4 pieces], so that a
+// stage's scales are one contiguous 2 KB bulk copy.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#include <cstring>
+
+namespace nvc {
+
+constexpr int QQ_BM = 128;        // weight rows per tile (UMMA M)
+constexpr int QQ_KB = 256;        // k-values per stage: one 128-byte swizzle row of packed codes
+constexpr int QQ_STEP = 64;       // k-values per MMA
+constexpr int QQ_STAGES = 4;
+constexpr int QQ_THREADS = 192;   // warp 0 TMA, warp 1 MMA + tensor memory, warps 2-5 epilogue
+constexpr uint32_t QQ_SF_BYTES = 4 * 512;  // the scales of 128 rows x 256 k-values
+
+// [rows, K / 16] scale bytes -> the tensor core's pieces (see above); rows and k-blocks past the
+// ends are zero (a zero scale times the zero codes TMA fills in).
+__global__ void __launch_bounds__(256) qq_scale_layout_kernel(const uint8_t *__restrict__ scales, int64_t rows, int64_t per_row,
+                                                              uint8_t *__restrict__ out, int64_t row_tiles, int64_t kblocks) {
+    const int64_t at = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t total = row_tiles * kblocks * QQ_SF_BYTES;
+    if (at >= total) return;
+    const int64_t piece = at / 512, in_piece = at % 512;
+    const int64_t step = piece % 4, kb = (piece / 4) % kblocks, rt = piece / (4 * kblocks);
+    const int64_t r = rt * 128 + (in_piece % 16) / 4 * 32 + in_piece / 16;
+    const int64_t s = kb * 16 + step * 4 + in_piece % 4;
+    out[at] = (r < rows && s < per_row) ? scales[r * per_row + s] : (uint8_t)0;
+}
+
+// Shared-memory descriptor of one 512-byte scale piece for tcgen05.cp: 32 rows of 16 bytes, no
+// swizzle, 8-row core matrices 128 bytes apart.
+__device__ __forceinline__ uint64_t qq_sf_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(128 >> 4) << 32;  // stride byte offset
+    d |= (uint64_t)1 << 46;           // descriptor version for sm_100
+    return d;
+}
+__device__ __forceinline__ void qq_cp_scales(uint32_t tmem_addr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void qq_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+// Instruction descriptor of kind::mxf4nvf4: A and B E2M1 (format 1 of this kind), both K-major,
+// E4M3 scales (scale format 0), M = 128, N = n, scale-factor ids 0, K = 64.
+__host__ __device__ constexpr uint32_t qq_idesc(int n) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (0u << 23) | ((uint32_t)(QQ_BM >> 4) << 24);
+}
+// untiled bulk copy global -> shared, completing on an mbarrier
+__device__ __forceinline__ void qq_bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+struct QqParams {
+    const uint8_t *sfa, *sfb;  // re-laid-out scales of the weights / the activations
+    uint16_t *y;               // bfloat16 [tokens, N]
+    int32_t *error;
+    int32_t tokens, N, kblocks;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(QQ_THREADS, 1)
+qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, QqParams p) {
+    constexpr uint32_t A_BYTES = QQ_BM * 128, B_BYTES = BN * 128;
+    constexpr uint32_t SFB_BYTES = (BN / 128) * QQ_SF_BYTES;
+    constexpr uint32_t STAGE_TX = A_BYTES + B_BYTES + QQ_SF_BYTES + SFB_BYTES;
+    // tensor-memory columns behind the accumulator: per MMA step 4 columns of weight scales (128 rows) and
+    // 4 per 128 tokens of activation scales, the tokens' halves side by side
+    constexpr int SFA_COL = BN, SFB_COL = BN + 16, SFB_STEP = 4 * (BN / 128);
+    constexpr int TMEM_COLS = BN + 16 + 4 * SFB_STEP <= 256 ? 256 : 512;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *as = smem;                                  // [stage][128 rows x 128 B], 128-byte swizzle
+    uint8_t *bs = as + QQ_STAGES * A_BYTES;              // [stage][BN rows x 128 B]
+    uint8_t *sfa = bs + QQ_STAGES * B_BYTES;             // [stage][4 pieces x 512 B]
+    uint8_t *sfb = sfa + QQ_STAGES * QQ_SF_BYTES;        // [stage][BN / 128][4 pieces x 512 B]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sfb + QQ_STAGES * SFB_BYTES);
+    uint64_t *full = bars, *empty = full + QQ_STAGES, *accfull = empty + QQ_STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accfull + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    uint8_t *stage_out = reinterpret_cast<uint8_t *>(bars) + 256;  // epilogue: [4 warps][32 tokens][32 rows] bfloat16
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * QQ_BM, tok0 = blockIdx.y * BN;
+    if (tid == 0) {
+        for (int s = 0; s < QQ_STAGES; s++) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(accfull, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ── producer: codes by TMA, scales by bulk copies, one barrier per stage ───────────────
+        if (lane == 0) {
+            const uint8_t *sfa_src = p.sfa + (size_t)blockIdx.x * p.kblocks * QQ_SF_BYTES;
+            const uint8_t *sfb_src = p.sfb + (size_t)blockIdx.y * (BN / 128) * p.kblocks * QQ_SF_BYTES;
+            bool ok = true;
+            for (int kb = 0; kb < p.kblocks && ok; kb++) {
+                const uint32_t s = kb % QQ_STAGES, ph = (kb / QQ_STAGES) & 1;
+                ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(full + s, STAGE_TX);
+                tma_load_2d(as + s * A_BYTES, &tmap_w, kb * 128, n0, full + s);
+                tma_load_2d(bs + s * B_BYTES, &tmap_x, kb * 128, tok0, full + s);
+                qq_bulk_load(sfa + s * QQ_SF_BYTES, sfa_src + (size_t)kb * QQ_SF_BYTES, QQ_SF_BYTES, full + s);
+#pragma unroll
+                for (int h = 0; h < BN / 128; h++)
+                    qq_bulk_load(sfb + s * SFB_BYTES + h * QQ_SF_BYTES, sfb_src + ((size_t)h * p.kblocks + kb) * QQ_SF_BYTES, QQ_SF_BYTES,
+                                 full + s);
+            }
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer: per 64 k-values the scales go shared -> tensor memory, then one MMA ─────
+        if (lane == 0) {
+            constexpr uint32_t idesc = qq_idesc(BN);
+            bool ok = true;
+            for (int kb = 0; kb < p.kblocks && ok; kb++) {
+                const uint32_t s = kb % QQ_STAGES, ph = (kb / QQ_STAGES) & 1;
+                ok = mbar_wait(full + s, ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t ad = umma_desc(smem_u32(as + s * A_BYTES)), bd = umma_desc(smem_u32(bs + s * B_BYTES));
+#pragma unroll
+                for (int step = 0; step < QQ_KB / QQ_STEP; step++) {
+                    qq_cp_scales(tmem_base + SFA_COL + 4 * step, qq_sf_desc(smem_u32(sfa + s * QQ_SF_BYTES + step * 512)));
+#pragma unroll
+                    for (int h = 0; h < BN / 128; h++)
+                        qq_cp_scales(tmem_base + SFB_COL + SFB_STEP * step + 4 * h,
+                                     qq_sf_desc(smem_u32(sfb + s * SFB_BYTES + h * QQ_SF_BYTES + step * 512)));
+                    qq_mma(tmem_base, ad + (uint64_t)(2 * step), bd + (uint64_t)(2 * step), idesc, tmem_base + SFA_COL + 4 * step,
+                           tmem_base + SFB_COL + SFB_STEP * step, kb != 0 || step != 0);
+                }
+                tc_commit(empty + s);
+            }
+            tc_commit(accfull);
+        }
+    } else {
+        // ── epilogue: warp q owns tensor-memory lanes 32 q .. 32 q + 31 = weight rows n0 + 32 q + lane ──
+        const int q = warp & 3;
+        bool ok = mbar_wait(accfull, 0, abort_flag);
+        tc_fence_after();
+        const bool wide = (p.N & 7) == 0 && ((uintptr_t)p.y & 15) == 0;
+        uint8_t *mine = stage_out + q * 2048;
+        const int t8 = lane >> 2, g8 = lane & 3;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32 && ok; c++) {
+            uint32_t v[32];
+            tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c * 32, v);
+            tc_ld_wait();
+            if (tok0 + c * 32 >= p.tokens) continue;
+            if (wide) {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    *reinterpret_cast<uint16_t *>(mine + j * 64 + lane * 2) = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(v[j])));
+                __syncwarp();
+                const int ng = n0 + q * 32 + g8 * 8;
+                uint16_t *dst = p.y + (size_t)(tok0 + c * 32 + t8) * p.N + ng;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint4 piece = *reinterpret_cast<const uint4 *>(mine + (i * 8 + t8) * 64 + g8 * 16);
+                    if (ng < p.N && tok0 + c * 32 + i * 8 + t8 < p.tokens) *reinterpret_cast<uint4 *>(dst + (size_t)(i * 8) * p.N) = piece;
+                }
+                __syncwarp();
+            } else {
+                const int n = n0 + q * 32 + lane;
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int tok = tok0 + c * 32 + j;
+                        if (tok < p.tokens) p.y[(size_t)tok * p.N + n] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(v[j])));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag && p.error) *p.error = 1;
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*QqEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+static int32_t qq_map(CUtensorMap *map, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+    static QqEncodeFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return (QqEncodeFn)ptr;
+    }();
+    if (!fn) return set_error(NVC_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {row_bytes, rows}, strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows}, estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(NVC_ERR_DRIVER, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return NVC_OK;
+}
+
+template <int BN>
+static int32_t qq_launch(nvc_device *dev, const CUtensorMap &mw, const CUtensorMap &mx, const QqParams &p, int64_t tokens, int64_t N) {
+    constexpr size_t smem = 1024 + QQ_STAGES * (QQ_BM * 128 + BN * 128 + QQ_SF_BYTES + (BN / 128) * QQ_SF_BYTES) + 256 + 4 * 2048;
+    auto kernel = qqmm_kernel<BN>;
+    static bool configured[64] = {};
+    static std::mutex mu;
+    if (dev->ordinal < 0 || dev->ordinal >= 64) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: device ordinal %d", dev->ordinal);
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (!configured[dev->ordinal]) {
+            NVC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured[dev->ordinal] = true;
+        }
+    }
+    dim3 grid((unsigned)((N + QQ_BM - 1) / QQ_BM), (unsigned)((tokens + BN - 1) / BN));
+    kernel<<<grid, QQ_THREADS, smem, dev->stream>>>(mw, mx, p);
+    return check_launch(dev, "qqmm_kernel");
+}
+
+}  // namespace nvc
+
+using namespace nvc;
+
+extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w, const void *w_scales, int64_t M,
+                            int64_t N, int64_t K, void *y) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("qqmm", q));
+    if (q->mode != NVC_NVFP4) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: only nvfp4 weights take the block-scaled path");
+    if (dtype != NVC_BF16) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: bfloat16 activations only (dtype %d)", dtype);
+    if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
+        return set_error(NVC_ERR_INVALID_ARGUMENT, "qqmm: invalid shape");
+    if (K % QQ_STEP != 0) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: K = %lld is not a multiple of %d", (long long)K, QQ_STEP);
+    if (M * N == 0) return NVC_OK;
+    if (K == 0) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: empty inner dimension");
+    if (!x || !w || !w_scales || !y) return set_error(NVC_ERR_INVALID_ARGUMENT, "qqmm: null operand");
+    if ((uintptr_t)w % 16 != 0 || (K / 2) % 16 != 0) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: the packed weights must be 16-byte aligned rows");
+    if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: not inside a recorded step (it takes scratch from the pool)");
+
+    const int bn = M > 128 ? 256 : 128;
+    const int64_t kblocks = (K + QQ_KB - 1) / QQ_KB, wt = (N + 127) / 128, xt = (M + bn - 1) / bn * (bn / 128);
+    void *xq = nullptr, *xs = nullptr, *sfa = nullptr, *sfb = nullptr;
+    NVC_TRY(dev->pool.alloc((size_t)M * (K / 2), &xq));
+    int32_t rc = dev->pool.alloc((size_t)M * (K / 16), &xs);
+    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)wt * kblocks * QQ_SF_BYTES, &sfa);
+    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)xt * kblocks * QQ_SF_BYTES, &sfb);
+    auto release = [&]() {  // (the pool hands the blocks out again in stream order)
+        if (xq) dev->pool.free(xq);
+        if (xs) dev->pool.free(xs);
+        if (sfa) dev->pool.free(sfa);
+        if (sfb) dev->pool.free(sfb);
+    };
+    if (rc != NVC_OK) {
+        release();
+        return rc;
+    }
+    // x through its quantization: the codes and scales the reference's quantize gives
+    rc = nvc_quantize(dev, q, NVC_BF16, x, M, K, nullptr, (uint32_t *)xq, xs, nullptr);
+    if (rc == NVC_OK) {
+        const int64_t na = wt * kblocks * QQ_SF_BYTES, nb = xt * kblocks * QQ_SF_BYTES;
+        qq_scale_layout_kernel<<<(unsigned)((na + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / 16, (uint8_t *)sfa, wt, kblocks);
+        qq_scale_layout_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)xs, M, K / 16, (uint8_t *)sfb, xt, kblocks);
+        rc = check_launch(dev, "qq_scale_layout_kernel");
+    }
+    CUtensorMap mw, mx;
+    if (rc == NVC_OK) rc = qq_map(&mw, w, (uint64_t)K / 2, (uint64_t)N, 128);
+    if (rc == NVC_OK) rc = qq_map(&mx, xq, (uint64_t)K / 2, (uint64_t)M, (uint32_t)bn);
+    if (rc == NVC_OK) rc = ensure_error_word(dev);
+    if (rc == NVC_OK) {
+        QqParams p{(const uint8_t *)sfa, (const uint8_t *)sfb, (uint16_t *)y, dev->error_word_dev, (int32_t)M, (int32_t)N, (int32_t)kblocks};
+        rc = bn == 256 ? qq_launch<256>(dev, mw, mx, p, M, N) : qq_launch<128>(dev, mw, mx, p, M, N);
+    }
+    release();
+    return rc;
+}

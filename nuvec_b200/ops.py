@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "qqmm", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -618,6 +618,28 @@ def quantized_embedding(q: Quantized, ids: Array) -> Array:
     c = quant._c()
     _check(_ffi.lib().nvc_quantized_embedding(dev._h, C.byref(c), dtype, q.weight.ptr, q.scales.ptr, _ptr(q.biases),
                                               q.weight.shape[0], cols, ids.ptr, ids.size, out.ptr))
+    return out
+
+
+def qqmm(x: Array, q: Quantized) -> Array:
+    """MLX's qqmm (crates/nuvec-core/src/products.rs:337-352): x through its own quantization in q's mode, times
+    the quantized weight transposed.  NVFP4 weights without a global scale, bfloat16 x [..., K]."""
+    quant = q.quant
+    quant.checked("qqmm")
+    if quant.mode == QuantMode.AFFINE:
+        raise InvalidArgument("qqmm: needs a floating-point mode (mxfp4, mxfp8 or nvfp4)")
+    if quant.mode != QuantMode.NVFP4 or q.global_scale is not None:
+        raise UnsupportedError("qqmm: only nvfp4 weights without a global scale take the block-scaled path")
+    if x.dtype != BF16 or x.ndim < 1 or q.weight.ndim != 2:
+        raise UnsupportedError("qqmm: bfloat16 activations [..., K] and a 2-D quantized weight expected")
+    K = x.shape[-1]
+    N = q.weight.shape[0]
+    if q.weight.shape[1] * 8 != K:
+        raise InvalidArgument(f"qqmm: shapes {list(x.shape)} and {list(q.weight.shape)} do not match")
+    M = x.size // K if K else 0
+    out = x.dev.empty(tuple(x.shape[:-1]) + (N,), BF16)
+    c = quant._c()
+    _check(_ffi.lib().nvc_qqmm(x.dev._h, C.byref(c), BF16, x.ptr, q.weight.ptr, q.scales.ptr, M, N, K, out.ptr))
     return out
 
 
