@@ -281,6 +281,9 @@ def main():
     ap.add_argument("--one", default=None, metavar="M,N,K,BITS,COPIES",
                     help="profiling driver: one product shape on COPIES distinct weight sets, each launched twice "
                          "(prints the device time per launch); what the ncu commands under profiles/ run")
+    ap.add_argument("--qqmm", default=None, metavar="M,N,K,COPIES",
+                    help="the NVFP4 x NVFP4 product on the block-scaled tensor-core path (nvc_qqmm: activations "
+                         "quantized on the way) next to the exact product of the same weights with bfloat16 activations")
     ap.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
                     help="diagnostic: replay a recorded decode step of LAYERS layers on the timeline build of the "
                          "library (python -m nuvec_b200.build --timeline) and print where each product's time goes")
@@ -320,6 +323,8 @@ def main():
         return
     if args.one:
         return one_shape(args, nv, _ffi, dev)
+    if args.qqmm:
+        return qqmm_shape(args, nv, _ffi, dev, peaks)
     if args.timeline:
         return timeline(args, nv, _ffi, dev)
     if args.workload == "moe":
@@ -743,6 +748,42 @@ def one_shape(args, nv, _ffi, dev):
                  "dequantizers 3", "epilogue"]
         out["role_cycles"] = {f"block {b}": {r: t[b, i].tolist() for i, r in enumerate(roles)} for b in range(2)}
     print(json.dumps(out))
+
+
+# ── NVFP4 x NVFP4 on the block-scaled path (--qqmm) ─────────────────────────────────────────
+def qqmm_shape(args, nv, _ffi, dev, peaks):
+    """nvc_qqmm (quantize x, lay out the scales, block-scaled MMA) and, beside it, nvc_quantized_matmul of
+    the same NVFP4 weights with bfloat16 activations (weights dequantized exactly into tensor memory), on
+    COPIES distinct weight sets; device time per product from CUDA events."""
+    M, N, K, copies = (int(v) for v in args.qqmm.split(","))
+    lib = _ffi.lib()
+    rng = np.random.default_rng(0)
+    quant = nv.Quant(nv.QuantMode("nvfp4"), 16, 4)
+    qc = quant._c()
+    codes = rng.integers(0, 2 ** 32, (N, K // 8), dtype=np.uint32)
+    scales = rng.integers(0x08, 0x30, (N, K // 16), dtype=np.uint8)
+    x = dev.array(nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32)), nv.BF16)
+    sets = [(dev.array(codes, nv.U32), dev.array(scales, nv.U8), dev.empty((M, N), nv.BF16)) for _ in range(copies)]
+    dev.synchronize()
+
+    def timed(call):
+        e0, e1 = dev.event(), dev.event()
+        for rnd in range(3):
+            if rnd == 1:
+                e0.record()
+            for c, s, y in sets:
+                assert call(c, s, y) == 0, _ffi.last_error()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_ms(e1) * 1e3 / (2 * copies)
+    us_qq = timed(lambda c, s, y: lib.nvc_qqmm(dev._h, C.byref(qc), nv.BF16, x.ptr, c.ptr, s.ptr, M, N, K, y.ptr))
+    us_exact = timed(lambda c, s, y: lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, c.ptr, s.ptr, None, None,
+                                                              M, N, K, K, 1, 0, 0, 0, y.ptr))
+    flops = 2.0 * M * N * K
+    print(json.dumps({"qqmm": args.qqmm, "us_qqmm": us_qq, "TFLOP/s_qqmm": flops / us_qq / 1e6,
+                      "us_exact_bf16_activations": us_exact, "TFLOP/s_exact": flops / us_exact / 1e6,
+                      "frac_of_measured_bf16_burst_qqmm": flops / us_qq / 1e6 / peaks["bf16_tflops"],
+                      "note": "qqmm includes the quantization of x and the layout of both scale arrays"}))
 
 
 # ── where a decode product's time goes (--timeline) ──────────────────────────────────────────

@@ -1,5 +1,6 @@
 // qqmm: the product of two operands that are BOTH quantized to NVFP4 (4-bit E2M1 codes, one E4M3
-// scale per 16 values) on the tensor cores' native block-scaled path,
+// scale per 16 values) or both to MXFP4 (one E8M0 scale per 32) on the tensor cores' native
+// block-scaled path,
 //
 //     y[tok, n] = sum_k q(x)[tok, k] * w[n, k]
 //
@@ -8,6 +9,9 @@
 // operands reach the MMA as packed 4-bit codes with their scale factors:
 //
 //   tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16  D(tmem), A(smem), B(smem), SFA(tmem), SFB(tmem)
+//   tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32      (MXFP4: two scales per row and MMA; a piece
+//                                                                 of four serves two MMAs, the second through
+//                                                                 scale-factor id 2 = byte 2 of the column)
 //
 // A block of 16 codes times 16 codes sums exactly in float32 (products of two 2-bit significands),
 // and so does the block sum times the two E4M3 scales (8 more significant bits); only the order in
@@ -36,19 +40,20 @@ constexpr int QQ_KB = 256;        // k-values per stage: one 128-byte swizzle ro
 constexpr int QQ_STEP = 64;       // k-values per MMA
 constexpr int QQ_STAGES = 4;
 constexpr int QQ_THREADS = 192;   // warp 0 TMA, warp 1 MMA + tensor memory, warps 2-5 epilogue
-constexpr uint32_t QQ_SF_BYTES = 4 * 512;  // the scales of 128 rows x 256 k-values
+// 512-byte scale pieces (128 rows x 4 scales) per 128 rows and stage: 4 with a scale per 16 values, 2 per 32
+__host__ __device__ constexpr int qq_pieces(int vs) { return QQ_KB / vs / 4; }
 
 // [rows, K / 16] scale bytes -> the tensor core's pieces (see above); rows and k-blocks past the
 // ends are zero (a zero scale times the zero codes TMA fills in).
 __global__ void __launch_bounds__(256) qq_scale_layout_kernel(const uint8_t *__restrict__ scales, int64_t rows, int64_t per_row,
-                                                              uint8_t *__restrict__ out, int64_t row_tiles, int64_t kblocks) {
+                                                              uint8_t *__restrict__ out, int64_t row_tiles, int64_t kblocks, int pieces) {
     const int64_t at = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    const int64_t total = row_tiles * kblocks * QQ_SF_BYTES;
+    const int64_t total = row_tiles * kblocks * pieces * 512;
     if (at >= total) return;
     const int64_t piece = at / 512, in_piece = at % 512;
-    const int64_t step = piece % 4, kb = (piece / 4) % kblocks, rt = piece / (4 * kblocks);
+    const int64_t step = piece % pieces, kb = (piece / pieces) % kblocks, rt = piece / (pieces * kblocks);
     const int64_t r = rt * 128 + (in_piece % 16) / 4 * 32 + in_piece / 16;
-    const int64_t s = kb * 16 + step * 4 + in_piece % 4;
+    const int64_t s = (kb * pieces + step) * 4 + in_piece % 4;
     out[at] = (r < rows && s < per_row) ? scales[r * per_row + s] : (uint8_t)0;
 }
 
@@ -64,18 +69,28 @@ __device__ __forceinline__ uint64_t qq_sf_desc(uint32_t smem_addr) {
 __device__ __forceinline__ void qq_cp_scales(uint32_t tmem_addr, uint64_t desc) {
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
 }
+template <int VS>
 __device__ __forceinline__ void qq_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
                                        uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+    if (VS == 16)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 }
-// Instruction descriptor of kind::mxf4nvf4: A and B E2M1 (format 1 of this kind), both K-major,
-// E4M3 scales (scale format 0), M = 128, N = n, scale-factor ids 0, K = 64.
-__host__ __device__ constexpr uint32_t qq_idesc(int n) {
-    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (0u << 23) | ((uint32_t)(QQ_BM >> 4) << 24);
+// Instruction descriptor of the 4-bit block-scaled kinds: A and B E2M1 (format 1 of these kinds), both
+// K-major, M = 128, N = n, K = 64; E4M3 scales (format 0) per 16 values or E8M0 (format 1) per 32;
+// `sf` = the byte of the scale columns this MMA starts at (0, or 2 for the second MMA of a piece).
+__host__ __device__ constexpr uint32_t qq_idesc(int n, int vs, uint32_t sf) {
+    return (sf << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((vs == 32 ? 1u : 0u) << 23) |
+           ((uint32_t)(QQ_BM >> 4) << 24) | (sf << 29);
 }
 // untiled bulk copy global -> shared, completing on an mbarrier
 __device__ __forceinline__ void qq_bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
@@ -90,10 +105,13 @@ struct QqParams {
     int32_t tokens, N, kblocks;
 };
 
-template <int BN>
+template <int BN, int VS>
 __global__ void __launch_bounds__(QQ_THREADS, 1)
 qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, QqParams p) {
     constexpr uint32_t A_BYTES = QQ_BM * 128, B_BYTES = BN * 128;
+    constexpr int PIECES = qq_pieces(VS);                  // scale pieces per 128 rows and stage
+    constexpr int STEPS_PER_PIECE = 4 / PIECES;            // MMAs a piece serves: 1 (4 scales per MMA) or 2
+    constexpr uint32_t QQ_SF_BYTES = PIECES * 512;
     constexpr uint32_t SFB_BYTES = (BN / 128) * QQ_SF_BYTES;
     constexpr uint32_t STAGE_TX = A_BYTES + B_BYTES + QQ_SF_BYTES + SFB_BYTES;
     // tensor-memory columns behind the accumulator: per MMA step 4 columns of weight scales (128 rows) and
@@ -104,8 +122,8 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *as = smem;                                  // [stage][128 rows x 128 B], 128-byte swizzle
     uint8_t *bs = as + QQ_STAGES * A_BYTES;              // [stage][BN rows x 128 B]
-    uint8_t *sfa = bs + QQ_STAGES * B_BYTES;             // [stage][4 pieces x 512 B]
-    uint8_t *sfb = sfa + QQ_STAGES * QQ_SF_BYTES;        // [stage][BN / 128][4 pieces x 512 B]
+    uint8_t *sfa = bs + QQ_STAGES * B_BYTES;             // [stage][pieces x 512 B]
+    uint8_t *sfb = sfa + QQ_STAGES * QQ_SF_BYTES;        // [stage][BN / 128][pieces x 512 B]
     uint64_t *bars = reinterpret_cast<uint64_t *>(sfb + QQ_STAGES * SFB_BYTES);
     uint64_t *full = bars, *empty = full + QQ_STAGES, *accfull = empty + QQ_STAGES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accfull + 1);
@@ -155,7 +173,6 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     } else if (warp == 1) {
         // ── MMA issuer: per 64 k-values the scales go shared -> tensor memory, then one MMA ─────
         if (lane == 0) {
-            constexpr uint32_t idesc = qq_idesc(BN);
             bool ok = true;
             for (int kb = 0; kb < p.kblocks && ok; kb++) {
                 const uint32_t s = kb % QQ_STAGES, ph = (kb / QQ_STAGES) & 1;
@@ -165,13 +182,18 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 const uint64_t ad = umma_desc(smem_u32(as + s * A_BYTES)), bd = umma_desc(smem_u32(bs + s * B_BYTES));
 #pragma unroll
                 for (int step = 0; step < QQ_KB / QQ_STEP; step++) {
-                    qq_cp_scales(tmem_base + SFA_COL + 4 * step, qq_sf_desc(smem_u32(sfa + s * QQ_SF_BYTES + step * 512)));
+                    const int piece = step / STEPS_PER_PIECE;
+                    const uint32_t sf = (uint32_t)(step % STEPS_PER_PIECE) * 2u;  // byte of the piece's columns this MMA starts at
+                    if (step % STEPS_PER_PIECE == 0) {
+                        qq_cp_scales(tmem_base + SFA_COL + 4 * piece, qq_sf_desc(smem_u32(sfa + s * QQ_SF_BYTES + piece * 512)));
 #pragma unroll
-                    for (int h = 0; h < BN / 128; h++)
-                        qq_cp_scales(tmem_base + SFB_COL + SFB_STEP * step + 4 * h,
-                                     qq_sf_desc(smem_u32(sfb + s * SFB_BYTES + h * QQ_SF_BYTES + step * 512)));
-                    qq_mma(tmem_base, ad + (uint64_t)(2 * step), bd + (uint64_t)(2 * step), idesc, tmem_base + SFA_COL + 4 * step,
-                           tmem_base + SFB_COL + SFB_STEP * step, kb != 0 || step != 0);
+                        for (int h = 0; h < BN / 128; h++)
+                            qq_cp_scales(tmem_base + SFB_COL + SFB_STEP * piece + 4 * h,
+                                         qq_sf_desc(smem_u32(sfb + s * SFB_BYTES + h * QQ_SF_BYTES + piece * 512)));
+                    }
+                    qq_mma<VS>(tmem_base, ad + (uint64_t)(2 * step), bd + (uint64_t)(2 * step), qq_idesc(BN, VS, sf),
+                               (tmem_base + SFA_COL + 4 * piece) | (sf << 30), (tmem_base + SFB_COL + SFB_STEP * piece) | (sf << 30),
+                               kb != 0 || step != 0);
                 }
                 tc_commit(empty + s);
             }
@@ -246,10 +268,11 @@ static int32_t qq_map(CUtensorMap *map, const void *base, uint64_t row_bytes, ui
     return NVC_OK;
 }
 
-template <int BN>
+template <int BN, int VS>
 static int32_t qq_launch(nvc_device *dev, const CUtensorMap &mw, const CUtensorMap &mx, const QqParams &p, int64_t tokens, int64_t N) {
-    constexpr size_t smem = 1024 + QQ_STAGES * (QQ_BM * 128 + BN * 128 + QQ_SF_BYTES + (BN / 128) * QQ_SF_BYTES) + 256 + 4 * 2048;
-    auto kernel = qqmm_kernel<BN>;
+    constexpr size_t sf_bytes = qq_pieces(VS) * 512;
+    constexpr size_t smem = 1024 + QQ_STAGES * (QQ_BM * 128 + BN * 128 + sf_bytes + (BN / 128) * sf_bytes) + 256 + 4 * 2048;
+    auto kernel = qqmm_kernel<BN, VS>;
     static bool configured[64] = {};
     static std::mutex mu;
     if (dev->ordinal < 0 || dev->ordinal >= 64) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: device ordinal %d", dev->ordinal);
@@ -273,7 +296,10 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
                             int64_t N, int64_t K, void *y) {
     NVC_TRY(make_current(dev));
     NVC_TRY(check_quant("qqmm", q));
-    if (q->mode != NVC_NVFP4) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: only nvfp4 weights take the block-scaled path");
+    if (q->mode != NVC_NVFP4 && q->mode != NVC_MXFP4)
+        return set_error(NVC_ERR_UNSUPPORTED, "qqmm: nvfp4 and mxfp4 weights take the block-scaled path (mode %d)", q->mode);
+    const int vs = q->group_size;  // 16 (nvfp4) or 32 (mxfp4)
+    const size_t sf_bytes = (size_t)qq_pieces(vs) * 512;
     if (dtype != NVC_BF16) return set_error(NVC_ERR_UNSUPPORTED, "qqmm: bfloat16 activations only (dtype %d)", dtype);
     if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX)
         return set_error(NVC_ERR_INVALID_ARGUMENT, "qqmm: invalid shape");
@@ -288,9 +314,9 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
     const int64_t kblocks = (K + QQ_KB - 1) / QQ_KB, wt = (N + 127) / 128, xt = (M + bn - 1) / bn * (bn / 128);
     void *xq = nullptr, *xs = nullptr, *sfa = nullptr, *sfb = nullptr;
     NVC_TRY(dev->pool.alloc((size_t)M * (K / 2), &xq));
-    int32_t rc = dev->pool.alloc((size_t)M * (K / 16), &xs);
-    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)wt * kblocks * QQ_SF_BYTES, &sfa);
-    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)xt * kblocks * QQ_SF_BYTES, &sfb);
+    int32_t rc = dev->pool.alloc((size_t)M * (K / vs), &xs);
+    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)wt * kblocks * sf_bytes, &sfa);
+    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)xt * kblocks * sf_bytes, &sfb);
     auto release = [&]() {  // (the pool hands the blocks out again in stream order)
         if (xq) dev->pool.free(xq);
         if (xs) dev->pool.free(xs);
@@ -304,9 +330,12 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
     // x through its quantization: the codes and scales the reference's quantize gives
     rc = nvc_quantize(dev, q, NVC_BF16, x, M, K, nullptr, (uint32_t *)xq, xs, nullptr);
     if (rc == NVC_OK) {
-        const int64_t na = wt * kblocks * QQ_SF_BYTES, nb = xt * kblocks * QQ_SF_BYTES;
-        qq_scale_layout_kernel<<<(unsigned)((na + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / 16, (uint8_t *)sfa, wt, kblocks);
-        qq_scale_layout_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)xs, M, K / 16, (uint8_t *)sfb, xt, kblocks);
+        const int64_t na = wt * kblocks * (int64_t)sf_bytes, nb = xt * kblocks * (int64_t)sf_bytes;
+        const int pieces = qq_pieces(vs);
+        qq_scale_layout_kernel<<<(unsigned)((na + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / vs, (uint8_t *)sfa, wt, kblocks,
+                                                                                      pieces);
+        qq_scale_layout_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)xs, M, K / vs, (uint8_t *)sfb, xt, kblocks,
+                                                                                      pieces);
         rc = check_launch(dev, "qq_scale_layout_kernel");
     }
     CUtensorMap mw, mx;
@@ -315,7 +344,8 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
     if (rc == NVC_OK) rc = ensure_error_word(dev);
     if (rc == NVC_OK) {
         QqParams p{(const uint8_t *)sfa, (const uint8_t *)sfb, (uint16_t *)y, dev->error_word_dev, (int32_t)M, (int32_t)N, (int32_t)kblocks};
-        rc = bn == 256 ? qq_launch<256>(dev, mw, mx, p, M, N) : qq_launch<128>(dev, mw, mx, p, M, N);
+        if (vs == 16) rc = bn == 256 ? qq_launch<256, 16>(dev, mw, mx, p, M, N) : qq_launch<128, 16>(dev, mw, mx, p, M, N);
+        else rc = bn == 256 ? qq_launch<256, 32>(dev, mw, mx, p, M, N) : qq_launch<128, 32>(dev, mw, mx, p, M, N);
     }
     release();
     return rc;

@@ -623,13 +623,13 @@ def quantized_embedding(q: Quantized, ids: Array) -> Array:
 
 def qqmm(x: Array, q: Quantized) -> Array:
     """MLX's qqmm (crates/nuvec-core/src/products.rs:337-352): x through its own quantization in q's mode, times
-    the quantized weight transposed.  NVFP4 weights without a global scale, bfloat16 x [..., K]."""
+    the quantized weight transposed.  NVFP4 (without a global scale) or MXFP4 weights, bfloat16 x [..., K]."""
     quant = q.quant
     quant.checked("qqmm")
     if quant.mode == QuantMode.AFFINE:
         raise InvalidArgument("qqmm: needs a floating-point mode (mxfp4, mxfp8 or nvfp4)")
-    if quant.mode != QuantMode.NVFP4 or q.global_scale is not None:
-        raise UnsupportedError("qqmm: only nvfp4 weights without a global scale take the block-scaled path")
+    if quant.mode not in (QuantMode.NVFP4, QuantMode.MXFP4) or q.global_scale is not None:
+        raise UnsupportedError("qqmm: nvfp4 (without a global scale) and mxfp4 weights take the block-scaled path")
     if x.dtype != BF16 or x.ndim < 1 or q.weight.ndim != 2:
         raise UnsupportedError("qqmm: bfloat16 activations [..., K] and a 2-D quantized weight expected")
     K = x.shape[-1]

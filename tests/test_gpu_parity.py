@@ -550,9 +550,10 @@ def test_quantized_embedding_is_take_then_dequantize(be):
         assert np.array_equal(got, want), name
 
 
+@pytest.mark.parametrize("mode", ["nvfp4", "mxfp4"])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 256), (64, 256, 512), (1, 128, 64), (300, 384, 1024), (96, 256, 2880),
                                    (513, 1000, 320), (2048, 1024, 4096)])
-def test_qqmm_on_the_block_scaled_tensor_core_path(be, M, N, K):
+def test_qqmm_on_the_block_scaled_tensor_core_path(be, M, N, K, mode):
     # MLX's qqmm (crates/nuvec-core/src/products.rs:337-352): x through its own NVFP4 quantization, then the
     # ordinary quantized product.  The kernel feeds both operands to tcgen05.mma.kind::mxf4nvf4.block_scale
     # as 4-bit codes with their scales; every block's scaled sum is exact in float32, so the result
@@ -560,17 +561,17 @@ def test_qqmm_on_the_block_scaled_tensor_core_path(be, M, N, K):
     import nuvec_b200 as nv
     dev = nv.Device.shared(0)
     rng = np.random.default_rng(M * 7 + N * 3 + K)
-    gs, bits = 16, 4
+    omode, gs, bits = (oracle.NVFP4, 16, 4) if mode == "nvfp4" else (oracle.MXFP4, 32, 4)
     w = rand(rng, (N, K), oracle.BF16, 0.05)
-    wc, ws, _ = oracle.quantize(w, oracle.BF16, oracle.NVFP4, gs, bits)
+    wc, ws, _ = oracle.quantize(w, oracle.BF16, omode, gs, bits)
     x = rand(rng, (M, K), oracle.BF16)
-    xc, xs, _ = oracle.quantize(x, oracle.BF16, oracle.NVFP4, gs, bits)
-    xhat = oracle.dequantize(xc, xs, None, oracle.BF16, oracle.NVFP4, gs, bits)   # fake_quant(x)
-    want = oracle.quantized_matmul(xhat, wc, ws, None, oracle.BF16, oracle.NVFP4, gs, bits)
-    q = nv.Quantized(dev.array(wc, nv.U32), dev.array(ws, nv.U8), None, nv.Quant(nv.QuantMode("nvfp4"), gs, bits))
+    xc, xs, _ = oracle.quantize(x, oracle.BF16, omode, gs, bits)
+    xhat = oracle.dequantize(xc, xs, None, oracle.BF16, omode, gs, bits)   # fake_quant(x)
+    want = oracle.quantized_matmul(xhat, wc, ws, None, oracle.BF16, omode, gs, bits)
+    q = nv.Quantized(dev.array(wc, nv.U32), dev.array(ws, nv.U8), None, nv.Quant(nv.QuantMode(mode), gs, bits))
     got = nv.qqmm(dev.array(x, nv.BF16), q).to_numpy().view(np.uint16)
-    assert_product_tight(got, want, oracle.BF16, f"qqmm {M}x{N}x{K}")
+    assert_product_tight(got, want, oracle.BF16, f"qqmm {mode} {M}x{N}x{K}")
     # and it is NOT the product of the unquantized activations: the activation rounding is the operation
-    plain = oracle.quantized_matmul(x, wc, ws, None, oracle.BF16, oracle.NVFP4, gs, bits)
+    plain = oracle.quantized_matmul(x, wc, ws, None, oracle.BF16, omode, gs, bits)
     if K >= 256 and M > 1:
         assert np.abs(oracle.to_f32(got, oracle.BF16) - oracle.to_f32(plain, oracle.BF16)).max() > 0
