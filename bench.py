@@ -682,6 +682,10 @@ def main():
     if not args.no_prefill:
         line["also"] = [prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier, not args.no_check)]
 
+    # ── the same prefill shape with both operands NVFP4 on the block-scaled path (one GPU) ─────
+    if not args.no_prefill and world == 1:
+        line["also"].append(qqmm_leg(nv, _ffi, dev, peaks, not args.no_check))
+
     # ── CPU baseline on this host's cores (rank 0, bounded sample) ───────────────────────────
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = use_all_host_threads()
@@ -777,10 +781,19 @@ def qqmm_shape(args, nv, _ffi, dev, peaks):
         e1.synchronize()
         return e0.elapsed_ms(e1) * 1e3 / (2 * copies)
     us_qq = timed(lambda c, s, y: lib.nvc_qqmm(dev._h, C.byref(qc), nv.BF16, x.ptr, c.ptr, s.ptr, M, N, K, y.ptr))
+    lib.nvc_qqmm_scales_bytes.restype = C.c_size_t
+    laid = []
+    for c, sc, y in sets:
+        buf = dev.empty((lib.nvc_qqmm_scales_bytes(C.byref(qc), N, K),), nv.U8)
+        assert lib.nvc_qqmm_prepare_scales(dev._h, C.byref(qc), sc.ptr, N, K, buf.ptr) == 0, _ffi.last_error()
+        laid.append(buf)
+    by_codes = {c.ptr.value: b for (c, _, _), b in zip(sets, laid)}
+    us_prep = timed(lambda c, s, y: lib.nvc_qqmm_prepared(dev._h, C.byref(qc), nv.BF16, x.ptr, c.ptr, by_codes[c.ptr.value].ptr, M, N, K, y.ptr))
     us_exact = timed(lambda c, s, y: lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, c.ptr, s.ptr, None, None,
                                                               M, N, K, K, 1, 0, 0, 0, y.ptr))
     flops = 2.0 * M * N * K
     print(json.dumps({"qqmm": args.qqmm, "us_qqmm": us_qq, "TFLOP/s_qqmm": flops / us_qq / 1e6,
+                      "us_qqmm_prepared_scales": us_prep, "TFLOP/s_qqmm_prepared_scales": flops / us_prep / 1e6,
                       "us_exact_bf16_activations": us_exact, "TFLOP/s_exact": flops / us_exact / 1e6,
                       "frac_of_measured_bf16_burst_qqmm": flops / us_qq / 1e6 / peaks["bf16_tflops"],
                       "note": "qqmm includes the quantization of x and the layout of both scale arrays"}))
@@ -1169,6 +1182,66 @@ def config_sweep(nv, _ffi, dev, peaks):
             moe("C5 moe down", T, 32, 4, 2880, 2880, quant, 10)
     return rows
 
+
+
+def qqmm_leg(nv, _ffi, dev, peaks, check=True):
+    """MLX's qqmm at the prefill shape: weights quantized to NVFP4 with the reference's quantize, x quantized
+    on the way by nvc_qqmm, the product on tcgen05.mma.kind::mxf4nvf4.block_scale.  Checked against the
+    oracle's product of the two dequantized operands on 64 weight rows before it is timed."""
+    M, N, K = PREFILL
+    rng = np.random.default_rng(2)
+    quant = nv.Quant(nv.QuantMode("nvfp4"), 16, 4)
+    w = nv.f32_to_bf16(rng.standard_normal((N, K), dtype=np.float32) * 0.02)
+    q0 = nv.quantize(dev.array(w, nv.BF16), quant)
+    xh = nv.f32_to_bf16(rng.standard_normal((M, K), dtype=np.float32))
+    x = dev.array(xh, nv.BF16)
+    copies = 4
+    sets = []
+    for i in range(copies):
+        c, sc = dev.empty(q0.weight.shape, nv.U32), dev.empty(q0.scales.shape, nv.U8)
+        c.copy_from(q0.weight), sc.copy_from(q0.scales)
+        sets.append((nv.Quantized(c, sc, None, quant), dev.empty((M, N), nv.BF16)))
+    lib = _ffi.lib()
+    qc = quant._c()
+
+    def run(qw, y):
+        rc = lib.nvc_qqmm(dev._h, C.byref(qc), nv.BF16, x.ptr, qw.weight.ptr, qw.scales.ptr, M, N, K, y.ptr)
+        assert rc == 0, _ffi.last_error()
+    parity = None
+    if check:
+        import oracle
+        rows, toks = 64, 256
+        run(*sets[0])
+        got = nv.bf16_to_f32(sets[0][1].to_numpy().view(np.uint16)[:toks, :rows])
+        wc, ws = q0.weight.to_numpy()[:rows], q0.scales.to_numpy()[:rows]
+        xc, xs, _ = oracle.quantize(xh[:toks], oracle.BF16, oracle.NVFP4, 16, 4)
+        xhat = oracle.dequantize(xc, xs, None, oracle.BF16, oracle.NVFP4, 16, 4)
+        want = nv.bf16_to_f32(oracle.quantized_matmul(xhat, wc, ws, None, oracle.BF16, oracle.NVFP4, 16, 4))
+        bound = 1e-2 * np.abs(want).max(-1, keepdims=True)
+        worst = float((np.abs(got - want) / bound).max())
+        if worst > 1.0:
+            raise SystemExit(f"parity check failed: qqmm differs from the oracle ({worst:.3f} of the bound)")
+        parity = {"status": "ok", "worst_error_over_bound": worst,
+                  "what": f"{toks} token rows x {rows} weight rows against the oracle's product of the dequantized operands"}
+    for qw, y in sets:
+        run(qw, y)
+    dev.synchronize()
+    e0, e1 = dev.event(), dev.event()
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        for qw, y in sets:
+            run(qw, y)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_ms(e1) / (reps * copies)
+    tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    return {"workload": f"qqmm M={M} K={K} N={N}: NVFP4 x NVFP4 (activations quantized on the way), block-scaled MMA",
+            "metric": "qqmm TFLOP/s (M=2048)", "value": tf, "unit": "TFLOP/s", "ms_per_product": ms,
+            "gpu_launches": reps * copies * 4, "parity_check": "ok" if parity else "skipped", "parity": parity,
+            "roofline": {"kernel": "qqmm_kernel", "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " (bf16 burst: no measured 4-bit peak exists; nominal dense fp4 is 4x the bf16 figure)"}}
 
 
 def prefill_bench(nv, _ffi, dev, peaks, rank, world, timed, barrier, check=True):

@@ -213,6 +213,15 @@ int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, int32
  * activations and the two scale arrays in the tensor core's layout): not inside a recorded step. */
 int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w,
                  const void *w_scales, int64_t M, int64_t N, int64_t K, void *y);
+/* The weight's scales laid out once (at load time) the way the tensor core reads them, instead of at every
+ * call: nvc_qqmm_scales_bytes gives the size of that array (0 for an unsupported quantization),
+ * nvc_qqmm_prepare_scales fills it (out: device memory, 16-byte aligned), nvc_qqmm_prepared is nvc_qqmm with
+ * it in place of w_scales. */
+size_t nvc_qqmm_scales_bytes(const nvc_quant *q, int64_t N, int64_t K);
+int32_t nvc_qqmm_prepare_scales(nvc_device *dev, const nvc_quant *q, const void *w_scales, int64_t N, int64_t K,
+                                void *out);
+int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w,
+                          const void *laid_out_scales, int64_t M, int64_t N, int64_t K, void *y);
 
 /* fast::moe_route (crates/nuvec-core/src/fast/imp.rs:2652-2672; kernel crates/nuvec-kernels/src/metal/moe.metal):
  * per row of `experts` router probabilities (float dtype, dense [rows, experts]) the indices

@@ -43,18 +43,35 @@ constexpr int QQ_THREADS = 192;   // warp 0 TMA, warp 1 MMA + tensor memory, war
 // 512-byte scale pieces (128 rows x 4 scales) per 128 rows and stage: 4 with a scale per 16 values, 2 per 32
 __host__ __device__ constexpr int qq_pieces(int vs) { return QQ_KB / vs / 4; }
 
-// [rows, K / 16] scale bytes -> the tensor core's pieces (see above); rows and k-blocks past the
-// ends are zero (a zero scale times the zero codes TMA fills in).
+// [rows, K / vs] scale bytes -> the tensor core's pieces (see above); rows and k-blocks past the
+// ends are zero (a zero scale times the zero codes TMA fills in).  One thread per 16 bytes of a
+// piece: the four scales of one MMA step for rows r, r + 32, r + 64, r + 96.
 __global__ void __launch_bounds__(256) qq_scale_layout_kernel(const uint8_t *__restrict__ scales, int64_t rows, int64_t per_row,
                                                               uint8_t *__restrict__ out, int64_t row_tiles, int64_t kblocks, int pieces) {
-    const int64_t at = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    const int64_t total = row_tiles * kblocks * pieces * 512;
+    const int64_t at = (int64_t)blockIdx.x * 256 + threadIdx.x;  // index of the 16-byte unit
+    const int64_t total = row_tiles * kblocks * pieces * 32;
     if (at >= total) return;
-    const int64_t piece = at / 512, in_piece = at % 512;
+    const int64_t piece = at >> 5, m0 = at & 31;
     const int64_t step = piece % pieces, kb = (piece / pieces) % kblocks, rt = piece / (pieces * kblocks);
-    const int64_t r = rt * 128 + (in_piece % 16) / 4 * 32 + in_piece / 16;
-    const int64_t s = (kb * pieces + step) * 4 + in_piece % 4;
-    out[at] = (r < rows && s < per_row) ? scales[r * per_row + s] : (uint8_t)0;
+    const int64_t s0 = (kb * pieces + step) * 4;
+    uint32_t words[4];
+#pragma unroll
+    for (int m1 = 0; m1 < 4; m1++) {
+        const int64_t r = rt * 128 + m1 * 32 + m0;
+        uint32_t w = 0;
+        if (r < rows) {
+            const uint8_t *src = scales + r * per_row + s0;
+            if (s0 + 4 <= per_row && ((uintptr_t)src & 3) == 0) {
+                w = *reinterpret_cast<const uint32_t *>(src);
+            } else {
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+                    if (s0 + b < per_row) w |= (uint32_t)src[b] << (8 * b);
+            }
+        }
+        words[m1] = w;
+    }
+    reinterpret_cast<uint4 *>(out)[at] = make_uint4(words[0], words[1], words[2], words[3]);
 }
 
 // Shared-memory descriptor of one 512-byte scale piece for tcgen05.cp: 32 rows of 16 bytes, no
@@ -292,8 +309,9 @@ static int32_t qq_launch(nvc_device *dev, const CUtensorMap &mw, const CUtensorM
 
 using namespace nvc;
 
-extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w, const void *w_scales, int64_t M,
-                            int64_t N, int64_t K, void *y) {
+// `prepared`: w_scales already is in the tensor core's layout (nvc_qqmm_prepare_scales).
+static int32_t qqmm_impl(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w, const void *w_scales, int64_t M,
+                         int64_t N, int64_t K, void *y, bool prepared) {
     NVC_TRY(make_current(dev));
     NVC_TRY(check_quant("qqmm", q));
     if (q->mode != NVC_NVFP4 && q->mode != NVC_MXFP4)
@@ -315,7 +333,7 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
     void *xq = nullptr, *xs = nullptr, *sfa = nullptr, *sfb = nullptr;
     NVC_TRY(dev->pool.alloc((size_t)M * (K / 2), &xq));
     int32_t rc = dev->pool.alloc((size_t)M * (K / vs), &xs);
-    if (rc == NVC_OK) rc = dev->pool.alloc((size_t)wt * kblocks * sf_bytes, &sfa);
+    if (rc == NVC_OK && !prepared) rc = dev->pool.alloc((size_t)wt * kblocks * sf_bytes, &sfa);
     if (rc == NVC_OK) rc = dev->pool.alloc((size_t)xt * kblocks * sf_bytes, &sfb);
     auto release = [&]() {  // (the pool hands the blocks out again in stream order)
         if (xq) dev->pool.free(xq);
@@ -332,10 +350,11 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
     if (rc == NVC_OK) {
         const int64_t na = wt * kblocks * (int64_t)sf_bytes, nb = xt * kblocks * (int64_t)sf_bytes;
         const int pieces = qq_pieces(vs);
-        qq_scale_layout_kernel<<<(unsigned)((na + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / vs, (uint8_t *)sfa, wt, kblocks,
-                                                                                      pieces);
-        qq_scale_layout_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)xs, M, K / vs, (uint8_t *)sfb, xt, kblocks,
-                                                                                      pieces);
+        if (!prepared)
+            qq_scale_layout_kernel<<<(unsigned)((na / 16 + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / vs, (uint8_t *)sfa, wt,
+                                                                                               kblocks, pieces);
+        qq_scale_layout_kernel<<<(unsigned)((nb / 16 + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)xs, M, K / vs, (uint8_t *)sfb, xt, kblocks,
+                                                                                           pieces);
         rc = check_launch(dev, "qq_scale_layout_kernel");
     }
     CUtensorMap mw, mx;
@@ -343,10 +362,39 @@ extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, 
     if (rc == NVC_OK) rc = qq_map(&mx, xq, (uint64_t)K / 2, (uint64_t)M, (uint32_t)bn);
     if (rc == NVC_OK) rc = ensure_error_word(dev);
     if (rc == NVC_OK) {
-        QqParams p{(const uint8_t *)sfa, (const uint8_t *)sfb, (uint16_t *)y, dev->error_word_dev, (int32_t)M, (int32_t)N, (int32_t)kblocks};
+        QqParams p{prepared ? (const uint8_t *)w_scales : (const uint8_t *)sfa, (const uint8_t *)sfb, (uint16_t *)y, dev->error_word_dev, (int32_t)M, (int32_t)N, (int32_t)kblocks};
         if (vs == 16) rc = bn == 256 ? qq_launch<256, 16>(dev, mw, mx, p, M, N) : qq_launch<128, 16>(dev, mw, mx, p, M, N);
         else rc = bn == 256 ? qq_launch<256, 32>(dev, mw, mx, p, M, N) : qq_launch<128, 32>(dev, mw, mx, p, M, N);
     }
     release();
     return rc;
+}
+
+extern "C" int32_t nvc_qqmm(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w, const void *w_scales, int64_t M,
+                            int64_t N, int64_t K, void *y) {
+    return qqmm_impl(dev, q, dtype, x, w, w_scales, M, N, K, y, false);
+}
+
+extern "C" size_t nvc_qqmm_scales_bytes(const nvc_quant *q, int64_t N, int64_t K) {
+    if (!q || (q->group_size != 16 && q->group_size != 32) || N <= 0 || K <= 0) return 0;
+    return (size_t)((N + 127) / 128) * (size_t)((K + QQ_KB - 1) / QQ_KB) * (size_t)qq_pieces(q->group_size) * 512;
+}
+
+extern "C" int32_t nvc_qqmm_prepare_scales(nvc_device *dev, const nvc_quant *q, const void *w_scales, int64_t N, int64_t K, void *out) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("qqmm_prepare_scales", q));
+    if (q->mode != NVC_NVFP4 && q->mode != NVC_MXFP4) return set_error(NVC_ERR_UNSUPPORTED, "qqmm_prepare_scales: nvfp4 or mxfp4 only");
+    if (N < 0 || K < 0 || K % QQ_STEP != 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "qqmm_prepare_scales: invalid shape");
+    const size_t bytes = nvc_qqmm_scales_bytes(q, N, K);
+    if (bytes == 0) return NVC_OK;
+    if (!w_scales || !out || (uintptr_t)out % 16 != 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "qqmm_prepare_scales: null or unaligned operand");
+    const int64_t wt = (N + 127) / 128, kblocks = (K + QQ_KB - 1) / QQ_KB;
+    qq_scale_layout_kernel<<<(unsigned)((bytes / 16 + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / q->group_size, (uint8_t *)out, wt,
+                                                                                          kblocks, qq_pieces(q->group_size));
+    return check_launch(dev, "qq_scale_layout_kernel");
+}
+
+extern "C" int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w, const void *laid_out_scales,
+                                     int64_t M, int64_t N, int64_t K, void *y) {
+    return qqmm_impl(dev, q, dtype, x, w, laid_out_scales, M, N, K, y, true);
 }

@@ -207,8 +207,27 @@ quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t
     const float max_element = BITS == 4 ? 6.0f : 448.0f;
     const bool has = global != nullptr;
     const float scale_enc = has ? ftz(__fdiv_rn(448.0f * 6.0f, *global)) : 1.0f;
+    // The group's values, once: 16-byte loads where the type and the alignment allow (the qqmm path
+    // quantizes its activations with this kernel on every call), element by element otherwise.
+    float vals[32];
+    if (sizeof(T) == 2 && ((uintptr_t)(w + base) & 15) == 0) {
+#pragma unroll
+        for (int v4 = 0; v4 < 4; v4++) {
+            if (8 * v4 >= gs) break;
+            const uint4 raw = reinterpret_cast<const uint4 *>(w + base)[v4];
+            const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; e++) vals[8 * v4 + e] = ftz(DT<T>::load(h, e));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j < gs) vals[j] = ftz(DT<T>::load(w, base + j));
+    }
     float amax = 0.0f;
-    for (int j = 0; j < gs; j++) amax = fmaxf(amax, fabsf(ftz(DT<T>::load(w, base + j))));
+#pragma unroll
+    for (int j = 0; j < 32; j++)
+        if (j < gs) amax = fmaxf(amax, fabsf(vals[j]));
     float scale = ftz(__fdiv_rn(amax, max_element));
     if (has) scale = ftz(__fmul_rn(scale, scale_enc));
     uint32_t code;
@@ -223,15 +242,30 @@ quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t
     scales[g] = (uint8_t)code;
     decoded = ftz(decoded);
     float inverse = decoded == 0.0f ? 0.0f : ftz(__fdiv_rn(has ? scale_enc : 1.0f, decoded));
-    for (int j = 0; j < gs; j += 2) {
-        float a = canonical(ftz(__fmul_rn(ftz(DT<T>::load(w, base + j)), inverse)));
-        float b = canonical(ftz(__fmul_rn(ftz(DT<T>::load(w, base + j + 1)), inverse)));
-        if (BITS == 8) {
-            codes[base + j] = (uint8_t)e4m3_from_f32(a);
-            codes[base + j + 1] = (uint8_t)e4m3_from_f32(b);
-        } else {
-            codes[(base + j) >> 1] = (uint8_t)(e2m1_from_f32(a) | (e2m1_from_f32(b) << 4));
+    if (BITS == 4) {
+        // eight codes per 32-bit word, low nibble first; the group's words go out together
+        uint32_t words[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+            if (8 * wd >= gs) break;
+            uint32_t word = 0;
+#pragma unroll
+            for (int e = 0; e < 8; e++)
+                word |= (uint32_t)e2m1_from_f32(canonical(ftz(__fmul_rn(vals[8 * wd + e], inverse)))) << (4 * e);
+            words[wd] = word;
         }
+        uint32_t *dst = reinterpret_cast<uint32_t *>(codes + (base >> 1));  // (groups are multiples of 8 values: word-aligned)
+        if (gs == 32 && ((uintptr_t)dst & 15) == 0) *reinterpret_cast<uint4 *>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+        else if (gs == 16 && ((uintptr_t)dst & 7) == 0) *reinterpret_cast<uint2 *>(dst) = make_uint2(words[0], words[1]);
+        else {
+#pragma unroll
+            for (int wd = 0; wd < 4; wd++)
+                if (8 * wd < gs) dst[wd] = words[wd];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j < gs) codes[base + j] = (uint8_t)e4m3_from_f32(canonical(ftz(__fmul_rn(vals[j], inverse))));
     }
 }
 

@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "qqmm", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "qqmm", "qqmm_prepare_scales", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -621,7 +621,19 @@ def quantized_embedding(q: Quantized, ids: Array) -> Array:
     return out
 
 
-def qqmm(x: Array, q: Quantized) -> Array:
+def qqmm_prepare_scales(q: Quantized) -> Array:
+    """The weight's scales laid out once the way the tensor core reads them (for qqmm(..., prepared=...))."""
+    c = q.quant._c()
+    N, K = q.weight.shape[0], q.weight.shape[1] * 8
+    nbytes = _ffi.lib().nvc_qqmm_scales_bytes(C.byref(c), N, K)
+    if nbytes == 0:
+        raise UnsupportedError("qqmm_prepare_scales: nvfp4 or mxfp4 weights expected")
+    out = q.weight.dev.empty((nbytes,), U8)
+    _check(_ffi.lib().nvc_qqmm_prepare_scales(q.weight.dev._h, C.byref(c), q.scales.ptr, N, K, out.ptr))
+    return out
+
+
+def qqmm(x: Array, q: Quantized, prepared: Optional[Array] = None) -> Array:
     """MLX's qqmm (crates/nuvec-core/src/products.rs:337-352): x through its own quantization in q's mode, times
     the quantized weight transposed.  NVFP4 (without a global scale) or MXFP4 weights, bfloat16 x [..., K]."""
     quant = q.quant
@@ -639,7 +651,10 @@ def qqmm(x: Array, q: Quantized) -> Array:
     M = x.size // K if K else 0
     out = x.dev.empty(tuple(x.shape[:-1]) + (N,), BF16)
     c = quant._c()
-    _check(_ffi.lib().nvc_qqmm(x.dev._h, C.byref(c), BF16, x.ptr, q.weight.ptr, q.scales.ptr, M, N, K, out.ptr))
+    if prepared is not None:
+        _check(_ffi.lib().nvc_qqmm_prepared(x.dev._h, C.byref(c), BF16, x.ptr, q.weight.ptr, prepared.ptr, M, N, K, out.ptr))
+    else:
+        _check(_ffi.lib().nvc_qqmm(x.dev._h, C.byref(c), BF16, x.ptr, q.weight.ptr, q.scales.ptr, M, N, K, out.ptr))
     return out
 
 

@@ -571,6 +571,9 @@ def test_qqmm_on_the_block_scaled_tensor_core_path(be, M, N, K, mode):
     q = nv.Quantized(dev.array(wc, nv.U32), dev.array(ws, nv.U8), None, nv.Quant(nv.QuantMode(mode), gs, bits))
     got = nv.qqmm(dev.array(x, nv.BF16), q).to_numpy().view(np.uint16)
     assert_product_tight(got, want, oracle.BF16, f"qqmm {mode} {M}x{N}x{K}")
+    # the same with the weight's scales laid out beforehand: the same bits
+    again = nv.qqmm(dev.array(x, nv.BF16), q, nv.qqmm_prepare_scales(q)).to_numpy().view(np.uint16)
+    assert np.array_equal(again, got)
     # and it is NOT the product of the unquantized activations: the activation rounding is the operation
     plain = oracle.quantized_matmul(x, wc, ws, None, oracle.BF16, omode, gs, bits)
     if K >= 256 and M > 1:
