@@ -184,6 +184,23 @@ __device__ __forceinline__ uint32_t e2m1_from_f32(float x) {
     return code | sign;
 }
 
+// Eight values to eight E2M1 codes in one word, value 0 in the low nibble, with the hardware's
+// conversion: round to nearest even on the E2M1 grid, saturate at 6, NaN to +6 (code 7), the sign of
+// a zero result kept: code for code the function above (fp8.rs:48-73; its thresholds 0.25, 0.75,
+// 1.25, 1.75, 2.5, 3.5, 5 are the grid's ties, each going to the neighbour with an even mantissa).
+__device__ __forceinline__ uint32_t e2m1x8_from_f32(const float *v) {
+    uint32_t word;
+    asm("{\n\t.reg .b8 c0, c1, c2, c3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 c0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 c1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 c2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 c3, %8, %7;\n\t"
+        "mov.b32 %0, {c0, c1, c2, c3};\n\t}"
+        : "=r"(word)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return word;
+}
+
 // The E8M0 code of mx_scale_round_up(x) for x >= 0 (fp8.rs:84-93, 124-130): the smallest
 // power of two that is not below x, i.e. the exponent field, plus one when any mantissa bit
 // is set, capped at 254; 0 for zero and 0xFF for Inf/NaN.
@@ -248,11 +265,10 @@ quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t
 #pragma unroll
         for (int wd = 0; wd < 4; wd++) {
             if (8 * wd >= gs) break;
-            uint32_t word = 0;
+            float scaled[8];  // (a product below the normal range becomes a zero code either way)
 #pragma unroll
-            for (int e = 0; e < 8; e++)
-                word |= (uint32_t)e2m1_from_f32(canonical(ftz(__fmul_rn(vals[8 * wd + e], inverse)))) << (4 * e);
-            words[wd] = word;
+            for (int e = 0; e < 8; e++) scaled[e] = __fmul_rn(vals[8 * wd + e], inverse);
+            words[wd] = e2m1x8_from_f32(scaled);
         }
         uint32_t *dst = reinterpret_cast<uint32_t *>(codes + (base >> 1));  // (groups are multiples of 8 values: word-aligned)
         if (gs == 32 && ((uintptr_t)dst & 15) == 0) *reinterpret_cast<uint4 *>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
@@ -263,9 +279,26 @@ quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t
                 if (8 * wd < gs) dst[wd] = words[wd];
         }
     } else {
+        // one byte per code: 16 of them to a store where the alignment allows
 #pragma unroll
-        for (int j = 0; j < 32; j++)
-            if (j < gs) codes[base + j] = (uint8_t)e4m3_from_f32(canonical(ftz(__fmul_rn(vals[j], inverse))));
+        for (int part = 0; part < 2; part++) {
+            if (16 * part >= gs) break;
+            uint32_t words[4];
+#pragma unroll
+            for (int wd = 0; wd < 4; wd++) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    word |= (uint32_t)e4m3_from_f32(canonical(ftz(__fmul_rn(vals[16 * part + 4 * wd + e], inverse)))) << (8 * e);
+                words[wd] = word;
+            }
+            uint8_t *dst = codes + base + 16 * part;
+            if (((uintptr_t)dst & 15) == 0) *reinterpret_cast<uint4 *>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+            else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) dst[j] = (uint8_t)(words[j >> 2] >> (8 * (j & 3)));
+            }
+        }
     }
 }
 

@@ -187,6 +187,10 @@ float orc_e8m0_to_f32(uint8_t code) {
 static inline float ftz(float x) {
     return fpclassify(x) == FP_SUBNORMAL ? copysignf(0.0f, x) : x;
 }
+/* f32::max / f32::min: a NaN operand of either kind is ignored.  (The C library's fmaxf and fminf
+ * return NaN for a SIGNALLING NaN operand, which Rust's do not, so they are spelled out.) */
+static inline float max_f32(float a, float b) { return b != b ? a : a != a ? b : (a > b ? a : b); }
+static inline float min_f32(float a, float b) { return b != b ? a : a != a ? b : (a < b ? a : b); }
 /* fp8.rs:117-119 */
 static inline float canonical(float x) { return isnan(x) ? bits_f32(0x7FC00000u) : x; }
 
@@ -235,16 +239,16 @@ static void quantize_affine(int gs, int bits, int dtype, const void *w, size_t c
         float lo = INFINITY, hi = -INFINITY;
         for (int j = 0; j < gs; j++) {
             float v = load_f32(w, g * gs + j, dtype);
-            lo = fminf(lo, v); /* f32::min/max ignore a NaN operand, as fminf/fmaxf */
-            hi = fmaxf(hi, v);
+            lo = min_f32(lo, v); /* f32::min/max ignore a NaN operand */
+            hi = max_f32(hi, v);
         }
         float scale, bias;
         if (bits == 1) {
-            scale = fmaxf(hi - lo, eps);
+            scale = max_f32(hi - lo, eps);
             bias = lo;
         } else {
             int wide = fabsf(lo) > fabsf(hi);
-            scale = fmaxf((hi - lo) / n_bins, eps);
+            scale = max_f32((hi - lo) / n_bins, eps);
             scale = wide ? scale : -scale;
             float edge = wide ? lo : hi;
             float q0 = rintf(edge / scale);
@@ -283,7 +287,7 @@ static void quantize_fp(int gs, int bits, int dtype, const void *w, size_t count
     size_t groups = count / (size_t)gs;
     for (size_t g = 0; g < groups; g++) {
         float amax = 0.0f;
-        for (int j = 0; j < gs; j++) amax = fmaxf(amax, fabsf(ftz(load_f32(w, g * gs + j, dtype))));
+        for (int j = 0; j < gs; j++) amax = max_f32(amax, fabsf(ftz(load_f32(w, g * gs + j, dtype))));
         float scale = ftz(amax / max_element);
         if (has_enc) scale = ftz(scale * scale_enc);
         uint8_t code;

@@ -75,6 +75,28 @@ def test_fp_quantize_dequantize_bit_exact(be, mode, gs, bits, dt):
             assert np.array_equal(d0.view(np.uint8), d1.view(np.uint8)), f"global={g} out={out}"
 
 
+@pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
+def test_fp4_quantize_every_bfloat16_pattern(be, mode, gs):
+    # The 4-bit codes come from the hardware's conversion instruction: every bfloat16 bit pattern
+    # (NaNs, infinities, both zeros, subnormals, every tie of the E2M1 grid) goes through it under
+    # several group scales and must give the oracle's code.  The first value of a group fixes the
+    # scale (6 * 2^k decodes to exactly 2^k), the others sweep the patterns.
+    patterns = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    per = gs - 1
+    pad = (-len(patterns)) % per
+    sweep = np.concatenate([patterns, np.zeros(pad, np.uint16)]).reshape(-1, per)
+    for k in (-3, 0, 5) if mode == oracle.NVFP4 else (-120, -3, 0, 40):
+        lead = oracle.from_f32(np.full((len(sweep), 1), 6.0 * 2.0 ** k, np.float32), oracle.BF16)
+        w = np.concatenate([lead.view(np.uint16).reshape(-1, 1), sweep], axis=1).view(lead.dtype)
+        c0, s0, _ = oracle.quantize(w, oracle.BF16, mode, gs, 4)
+        c1, s1, _ = be.quantize(w, oracle.BF16, mode, gs, 4)
+        bad = np.nonzero(s0.reshape(-1) != s1.reshape(-1))[0]
+        assert len(bad) == 0, f"scales, k={k}: group {bad[0]} oracle {s0.reshape(-1)[bad[0]]} device {s1.reshape(-1)[bad[0]]} values {[hex(v) for v in w[bad[0]]]}"
+        bad = np.nonzero((c0.view(np.uint8).reshape(len(w), -1) != c1.view(np.uint8).reshape(len(w), -1)).any(axis=1))[0]
+        assert len(bad) == 0, (f"codes, k={k}: group {bad[0]} oracle {c0.view(np.uint8).reshape(len(w), -1)[bad[0]]} "
+                               f"device {c1.view(np.uint8).reshape(len(w), -1)[bad[0]]} values {[hex(v) for v in w[bad[0]]]}")
+
+
 def test_dequantize_full_size_checksum(be):
     # The headline decode matrix (4096 x 4096, 4 bits, groups of 64): bit-exact at full size.
     rng = np.random.default_rng(0)

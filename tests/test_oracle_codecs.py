@@ -129,3 +129,21 @@ def test_few_row_products_do_not_depend_on_the_row_count():
     for m in (1, 5, 16):
         part = oracle.quantized_matmul(x[:m], codes, scales, biases, oracle.BF16)
         assert np.array_equal(part, full[:m])
+
+
+@pytest.mark.parametrize("nan_bits", [0x7FC00000, 0x7F800001, 0xFF800001, 0xFFC00000])
+def test_a_nan_of_either_kind_is_ignored_by_the_group_extremes(nan_bits):
+    # kernels.rs:935 (and :785-790 for affine) fold with f32::max / f32::min, which return the other
+    # operand for a NaN, quiet or signalling; the C library's fmaxf does not for a signalling one.
+    w = np.linspace(-1.0, 3.0, 64, dtype=np.float32).reshape(1, 64)
+    poisoned = w.copy()
+    poisoned.view(np.uint32)[0, 5] = nan_bits
+    for mode, gs, bits in ((oracle.MXFP4, 32, 4), (oracle.NVFP4, 16, 4), (oracle.MXFP8, 32, 8)):
+        _, s0, _ = oracle.quantize(w, oracle.F32, mode, gs, bits)
+        _, s1, _ = oracle.quantize(poisoned, oracle.F32, mode, gs, bits)
+        assert np.array_equal(s0, s1)
+    clean = w.copy()
+    clean[0, 5] = clean[0, 6]                                # an interior value: the extremes stay
+    _, s0, b0 = oracle.quantize(clean, oracle.F32, oracle.AFFINE, 64, 4)
+    _, s1, b1 = oracle.quantize(poisoned, oracle.F32, oracle.AFFINE, 64, 4)
+    assert np.array_equal(s0.view(np.uint8), s1.view(np.uint8)) and np.array_equal(b0.view(np.uint8), b1.view(np.uint8))
