@@ -792,6 +792,14 @@ def qqmm_shape(args, nv, _ffi, dev, peaks):
     us_exact = timed(lambda c, s, y: lib.nvc_quantized_matmul(dev._h, C.byref(qc), nv.BF16, 1, x.ptr, c.ptr, s.ptr, None, None,
                                                               M, N, K, K, 1, 0, 0, 0, y.ptr))
     flops = 2.0 * M * N * K
+    if args.timeline:
+        # the timeline build: cycles of block (0, 0) of the last launch, per role
+        buf = (C.c_longlong * 12)()
+        lib.nvc_debug_qqmm_timing.restype = C.c_int32
+        assert lib.nvc_debug_qqmm_timing(buf) == 0
+        t = np.array(list(buf)).reshape(3, 4)
+        print(json.dumps({"qqmm_role_cycles": {r: {"start": int(t[i, 0]), "end": int(t[i, 1]), "in_waits": int(t[i, 2])}
+                                               for i, r in enumerate(["producer", "mma issuer", "epilogue"])}}))
     print(json.dumps({"qqmm": args.qqmm, "us_qqmm": us_qq, "TFLOP/s_qqmm": flops / us_qq / 1e6,
                       "us_qqmm_prepared_scales": us_prep, "TFLOP/s_qqmm_prepared_scales": flops / us_prep / 1e6,
                       "us_exact_bf16_activations": us_exact, "TFLOP/s_exact": flops / us_exact / 1e6,

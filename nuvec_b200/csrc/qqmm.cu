@@ -24,10 +24,19 @@
 // 128 weight rows x BN tokens, a TMA producer thread, an MMA thread and four epilogue warps.
 //
 // Scale-factor layout.  For one MMA (128 rows, 64 k-values = 4 scales per row) the tensor core reads
-// 512 bytes placed by tcgen05.cp.32x128b.warpx4: byte (r % 32) * 16 + (r / 32) * 4 + s holds the
-// scale of row r, k-block s.  The arrays of the reference ([rows, K / 16], one byte per scale) are
-// re-laid-out into such 512-byte pieces, [row tile of 128][k-block of 256][4 pieces], so that a
-// stage's scales are one contiguous 2 KB bulk copy.
+// four 32-bit columns of tensor memory: lane r % 32 of EVERY 32-lane quarter, column r / 32, byte s
+// holds the scale of row r, k-block s.  The arrays of the reference ([rows, K / 16], one byte per
+// scale) are re-laid-out into 512-byte pieces in that order -- byte (r % 32) * 16 + (r / 32) * 4 + s,
+// [row tile of 128][k-block of 256][4 pieces] -- so that a stage's scales are one contiguous 2 KB
+// bulk copy and a lane's four columns of a piece are one 16-byte shared-memory load.
+//
+// How the scales reach tensor memory.  tcgen05.cp (32x128b.warpx4) would do it, but it runs in the
+// same in-order queue as the MMAs and, measured here, costs about as much as a quarter of an MMA
+// whatever its shape; with three per MMA (one for the weights' scales, two for 256 tokens') the tensor
+// pipe sat idle more than half of the main loop.  Instead the four epilogue warps, idle until the
+// accumulator is complete, carry them: each warp owns one 32-lane quarter of tensor memory, reads a
+// stage's pieces from shared memory and writes them to its quarter with tcgen05.st, into the stage's
+// own set of scale columns, and signals the MMA thread.  The MMA queue holds MMAs only.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -74,17 +83,9 @@ __global__ void __launch_bounds__(256) qq_scale_layout_kernel(const uint8_t *__r
     reinterpret_cast<uint4 *>(out)[at] = make_uint4(words[0], words[1], words[2], words[3]);
 }
 
-// Shared-memory descriptor of one 512-byte scale piece for tcgen05.cp: 32 rows of 16 bytes, no
-// swizzle, 8-row core matrices 128 bytes apart.
-__device__ __forceinline__ uint64_t qq_sf_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(128 >> 4) << 32;  // stride byte offset
-    d |= (uint64_t)1 << 46;           // descriptor version for sm_100
-    return d;
-}
-__device__ __forceinline__ void qq_cp_scales(uint32_t tmem_addr, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+// four 32-bit columns of the executing warp's quarter of tensor memory, one value per lane and column
+__device__ __forceinline__ void qq_st4(uint32_t taddr, const uint4 &v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 template <int VS>
 __device__ __forceinline__ void qq_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
@@ -115,6 +116,24 @@ __device__ __forceinline__ void qq_bulk_load(void *dst, const void *src, uint32_
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// Diagnostic builds only (-DNUVEC_TIMELINE): block (0, 0) records, per role, the clock cycles from the
+// kernel's first instruction to the role's start and end, and the cycles inside its waits.
+#ifdef NUVEC_TIMELINE
+__device__ long long g_qq_timing[3][4];
+#define QQT_BEGIN long long qqt_wait_ = 0; const long long qqt_start_ = clock64();
+#define QQT_WAIT(...) { const long long qqt_t_ = clock64(); __VA_ARGS__; qqt_wait_ += clock64() - qqt_t_; }
+#define QQT_END(role)                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0) {                                  \
+        g_qq_timing[role][0] = qqt_start_ - qqt_entry_;                         \
+        g_qq_timing[role][1] = clock64() - qqt_entry_;                          \
+        g_qq_timing[role][2] = qqt_wait_;                                       \
+    }
+#else
+#define QQT_BEGIN
+#define QQT_WAIT(...) { __VA_ARGS__; }
+#define QQT_END(role)
+#endif
+
 struct QqParams {
     const uint8_t *sfa, *sfb;  // re-laid-out scales of the weights / the activations
     uint16_t *y;               // bfloat16 [tokens, N]
@@ -125,16 +144,20 @@ struct QqParams {
 template <int BN, int VS>
 __global__ void __launch_bounds__(QQ_THREADS, 1)
 qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, QqParams p) {
+#ifdef NUVEC_TIMELINE
+    const long long qqt_entry_ = clock64();
+#endif
     constexpr uint32_t A_BYTES = QQ_BM * 128, B_BYTES = BN * 128;
     constexpr int PIECES = qq_pieces(VS);                  // scale pieces per 128 rows and stage
     constexpr int STEPS_PER_PIECE = 4 / PIECES;            // MMAs a piece serves: 1 (4 scales per MMA) or 2
     constexpr uint32_t QQ_SF_BYTES = PIECES * 512;
     constexpr uint32_t SFB_BYTES = (BN / 128) * QQ_SF_BYTES;
     constexpr uint32_t STAGE_TX = A_BYTES + B_BYTES + QQ_SF_BYTES + SFB_BYTES;
-    // tensor-memory columns behind the accumulator: per MMA step 4 columns of weight scales (128 rows) and
-    // 4 per 128 tokens of activation scales, the tokens' halves side by side
-    constexpr int SFA_COL = BN, SFB_COL = BN + 16, SFB_STEP = 4 * (BN / 128);
-    constexpr int TMEM_COLS = BN + 16 + 4 * SFB_STEP <= 256 ? 256 : 512;
+    // tensor-memory columns behind the accumulator, one set per stage: per piece 4 columns of weight scales
+    // (128 rows), then per piece 4 per 128 tokens of activation scales, the tokens' halves side by side
+    constexpr int SFB_STEP = 4 * (BN / 128), SFA_COLS = 4 * PIECES, SF_STAGE_COLS = SFA_COLS + SFB_STEP * PIECES;
+    constexpr int TMEM_COLS = BN + QQ_STAGES * SF_STAGE_COLS <= 256 ? 256 : 512;
+    static_assert(BN + QQ_STAGES * SF_STAGE_COLS <= 512, "accumulator and scale columns exceed tensor memory");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *as = smem;                                  // [stage][128 rows x 128 B], 128-byte swizzle
@@ -142,7 +165,7 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     uint8_t *sfa = bs + QQ_STAGES * B_BYTES;             // [stage][pieces x 512 B]
     uint8_t *sfb = sfa + QQ_STAGES * QQ_SF_BYTES;        // [stage][BN / 128][pieces x 512 B]
     uint64_t *bars = reinterpret_cast<uint64_t *>(sfb + QQ_STAGES * SFB_BYTES);
-    uint64_t *full = bars, *empty = full + QQ_STAGES, *accfull = empty + QQ_STAGES;
+    uint64_t *full = bars, *empty = full + QQ_STAGES, *sfready = empty + QQ_STAGES, *accfull = sfready + QQ_STAGES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accfull + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     uint8_t *stage_out = reinterpret_cast<uint8_t *>(bars) + 256;  // epilogue: [4 warps][32 tokens][32 rows] bfloat16
@@ -153,6 +176,7 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
         for (int s = 0; s < QQ_STAGES; s++) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
+            mbar_init(sfready + s, 4);  // one arrival per epilogue warp
         }
         mbar_init(accfull, 1);
         *abort_flag = 0;
@@ -173,9 +197,10 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
             const uint8_t *sfa_src = p.sfa + (size_t)blockIdx.x * p.kblocks * QQ_SF_BYTES;
             const uint8_t *sfb_src = p.sfb + (size_t)blockIdx.y * (BN / 128) * p.kblocks * QQ_SF_BYTES;
             bool ok = true;
+            QQT_BEGIN
             for (int kb = 0; kb < p.kblocks && ok; kb++) {
                 const uint32_t s = kb % QQ_STAGES, ph = (kb / QQ_STAGES) & 1;
-                ok = mbar_wait(empty + s, ph ^ 1, abort_flag);
+                QQT_WAIT(ok = mbar_wait(empty + s, ph ^ 1, abort_flag))
                 if (!ok) break;
                 mbar_expect_tx(full + s, STAGE_TX);
                 tma_load_2d(as + s * A_BYTES, &tmap_w, kb * 128, n0, full + s);
@@ -186,40 +211,60 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                     qq_bulk_load(sfb + s * SFB_BYTES + h * QQ_SF_BYTES, sfb_src + ((size_t)h * p.kblocks + kb) * QQ_SF_BYTES, QQ_SF_BYTES,
                                  full + s);
             }
+            QQT_END(0)
         }
     } else if (warp == 1) {
-        // ── MMA issuer: per 64 k-values the scales go shared -> tensor memory, then one MMA ─────
+        // ── MMA issuer: four MMAs of 64 k-values per stage, once the stage's scales are in tensor memory ──
         if (lane == 0) {
             bool ok = true;
+            QQT_BEGIN
             for (int kb = 0; kb < p.kblocks && ok; kb++) {
                 const uint32_t s = kb % QQ_STAGES, ph = (kb / QQ_STAGES) & 1;
-                ok = mbar_wait(full + s, ph, abort_flag);
+                QQT_WAIT(ok = mbar_wait(full + s, ph, abort_flag) && mbar_wait(sfready + s, ph, abort_flag))
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t ad = umma_desc(smem_u32(as + s * A_BYTES)), bd = umma_desc(smem_u32(bs + s * B_BYTES));
+                const uint32_t sf_cols = tmem_base + BN + s * SF_STAGE_COLS;
 #pragma unroll
                 for (int step = 0; step < QQ_KB / QQ_STEP; step++) {
                     const int piece = step / STEPS_PER_PIECE;
                     const uint32_t sf = (uint32_t)(step % STEPS_PER_PIECE) * 2u;  // byte of the piece's columns this MMA starts at
-                    if (step % STEPS_PER_PIECE == 0) {
-                        qq_cp_scales(tmem_base + SFA_COL + 4 * piece, qq_sf_desc(smem_u32(sfa + s * QQ_SF_BYTES + piece * 512)));
-#pragma unroll
-                        for (int h = 0; h < BN / 128; h++)
-                            qq_cp_scales(tmem_base + SFB_COL + SFB_STEP * piece + 4 * h,
-                                         qq_sf_desc(smem_u32(sfb + s * SFB_BYTES + h * QQ_SF_BYTES + piece * 512)));
-                    }
                     qq_mma<VS>(tmem_base, ad + (uint64_t)(2 * step), bd + (uint64_t)(2 * step), qq_idesc(BN, VS, sf),
-                               (tmem_base + SFA_COL + 4 * piece) | (sf << 30), (tmem_base + SFB_COL + SFB_STEP * piece) | (sf << 30),
-                               kb != 0 || step != 0);
+                               (sf_cols + 4 * piece) | (sf << 30), (sf_cols + SFA_COLS + SFB_STEP * piece) | (sf << 30), kb != 0 || step != 0);
                 }
                 tc_commit(empty + s);
             }
             tc_commit(accfull);
+            QQT_END(1)
         }
     } else {
-        // ── epilogue: warp q owns tensor-memory lanes 32 q .. 32 q + 31 = weight rows n0 + 32 q + lane ──
+        // ── warps 2-5.  Warp q owns tensor-memory lanes 32 q .. 32 q + 31.  During the main loop it carries
+        //    each stage's scales from shared memory to the stage's scale columns of its lanes (every quarter
+        //    holds the same columns); then it is the epilogue of weight rows n0 + 32 q + lane. ──
         const int q = warp & 3;
-        bool ok = mbar_wait(accfull, 0, abort_flag);
+        const uint32_t quarter = tmem_base + ((uint32_t)(q * 32) << 16);
+        bool ok = true;
+        QQT_BEGIN
+        for (int kb = 0; kb < p.kblocks && ok; kb++) {
+            const uint32_t s = kb % QQ_STAGES, ph = (kb / QQ_STAGES) & 1;
+            // (the stage's columns are free: its data arrived, so the producer saw the MMAs that read them complete)
+            QQT_WAIT(ok = mbar_wait(full + s, ph, abort_flag))
+            if (!ok) break;
+            const uint32_t sf_cols = quarter + BN + s * SF_STAGE_COLS;
+#pragma unroll
+            for (int piece = 0; piece < PIECES; piece++) {
+                qq_st4(sf_cols + 4 * piece, *reinterpret_cast<const uint4 *>(sfa + s * QQ_SF_BYTES + piece * 512 + lane * 16));
+#pragma unroll
+                for (int h = 0; h < BN / 128; h++)
+                    qq_st4(sf_cols + SFA_COLS + SFB_STEP * piece + 4 * h,
+                           *reinterpret_cast<const uint4 *>(sfb + s * SFB_BYTES + h * QQ_SF_BYTES + piece * 512 + lane * 16));
+            }
+            tc_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sfready + s);
+        }
+        if (ok) { QQT_WAIT(ok = mbar_wait(accfull, 0, abort_flag)) }
         tc_fence_after();
         const bool wide = (p.N & 7) == 0 && ((uintptr_t)p.y & 15) == 0;
         uint8_t *mine = stage_out + q * 2048;
@@ -254,6 +299,7 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
                 }
             }
         }
+        if (warp == 2 && lane == 0) { QQT_END(2) }
     }
     tc_fence_before();
     __syncthreads();
@@ -398,3 +444,14 @@ extern "C" int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_
                                      int64_t M, int64_t N, int64_t K, void *y) {
     return qqmm_impl(dev, q, dtype, x, w, laid_out_scales, M, N, K, y, true);
 }
+
+#ifdef NUVEC_TIMELINE
+// Diagnostic build only: out[role][slot] of block (0, 0) in the last qqmm launch; roles 0 producer,
+// 1 MMA issuer, 2 warp 2 (scale carrier, then epilogue); slots: cycles from the kernel's entry to the
+// role's start, to its end, cycles inside its waits, unused.
+extern "C" int32_t nvc_debug_qqmm_timing(long long *out) {
+    if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpyFromSymbol(out, nvc::g_qq_timing, sizeof(long long) * 12) != cudaSuccess)
+        return NVC_ERR_DRIVER;
+    return NVC_OK;
+}
+#endif
