@@ -223,6 +223,18 @@ int32_t nvc_qqmm_prepare_scales(nvc_device *dev, const nvc_quant *q, const void 
 int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w,
                           const void *laid_out_scales, int64_t M, int64_t N, int64_t K, void *y);
 
+/* convert_packed (crates/nuvec-lm/src/quant.rs:36-199) for one layer of an AutoAWQ or GPTQ checkpoint, on the
+ * device: qweight (int32, AWQ [inputs, outputs / 8], GPTQ [inputs * bits / 32, outputs]), qzeros (int32
+ * [groups, outputs * bits / 32], or NULL for the symmetric zero 2^(bits - 1); GPTQ v1 stores zero - 1) and
+ * scales ([groups, outputs], float16 / bfloat16 / float32) become MLX's affine layout: codes uint32
+ * [outputs, inputs * bits / 32], scales and biases [outputs, groups] with bias = -zero * scale (float32
+ * product, rounded to the scales' type).  bits 2, 4 or 8 (AWQ: 4); inputs a multiple of group_size.  GPTQ's
+ * g_idx is the caller's to check (it must be the identity grouping, quant.rs:97-111). */
+enum { NVC_PACKED_AWQ = 0, NVC_PACKED_GPTQ_V1 = 1, NVC_PACKED_GPTQ_V2 = 2 };
+int32_t nvc_convert_packed(nvc_device *dev, int32_t format, int32_t bits, int32_t group_size, int32_t scale_dtype,
+                           const int32_t *qweight, const int32_t *qzeros, const void *scales, int64_t inputs,
+                           int64_t outputs, uint32_t *out_codes, void *out_scales, void *out_biases);
+
 /* fast::moe_route (crates/nuvec-core/src/fast/imp.rs:2652-2672; kernel crates/nuvec-kernels/src/metal/moe.metal):
  * per row of `experts` router probabilities (float dtype, dense [rows, experts]) the indices
  * (uint32 [rows, k]) of the k largest in the stable ascending order of a sort with NaN last, and
