@@ -281,6 +281,9 @@ def main():
     ap.add_argument("--one", default=None, metavar="M,N,K,BITS,COPIES",
                     help="profiling driver: one product shape on COPIES distinct weight sets, each launched twice "
                          "(prints the device time per launch); what the ncu commands under profiles/ run")
+    ap.add_argument("--checkpoint", action="store_true",
+                    help="diagnostic: device time of the checkpoint-format conversions (AWQ / GPTQ layer, gpt-oss gate/up split) "
+                         "at the sizes of the configurations, against the bytes they read and write")
     ap.add_argument("--qqmm", default=None, metavar="M,N,K,COPIES",
                     help="the NVFP4 x NVFP4 product on the block-scaled tensor-core path (nvc_qqmm: activations "
                          "quantized on the way) next to the exact product of the same weights with bfloat16 activations")
@@ -323,6 +326,8 @@ def main():
         return
     if args.one:
         return one_shape(args, nv, _ffi, dev)
+    if args.checkpoint:
+        return checkpoint_conversions(nv, dev, peaks)
     if args.qqmm:
         return qqmm_shape(args, nv, _ffi, dev, peaks)
     if args.timeline:
@@ -805,6 +810,46 @@ def qqmm_shape(args, nv, _ffi, dev, peaks):
                       "us_exact_bf16_activations": us_exact, "TFLOP/s_exact": flops / us_exact / 1e6,
                       "frac_of_measured_bf16_burst_qqmm": flops / us_qq / 1e6 / peaks["bf16_tflops"],
                       "note": "qqmm includes the quantization of x and the layout of both scale arrays"}))
+
+
+# ── checkpoint-format conversions (--checkpoint) ───────────────────────────────────────────────
+def checkpoint_conversions(nv, dev, peaks):
+    """Device time of nvc_convert_packed for one AWQ and one GPTQ layer of the dense configuration's gate+up
+    projection (4096 -> 24576, 4-bit, groups of 128) and of the gate / up split of a gpt-oss layer's MXFP4
+    experts (32 experts x 5760 rows x 2880), each against the bytes it has to read and write."""
+    from nuvec_b200 import checkpoint as ck
+    rng = np.random.default_rng(0)
+    rows = []
+
+    def timed(fn, reps=10):
+        fn()
+        e0, e1 = dev.event(), dev.event()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_ms(e1) * 1e3 / reps
+
+    inputs, outputs, group = 4096, 24576, 128
+    scales = dev.array(rng.uniform(0.001, 0.01, (inputs // group, outputs)).astype(np.float16), nv.F16)
+    zeros = dev.array(rng.integers(0, 2 ** 31, (inputs // group, outputs // 8), dtype=np.int32), nv.I32)
+    quant = nv.Quant.affine(group, 4)
+    for name, fmt, shape in (("awq", ck.AWQ, (inputs, outputs // 8)), ("gptq", ck.GPTQ_V2, (inputs // 8, outputs))):
+        qw = dev.array(rng.integers(0, 2 ** 31, shape, dtype=np.int32), nv.I32)
+        us = timed(lambda: ck.convert_packed_layer(dev, fmt, quant, qw, scales, zeros, None, name))
+        moved = 2 * qw.nbytes + 3 * scales.nbytes + zeros.nbytes
+        rows.append({"conversion": f"{name} 4-bit g128 layer {inputs} -> {outputs}", "us": us, "GB/s": moved / us / 1e3,
+                     "frac_of_measured_hbm": moved / us / 1e3 / peaks["hbm_gbs"]})
+    E, R, K = 32, 5760, 2880
+    blocks = dev.array(rng.integers(0, 256, (E, R, K // 32, 16), dtype=np.uint8), nv.U8)
+    sc = dev.array(rng.integers(100, 140, (E, R, K // 32), dtype=np.uint8), nv.U8)
+    us = timed(lambda: ck.sanitize_gpt_oss({"l.experts.gate_up_proj_blocks": blocks, "l.experts.gate_up_proj_scales": sc}), reps=5)
+    moved = 2 * (blocks.nbytes + sc.nbytes)
+    rows.append({"conversion": f"gpt-oss gate/up split, {E} experts x {R} rows x {K} (blocks + scales)", "us": us,
+                 "GB/s": moved / us / 1e3, "frac_of_measured_hbm": moved / us / 1e3 / peaks["hbm_gbs"],
+                 "note": "four nvc_take_strided calls"})
+    print(json.dumps({"checkpoint_conversions": rows}))
 
 
 # ── where a decode product's time goes (--timeline) ──────────────────────────────────────────

@@ -235,6 +235,12 @@ int32_t nvc_convert_packed(nvc_device *dev, int32_t format, int32_t bits, int32_
                            const int32_t *qweight, const int32_t *qzeros, const void *scales, int64_t inputs,
                            int64_t outputs, uint32_t *out_codes, void *out_scales, void *out_biases);
 
+/* `v[..., first::step, :]` of a dense array seen as [outer, n, inner_bytes]: out[o, j, :] = src[o, first + j * step, :]
+ * for j < ceil((n - first) / step).  With step 2 it takes apart the interleaved gate and up rows of gpt-oss's
+ * fused experts (`v.take(arange(first, n, 2), axis)`, crates/nuvec-lm/src/lib.rs:414-420, 431-440). */
+int32_t nvc_take_strided(nvc_device *dev, const void *src, int64_t outer, int64_t n, int64_t inner_bytes,
+                         int64_t first, int64_t step, void *out);
+
 /* fast::moe_route (crates/nuvec-core/src/fast/imp.rs:2652-2672; kernel crates/nuvec-kernels/src/metal/moe.metal):
  * per row of `experts` router probabilities (float dtype, dense [rows, experts]) the indices
  * (uint32 [rows, k]) of the k largest in the stable ascending order of a sort with NaN last, and

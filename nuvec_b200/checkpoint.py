@@ -112,21 +112,18 @@ def mxfp4_from_hf_blocks(blocks: Array) -> Array:
 
 
 def split_interleaved(v: Array, first: int, axis: int) -> Array:
-    """``v[..., first::2, ...]`` along ``axis`` (-1 or -2), on the device: a take of rows (lib.rs:414-420)."""
+    """``v[..., first::2, ...]`` along ``axis`` (-1 or -2), on the device (lib.rs:414-420)."""
     if axis not in (-1, -2) or v.ndim < -axis:
         raise InvalidArgument(f"split_interleaved: axis {axis} of {list(v.shape)}")
     n = v.shape[axis]
     inner = 1 if axis == -1 else v.shape[-1]
     outer = v.size // (n * inner) if n * inner else 0
-    picked = np.arange(first, n, 2, dtype=np.int64)
-    rows = (np.arange(outer, dtype=np.int64)[:, None] * n + picked[None, :]).reshape(-1)
-    if rows.size and rows.max() >= 2 ** 32:
-        raise UnsupportedError("split_interleaved: more than 2^32 rows")
-    flat = v.reshape(outer * n, inner)
-    out = ops.take_rows(flat, v.dev.array(rows.astype(np.uint32), U32))
     shape = list(v.shape)
-    shape[axis] = len(picked)
-    return out.reshape(tuple(shape))
+    shape[axis] = len(range(first, n, 2))
+    out = v.dev.empty(tuple(shape), v.dtype)
+    from . import _ffi
+    ops._check(_ffi.lib().nvc_take_strided(v.dev._h, v.ptr, outer, n, inner * v.itemsize, first, 2, out.ptr))
+    return out
 
 
 def sanitize_gpt_oss(weights: Dict[str, Array]) -> Dict[str, Array]:

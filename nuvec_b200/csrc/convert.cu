@@ -16,7 +16,7 @@
 //   biases  -zero (float32) times the scale (float32), rounded to the scales' type, [outputs, groups].
 //
 // gpt-oss's MXFP4 `*_blocks` need no kernel: their bytes are MLX's codes already (quant.rs:24-34) and the
-// gate / up rows are taken apart with nvc_take_rows.
+// gate / up rows are taken apart with nvc_take_strided (below).
 #include "common.cuh"
 
 namespace nvc {
@@ -39,13 +39,32 @@ __global__ void __launch_bounds__(256) awq_codes_kernel(const uint32_t *__restri
     if (c0 + oc >= cols) return;
     const int shift = 4 * kAwqOrder[c];
     uint32_t *dst = out + ((c0 + oc) * 8 + c) * W + i0 / 8;
+    uint32_t made[8];
 #pragma unroll
     for (int wi = 0; wi < 8; wi++) {
-        if (i0 + wi * 8 >= inputs) break;
         uint32_t word = 0;
 #pragma unroll
         for (int k = 0; k < 8; k++) word |= ((tile[wi * 8 + k][oc] >> shift) & 15u) << (4 * k);
-        dst[wi] = word;
+        made[wi] = word;
+    }
+    if (i0 + 64 <= inputs && ((uintptr_t)dst & 15) == 0) {  // the thread's 32 bytes as two 16-byte stores
+        reinterpret_cast<uint4 *>(dst)[0] = make_uint4(made[0], made[1], made[2], made[3]);
+        reinterpret_cast<uint4 *>(dst)[1] = make_uint4(made[4], made[5], made[6], made[7]);
+    } else {
+#pragma unroll
+        for (int wi = 0; wi < 8; wi++)
+            if (i0 + wi * 8 < inputs) dst[wi] = made[wi];
+    }
+}
+
+// out[o, j, :] = src[o, first + j * step, :] for rows of inner_bytes bytes, in units of UNIT bytes.
+template <typename U>
+__global__ void __launch_bounds__(256) take_strided_kernel(const U *__restrict__ src, U *__restrict__ out, int64_t n, int64_t picked, int64_t inner,
+                                                           int64_t first, int64_t step, int64_t total) {
+    for (int64_t at = (int64_t)blockIdx.x * 256 + threadIdx.x; at < total; at += (int64_t)gridDim.x * 256) {
+        const int64_t c = at % inner, row = at / inner;
+        const int64_t j = row % picked, o = row / picked;
+        out[at] = src[(o * n + first + j * step) * inner + c];
     }
 }
 
@@ -135,4 +154,27 @@ extern "C" int32_t nvc_convert_packed(nvc_device *dev, int32_t format, int32_t b
         packed_scales_kernel<float><<<blocks, 256, 0, dev->stream>>>((const float *)scales, (const uint32_t *)qzeros, (float *)out_scales,
                                                                      (float *)out_biases, groups, outputs, format, bits);
     return check_launch(dev, "packed_scales_kernel");
+}
+
+extern "C" int32_t nvc_take_strided(nvc_device *dev, const void *src, int64_t outer, int64_t n, int64_t inner_bytes, int64_t first, int64_t step,
+                                    void *out) {
+    NVC_TRY(make_current(dev));
+    if (outer < 0 || n < 0 || inner_bytes < 0 || first < 0 || step < 1) return set_error(NVC_ERR_INVALID_ARGUMENT, "take_strided: invalid shape");
+    const int64_t picked = first < n ? (n - first + step - 1) / step : 0;
+    const int64_t bytes = outer * picked * inner_bytes;
+    if (bytes == 0) return NVC_OK;
+    if (!src || !out) return set_error(NVC_ERR_INVALID_ARGUMENT, "take_strided: null operand");
+    const uintptr_t both = (uintptr_t)src | (uintptr_t)out | (uintptr_t)inner_bytes;
+    const int unit = both % 16 == 0 ? 16 : both % 8 == 0 ? 8 : both % 4 == 0 ? 4 : both % 2 == 0 ? 2 : 1;
+    const int64_t total = bytes / unit, inner = inner_bytes / unit;
+    int64_t want = (total + 255) / 256, cap = (int64_t)dev->prop.multiProcessorCount * 16;
+    const unsigned blocks = (unsigned)(want < cap ? want : cap);
+    switch (unit) {
+        case 16: take_strided_kernel<uint4><<<blocks, 256, 0, dev->stream>>>((const uint4 *)src, (uint4 *)out, n, picked, inner, first, step, total); break;
+        case 8: take_strided_kernel<uint2><<<blocks, 256, 0, dev->stream>>>((const uint2 *)src, (uint2 *)out, n, picked, inner, first, step, total); break;
+        case 4: take_strided_kernel<uint32_t><<<blocks, 256, 0, dev->stream>>>((const uint32_t *)src, (uint32_t *)out, n, picked, inner, first, step, total); break;
+        case 2: take_strided_kernel<uint16_t><<<blocks, 256, 0, dev->stream>>>((const uint16_t *)src, (uint16_t *)out, n, picked, inner, first, step, total); break;
+        default: take_strided_kernel<uint8_t><<<blocks, 256, 0, dev->stream>>>((const uint8_t *)src, (uint8_t *)out, n, picked, inner, first, step, total); break;
+    }
+    return check_launch(dev, "take_strided_kernel");
 }
