@@ -223,6 +223,22 @@ int32_t nvc_qqmm_prepare_scales(nvc_device *dev, const nvc_quant *q, const void 
 int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w,
                           const void *laid_out_scales, int64_t M, int64_t N, int64_t K, void *y);
 
+/* fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722, fast/imp.rs:3940-4096): attention of one query
+ * row per head over an affine-quantized KV cache, without a mask,
+ *   out[b, h, 0, :] = softmax(scale * q[b, h, 0, :] . K[b, h / rep, s, :] over s [, sinks[h]]) . V[b, h / rep, s, :]
+ * q and out [B, Hq, 1, D] of `dtype` (float16 / bfloat16 / float32), K and V codes uint32 [B, Hkv, S, D * bits / 32],
+ * their scales and biases [B, Hkv, S, D / group_size] of `dtype`, sinks [Hq] of `dtype` or NULL (a sink joins the
+ * softmax's denominator only).  `capacity` >= S is the number of rows between consecutive heads of every cache
+ * tensor (a cache is a view of a longer allocation).  The shapes the reference's kernel takes: D 64 or 128; 3, 4 or
+ * 8 bits; groups of 32, 64 or 128 within a head; Hq / Hkv 1, 2, 4 or 8.  Float32 throughout: within the float bound
+ * of attention over the dequantized cache (crates/nuvec-core/tests/quantized.rs:1964-2031).  Takes scratch from the
+ * pool: not inside a recorded step. */
+int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *quant, int32_t dtype, const void *q,
+                                const uint32_t *k_codes, const void *k_scales, const void *k_biases,
+                                const uint32_t *v_codes, const void *v_scales, const void *v_biases, const void *sinks,
+                                int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t capacity, float scale,
+                                void *out);
+
 /* convert_packed (crates/nuvec-lm/src/quant.rs:36-199) for one layer of an AutoAWQ or GPTQ checkpoint, on the
  * device: qweight (int32, AWQ [inputs, outputs / 8], GPTQ [inputs * bits / 32, outputs]), qzeros (int32
  * [groups, outputs * bits / 32], or NULL for the symmetric zero 2^(bits - 1); GPTQ v1 stores zero - 1) and

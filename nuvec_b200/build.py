@@ -16,7 +16,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libnuvec_cuda.so"
 TIMELINE_LIB = PKG / "libnuvec_cuda_timeline.so"
-SOURCES = ["runtime.cu", "quantize.cu", "qmv.cu", "qmm.cu", "qqmm.cu", "ops.cu", "moe.cu", "convert.cu", "peer.cu", "comm_nccl.cpp"]
+SOURCES = ["runtime.cu", "quantize.cu", "qmv.cu", "qmm.cu", "qqmm.cu", "ops.cu", "moe.cu", "convert.cu", "attention.cu", "peer.cu", "comm_nccl.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
          "-Xcompiler", "-Wall", "-diag-suppress", "177"]

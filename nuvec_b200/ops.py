@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "qqmm", "qqmm_prepare_scales", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "quantized_attention", "qqmm", "qqmm_prepare_scales", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -655,6 +655,43 @@ def qqmm(x: Array, q: Quantized, prepared: Optional[Array] = None) -> Array:
         _check(_ffi.lib().nvc_qqmm_prepared(x.dev._h, C.byref(c), BF16, x.ptr, q.weight.ptr, prepared.ptr, M, N, K, out.ptr))
     else:
         _check(_ffi.lib().nvc_qqmm(x.dev._h, C.byref(c), BF16, x.ptr, q.weight.ptr, q.scales.ptr, M, N, K, out.ptr))
+    return out
+
+
+def quantized_attention(q: Array, k: Quantized, v: Quantized, scale: float, sinks: Optional[Array] = None,
+                        length: Optional[int] = None) -> Array:
+    """fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722): one query row per head, q [B, Hq, 1, D], over
+    affine-quantized keys and values (codes [B, Hkv, S, D * bits / 32], scales and biases [B, Hkv, S, D / group_size]),
+    no mask, optional per-head sinks [Hq].  ``length`` attends to the first ``length`` keys of a longer cache (the
+    reference's cache views, ``k.weight.i((.., .., ..length))``).  Only the shapes the reference's kernel takes run
+    (fast/imp.rs:3944-3993); the composition it falls back to for several query rows is not built."""
+    if k.quant != v.quant or k.quant.mode != QuantMode.AFFINE:
+        raise InvalidArgument("quantized_attention: keys and values need one affine quantization")
+    if k.biases is None or v.biases is None:
+        raise InvalidArgument("quantized_attention: affine biases missing")
+    if q.ndim != 4 or k.weight.ndim != 4 or v.weight.ndim != 4:
+        raise InvalidArgument("quantized_attention: queries, keys and values must be 4-D")
+    quant = k.quant
+    gs, bits = quant.checked("quantized_attention")
+    B, Hq, L, D = q.shape
+    Bk, Hkv, cap, words = k.weight.shape
+    S = cap if length is None else int(length)
+    groups = D // gs if gs else 0
+    side_ok = all(t.weight.shape == (B, Hkv, cap, words) and t.weight.dtype == U32 and words * 32 == D * bits
+                  and t.scales.shape == (B, Hkv, cap, groups) and t.biases.shape == t.scales.shape
+                  and t.scales.dtype == q.dtype and t.biases.dtype == q.dtype for t in (k, v))
+    if not side_ok or not 0 <= S <= cap:
+        raise InvalidArgument(f"quantized_attention: cache of shape {list(k.weight.shape)} / {list(v.weight.shape)} does not "
+                              f"match queries {list(q.shape)}")
+    if sinks is not None and (sinks.shape != (Hq,) or sinks.dtype != q.dtype):
+        raise InvalidArgument(f"quantized_attention: sinks must be [{Hq}] of the queries' dtype")
+    if L != 1:
+        raise UnsupportedError("quantized_attention: one query row per head (the composition for several rows is not built)")
+    out = q.dev.empty((B, Hq, 1, D), q.dtype)
+    c = quant._c()
+    _check(_ffi.lib().nvc_quantized_attention(q.dev._h, C.byref(c), q.dtype, q.ptr, k.weight.ptr, k.scales.ptr, k.biases.ptr,
+                                              v.weight.ptr, v.scales.ptr, v.biases.ptr, _ptr(sinks), B, Hq, Hkv, S, D, cap,
+                                              float(scale), out.ptr))
     return out
 
 
