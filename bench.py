@@ -281,6 +281,9 @@ def main():
     ap.add_argument("--one", default=None, metavar="M,N,K,BITS,COPIES",
                     help="profiling driver: one product shape on COPIES distinct weight sets, each launched twice "
                          "(prints the device time per launch); what the ncu commands under profiles/ run")
+    ap.add_argument("--attention", action="store_true",
+                    help="diagnostic: decode attention over a quantized KV cache at the reference's benchmark shapes "
+                         "(32 query / 8 key heads of 128, groups of 64, 8 and 4 bits, 1K-64K keys)")
     ap.add_argument("--checkpoint", action="store_true",
                     help="diagnostic: device time of the checkpoint-format conversions (AWQ / GPTQ layer, gpt-oss gate/up split) "
                          "at the sizes of the configurations, against the bytes they read and write")
@@ -326,6 +329,8 @@ def main():
         return
     if args.one:
         return one_shape(args, nv, _ffi, dev)
+    if args.attention:
+        return attention_shapes(nv, dev, peaks)
     if args.checkpoint:
         return checkpoint_conversions(nv, dev, peaks)
     if args.qqmm:
@@ -810,6 +815,40 @@ def qqmm_shape(args, nv, _ffi, dev, peaks):
                       "us_exact_bf16_activations": us_exact, "TFLOP/s_exact": flops / us_exact / 1e6,
                       "frac_of_measured_bf16_burst_qqmm": flops / us_qq / 1e6 / peaks["bf16_tflops"],
                       "note": "qqmm includes the quantization of x and the layout of both scale arrays"}))
+
+
+# ── decode attention over a quantized cache (--attention) ────────────────────────────────────
+def attention_shapes(nv, dev, peaks):
+    """nvc_quantized_attention at the shapes of the reference's benchmark (crates/nuvec-core/benches/kv_attention.rs):
+    one query row, 32 query and 8 key heads of size 128, groups of 64, 8- and 4-bit caches of 1K to 64K keys; 32
+    independent calls (distinct queries) per timing, device time per call against the cache bytes it has to read."""
+    rng = np.random.default_rng(0)
+    Hq, Hkv, D, gs, calls = 32, 8, 128, 64, 32
+    rows = []
+    for bits in (8, 4):
+        quant = nv.Quant.affine(gs, bits)
+        for S in (1024, 4096, 16384, 32768, 65536):
+            def side():
+                return nv.Quantized(dev.array(rng.integers(0, 2 ** 32, (1, Hkv, S, D * bits // 32), dtype=np.uint32), nv.U32),
+                                    dev.array(nv.f32_to_bf16(rng.uniform(0.01, 0.05, (1, Hkv, S, D // gs)).astype(np.float32)), nv.BF16),
+                                    dev.array(nv.f32_to_bf16(rng.uniform(-0.4, -0.1, (1, Hkv, S, D // gs)).astype(np.float32)), nv.BF16), quant)
+            k, v = side(), side()
+            qs = [dev.array(nv.f32_to_bf16(rng.standard_normal((1, Hq, 1, D)).astype(np.float32)), nv.BF16) for _ in range(calls)]
+            scale = D ** -0.5
+            for q in qs[:4]:
+                nv.quantized_attention(q, k, v, scale)
+            e0, e1 = dev.event(), dev.event()
+            e0.record()
+            for q in qs:
+                nv.quantized_attention(q, k, v, scale)
+            e1.record()
+            e1.synchronize()
+            us = e0.elapsed_ms(e1) * 1e3 / calls
+            cache = 2 * (k.weight.nbytes + k.scales.nbytes + k.biases.nbytes)
+            rows.append({"bits": bits, "keys": S, "us": us, "cache_GB/s": cache / us / 1e3, "frac_of_measured_hbm": cache / us / 1e3 / peaks["hbm_gbs"],
+                         "cache_MB": cache / 1e6})
+    print(json.dumps({"quantized_attention": rows, "shape": "1 x 32 query / 8 key heads x 128, groups of 64, bfloat16",
+                      "note": "caches up to 16K keys (q8) / 32K keys (q4) fit the 126 MB L2 and are re-read from it by the 32 calls"}))
 
 
 # ── checkpoint-format conversions (--checkpoint) ───────────────────────────────────────────────

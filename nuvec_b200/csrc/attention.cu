@@ -51,8 +51,11 @@ __device__ __forceinline__ uint32_t qa_code(const uint32_t *row, int d) {
     return v & 7u;
 }
 
+// an integer below 2^23 as a float without the conversion unit (a quarter-rate instruction otherwise)
+__device__ __forceinline__ float qa_float(uint32_t c) { return __uint_as_float(0x4B000000u | c) - 8388608.0f; }
+
 template <typename T, int BITS, int D, int GS>
-__global__ void __launch_bounds__(QA_THREADS) qattn_split_kernel(QAttnParams p) {
+__global__ void __launch_bounds__(QA_THREADS, 5) qattn_split_kernel(QAttnParams p) {
     constexpr int W = D * BITS / 32, G = D / GS, DPT = D / 64;
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int rep = p.Hq / p.Hkv, t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(QA_THREADS) qattn_split_kernel(QAttnParams p) 
                 for (int h = 0; h < QA_MAX_REP; h++) a[h] = 0.0f;
 #pragma unroll
                 for (int d = g * GS; d < (g + 1) * GS; d++) {
-                    const float c = (float)qa_code<BITS>(row, d);
+                    const float c = qa_float(qa_code<BITS>(row, d));
                     const float4 q0 = *reinterpret_cast<const float4 *>(&qs[d][0]);
                     a[0] = fmaf(c, q0.x, a[0]); a[1] = fmaf(c, q0.y, a[1]); a[2] = fmaf(c, q0.z, a[2]); a[3] = fmaf(c, q0.w, a[3]);
                     if (rep > 4) {
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(QA_THREADS) qattn_split_kernel(QAttnParams p) 
             for (int j = 0; j < DPT; j++) {
                 const int d = dl * DPT + j;
                 const float2 sb = vsb[s][d / GS];
-                const float v = fmaf(sb.x, (float)qa_code<BITS>(vrow[s], d), sb.y);
+                const float v = fmaf(sb.x, qa_float(qa_code<BITS>(vrow[s], d)), sb.y);
                 acc[j][0] = fmaf(p0.x, v, acc[j][0]); acc[j][1] = fmaf(p0.y, v, acc[j][1]);
                 acc[j][2] = fmaf(p0.z, v, acc[j][2]); acc[j][3] = fmaf(p0.w, v, acc[j][3]);
                 if (rep > 4) {
@@ -289,9 +292,9 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
         return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: null operand");
     if (((uintptr_t)k_codes | (uintptr_t)v_codes) % 16 != 0) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: the codes must be 16-byte aligned");
     if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: not inside a recorded step (it takes scratch from the pool)");
-    // splits: enough blocks for every multiprocessor twice over, whole tiles of 128 keys each
+    // splits: enough blocks to keep five on every multiprocessor (what their registers allow), whole tiles of 128 keys each
     const int64_t tiles = S > 0 ? (S + QA_TILE - 1) / QA_TILE : 1;
-    int64_t splits = (2 * (int64_t)dev->prop.multiProcessorCount + B * Hkv - 1) / (B * Hkv);
+    int64_t splits = (5 * (int64_t)dev->prop.multiProcessorCount + B * Hkv - 1) / (B * Hkv);
     if (splits > tiles) splits = tiles;
     if (splits < 1) splits = 1;
     const int64_t chunk = (tiles + splits - 1) / splits * QA_TILE;
