@@ -27,6 +27,9 @@
 namespace nvc {
 
 constexpr int QA_THREADS = 128, QA_TILE = 128, QA_MAX_REP = 8;
+#ifndef QA_MMA_BLOCKS
+#define QA_MMA_BLOCKS 3
+#endif
 
 struct QAttnParams {
     const void *q;                               // [B, Hq, 1, D]
@@ -223,6 +226,240 @@ __global__ void __launch_bounds__(QA_THREADS, 5) qattn_split_kernel(QAttnParams 
     }
 }
 
+// ── the tensor-core form (16-bit types, 4- and 8-bit codes) ─────────────────────────────────────────────
+// mma.sync m16n8k16 (float16 operands, float32 accumulators): the rows of the A operand are the key head's
+// query heads (8 of the 16 rows at most are used), a code enters as the exact float16 integer 1024 + code
+// (0x6400 | code), and the offset is taken out again with sums the kernel keeps anyway:
+//   scores   S_g[h, key] = sum over the group's dims of q[h, d] * (1024 + code[key, d])        (tensor cores)
+//            score[h, key] = sum_g  s_g[key] * (S_g - 1024 * qsum_g[h]) + b_g[key] * qsum_g[h]
+//   values   O[h, d] += sum over keys of (p[h, key] * s_g(d)[key]) * (1024 + code[key, d])      (tensor cores)
+//            out[h, d] = O[h, d] + sum over keys of (p * b_g(d)[key] - 1024 * p * s_g(d)[key])
+// A warp owns 32 keys of a tile of 128: its score accumulators (C fragments, 16 heads x 8 keys) are, pairwise,
+// exactly the A fragments (16 heads x 16 keys) of its value products, so the probabilities never leave
+// registers; the four warps' outputs are added at the end.  q * scale and p * s are rounded to float16
+// (11 significant bits, three more than the bfloat16 the reference's composition rounds them to).
+__device__ __forceinline__ void qa_mma(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    const uint32_t zero = 0u;  // rows 8-15 of A (no heads there)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t qa_pack_f16(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ float2 qa_unpack_f16(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2 *>(&v)); }
+
+template <typename T, int BITS, int D, int GS>
+__global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QAttnParams p) {
+    static_assert(BITS == 4 || BITS == 8, "codes that fill bytes");
+    constexpr int W = D * BITS / 32, G = D / GS, KS = D / 16, NBD = D / 8, WP = W + 1;  // WP: padded row of the value tile
+    constexpr int KS_PER_G = GS / 16, NBD_PER_G = GS / 8;
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int rep = p.Hq / p.Hkv, t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int g8 = lane >> 2, c = lane & 3;  // the fragments' group (a head, a key or a dim) and pair index
+    const int s0 = split * p.chunk, s1 = min(p.S, s0 + p.chunk);
+    const bool head = g8 < rep;
+
+    __shared__ float wred[2][4][8];
+    constexpr int VWORDS = QA_TILE * WP, RWORDS = 4 * 8 * D;
+    __shared__ __align__(16) uint32_t vtile[VWORDS > RWORDS ? VWORDS : RWORDS];
+
+    // the head's scaled queries as A fragments, and their sums per group (of the rounded values)
+    uint32_t qa0[KS], qa2[KS];
+    float qsum[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) qsum[g] = 0.0f;
+    {
+        const T *q = (const T *)p.q + ((size_t)b * p.Hq + hk * rep + (head ? g8 : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const int d = 16 * ks + 2 * c;
+            qa0[ks] = head ? qa_pack_f16(DT<T>::load(q, d) * p.scale, DT<T>::load(q, d + 1) * p.scale) : 0u;
+            qa2[ks] = head ? qa_pack_f16(DT<T>::load(q, d + 8) * p.scale, DT<T>::load(q, d + 9) * p.scale) : 0u;
+            const float2 u = qa_unpack_f16(qa0[ks]), v = qa_unpack_f16(qa2[ks]);
+            qsum[ks / KS_PER_G] += (u.x + u.y) + (v.x + v.y);
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            qsum[g] += __shfl_xor_sync(0xFFFFFFFFu, qsum[g], 1);
+            qsum[g] += __shfl_xor_sync(0xFFFFFFFFu, qsum[g], 2);
+        }
+    }
+
+    const size_t head_row = ((size_t)b * p.Hkv + hk) * p.capacity;
+    float m = -INFINITY, l = 0.0f;  // of head g8
+    float oc[NBD][4], side[G];      // outputs [head g8][dims 8 nbd + 2 c, + 1] (rows 8-15 idle); bias / offset terms per group
+#pragma unroll
+    for (int i = 0; i < NBD; i++) oc[i][0] = oc[i][1] = oc[i][2] = oc[i][3] = 0.0f;
+#pragma unroll
+    for (int g = 0; g < G; g++) side[g] = 0.0f;
+
+    for (int base = s0; base < s1; base += QA_TILE) {
+        const int keys = min(QA_TILE, s1 - base);
+        // ── the tile's value codes into shared memory, rows padded by a word (the fragments read four rows at once) ──
+        {
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.vw + (head_row + base) * W);
+            for (int i = t; i < keys * W / 4; i += QA_THREADS) {
+                const uint4 v = src[i];
+                const int row = (4 * i) / W, col = (4 * i) % W;
+                uint32_t *dst = vtile + row * WP + col;
+                dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+            }
+        }
+        // ── scores of the warp's 32 keys: four blocks of 8 keys ──
+        float sc[4][2];
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) {
+            const int kfrag = warp * 32 + nb * 8;                       // first key of the block, within the tile
+            const int krow = min(kfrag + g8, keys - 1);                 // the key whose codes this lane feeds (clamped: masked below)
+            const uint32_t *row = p.kw + (head_row + base + krow) * W;
+            float cg[G][4];
+#pragma unroll
+            for (int g = 0; g < G; g++) cg[g][0] = cg[g][1] = cg[g][2] = cg[g][3] = 0.0f;
+#pragma unroll
+            for (int q4 = 0; q4 < W / 4; q4++) {
+                const uint4 v = reinterpret_cast<const uint4 *>(row)[q4];
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                if (BITS == 4) {
+                    // words 4 q4 .. + 3 = dims 32 q4 .. + 31 = two steps of 16 dims; the lane's codes are byte c of every word
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const int ks = 2 * q4 + half;
+                        uint32_t bf[2];
+#pragma unroll
+                        for (int j = 0; j < 2; j++) {
+                            const uint32_t byte = __byte_perm(w[2 * half + j], 0, 0x4440 | c);
+                            bf[j] = ((byte | (byte << 12)) & 0x000F000Fu) | 0x64006400u;
+                        }
+                        qa_mma(cg[ks / KS_PER_G], qa0[ks], qa2[ks], bf[0], bf[1]);
+                    }
+                } else {
+                    // words 4 q4 .. + 3 = dims 16 q4 .. + 15 = one step; dims 2 c, 2 c + 1 are a half of word c / 2, dims + 8 of word 2 + c / 2
+                    const int ks = q4;
+                    const uint32_t lo = (c & 2) ? w[1] : w[0], hi = (c & 2) ? w[3] : w[2];
+                    const uint32_t sel = (c & 1) ? 0x4342u : 0x4140u;
+                    qa_mma(cg[ks / KS_PER_G], qa0[ks], qa2[ks], __byte_perm(lo, 0, sel) | 0x64006400u, __byte_perm(hi, 0, sel) | 0x64006400u);
+                }
+            }
+            // the C fragment holds [head g8][keys kfrag + 2 c, + 1]
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int key = min(kfrag + 2 * c + j, keys - 1);
+                float sv = 0.0f;
+#pragma unroll
+                for (int g = 0; g < G; g++) {
+                    const float ks_ = DT<T>::load((const T *)p.ks, (head_row + base + key) * G + g);
+                    const float kb_ = DT<T>::load((const T *)p.kb, (head_row + base + key) * G + g);
+                    sv = fmaf(ks_, cg[g][j] - 1024.0f * qsum[g], fmaf(kb_, qsum[g], sv));
+                }
+                sc[nb][j] = sv;
+            }
+        }
+        // ── running maximum and denominator of head g8 ──
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const bool valid = head && warp * 32 + nb * 8 + 2 * c + j < keys;
+                if (!valid) sc[nb][j] = -INFINITY;
+                tmax = fmaxf(tmax, sc[nb][j]);
+            }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 2));
+        if (c == 0) wred[0][warp][g8] = tmax;
+        __syncthreads();  // (also: the value tile is complete)
+        const float mn = fmaxf(fmaxf(m, fmaxf(wred[0][0][g8], wred[0][1][g8])), fmaxf(wred[0][2][g8], wred[0][3][g8]));
+        const float corr = m == -INFINITY ? 0.0f : expf(m - mn);
+        m = mn;
+        float psum = 0.0f;
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                sc[nb][j] = sc[nb][j] == -INFINITY ? 0.0f : expf(sc[nb][j] - mn);
+                psum += sc[nb][j];
+            }
+        psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 1);
+        psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 2);
+        if (c == 0) wred[1][warp][g8] = psum;
+        __syncthreads();
+        l = fmaf(l, corr, (wred[1][0][g8] + wred[1][1][g8]) + (wred[1][2][g8] + wred[1][3][g8]));
+#pragma unroll
+        for (int i = 0; i < NBD; i++) {
+            oc[i][0] *= corr;
+            oc[i][1] *= corr;
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) side[g] *= corr;
+        // ── values: two steps of 16 keys; the probabilities times the keys' value scales are the A fragments ──
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const int r0 = warp * 32 + kk * 16 + 2 * c;  // the lane's keys within the tile: r0, r0 + 1, r0 + 8, r0 + 9
+            uint32_t pa0[G], pa2[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                float ps[4], pb = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int key = min(r0 + (i & 1) + 8 * (i >> 1), keys - 1);
+                    const float pv = sc[2 * kk + (i >> 1)][i & 1];  // (zero for keys past the end)
+                    ps[i] = pv * DT<T>::load((const T *)p.vs, (head_row + base + key) * G + g);
+                    pb = fmaf(pv, DT<T>::load((const T *)p.vb, (head_row + base + key) * G + g), pb);
+                }
+                pa0[g] = qa_pack_f16(ps[0], ps[1]);
+                pa2[g] = qa_pack_f16(ps[2], ps[3]);
+                const float2 u = qa_unpack_f16(pa0[g]), v = qa_unpack_f16(pa2[g]);
+                side[g] += pb - 1024.0f * ((u.x + u.y) + (v.x + v.y));
+            }
+            const uint32_t *v0 = vtile + r0 * WP, *v1 = v0 + WP, *v2 = v0 + 8 * WP, *v3 = v0 + 9 * WP;
+#pragma unroll
+            for (int nbd = 0; nbd < NBD; nbd++) {
+                uint32_t b0, b1;
+                if (BITS == 4) {
+                    const int sh = 4 * g8;  // dim 8 nbd + g8 = nibble g8 of word nbd
+                    b0 = (((v0[nbd] >> sh) & 0xFu) | (((v1[nbd] >> sh) & 0xFu) << 16)) | 0x64006400u;
+                    b1 = (((v2[nbd] >> sh) & 0xFu) | (((v3[nbd] >> sh) & 0xFu) << 16)) | 0x64006400u;
+                } else {
+                    const int wd = 2 * nbd + (g8 >> 2), sh = 8 * (g8 & 3);  // byte g8 % 4 of word 2 nbd + g8 / 4
+                    b0 = (((v0[wd] >> sh) & 0xFFu) | (((v1[wd] >> sh) & 0xFFu) << 16)) | 0x64006400u;
+                    b1 = (((v2[wd] >> sh) & 0xFFu) | (((v3[wd] >> sh) & 0xFFu) << 16)) | 0x64006400u;
+                }
+                qa_mma(oc[nbd], pa0[nbd / NBD_PER_G], pa2[nbd / NBD_PER_G], b0, b1);
+            }
+        }
+        __syncthreads();  // the value tile and wred are rewritten by the next tile
+    }
+
+    // ── the four warps' outputs together, then this split's partial result ──
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        side[g] += __shfl_xor_sync(0xFFFFFFFFu, side[g], 1);
+        side[g] += __shfl_xor_sync(0xFFFFFFFFu, side[g], 2);
+    }
+    float *wsum = reinterpret_cast<float *>(vtile);  // [warp][head][D]
+    if (head) {
+#pragma unroll
+        for (int nbd = 0; nbd < NBD; nbd++) {
+            float *dst = wsum + ((warp * 8 + g8) * D) + 8 * nbd + 2 * c;
+            dst[0] = oc[nbd][0] + side[nbd / NBD_PER_G];
+            dst[1] = oc[nbd][1] + side[nbd / NBD_PER_G];
+        }
+    }
+    __syncthreads();
+    for (int i = t; i < D * rep; i += QA_THREADS) {
+        const int h = i / D, d = i % D;
+        float *dst = p.part + (((size_t)b * p.Hq + hk * rep + h) * p.splits + split) * (D + 2);
+        dst[d] = (wsum[(0 * 8 + h) * D + d] + wsum[(1 * 8 + h) * D + d]) + (wsum[(2 * 8 + h) * D + d] + wsum[(3 * 8 + h) * D + d]);
+    }
+    if (warp == 0 && c == 0 && head) {
+        float *dst = p.part + (((size_t)b * p.Hq + hk * rep + g8) * p.splits + split) * (D + 2);
+        dst[D] = m;
+        dst[D + 1] = l;
+    }
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(D) qattn_combine_kernel(QAttnParams p) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
@@ -243,9 +480,28 @@ __global__ void __launch_bounds__(D) qattn_combine_kernel(QAttnParams p) {
     DT<T>::store((T *)p.out, ((size_t)b * p.Hq + h) * D + d, den > 0.0f ? __fdiv_rn(num, den) : 0.0f);
 }
 
+// 16-bit types with 4- or 8-bit codes run on the tensor cores (switch: NUVEC_QATTN_MMA=0)
+static bool qattn_uses_mma(int dtype, int bits) {
+    static const bool mma_on = !(getenv("NUVEC_QATTN_MMA") && atoi(getenv("NUVEC_QATTN_MMA")) == 0);
+    return mma_on && dtype != NVC_F32 && bits != 3;
+}
+
+template <typename T, int BITS, int D, int GS>
+static void qattn_launch_mma(nvc_device *dev, const QAttnParams &p, dim3 grid) {
+    if constexpr (sizeof(T) == 2 && (BITS == 4 || BITS == 8) && D % GS == 0) qattn_mma_kernel<T, BITS, D, GS><<<grid, QA_THREADS, 0, dev->stream>>>(p);
+}
+
 template <typename T, int BITS, int D>
 static int32_t qattn_launch(nvc_device *dev, const QAttnParams &p, int gs) {
     dim3 grid((unsigned)p.splits, (unsigned)p.Hkv, (unsigned)p.B);
+    if (qattn_uses_mma(sizeof(T) == 2 ? NVC_F16 : NVC_F32, BITS)) {
+        if (gs == 32) qattn_launch_mma<T, BITS, D, 32>(dev, p, grid);
+        else if (gs == 64) qattn_launch_mma<T, BITS, D, 64>(dev, p, grid);
+        else qattn_launch_mma<T, BITS, D, D == 128 ? 128 : 64>(dev, p, grid);
+        NVC_TRY(check_launch(dev, "qattn_mma_kernel"));
+        qattn_combine_kernel<T, D><<<dim3((unsigned)p.Hq, (unsigned)p.B), D, 0, dev->stream>>>(p);
+        return check_launch(dev, "qattn_combine_kernel");
+    }
     if (gs == 32) qattn_split_kernel<T, BITS, D, 32><<<grid, QA_THREADS, 0, dev->stream>>>(p);
     else if (gs == 64) qattn_split_kernel<T, BITS, D, 64><<<grid, QA_THREADS, 0, dev->stream>>>(p);
     else if (D == 128) qattn_split_kernel<T, BITS, D, D == 128 ? 128 : 64><<<grid, QA_THREADS, 0, dev->stream>>>(p);
@@ -292,9 +548,11 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
         return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: null operand");
     if (((uintptr_t)k_codes | (uintptr_t)v_codes) % 16 != 0) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: the codes must be 16-byte aligned");
     if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: not inside a recorded step (it takes scratch from the pool)");
-    // splits: enough blocks to keep five on every multiprocessor (what their registers allow), whole tiles of 128 keys each
+    // splits: one wave of as many blocks as stay resident together (what their registers allow: three of the
+    // tensor-core kernel, five of the other, per multiprocessor), whole tiles of 128 keys each
     const int64_t tiles = S > 0 ? (S + QA_TILE - 1) / QA_TILE : 1;
-    int64_t splits = (5 * (int64_t)dev->prop.multiProcessorCount + B * Hkv - 1) / (B * Hkv);
+    const int per_sm = qattn_uses_mma(dtype, bits) ? QA_MMA_BLOCKS : 5;
+    int64_t splits = per_sm * (int64_t)dev->prop.multiProcessorCount / (B * Hkv);
     if (splits > tiles) splits = tiles;
     if (splits < 1) splits = 1;
     const int64_t chunk = (tiles + splits - 1) / splits * QA_TILE;
