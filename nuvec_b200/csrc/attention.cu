@@ -15,13 +15,14 @@
 // A cache is a view of a longer allocation (capacity beyond the keys): `capacity` is the number
 // of rows between consecutive heads of every cache tensor.
 //
-// Two kernels.  qattn_split: one block per (split of the keys, key head, batch) walks its keys in
-// tiles of 128 with a running maximum and denominator per query head.  Scores: one thread per key
-// reads the key's codes once and multiplies them with all rep query rows (float32 queries in
-// shared memory, the group's scale and bias applied per group: s * sum(code * q) + b * sum(q)).
-// Values: the tile's codes, scales and biases are staged in shared memory with 16-byte loads; 64
-// threads x 2 key halves each own D / 64 output columns and accumulate p * (s * code + b).
-// qattn_combine merges the splits (and the sink) and rounds to the output type.
+// Every form splits the keys: one block of four warps per (split, key head, batch) walks its keys in tiles of
+// 128 with a running maximum and denominator per query head, and qattn_combine merges the splits (and the sink)
+// and rounds to the output type.  qattn_split_kernel (float32, and 3-bit codes) works on the CUDA cores:
+// scores by one thread per key, which reads the key's codes once and multiplies them with all rep query rows
+// (float32 queries in shared memory, the group's scale and bias applied per group: s * sum(code * q) +
+// b * sum(q)); values staged in shared memory with 16-byte loads, 64 threads x 2 key halves each own D / 64
+// output columns and accumulate p * (s * code + b).  qattn_mma_kernel (16-bit types, 4- and 8-bit codes) does
+// both products on the tensor cores; see there.
 #include "common.cuh"
 
 namespace nvc {
