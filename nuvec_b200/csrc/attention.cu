@@ -263,6 +263,9 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
     const bool head = g8 < rep;
 
     __shared__ float wred[2][4][8];
+    __shared__ float4 sbt[QA_TILE][G];  // the tile's (key scale, key bias, value scale, value bias) per key and group
+    constexpr int KP = W + 4;  // padded row of the key tile: eight rows' 16-byte reads fall into distinct banks
+    __shared__ __align__(16) uint32_t ktile[QA_TILE * KP];
     constexpr int VWORDS = QA_TILE * WP, RWORDS = 4 * 8 * D;
     __shared__ __align__(16) uint32_t vtile[VWORDS > RWORDS ? VWORDS : RWORDS];
 
@@ -298,23 +301,32 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
 
     for (int base = s0; base < s1; base += QA_TILE) {
         const int keys = min(QA_TILE, s1 - base);
-        // ── the tile's value codes into shared memory, rows padded by a word (the fragments read four rows at once) ──
+        // ── the tile's codes into shared memory with 16-byte loads, all in flight together; value rows padded by a
+        //    word (the fragments read four rows at once), key rows by four ──
         {
-            const uint4 *src = reinterpret_cast<const uint4 *>(p.vw + (head_row + base) * W);
+            const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kw + (head_row + base) * W);
+            const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vw + (head_row + base) * W);
             for (int i = t; i < keys * W / 4; i += QA_THREADS) {
-                const uint4 v = src[i];
+                const uint4 kv = ksrc[i], v = vsrc[i];
                 const int row = (4 * i) / W, col = (4 * i) % W;
+                *reinterpret_cast<uint4 *>(ktile + row * KP + col) = kv;
                 uint32_t *dst = vtile + row * WP + col;
                 dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
             }
+            for (int i = t; i < keys * G; i += QA_THREADS) {
+                const size_t at = (head_row + base) * G + i;
+                sbt[0][i] = make_float4(DT<T>::load((const T *)p.ks, at), DT<T>::load((const T *)p.kb, at), DT<T>::load((const T *)p.vs, at),
+                                        DT<T>::load((const T *)p.vb, at));
+            }
         }
+        __syncthreads();
         // ── scores of the warp's 32 keys: four blocks of 8 keys ──
         float sc[4][2];
 #pragma unroll
         for (int nb = 0; nb < 4; nb++) {
             const int kfrag = warp * 32 + nb * 8;                       // first key of the block, within the tile
             const int krow = min(kfrag + g8, keys - 1);                 // the key whose codes this lane feeds (clamped: masked below)
-            const uint32_t *row = p.kw + (head_row + base + krow) * W;
+            const uint32_t *row = ktile + krow * KP;
             float cg[G][4];
 #pragma unroll
             for (int g = 0; g < G; g++) cg[g][0] = cg[g][1] = cg[g][2] = cg[g][3] = 0.0f;
@@ -350,9 +362,8 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
                 float sv = 0.0f;
 #pragma unroll
                 for (int g = 0; g < G; g++) {
-                    const float ks_ = DT<T>::load((const T *)p.ks, (head_row + base + key) * G + g);
-                    const float kb_ = DT<T>::load((const T *)p.kb, (head_row + base + key) * G + g);
-                    sv = fmaf(ks_, cg[g][j] - 1024.0f * qsum[g], fmaf(kb_, qsum[g], sv));
+                    const float4 sb = sbt[key][g];
+                    sv = fmaf(sb.x, cg[g][j] - 1024.0f * qsum[g], fmaf(sb.y, qsum[g], sv));
                 }
                 sc[nb][j] = sv;
             }
@@ -370,7 +381,7 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
         tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 1));
         tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 2));
         if (c == 0) wred[0][warp][g8] = tmax;
-        __syncthreads();  // (also: the value tile is complete)
+        __syncthreads();
         const float mn = fmaxf(fmaxf(m, fmaxf(wred[0][0][g8], wred[0][1][g8])), fmaxf(wred[0][2][g8], wred[0][3][g8]));
         const float corr = m == -INFINITY ? 0.0f : expf(m - mn);
         m = mn;
@@ -406,8 +417,9 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
                 for (int i = 0; i < 4; i++) {
                     const int key = min(r0 + (i & 1) + 8 * (i >> 1), keys - 1);
                     const float pv = sc[2 * kk + (i >> 1)][i & 1];  // (zero for keys past the end)
-                    ps[i] = pv * DT<T>::load((const T *)p.vs, (head_row + base + key) * G + g);
-                    pb = fmaf(pv, DT<T>::load((const T *)p.vb, (head_row + base + key) * G + g), pb);
+                    const float4 sb = sbt[key][g];
+                    ps[i] = pv * sb.z;
+                    pb = fmaf(pv, sb.w, pb);
                 }
                 pa0[g] = qa_pack_f16(ps[0], ps[1]);
                 pa2[g] = qa_pack_f16(ps[2], ps[3]);
@@ -430,7 +442,7 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
                 qa_mma(oc[nbd], pa0[nbd / NBD_PER_G], pa2[nbd / NBD_PER_G], b0, b1);
             }
         }
-        __syncthreads();  // the value tile and wred are rewritten by the next tile
+        __syncthreads();  // the value tile, the scales and wred are rewritten by the next tile
     }
 
     // ── the four warps' outputs together, then this split's partial result ──
