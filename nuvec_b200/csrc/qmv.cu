@@ -414,6 +414,29 @@ template <int KIND> struct UnpackFp4 {
 };
 template <> struct Unpack<40> : UnpackFp4<1> {};
 template <> struct Unpack<41> : UnpackFp4<3> {};
+// 8-bit floating point (kernel "bits" 42 = mxfp8: E4M3 codes, one E8M0 scale per 32 values).  The code's
+// seven magnitude bits become exponent[3:0] and mantissa[6:4] of a bfloat16 whose value is the
+// magnitude * 2^-120 (the subnormal codes included: they are bfloat16 subnormals); multiplying by 2^120
+// restores the value (4 significant bits) and the scale is a power of two: the operand equals the
+// reference's float32 decode (crates/nuvec-core/src/kernels.rs:976-1009, fp8.rs:39-44).  The two NaN
+// codes (0x7F, 0xFF), which the reference's quantizer never writes (it saturates at 448), read as 480.
+// register 0 = codes (0, 2), register 1 = codes (1, 3), as for 8-bit affine.
+template <> struct Unpack<42> {
+    static constexpr int WBITS = 8, FP = 1;
+    static constexpr int UW = 1;
+    static constexpr int CODES = 4;
+    static constexpr int AREGS = 2;
+    static __device__ __forceinline__ void run(const uint32_t *u, const GroupConsts &c, uint32_t (&r)[2]) {
+        const uint32_t w = u[0];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint32_t x = w >> (8 * i);  // bytes i and i + 2 in the low byte of each half
+            const uint32_t bits = lop3_and_or(x << 8, 0x80008000u, (x << 4) & 0x07F007F0u);
+            r[i] = bf2_mul(bf2_mul(bits, 0x7B807B80u), c.s2);
+        }
+    }
+    static __device__ __forceinline__ void permute(const uint16_t *x, uint16_t *out) { Unpack<8>::permute(x, out); }
+};
 // bfloat16 pair {s, s} of a scale code: E8M0 (2^(code - 127); code 0 decodes to a float32 subnormal
 // that the reference flushes to zero) or E4M3 (subnormal results flushed likewise).
 __device__ __forceinline__ uint32_t fp4_scale2(uint32_t code, bool e8m0) {
@@ -1235,15 +1258,16 @@ __global__ void __launch_bounds__(QMV_THREADS, QMV_BLOCKS_PER_SM) qmv_affine_ker
 // ── host side ──────────────────────────────────────────────────────────────────────────
 
 // A unit is the smallest run of words that holds whole codes: one word, or three for 3 and 6 bits.
-// (`bits` below is the kernel's kind: the affine bit width, or 40 = mxfp4, 41 = nvfp4.)
-static bool kind_fp(int bits) { return bits == 40 || bits == 41; }
-static int code_bits(int bits) { return kind_fp(bits) ? 4 : bits; }
+// (`bits` below is the kernel's kind: the affine bit width, or 40 = mxfp4, 41 = nvfp4, 42 = mxfp8.)
+static bool kind_fp(int bits) { return bits == 40 || bits == 41 || bits == 42; }
+static int code_bits(int bits) { return bits == 42 ? 8 : kind_fp(bits) ? 4 : bits; }
 static int unit_words(int bits) { return bits == 3 || bits == 6 ? 3 : 1; }
 static int codes_per_word(int bits) { return unit_words(bits) * 32 / code_bits(bits); }  // codes per unit
 int qmv_kind(int32_t mode, int32_t bits) {
     if (mode == NVC_AFFINE) return bits;
     if (mode == NVC_MXFP4 && bits == 4) return 40;
     if (mode == NVC_NVFP4 && bits == 4) return 41;
+    if (mode == NVC_MXFP8 && bits == 8) return 42;
     return 0;
 }
 
@@ -1416,6 +1440,7 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     NVC_QMV(4, 1) NVC_QMV(4, 2) NVC_QMV(4, 4) NVC_QMV(4, 8) NVC_QMV(8, 1) NVC_QMV(8, 2) NVC_QMV(8, 4) NVC_QMV(8, 8)
     NVC_QMV(2, 1) NVC_QMV(2, 2) NVC_QMV(3, 1) NVC_QMV(6, 1) NVC_QMV(6, 2)
     NVC_QMV(40, 1) NVC_QMV(40, 2) NVC_QMV(40, 4) NVC_QMV(41, 1) NVC_QMV(41, 2) NVC_QMV(41, 4)
+    NVC_QMV(42, 1) NVC_QMV(42, 2) NVC_QMV(42, 4)
 #undef NVC_QMV
     return set_error(NVC_ERR_UNSUPPORTED, "qmv: no kernel for %d bits, group size %d", bits, p.gs);
 }

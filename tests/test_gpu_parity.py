@@ -396,6 +396,46 @@ def test_qmm_fp4(be, mode, gs, M, N, K):
     assert np.array_equal(got, dense[:, ks].T)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(72, 1024), (160, 2880), (33, 96)])
+def test_qmv_mxfp8(be, M, N, K):
+    # MXFP8 weights (E4M3 codes, E8M0 scale per 32) on the few-row kernel: within one output rounding of the
+    # oracle, and unit rows return the oracle's float32 decode bit for bit
+    rng = np.random.default_rng(M + N + K)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    w.reshape(-1)[:6] = oracle.from_f32(np.array([0.0, -0.0, 1e-4, -0.5, 3.0, 1e-7], np.float32), oracle.BF16)
+    c, s, _ = oracle.quantize(w, oracle.BF16, oracle.MXFP8, 32, 8)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, None, oracle.BF16, oracle.MXFP8, 32, 8)
+    got = be.quantized_matmul(x, c, s, None, oracle.BF16, oracle.MXFP8, 32, 8, True)
+    assert_product_tight(got, want, oracle.BF16, f"M{M} N{N} K{K}")
+    dense = oracle.to_f32(oracle.dequantize(c, s, None, oracle.F32, oracle.MXFP8, 32, 8), oracle.F32)
+    ks = rng.permutation(K)[:8]
+    xu = np.zeros((8, K), np.float32)
+    xu[np.arange(8), ks] = 1.0
+    got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(xu, oracle.BF16), c, s, None, oracle.BF16, oracle.MXFP8, 32, 8, True), oracle.BF16)
+    assert np.array_equal(got, dense[:, ks].T)
+
+
+def test_qmv_mxfp8_every_code(be):
+    # every E4M3 code the quantizer can write (all but the two NaN codes), subnormals included, under several
+    # scales: the kernel's operand is the oracle's decode
+    codes = np.array([v for v in range(256) if v & 0x7F != 0x7F], np.uint8)
+    K = 256
+    rows = np.resize(codes, (64, K))
+    for r in range(64):
+        rows[r] = np.roll(rows[r], 7 * r)
+    c = np.ascontiguousarray(rows).view(np.uint32)
+    rng = np.random.default_rng(0)
+    s = rng.integers(110, 140, (64, K // 32), dtype=np.uint8)
+    dense = oracle.to_f32(oracle.dequantize(c, s, None, oracle.F32, oracle.MXFP8, 32, 8), oracle.F32)
+    for k0 in range(0, K, 8):
+        xu = np.zeros((8, K), np.float32)
+        xu[np.arange(8), np.arange(k0, k0 + 8)] = 1.0
+        got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(xu, oracle.BF16), c, s, None, oracle.BF16, oracle.MXFP8, 32, 8, True), oracle.BF16)
+        assert np.array_equal(got, dense[:, k0:k0 + 8].T), k0
+
+
 def moe_case(rng, T, E, topk, N, K, mode=oracle.AFFINE, gs=64, bits=4):
     w = rand(rng, (E, N, K), oracle.BF16, 0.02)
     c, s, b = oracle.quantize(w, oracle.BF16, mode, gs, bits)
