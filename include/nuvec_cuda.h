@@ -223,6 +223,15 @@ int32_t nvc_qqmm_prepare_scales(nvc_device *dev, const nvc_quant *q, const void 
 int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, const uint32_t *w,
                           const void *laid_out_scales, int64_t M, int64_t N, int64_t K, void *y);
 
+/* crate::with_row_exact (crates/nuvec-core/src/lib.rs:160-193): while on, quantized and gathered products of up to
+ * 8 rows (ROW_INDEPENDENT_ROWS) give each row the bits of its one-row product: the few-row kernel cuts every such
+ * product the way it cuts one row of one batch (the cuts decide the order of a row's float32 sums), rows that do
+ * not fit the kernel together run as many at a time as fit, and gathers take the grouped kernel only beyond 64
+ * rows (quantized.rs:723-731).  Off by default: products are cut for speed, and a row's bits may depend on the
+ * number of rows and batches multiplied with it. */
+int32_t nvc_set_row_exact(nvc_device *dev, int32_t on);
+int32_t nvc_row_exact(nvc_device *dev);
+
 /* fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722, fast/imp.rs:3940-4096): attention of one query
  * row per head over an affine-quantized KV cache, without a mask,
  *   out[b, h, 0, :] = softmax(scale * q[b, h, 0, :] . K[b, h / rep, s, :] over s [, sinks[h]]) . V[b, h / rep, s, :]

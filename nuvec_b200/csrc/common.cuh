@@ -65,6 +65,7 @@ struct nvc_device {
     nvc::Pool pool;
     uint64_t launches = 0;
     bool capturing = false;   // between nvc_graph_begin and nvc_graph_end
+    bool row_exact = false;   // nvc_set_row_exact: few-row products keep every row's one-row bits
     uint64_t captured = 0;    // kernels recorded by the open capture
     // Scratch owned by the handle and reused between calls (split-K partials and their
     // arrival counters); grown on demand from the pool.

@@ -31,7 +31,17 @@ static int32_t check_product(const char *op, const nvc_quant *q, int32_t dtype, 
 
 // The reference's rule for the grouped kernel (quantized.rs:724-731): at least 16 rows and 4
 // per expert on average.
-static bool grouped(int64_t rows, int64_t experts) { return rows >= 16 && rows / (experts > 0 ? experts : 1) >= 4; }
+// Row-exact (crate::with_row_exact): more rows than the row-independent region, 8 tokens with up to 8 experts.
+static bool grouped(int64_t rows, int64_t experts, bool row_exact) {
+    return rows >= (row_exact ? 65 : 16) && rows / (experts > 0 ? experts : 1) >= 4;
+}
+
+extern "C" int32_t nvc_set_row_exact(nvc_device *dev, int32_t on) {
+    if (!dev) return set_error(NVC_ERR_INVALID_ARGUMENT, "set_row_exact: null device");
+    dev->row_exact = on != 0;
+    return NVC_OK;
+}
+extern "C" int32_t nvc_row_exact(nvc_device *dev) { return dev && dev->row_exact ? 1 : 0; }
 
 __global__ void sorted_offsets_kernel(const uint32_t *__restrict__ idx, int64_t rows, int64_t groups,
                                       int32_t *__restrict__ out) {
@@ -92,6 +102,36 @@ extern "C" int32_t nvc_quantized_matmul(nvc_device *dev, const nvc_quant *q, int
         p.x_vec = ((uintptr_t)x % 16 == 0) && (ldx % 8 == 0) && (x_batch_stride % 8 == 0);
         p.global = global_scale; p.expert_global = 0;
         return launch_qmv_affine(dev, qmv_kind(q->mode, q->bits), p, batch);
+    }
+    if (dev->row_exact && M > 1 && M <= 8 &&
+        qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, 1, N, K, x, ldx, x_batch_stride, w, w_batch_stride)) {
+        // Row-exact and too many rows for the few-row kernel's shared memory at once: as many rows at a time as fit
+        // (every launch is cut like a one-row product, so every row keeps its one-row bits).
+        int64_t fit = 1;
+        while (fit + 1 <= M && qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, fit + 1, N, K, x, ldx, x_batch_stride, w,
+                                                   w_batch_stride))
+            fit++;
+        const size_t esz = dtype_size(dtype);
+        for (int64_t r0 = 0; r0 < M; r0 += fit) {
+            const int64_t m = M - r0 < fit ? M - r0 : fit;
+            for (int64_t b = 0; b < batch; b++) {
+                QmvParams p{};
+                p.x = (const char *)x + (b * x_batch_stride + r0 * ldx) * esz;
+                p.w = w + b * w_batch_stride;
+                const size_t ssz = q->mode == NVC_AFFINE ? esz : 1;
+                p.scales = (const char *)scales + b * s_batch_stride * ssz;
+                p.biases = biases ? (const char *)biases + b * s_batch_stride * ssz : nullptr;
+                p.lhs = nullptr; p.rhs = nullptr;
+                p.y = (char *)y + (b * M + r0) * N * esz;
+                p.N = N; p.K = K; p.ldx = ldx;
+                p.x_batch_stride = 0; p.w_batch_stride = 0; p.s_batch_stride = 0;
+                p.M = (int32_t)m; p.gs = q->group_size;
+                p.x_vec = ((uintptr_t)p.x % 16 == 0) && (ldx % 8 == 0);
+                p.global = global_scale; p.expert_global = 0;
+                NVC_TRY(launch_qmv_affine(dev, qmv_kind(q->mode, q->bits), p, 1));
+            }
+        }
+        return NVC_OK;
     }
     if (qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, ldx, w)) {
         for (int64_t b = 0; b < batch; b++) {
@@ -169,7 +209,7 @@ extern "C" int32_t nvc_gather_qmm(nvc_device *dev, const nvc_quant *q, int32_t d
     // kernel does not take go to the tensor-core kernel whatever the count.
     const bool few_rows_ok = M <= 8 && qmv_affine_eligible(q->mode, q->group_size, q->bits, dtype, transpose, M, N, K, x, K,
                                                            M * K, w, w_stride);
-    if (sorted && !lhs && M == 1 && (grouped(rows, experts) || !few_rows_ok) &&
+    if (sorted && !lhs && M == 1 && (grouped(rows, experts, dev->row_exact) || !few_rows_ok) &&
         qmm_eligible(q->mode, q->group_size, q->bits, dtype, transpose, rows, N, K, x, K, w)) {
         const int32_t *offs = offsets;
         if (!offs) {

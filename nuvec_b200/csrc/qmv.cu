@@ -1381,10 +1381,15 @@ int32_t launch_qmv_affine(nvc_device *dev, int32_t bits, QmvParams p, int64_t ba
     // Blocks: as many as stay resident (two per multiprocessor while shared memory allows), but
     // no more than give every warp a few iterations.
     // (each block also takes 1 KB of shared memory the system reserves)
-    int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(smem + 1024);
+    // Row-exact products (nvc_set_row_exact) are cut as one row of one batch would be, whatever M and the
+    // number of batches are: the cuts decide the order of a row's float32 sums, and every row must get the
+    // bits of its one-row product.  (Blocks beyond the resident ones queue; none waits for another.)
+    const size_t plan_smem = dev->row_exact ? qmv_smem(1, p.K, bits, wpl) : smem;
+    const int64_t plan_batch = dev->row_exact ? 1 : batch;
+    int64_t per_sm = (int64_t)(227 * 1024) / (int64_t)(plan_smem + 1024);
     if (per_sm > QMV_BLOCKS_PER_SM) per_sm = QMV_BLOCKS_PER_SM;
     if (per_sm < 1) per_sm = 1;
-    int64_t blocks = per_sm * dev->prop.multiProcessorCount / batch;
+    int64_t blocks = per_sm * dev->prop.multiProcessorCount / plan_batch;
     const int64_t min_iters = 4;
     const int64_t useful = (total + QMV_WARPS * min_iters - 1) / (QMV_WARPS * min_iters);
     if (blocks > useful) blocks = useful;

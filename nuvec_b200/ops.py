@@ -148,6 +148,21 @@ class Device:
     def reset_peak(self):
         _check(_ffi.lib().nvc_reset_peak(self._h))
 
+    def row_exact(self):
+        """``with dev.row_exact():`` crate::with_row_exact (crates/nuvec-core/src/lib.rs:175-186): products of up to 8
+        rows built inside give each row the bits of its one-row product."""
+        dev = self
+
+        class _RowExact:
+            def __enter__(self):
+                self.before = _ffi.lib().nvc_row_exact(dev._h)
+                _check(_ffi.lib().nvc_set_row_exact(dev._h, 1))
+
+            def __exit__(self, *exc):
+                _check(_ffi.lib().nvc_set_row_exact(dev._h, self.before))
+                return False
+        return _RowExact()
+
     # arrays
     def empty(self, shape: Sequence[int], dtype: int) -> "Array":
         return Array(self, tuple(int(d) for d in shape), dtype)

@@ -640,3 +640,45 @@ def test_qqmm_on_the_block_scaled_tensor_core_path(be, M, N, K, mode):
     plain = oracle.quantized_matmul(x, wc, ws, None, oracle.BF16, omode, gs, bits)
     if K >= 256 and M > 1:
         assert np.abs(oracle.to_f32(got, oracle.BF16) - oracle.to_f32(plain, oracle.BF16)).max() > 0
+
+
+@pytest.mark.parametrize("mode,gs,bits,N,K", [(oracle.AFFINE, 64, 4, 264, 4096), (oracle.AFFINE, 64, 4, 512, 12288),
+                                               (oracle.AFFINE, 32, 3, 96, 1024), (oracle.AFFINE, 128, 8, 4096, 4096),
+                                               (oracle.MXFP4, 32, 4, 160, 2880), (oracle.MXFP8, 32, 8, 136, 2048)])
+def test_row_exact_products_give_each_row_its_one_row_bits(be, mode, gs, bits, N, K):
+    # crate::with_row_exact (crates/nuvec-core/src/lib.rs:160-193; the reference's tests/few_rows.rs): up to 8 rows,
+    # each with the bits of the same row multiplied alone -- also where 8 rows do not fit the few-row kernel together
+    # (K = 12288) and with several batches
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(N + K + bits)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    c, s, b = oracle.quantize(w, oracle.BF16, mode, gs, bits)
+    x = rand(rng, (8, K), oracle.BF16)
+    with dev.row_exact():
+        alone = [be.quantized_matmul(x[i:i + 1], c, s, b, oracle.BF16, mode, gs, bits, True) for i in range(8)]
+        for M in (2, 3, 5, 8):
+            got = be.quantized_matmul(x[:M], c, s, b, oracle.BF16, mode, gs, bits, True)
+            for i in range(M):
+                assert np.array_equal(got[i:i + 1], alone[i]), f"M={M} row {i}"
+    # the one-row product itself is the same inside and outside the mode
+    assert np.array_equal(be.quantized_matmul(x[:1], c, s, b, oracle.BF16, mode, gs, bits, True), alone[0])
+    want = oracle.quantized_matmul(x, c, s, b, oracle.BF16, mode, gs, bits)
+    assert_product_tight(np.concatenate(alone), want, oracle.BF16)
+
+
+def test_row_exact_gathers_give_each_row_its_one_row_bits(be):
+    # 5 tokens x 4 experts = 20 sorted rows: outside the mode they take the grouped kernel (16+ rows, 4 per expert),
+    # inside it every row is its own product and has the bits of that row gathered alone
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(77)
+    T, E, topk, N, K = 5, 4, 4, 256, 1024
+    c, s, b, rhs, xr = moe_case(rng, T, E, topk, N, K)
+    with dev.row_exact():
+        got = be.gather_qmm(xr, c, s, b, None, rhs, oracle.BF16, oracle.AFFINE, 64, 4, True, None, True)
+        for i in (0, 7, 19):
+            one = be.gather_qmm(xr[i:i + 1], c, s, b, None, rhs[i:i + 1], oracle.BF16, oracle.AFFINE, 64, 4, True, None, True)
+            assert np.array_equal(got[i:i + 1], one), i
+    want = oracle.gather_qmm(xr, c, s, b, np.arange(len(rhs)), rhs, oracle.BF16, oracle.AFFINE, 64, 4, True, None)
+    assert_product_tight(got, want, oracle.BF16)
