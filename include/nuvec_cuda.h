@@ -168,6 +168,13 @@ int32_t nvc_dequantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const
                        const void *scales, const void *biases, const float *global_scale,
                        int64_t rows, int64_t cols, void *out, int32_t fused);
 
+/* FastOp::QuantizeDequantize (crates/nuvec-core/src/products.rs:306-315; MLX's fp_quantize_dequantize): x [rows, cols]
+ * through its quantization in a floating-point mode -- the values its codes represent, in x's dtype (with the
+ * optional nvfp4 global scale).  The activation side of qqmm and gather_qqmm (products.rs:337-352, 437-463): the
+ * reference multiplies the result with nvc_quantized_matmul / nvc_gather_qmm.  Takes scratch from the pool. */
+int32_t nvc_quantize_dequantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, int64_t rows,
+                                int64_t cols, const float *global_scale, void *out);
+
 /* Primitive::QuantizedMatmul (crates/nuvec-core/src/quantized.rs:453-537, shape rule
  * primitive.rs:1279-1323; CPU result kernels.rs:1091-1142).
  *   y[b] = x[b] (M x K, row stride ldx) * dequantize(w[b])^T      (transpose != 0)

@@ -414,3 +414,25 @@ extern "C" int32_t nvc_quantized_embedding(nvc_device *dev, const nvc_quant *q, 
     default: return dequantize_typed<__nv_bfloat16>(dev, q, codes, scales, biases, nullptr, total, out, 0, pick);
     }
 }
+
+// FastOp::QuantizeDequantize (crates/nuvec-core/src/products.rs:306-315, MLX's fp_quantize_dequantize): x through
+// its quantization in a floating-point mode, the values the codes represent, in x's dtype -- the activation side of
+// qqmm and gather_qqmm.  The reference's quantize followed by its dequantize; codes and scales pass through pool
+// scratch (so not inside a recorded step).
+extern "C" int32_t nvc_quantize_dequantize(nvc_device *dev, const nvc_quant *q, int32_t dtype, const void *x, int64_t rows, int64_t cols,
+                                           const float *global_scale, void *out) {
+    NVC_TRY(make_current(dev));
+    NVC_TRY(check_quant("quantize_dequantize", q));
+    if (q->mode == NVC_AFFINE) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantize_dequantize: needs a floating-point mode (mxfp4, mxfp8 or nvfp4)");
+    if (rows < 0 || cols < 0 || cols % q->group_size != 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantize_dequantize: invalid shape");
+    if (rows * cols == 0) return NVC_OK;
+    if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "quantize_dequantize: not inside a recorded step (it takes scratch from the pool)");
+    void *codes = nullptr, *scales = nullptr;
+    NVC_TRY(dev->pool.alloc((size_t)rows * cols * q->bits / 8, &codes));
+    int32_t rc = dev->pool.alloc((size_t)rows * (cols / q->group_size), &scales);
+    if (rc == NVC_OK) rc = nvc_quantize(dev, q, dtype, x, rows, cols, global_scale, (uint32_t *)codes, scales, nullptr);
+    if (rc == NVC_OK) rc = nvc_dequantize(dev, q, dtype, (const uint32_t *)codes, scales, nullptr, global_scale, rows, cols, out, 0);
+    if (codes) dev->pool.free(codes);  // (the pool hands the blocks out again in stream order)
+    if (scales) dev->pool.free(scales);
+    return rc;
+}

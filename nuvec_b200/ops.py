@@ -20,7 +20,7 @@ from . import _ffi
 from ._ffi import BF16, F16, F32, I32, U8, U32
 
 __all__ = ["Device", "Array", "QuantMode", "Quant", "Quantized", "GatherQmm", "quantize", "dequantize",
-           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "quantized_attention", "qqmm", "qqmm_prepare_scales", "NuvecError", "InvalidArgument",
+           "quantized_matmul", "gather_qmm", "sorted_offsets", "moe_route", "weighted_sum", "expert_bias_add", "moe_sort", "take_rows", "swiglu", "swiglu_oai", "quantized_embedding", "rms_norm", "add_rms_norm", "quantized_attention", "fake_quant", "gather_qqmm", "qqmm", "qqmm_prepare_scales", "NuvecError", "InvalidArgument",
            "UnsupportedError", "OutOfMemory", "NoDevice", "BackendError", "CommError",
            "f32_to_bf16", "bf16_to_f32"]
 
@@ -648,15 +648,58 @@ def qqmm_prepare_scales(q: Quantized) -> Array:
     return out
 
 
-def qqmm(x: Array, q: Quantized, prepared: Optional[Array] = None) -> Array:
+def fake_quant(x: Array, quant: Quant, global_scale: Optional[Array] = None) -> Array:
+    """x through its quantization in a floating-point mode: the values its codes represent, in x's dtype
+    (products.rs:306-315, MLX's fp_quantize_dequantize)."""
+    quant.checked("qqmm")
+    if quant.mode == QuantMode.AFFINE:
+        raise InvalidArgument("qqmm: needs a floating-point mode (mxfp4, mxfp8 or nvfp4)")
+    if x.dtype not in (F16, BF16, F32) or x.ndim < 1 or x.shape[-1] % quant.group_size != 0:
+        raise InvalidArgument(f"qqmm: a float activation [..., K] with K a multiple of {quant.group_size} expected, got {list(x.shape)}")
+    if global_scale is not None:
+        _check_global("qqmm", quant, global_scale)
+    K = x.shape[-1]
+    out = x.dev.empty(x.shape, x.dtype)
+    c = quant._c()
+    _check(_ffi.lib().nvc_quantize_dequantize(x.dev._h, C.byref(c), x.dtype, x.ptr, x.size // K if K else 0, K, _ptr(global_scale), out.ptr))
+    return out
+
+
+def _qq_scales(name: str, q: Quantized, global_scale_x: Optional[Array]):
+    """MLX's rule (products.rs:317-335): nvfp4 global scales for both operands or neither."""
+    if (global_scale_x is None) != (q.global_scale is None):
+        raise InvalidArgument(f"{name}: for nvfp4, give global scales for both the activations and the weight, or neither")
+
+
+def gather_qqmm(x: Array, q: Quantized, lhs_indices: Optional[Array] = None, rhs_indices: Optional[Array] = None,
+                sorted_indices: bool = False, global_scale_x: Optional[Array] = None) -> Array:
+    """MLX's gather_qqmm (products.rs:437-463): gather_qmm of the quantized activations with quantized experts
+    (w [E, N, K]), transposed.  The activations go through fake_quant, the product is the exact gather_qmm."""
+    name = "gather_qqmm"
+    _qq_scales(name, q, global_scale_x)
+    if q.quant.mode == QuantMode.AFFINE:
+        raise InvalidArgument(f"{name}: needs a floating-point mode (mxfp4, mxfp8 or nvfp4)")
+    if q.global_scale is not None and q.global_scale.size == 1 and q.weight.ndim > 2:
+        # MLX broadcasts the weight's one global scale to every expert
+        experts = tuple(q.weight.shape[:-2])
+        host = np.broadcast_to(q.global_scale.to_numpy().reshape(()), experts)
+        q = q.with_global_scale(x.dev.array(np.ascontiguousarray(host), F32))
+    xq = fake_quant(x, q.quant, global_scale_x)
+    return gather_qmm(xq, q, lhs_indices, rhs_indices, GatherQmm(True, sorted_indices))
+
+
+def qqmm(x: Array, q: Quantized, prepared: Optional[Array] = None, global_scale_x: Optional[Array] = None) -> Array:
     """MLX's qqmm (crates/nuvec-core/src/products.rs:337-352): x through its own quantization in q's mode, times
     the quantized weight transposed.  NVFP4 (without a global scale) or MXFP4 weights, bfloat16 x [..., K]."""
     quant = q.quant
     quant.checked("qqmm")
     if quant.mode == QuantMode.AFFINE:
         raise InvalidArgument("qqmm: needs a floating-point mode (mxfp4, mxfp8 or nvfp4)")
-    if quant.mode not in (QuantMode.NVFP4, QuantMode.MXFP4) or q.global_scale is not None:
-        raise UnsupportedError("qqmm: nvfp4 (without a global scale) and mxfp4 weights take the block-scaled path")
+    _qq_scales("qqmm", q, global_scale_x)
+    if quant.mode not in (QuantMode.NVFP4, QuantMode.MXFP4) or q.global_scale is not None or x.dtype != BF16:
+        # the reference's definition, step by step (products.rs:337-352): x through its quantization, then the exact
+        # quantized product (mxfp8, nvfp4 global scales, other activation types)
+        return quantized_matmul(fake_quant(x, quant, global_scale_x), q, True)
     if x.dtype != BF16 or x.ndim < 1 or q.weight.ndim != 2:
         raise UnsupportedError("qqmm: bfloat16 activations [..., K] and a 2-D quantized weight expected")
     K = x.shape[-1]

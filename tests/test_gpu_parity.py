@@ -682,3 +682,66 @@ def test_row_exact_gathers_give_each_row_its_one_row_bits(be):
             assert np.array_equal(got[i:i + 1], one), i
     want = oracle.gather_qmm(xr, c, s, b, np.arange(len(rhs)), rhs, oracle.BF16, oracle.AFFINE, 64, 4, True, None)
     assert_product_tight(got, want, oracle.BF16)
+
+
+@pytest.mark.parametrize("mode,gs,bits", [(oracle.MXFP4, 32, 4), (oracle.NVFP4, 16, 4), (oracle.MXFP8, 32, 8)])
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+def test_fake_quant_is_quantize_then_dequantize(be, mode, gs, bits, dt):
+    # FastOp::QuantizeDequantize (crates/nuvec-core/src/products.rs:306-315): the activation side of qqmm / gather_qqmm
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    dtype = DT[dt]
+    rng = np.random.default_rng(mode * 7 + dtype)
+    x = rand(rng, (13, 4 * gs), dtype, 1.0)
+    x.reshape(-1)[:4] = oracle.from_f32(np.array([0.0, -0.0, 1e-30, 500.0], np.float32), dtype)
+    code = {oracle.BF16: nv.BF16, oracle.F16: nv.F16, oracle.F32: nv.F32}[dtype]
+    for g in ([None] if mode != oracle.NVFP4 else [None, 2.5]):
+        c, s, _ = oracle.quantize(x, dtype, mode, gs, bits, g)
+        want = oracle.dequantize(c, s, None, dtype, mode, gs, bits, g)
+        gd = None if g is None else dev.array(np.array([g], np.float32), nv.F32)
+        xd = dev.array(x.view(np.float16) if dtype == oracle.F16 else x, code)
+        got = nv.fake_quant(xd, nv.Quant(be_mode(mode), gs, bits), gd).to_numpy()
+        assert np.array_equal(got.view(np.uint8), np.ascontiguousarray(want).view(np.uint8)), f"global={g}"
+
+
+def be_mode(mode):
+    import nuvec_b200 as nv
+    return {oracle.MXFP4: nv.QuantMode.MXFP4, oracle.NVFP4: nv.QuantMode.NVFP4, oracle.MXFP8: nv.QuantMode.MXFP8,
+            oracle.AFFINE: nv.QuantMode.AFFINE}[mode]
+
+
+@pytest.mark.parametrize("mode,gs,bits,scaled", [(oracle.MXFP4, 32, 4, False), (oracle.NVFP4, 16, 4, False), (oracle.NVFP4, 16, 4, True),
+                                                 (oracle.MXFP8, 32, 8, False)])
+def test_gather_qqmm_and_qqmm_with_global_scales(be, mode, gs, bits, scaled):
+    # MLX's gather_qqmm (products.rs:437-463) and qqmm with nvfp4 global scales (:317-352): the activations through
+    # their quantization (with their global scale), then the ordinary gathered / plain quantized product
+    import nuvec_b200 as nv
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(mode + scaled)
+    T, E, topk, N, K = 6, 8, 2, 96, 256
+    w = rand(rng, (E, N, K), oracle.BF16, 0.05)
+    gw, gx = (3.0, 1.5) if scaled else (None, None)
+    c, s, _ = oracle.quantize(w.reshape(E * N, K), oracle.BF16, mode, gs, bits, gw)
+    c, s = c.reshape(E, N, -1), s.reshape(E, N, -1)
+    x = rand(rng, (T, K), oracle.BF16)
+    rhs = np.sort(rng.integers(0, E, T * topk)).astype(np.uint32)
+    xr = np.repeat(x, topk, axis=0).reshape(T * topk, 1, K)
+    xc, xs, _ = oracle.quantize(xr.reshape(-1, K), oracle.BF16, mode, gs, bits, gx)
+    xhat = oracle.dequantize(xc, xs, None, oracle.BF16, mode, gs, bits, gx).reshape(T * topk, 1, K)
+    gexp = None if gw is None else np.full(E, gw, np.float32)
+    want = oracle.gather_qmm(xhat, c, s, None, np.arange(len(rhs)), rhs, oracle.BF16, mode, gs, bits, True, gexp)
+    q = nv.Quantized(dev.array(c, nv.U32), dev.array(s, nv.U8), None, nv.Quant(be_mode(mode), gs, bits),
+                     None if gw is None else dev.array(np.array([gw], np.float32), nv.F32))
+    gxd = None if gx is None else dev.array(np.array([gx], np.float32), nv.F32)
+    got = nv.gather_qqmm(dev.array(xr, nv.BF16), q, None, dev.array(rhs, nv.U32), True, gxd).to_numpy()
+    assert_product_tight(got.reshape(want.shape), want, oracle.BF16, "gather_qqmm")
+    # qqmm on one expert's matrix, with the global scales
+    one = nv.Quantized(q.weight[3], q.scales[3], None, q.quant, q.global_scale)
+    got2 = nv.qqmm(dev.array(x, nv.BF16), one, None, gxd).to_numpy()
+    xc2, xs2, _ = oracle.quantize(x, oracle.BF16, mode, gs, bits, gx)
+    xhat2 = oracle.dequantize(xc2, xs2, None, oracle.BF16, mode, gs, bits, gx)
+    want2 = oracle.quantized_matmul(xhat2, c[3], s[3], None, oracle.BF16, mode, gs, bits, True, gw)
+    assert_product_tight(got2, want2, oracle.BF16, "qqmm")
+    if scaled:
+        with pytest.raises(nv.InvalidArgument, match="both"):
+            nv.qqmm(dev.array(x, nv.BF16), one)
