@@ -239,10 +239,10 @@ int32_t nvc_qqmm_prepared(nvc_device *dev, const nvc_quant *q, int32_t dtype, co
 int32_t nvc_set_row_exact(nvc_device *dev, int32_t on);
 int32_t nvc_row_exact(nvc_device *dev);
 
-/* fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722, fast/imp.rs:3940-4096): attention of one query
- * row per head over an affine-quantized KV cache, without a mask,
- *   out[b, h, 0, :] = softmax(scale * q[b, h, 0, :] . K[b, h / rep, s, :] over s [, sinks[h]]) . V[b, h / rep, s, :]
- * q and out [B, Hq, 1, D] of `dtype` (float16 / bfloat16 / float32), K and V codes uint32 [B, Hkv, S, D * bits / 32],
+/* fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722, fast/imp.rs:3940-4096): attention over an
+ * affine-quantized KV cache, without a mask (every query row attends to all S keys; the cache is read once per row),
+ *   out[b, h, l, :] = softmax(scale * q[b, h, l, :] . K[b, h / rep, s, :] over s [, sinks[h]]) . V[b, h / rep, s, :]
+ * q and out [B, Hq, L, D] of `dtype` (float16 / bfloat16 / float32), K and V codes uint32 [B, Hkv, S, D * bits / 32],
  * their scales and biases [B, Hkv, S, D / group_size] of `dtype`, sinks [Hq] of `dtype` or NULL (a sink joins the
  * softmax's denominator only).  `capacity` >= S is the number of rows between consecutive heads of every cache
  * tensor (a cache is a view of a longer allocation).  The shapes the reference's kernel takes: D 64 or 128; 3, 4 or
@@ -252,8 +252,8 @@ int32_t nvc_row_exact(nvc_device *dev);
 int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *quant, int32_t dtype, const void *q,
                                 const uint32_t *k_codes, const void *k_scales, const void *k_biases,
                                 const uint32_t *v_codes, const void *v_scales, const void *v_biases, const void *sinks,
-                                int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D, int64_t capacity, float scale,
-                                void *out);
+                                int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t S, int64_t D, int64_t capacity,
+                                float scale, void *out);
 
 /* convert_packed (crates/nuvec-lm/src/quant.rs:36-199) for one layer of an AutoAWQ or GPTQ checkpoint, on the
  * device: qweight (int32, AWQ [inputs, outputs / 8], GPTQ [inputs * bits / 32, outputs]), qzeros (int32

@@ -3,7 +3,7 @@
 //
 //     out[b, h, 0, :] = softmax(scale * q[b, h, 0, :] . K[b, h / rep, s, :] over s [, sinks[h]]) . V[b, h / rep, s, :]
 //
-// for one query row per head, K and V as codes uint32 [B, Hkv, S, D * bits / 32] with scales and
+// for every query row of every head (no mask; a row at a time), K and V as codes uint32 [B, Hkv, S, D * bits / 32] with scales and
 // biases [B, Hkv, S, D / group_size], rep = Hq / Hkv query heads per key head, and an optional
 // per-head sink that joins the softmax's denominator only.  The shapes the reference's kernel takes
 // (fast/imp.rs:3944-3993): D 64 or 128, 3, 4 or 8 bits, groups of 32, 64 or 128, rep 1, 2, 4 or 8.
@@ -33,13 +33,14 @@ constexpr int QA_THREADS = 128, QA_TILE = 128, QA_MAX_REP = 8;
 #endif
 
 struct QAttnParams {
-    const void *q;                               // [B, Hq, 1, D]
+    const void *q;                               // [B, Hq, L, D]
     const uint32_t *kw, *vw;                     // codes
     const void *ks, *kb, *vs, *vb;               // scales, biases
     const void *sinks;                           // [Hq] or null
     float *part;                                 // [B, Hq, splits, D + 2]: acc, m, l
-    void *out;                                   // [B, Hq, 1, D]
+    void *out;                                   // [B, Hq, L, D]
     int32_t B, Hq, Hkv, S, capacity, splits, chunk;
+    int32_t L, l;                                // query rows per head, and the row this launch attends for
     float scale;
 };
 
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(QA_THREADS, 5) qattn_split_kernel(QAttnParams 
 
     for (int i = t; i < D * QA_MAX_REP; i += QA_THREADS) {
         const int d = i / QA_MAX_REP, h = i % QA_MAX_REP;
-        qs[d][h] = h < rep ? __fmul_rn(DT<T>::load((const T *)p.q, ((size_t)b * p.Hq + hk * rep + h) * D + d), p.scale) : 0.0f;
+        qs[d][h] = h < rep ? __fmul_rn(DT<T>::load((const T *)p.q, (((size_t)b * p.Hq + hk * rep + h) * p.L + p.l) * D + d), p.scale) : 0.0f;
     }
     __syncthreads();
     if (t < G * QA_MAX_REP) {
@@ -275,7 +276,7 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
 #pragma unroll
     for (int g = 0; g < G; g++) qsum[g] = 0.0f;
     {
-        const T *q = (const T *)p.q + ((size_t)b * p.Hq + hk * rep + (head ? g8 : 0)) * D;
+        const T *q = (const T *)p.q + (((size_t)b * p.Hq + hk * rep + (head ? g8 : 0)) * p.L + p.l) * D;
 #pragma unroll
         for (int ks = 0; ks < KS; ks++) {
             const int d = 16 * ks + 2 * c;
@@ -490,7 +491,7 @@ __global__ void __launch_bounds__(D) qattn_combine_kernel(QAttnParams p) {
         num = fmaf(w, part[j * (D + 2) + d], num);
         den = fmaf(w, part[j * (D + 2) + D + 1], den);
     }
-    DT<T>::store((T *)p.out, ((size_t)b * p.Hq + h) * D + d, den > 0.0f ? __fdiv_rn(num, den) : 0.0f);
+    DT<T>::store((T *)p.out, (((size_t)b * p.Hq + h) * p.L + p.l) * D + d, den > 0.0f ? __fdiv_rn(num, den) : 0.0f);
 }
 
 // 16-bit types with 4- or 8-bit codes run on the tensor cores (switch: NUVEC_QATTN_MMA=0)
@@ -541,18 +542,19 @@ using namespace nvc;
 
 extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *quant, int32_t dtype, const void *q, const uint32_t *k_codes,
                                            const void *k_scales, const void *k_biases, const uint32_t *v_codes, const void *v_scales,
-                                           const void *v_biases, const void *sinks, int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t D,
-                                           int64_t capacity, float scale, void *out) {
+                                           const void *v_biases, const void *sinks, int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t S,
+                                           int64_t D, int64_t capacity, float scale, void *out) {
     NVC_TRY(make_current(dev));
     NVC_TRY(check_quant("quantized_attention", quant));
     if (quant->mode != NVC_AFFINE) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: keys and values need one affine quantization");
     const int bits = quant->bits, gs = quant->group_size;
     if (dtype != NVC_F16 && dtype != NVC_BF16 && dtype != NVC_F32) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: unsupported dtype %d", dtype);
-    if (B < 0 || Hq < 0 || Hkv < 0 || S < 0 || capacity < S) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: invalid shape");
+    if (B < 0 || Hq < 0 || Hkv < 0 || L < 0 || S < 0 || capacity < S) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: invalid shape");
+    if (L > 64) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: %lld query rows per head (the cache is read once per row: up to 64)", (long long)L);
     if ((D != 64 && D != 128) || (bits != 3 && bits != 4 && bits != 8) || D % gs != 0)
         return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: head size %lld with %d bits in groups of %d (64 or 128; 3, 4 or 8; a group within a head)",
                          (long long)D, bits, gs);
-    if (B * Hq == 0) return NVC_OK;
+    if (B * Hq * L == 0) return NVC_OK;
     if (Hkv <= 0 || Hq % Hkv != 0) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: %lld query heads over %lld key heads", (long long)Hq, (long long)Hkv);
     const int64_t rep = Hq / Hkv;
     if (rep != 1 && rep != 2 && rep != 4 && rep != 8) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: %lld query heads per key head (1, 2, 4 or 8)", (long long)rep);
@@ -573,9 +575,14 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
     void *part = nullptr;
     NVC_TRY(dev->pool.alloc((size_t)B * Hq * splits * (D + 2) * sizeof(float), &part));
     QAttnParams p{q, k_codes, v_codes, k_scales, k_biases, v_scales, v_biases, sinks, (float *)part, out,
-                  (int32_t)B, (int32_t)Hq, (int32_t)Hkv, (int32_t)S, (int32_t)capacity, (int32_t)splits, (int32_t)chunk, scale};
-    int32_t rc = dtype == NVC_F16 ? qattn_typed<__half>(dev, p, bits, (int)D, gs)
-                 : dtype == NVC_BF16 ? qattn_typed<__nv_bfloat16>(dev, p, bits, (int)D, gs) : qattn_typed<float>(dev, p, bits, (int)D, gs);
+                  (int32_t)B, (int32_t)Hq, (int32_t)Hkv, (int32_t)S, (int32_t)capacity, (int32_t)splits, (int32_t)chunk, (int32_t)L, 0, scale};
+    int32_t rc = NVC_OK;
+    // no mask: every query row attends to all the keys; a row at a time (the partial results are reused in stream order)
+    for (int64_t l = 0; l < L && rc == NVC_OK; l++) {
+        p.l = (int32_t)l;
+        rc = dtype == NVC_F16 ? qattn_typed<__half>(dev, p, bits, (int)D, gs)
+             : dtype == NVC_BF16 ? qattn_typed<__nv_bfloat16>(dev, p, bits, (int)D, gs) : qattn_typed<float>(dev, p, bits, (int)D, gs);
+    }
     dev->pool.free(part);  // (the pool hands the block out again in stream order)
     return rc;
 }

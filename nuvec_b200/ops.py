@@ -718,11 +718,12 @@ def qqmm(x: Array, q: Quantized, prepared: Optional[Array] = None, global_scale_
 
 def quantized_attention(q: Array, k: Quantized, v: Quantized, scale: float, sinks: Optional[Array] = None,
                         length: Optional[int] = None) -> Array:
-    """fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722): one query row per head, q [B, Hq, 1, D], over
-    affine-quantized keys and values (codes [B, Hkv, S, D * bits / 32], scales and biases [B, Hkv, S, D / group_size]),
-    no mask, optional per-head sinks [Hq].  ``length`` attends to the first ``length`` keys of a longer cache (the
-    reference's cache views, ``k.weight.i((.., .., ..length))``).  Only the shapes the reference's kernel takes run
-    (fast/imp.rs:3944-3993); the composition it falls back to for several query rows is not built."""
+    """fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722): q [B, Hq, L, D] over affine-quantized keys
+    and values (codes [B, Hkv, S, D * bits / 32], scales and biases [B, Hkv, S, D / group_size]), no mask (every query
+    row attends to all the keys), optional per-head sinks [Hq].  ``length`` attends to the first ``length`` keys of a
+    longer cache (the reference's cache views, ``k.weight.i((.., .., ..length))``).  The head sizes, bit widths, group
+    sizes and head ratios of the reference's kernel (fast/imp.rs:3944-3993); up to 64 query rows, one pass over the
+    cache each."""
     if k.quant != v.quant or k.quant.mode != QuantMode.AFFINE:
         raise InvalidArgument("quantized_attention: keys and values need one affine quantization")
     if k.biases is None or v.biases is None:
@@ -743,12 +744,10 @@ def quantized_attention(q: Array, k: Quantized, v: Quantized, scale: float, sink
                               f"match queries {list(q.shape)}")
     if sinks is not None and (sinks.shape != (Hq,) or sinks.dtype != q.dtype):
         raise InvalidArgument(f"quantized_attention: sinks must be [{Hq}] of the queries' dtype")
-    if L != 1:
-        raise UnsupportedError("quantized_attention: one query row per head (the composition for several rows is not built)")
-    out = q.dev.empty((B, Hq, 1, D), q.dtype)
+    out = q.dev.empty((B, Hq, L, D), q.dtype)
     c = quant._c()
     _check(_ffi.lib().nvc_quantized_attention(q.dev._h, C.byref(c), q.dtype, q.ptr, k.weight.ptr, k.scales.ptr, k.biases.ptr,
-                                              v.weight.ptr, v.scales.ptr, v.biases.ptr, _ptr(sinks), B, Hq, Hkv, S, D, cap,
+                                              v.weight.ptr, v.scales.ptr, v.biases.ptr, _ptr(sinks), B, Hq, Hkv, L, S, D, cap,
                                               float(scale), out.ptr))
     return out
 

@@ -136,8 +136,14 @@ def test_batches_empty_caches_and_refusals():
     (qd,) = _upload(nv, dev, [q], dtype)
     with pytest.raises(nv.InvalidArgument, match="one affine quantization"):
         nv.quantized_attention(qd, kq, nv.Quantized(vq.weight, vq.scales, vq.biases, nv.Quant.affine(gs, 8)), 0.1)
-    with pytest.raises(nv.UnsupportedError, match="one query row"):
-        nv.quantized_attention(dev.array(np.zeros((3, 8, 2, D), np.uint16), nv.BF16), kq, vq, 0.1)
+    # several query rows per head, no mask: every row over all the keys (the reference's (8, 2, 37, 3) case and a longer one)
+    for Hq, Hkv, S, L in ((8, 2, 37, 3), (4, 4, 700, 5)):
+        k2, v2 = make_cache(rng, 2, Hkv, S, D, dtype, gs, bits), make_cache(rng, 2, Hkv, S, D, dtype, gs, bits)
+        q2 = oracle.from_f32(rng.standard_normal((2, Hq, L, D)).astype(np.float32), dtype)
+        got2 = _run(nv, dev, q2, k2, v2, dtype, gs, bits, 0.1, None, None)
+        close(got2, oat.dense(q2, k2, v2, dtype, gs, bits, 0.1), TOL[dtype], f"{L} query rows")
+    with pytest.raises(nv.UnsupportedError, match="query rows"):
+        nv.quantized_attention(dev.array(np.zeros((3, 8, 65, D), np.uint16), nv.BF16), kq, vq, 0.1)
     with pytest.raises(nv.InvalidArgument, match="sinks"):
         nv.quantized_attention(qd, kq, vq, 0.1, dev.array(np.zeros(4, np.uint16), nv.BF16))
     k6 = make_cache(rng, 1, 1, 8, D, dtype, gs, 6)
