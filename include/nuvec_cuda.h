@@ -248,12 +248,13 @@ int32_t nvc_row_exact(nvc_device *dev);
  * tensor (a cache is a view of a longer allocation).  The shapes the reference's kernel takes: D 64 or 128; 3, 4 or
  * 8 bits; groups of 32, 64 or 128 within a head; Hq / Hkv 1, 2, 4 or 8.  Float32 throughout: within the float bound
  * of attention over the dequantized cache (crates/nuvec-core/tests/quantized.rs:1964-2031).  Takes scratch from the
- * pool: not inside a recorded step. */
+ * pool: not inside a recorded step.  `causal` != 0: query row l stands at position S - L + l and attends to the keys
+ * up to it (AttentionMask::Causal over a cache that already holds the L new keys, crates/nuvec-lm/src/model.rs:1293-1340). */
 int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *quant, int32_t dtype, const void *q,
                                 const uint32_t *k_codes, const void *k_scales, const void *k_biases,
                                 const uint32_t *v_codes, const void *v_scales, const void *v_biases, const void *sinks,
                                 int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t S, int64_t D, int64_t capacity,
-                                float scale, void *out);
+                                float scale, int32_t causal, void *out);
 
 /* convert_packed (crates/nuvec-lm/src/quant.rs:36-199) for one layer of an AutoAWQ or GPTQ checkpoint, on the
  * device: qweight (int32, AWQ [inputs, outputs / 8], GPTQ [inputs * bits / 32, outputs]), qzeros (int32

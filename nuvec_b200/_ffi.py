@@ -93,7 +93,7 @@ SIGNATURES = {
     "nvc_qqmm_prepare_scales": (I32T, [P, QP, P, I64T, I64T, P]),
     "nvc_qqmm_prepared": (I32T, [P, QP, I32T, P, P, P, I64T, I64T, I64T, P]),
     "nvc_convert_packed": (I32T, [P, I32T, I32T, I32T, I32T, P, P, P, I64T, I64T, P, P, P]),
-    "nvc_quantized_attention": (I32T, [P, QP, I32T, P, P, P, P, P, P, P, P, I64T, I64T, I64T, I64T, I64T, I64T, I64T, C.c_float, P]),
+    "nvc_quantized_attention": (I32T, [P, QP, I32T, P, P, P, P, P, P, P, P, I64T, I64T, I64T, I64T, I64T, I64T, I64T, C.c_float, I32T, P]),
     "nvc_quantize_dequantize": (I32T, [P, QP, I32T, P, I64T, I64T, P, P]),
     "nvc_set_row_exact": (I32T, [P, I32T]),
     "nvc_row_exact": (I32T, [P]),

@@ -543,7 +543,7 @@ using namespace nvc;
 extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *quant, int32_t dtype, const void *q, const uint32_t *k_codes,
                                            const void *k_scales, const void *k_biases, const uint32_t *v_codes, const void *v_scales,
                                            const void *v_biases, const void *sinks, int64_t B, int64_t Hq, int64_t Hkv, int64_t L, int64_t S,
-                                           int64_t D, int64_t capacity, float scale, void *out) {
+                                           int64_t D, int64_t capacity, float scale, int32_t causal, void *out) {
     NVC_TRY(make_current(dev));
     NVC_TRY(check_quant("quantized_attention", quant));
     if (quant->mode != NVC_AFFINE) return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: keys and values need one affine quantization");
@@ -577,9 +577,12 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
     QAttnParams p{q, k_codes, v_codes, k_scales, k_biases, v_scales, v_biases, sinks, (float *)part, out,
                   (int32_t)B, (int32_t)Hq, (int32_t)Hkv, (int32_t)S, (int32_t)capacity, (int32_t)splits, (int32_t)chunk, (int32_t)L, 0, scale};
     int32_t rc = NVC_OK;
-    // no mask: every query row attends to all the keys; a row at a time (the partial results are reused in stream order)
+    // every query row attends to all the keys (or, causal, to those up to its position); a row at a time (the partial
+    // results are reused in stream order)
+    // (causal: query row l is the position S - L + l and attends to the keys up to it)
     for (int64_t l = 0; l < L && rc == NVC_OK; l++) {
         p.l = (int32_t)l;
+        if (causal) p.S = (int32_t)(S - (L - 1 - l) > 0 ? S - (L - 1 - l) : 0);
         rc = dtype == NVC_F16 ? qattn_typed<__half>(dev, p, bits, (int)D, gs)
              : dtype == NVC_BF16 ? qattn_typed<__nv_bfloat16>(dev, p, bits, (int)D, gs) : qattn_typed<float>(dev, p, bits, (int)D, gs);
     }

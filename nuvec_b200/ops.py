@@ -717,13 +717,13 @@ def qqmm(x: Array, q: Quantized, prepared: Optional[Array] = None, global_scale_
 
 
 def quantized_attention(q: Array, k: Quantized, v: Quantized, scale: float, sinks: Optional[Array] = None,
-                        length: Optional[int] = None) -> Array:
+                        length: Optional[int] = None, causal: bool = False) -> Array:
     """fast::quantized_attention (crates/nuvec-core/src/fast.rs:694-722): q [B, Hq, L, D] over affine-quantized keys
     and values (codes [B, Hkv, S, D * bits / 32], scales and biases [B, Hkv, S, D / group_size]), no mask (every query
     row attends to all the keys), optional per-head sinks [Hq].  ``length`` attends to the first ``length`` keys of a
     longer cache (the reference's cache views, ``k.weight.i((.., .., ..length))``).  The head sizes, bit widths, group
     sizes and head ratios of the reference's kernel (fast/imp.rs:3944-3993); up to 64 query rows, one pass over the
-    cache each."""
+    cache each.  ``causal``: query row l stands at position S - L + l and attends to the keys up to it."""
     if k.quant != v.quant or k.quant.mode != QuantMode.AFFINE:
         raise InvalidArgument("quantized_attention: keys and values need one affine quantization")
     if k.biases is None or v.biases is None:
@@ -748,7 +748,7 @@ def quantized_attention(q: Array, k: Quantized, v: Quantized, scale: float, sink
     c = quant._c()
     _check(_ffi.lib().nvc_quantized_attention(q.dev._h, C.byref(c), q.dtype, q.ptr, k.weight.ptr, k.scales.ptr, k.biases.ptr,
                                               v.weight.ptr, v.scales.ptr, v.biases.ptr, _ptr(sinks), B, Hq, Hkv, L, S, D, cap,
-                                              float(scale), out.ptr))
+                                              float(scale), int(bool(causal)), out.ptr))
     return out
 
 

@@ -31,7 +31,7 @@ def _dense_cache(codes, scales, biases, dtype, gs, bits):
     return (s32 * values + b32).astype(np.float32).reshape(B, H, S, D)
 
 
-def dense(q, k, v, dtype, gs, bits, scale, sinks=None):
+def dense(q, k, v, dtype, gs, bits, scale, sinks=None, causal=False):
     """q [B, Hq, L, D] of dtype; k, v = (codes, scales, biases) with [B, Hkv, S, ...]; returns float64 [B, Hq, L, D]."""
     q32 = to_f32(q, dtype).astype(np.float64)
     kd = _dense_cache(*k, dtype, gs, bits).astype(np.float64)
@@ -42,6 +42,9 @@ def dense(q, k, v, dtype, gs, bits, scale, sinks=None):
     for b in range(B):
         for h in range(Hq):
             s = (q32[b, h] * np.float64(np.float32(scale))) @ kd[b, h // rep].T          # [L, S]
+            if causal:  # row l stands at position S - L + l
+                S_ = s.shape[1]
+                s = np.where(np.arange(S_)[None, :] <= (S_ - L + np.arange(L))[:, None], s, -np.inf)
             if sinks is not None:
                 s = np.concatenate([s, np.full((L, 1), float(to_f32(sinks, dtype)[h]))], axis=1)
             m = s.max(axis=1, keepdims=True) if s.shape[1] else np.zeros((L, 1))

@@ -142,6 +142,18 @@ def test_batches_empty_caches_and_refusals():
         q2 = oracle.from_f32(rng.standard_normal((2, Hq, L, D)).astype(np.float32), dtype)
         got2 = _run(nv, dev, q2, k2, v2, dtype, gs, bits, 0.1, None, None)
         close(got2, oat.dense(q2, k2, v2, dtype, gs, bits, 0.1), TOL[dtype], f"{L} query rows")
+    # causal: row l at position S - L + l (a prefill of L tokens over a cache that already holds their keys)
+    for Hq, Hkv, S, L, sinks in ((8, 2, 37, 6, False), (4, 1, 300, 4, True), (4, 4, 3, 5, False)):
+        k2, v2 = make_cache(rng, 1, Hkv, S, D, dtype, gs, bits), make_cache(rng, 1, Hkv, S, D, dtype, gs, bits)
+        q2 = oracle.from_f32(rng.standard_normal((1, Hq, L, D)).astype(np.float32), dtype)
+        sk = oracle.from_f32(rng.standard_normal(Hq).astype(np.float32), dtype) if sinks else None
+        quant2 = nv.Quant.affine(gs, bits)
+        kq2, vq2 = nv.Quantized(*_upload(nv, dev, k2, dtype), quant2), nv.Quantized(*_upload(nv, dev, v2, dtype), quant2)
+        sd = _upload(nv, dev, [sk], dtype)[0] if sinks else None
+        got2 = oracle.to_f32(nv.quantized_attention(_upload(nv, dev, [q2], dtype)[0], kq2, vq2, 0.1, sd, causal=True).to_numpy(), dtype)
+        want2 = oat.dense(q2, k2, v2, dtype, gs, bits, 0.1, sk, causal=True)
+        want2 = np.nan_to_num(want2)          # rows before the first key (S < L) attend to nothing: zeros
+        close(got2, want2, TOL[dtype], f"causal S{S} L{L}")
     with pytest.raises(nv.UnsupportedError, match="query rows"):
         nv.quantized_attention(dev.array(np.zeros((3, 8, 65, D), np.uint16), nv.BF16), kq, vq, 0.1)
     with pytest.raises(nv.InvalidArgument, match="sinks"):
