@@ -122,6 +122,9 @@ int32_t ensure_scratch(nvc_device *dev, size_t bytes, void **out);
 int32_t ensure_counters(nvc_device *dev, size_t count, uint32_t **out);
 int32_t check_quant(const char *op, const nvc_quant *q);
 int32_t check_launch(nvc_device *dev, const char *kernel);
+// quantize.cu: bfloat16 x to nvfp4 / mxfp4 codes with the scales in the block-scaled MMA's layout (for qqmm.cu)
+int32_t quantize_fp4_laid(nvc_device *dev, const nvc_quant *q, const void *x, int64_t rows, int64_t cols, uint32_t *codes, uint8_t *laid,
+                          int64_t kblocks, int pieces);
 int32_t deliver_pending(nvc_device *dev);    // copies finished host-operand results out (the stream must be idle)
 int32_t ensure_error_word(nvc_device *dev);  // the host-mapped word kernels report a bounded wait's failure in
 

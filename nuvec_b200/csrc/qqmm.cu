@@ -376,14 +376,13 @@ static int32_t qqmm_impl(nvc_device *dev, const nvc_quant *q, int32_t dtype, con
 
     const int bn = M > 128 ? 256 : 128;
     const int64_t kblocks = (K + QQ_KB - 1) / QQ_KB, wt = (N + 127) / 128, xt = (M + bn - 1) / bn * (bn / 128);
-    void *xq = nullptr, *xs = nullptr, *sfa = nullptr, *sfb = nullptr;
+    void *xq = nullptr, *sfa = nullptr, *sfb = nullptr;
     NVC_TRY(dev->pool.alloc((size_t)M * (K / 2), &xq));
-    int32_t rc = dev->pool.alloc((size_t)M * (K / vs), &xs);
-    if (rc == NVC_OK && !prepared) rc = dev->pool.alloc((size_t)wt * kblocks * sf_bytes, &sfa);
+    int32_t rc = NVC_OK;
+    if (!prepared) rc = dev->pool.alloc((size_t)wt * kblocks * sf_bytes, &sfa);
     if (rc == NVC_OK) rc = dev->pool.alloc((size_t)xt * kblocks * sf_bytes, &sfb);
     auto release = [&]() {  // (the pool hands the blocks out again in stream order)
         if (xq) dev->pool.free(xq);
-        if (xs) dev->pool.free(xs);
         if (sfa) dev->pool.free(sfa);
         if (sfb) dev->pool.free(sfb);
     };
@@ -392,15 +391,18 @@ static int32_t qqmm_impl(nvc_device *dev, const nvc_quant *q, int32_t dtype, con
         return rc;
     }
     // x through its quantization: the codes and scales the reference's quantize gives
-    rc = nvc_quantize(dev, q, NVC_BF16, x, M, K, nullptr, (uint32_t *)xq, xs, nullptr);
-    if (rc == NVC_OK) {
-        const int64_t na = wt * kblocks * (int64_t)sf_bytes, nb = xt * kblocks * (int64_t)sf_bytes;
-        const int pieces = qq_pieces(vs);
-        if (!prepared)
-            qq_scale_layout_kernel<<<(unsigned)((na / 16 + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / vs, (uint8_t *)sfa, wt,
-                                                                                               kblocks, pieces);
-        qq_scale_layout_kernel<<<(unsigned)((nb / 16 + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)xs, M, K / vs, (uint8_t *)sfb, xt, kblocks,
-                                                                                           pieces);
+    // (its scales go straight into the tensor core's layout; rows past M up to the token tile are zero scales)
+    const int pieces = qq_pieces(vs);
+    rc = quantize_fp4_laid(dev, q, x, M, K, (uint32_t *)xq, (uint8_t *)sfb, kblocks, pieces);
+    if (rc == NVC_OK && xt * 128 > (M + 127) / 128 * 128)  // a 256-token tile whose second half holds no rows at all
+        rc = cudaMemsetAsync((uint8_t *)sfb + (size_t)((M + 127) / 128) * kblocks * sf_bytes, 0,
+                             (size_t)(xt - (M + 127) / 128) * kblocks * sf_bytes, dev->stream) == cudaSuccess
+                 ? NVC_OK
+                 : set_error(NVC_ERR_DRIVER, "qqmm: cudaMemsetAsync failed");
+    if (rc == NVC_OK && !prepared) {
+        const int64_t na = wt * kblocks * (int64_t)sf_bytes;
+        qq_scale_layout_kernel<<<(unsigned)((na / 16 + 255) / 256), 256, 0, dev->stream>>>((const uint8_t *)w_scales, N, K / vs, (uint8_t *)sfa, wt,
+                                                                                           kblocks, pieces);
         rc = check_launch(dev, "qq_scale_layout_kernel");
     }
     CUtensorMap mw, mx;

@@ -213,12 +213,35 @@ __device__ __forceinline__ uint32_t mx_scale_code(float x) {
     return code > 254u ? 254u : code;
 }
 
-template <typename T, int BITS>
+// LAID: the scales go straight into the block-scaled tensor-core layout of the qqmm kernel instead of the plain
+// [rows, groups] array: 512-byte pieces of 128 rows x 4 scales, byte (r % 32) * 16 + (r % 128 / 32) * 4 + s,
+// ordered [row tile][k-block of 256][piece]; the threads then cover the padded rows and groups too and write
+// the padding's zero scales.
+struct ScalePieces {
+    uint8_t *out;
+    int64_t rows, per_row, kblocks;
+    int pieces;
+};
+template <typename T, int BITS, bool LAID = false>
 __global__ void __launch_bounds__(128)
 quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales,
-                   const float *__restrict__ global, size_t groups, int gs) {
+                   const float *__restrict__ global, size_t groups, int gs, ScalePieces sp = ScalePieces{}) {
     size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= groups) return;
+    size_t laid_at = 0;
+    if (LAID) {
+        const int64_t padded = sp.kblocks * sp.pieces * 4;  // groups per row, padding included
+        const int64_t r = (int64_t)(g / (size_t)padded), gk = (int64_t)(g % (size_t)padded);
+        if (r >= (sp.rows + 127) / 128 * 128) return;
+        laid_at = (size_t)(((r / 128 * sp.kblocks + gk / (sp.pieces * 4)) * sp.pieces + (gk / 4) % sp.pieces) * 512 + (r % 32) * 16 +
+                           (r % 128 / 32) * 4 + gk % 4);
+        if (r >= sp.rows || gk >= sp.per_row) {
+            sp.out[laid_at] = 0;
+            return;
+        }
+        g = (size_t)(r * sp.per_row + gk);
+    } else if (g >= groups) {
+        return;
+    }
     const size_t base = g * (size_t)gs;
     const bool mx = gs == 32;
     const float max_element = BITS == 4 ? 6.0f : 448.0f;
@@ -256,7 +279,8 @@ quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t
         code = e4m3_from_f32(scale);
         decoded = e4m3_to_f32(code);
     }
-    scales[g] = (uint8_t)code;
+    if (LAID) sp.out[laid_at] = (uint8_t)code;
+    else scales[g] = (uint8_t)code;
     decoded = ftz(decoded);
     float inverse = decoded == 0.0f ? 0.0f : ftz(__fdiv_rn(has ? scale_enc : 1.0f, decoded));
     if (BITS == 4) {
@@ -413,6 +437,18 @@ extern "C" int32_t nvc_quantized_embedding(nvc_device *dev, const nvc_quant *q, 
     case NVC_F16: return dequantize_typed<__half>(dev, q, codes, scales, biases, nullptr, total, out, 0, pick);
     default: return dequantize_typed<__nv_bfloat16>(dev, q, codes, scales, biases, nullptr, total, out, 0, pick);
     }
+}
+
+// The activation side of nvc_qqmm: bfloat16 x [rows, cols] to 4-bit codes (nvfp4 or mxfp4, no global scale) with the
+// scales written straight into the tensor core's layout (laid: row_tiles x kblocks x pieces x 512 bytes).
+int32_t nvc::quantize_fp4_laid(nvc_device *dev, const nvc_quant *q, const void *x, int64_t rows, int64_t cols, uint32_t *codes, uint8_t *laid,
+                               int64_t kblocks, int pieces) {
+    const int64_t padded_rows = (rows + 127) / 128 * 128, padded_groups = kblocks * pieces * 4;
+    const size_t threads = (size_t)padded_rows * (size_t)padded_groups;
+    ScalePieces sp{laid, rows, cols / q->group_size, kblocks, pieces};
+    quantize_fp_kernel<__nv_bfloat16, 4, true><<<(unsigned)((threads + 127) / 128), 128, 0, dev->stream>>>(
+        (const __nv_bfloat16 *)x, (uint8_t *)codes, nullptr, nullptr, 0, q->group_size, sp);
+    return check_launch(dev, "quantize_fp_kernel");
 }
 
 // FastOp::QuantizeDequantize (crates/nuvec-core/src/products.rs:306-315, MLX's fp_quantize_dequantize): x through
