@@ -194,6 +194,7 @@ qqmm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ 
     if (warp == 0) {
         // ── producer: codes by TMA, scales by bulk copies, one barrier per stage ───────────────
         if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations' codes and scales are the previous kernel's
             const uint8_t *sfa_src = p.sfa + (size_t)blockIdx.x * p.kblocks * QQ_SF_BYTES;
             const uint8_t *sfb_src = p.sfb + (size_t)blockIdx.y * (BN / 128) * p.kblocks * QQ_SF_BYTES;
             bool ok = true;
@@ -347,7 +348,21 @@ static int32_t qq_launch(nvc_device *dev, const CUtensorMap &mw, const CUtensorM
         }
     }
     dim3 grid((unsigned)((N + QQ_BM - 1) / QQ_BM), (unsigned)((tokens + BN - 1) / BN));
-    kernel<<<grid, QQ_THREADS, smem, dev->stream>>>(mw, mx, p);
+    // Programmatic stream serialization: the blocks may start (barriers, tensor memory, descriptors) while the kernel
+    // before this one, the activations' quantization, drains; the producer thread synchronises with it on the device
+    // (griddepcontrol.wait) before its first load.  NUVEC_PDL=0 restores plain stream order.
+    static const bool pdl = [] { const char *e = getenv("NUVEC_PDL"); return !(e && *e == '0'); }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(QQ_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    NVC_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, p));
     return check_launch(dev, "qqmm_kernel");
 }
 

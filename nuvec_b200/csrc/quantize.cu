@@ -228,6 +228,7 @@ quantize_fp_kernel(const T *__restrict__ w, uint8_t *__restrict__ codes, uint8_t
                    const float *__restrict__ global, size_t groups, int gs, ScalePieces sp = ScalePieces{}) {
     size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t laid_at = 0;
+    if (LAID) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the product kernel may set itself up meanwhile
     if (LAID) {
         const int64_t padded = sp.kblocks * sp.pieces * 4;  // groups per row, padding included
         const int64_t r = (int64_t)(g / (size_t)padded), gk = (int64_t)(g % (size_t)padded);
