@@ -62,6 +62,7 @@ __device__ __forceinline__ float qa_float(uint32_t c) { return __uint_as_float(0
 template <typename T, int BITS, int D, int GS>
 __global__ void __launch_bounds__(QA_THREADS, 5) qattn_split_kernel(QAttnParams p) {
     constexpr int W = D * BITS / 32, G = D / GS, DPT = D / 64;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine kernel's blocks may become resident meanwhile
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int rep = p.Hq / p.Hkv, t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int s0 = split * p.chunk, s1 = min(p.S, s0 + p.chunk);
@@ -257,6 +258,7 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
     static_assert(BITS == 4 || BITS == 8, "codes that fill bytes");
     constexpr int W = D * BITS / 32, G = D / GS, KS = D / 16, NBD = D / 8, WP = W + 1;  // WP: padded row of the value tile
     constexpr int KS_PER_G = GS / 16, NBD_PER_G = GS / 8;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine kernel's blocks may become resident meanwhile
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int rep = p.Hq / p.Hkv, t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int g8 = lane >> 2, c = lane & 3;  // the fragments' group (a head, a key or a dim) and pair index
@@ -477,6 +479,7 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
 template <typename T, int D>
 __global__ void __launch_bounds__(D) qattn_combine_kernel(QAttnParams p) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the partial results are the split kernel's
     const float *part = p.part + ((size_t)b * p.Hq + h) * p.splits * (D + 2);
     float mx = -INFINITY;
     for (int j = 0; j < p.splits; j++) mx = fmaxf(mx, part[j * (D + 2) + D]);
@@ -492,6 +495,23 @@ __global__ void __launch_bounds__(D) qattn_combine_kernel(QAttnParams p) {
         den = fmaf(w, part[j * (D + 2) + D + 1], den);
     }
     DT<T>::store((T *)p.out, (((size_t)b * p.Hq + h) * p.L + p.l) * D + d, den > 0.0f ? __fdiv_rn(num, den) : 0.0f);
+}
+
+// The combine kernel, launched so that it may become resident while the split kernel runs (NUVEC_PDL=0: plain order).
+template <typename T, int D>
+static int32_t qattn_combine(nvc_device *dev, const QAttnParams &p) {
+    static const bool pdl = [] { const char *e = getenv("NUVEC_PDL"); return !(e && *e == '0'); }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)p.Hq, (unsigned)p.B);
+    cfg.blockDim = dim3(D);
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    NVC_CUDA(cudaLaunchKernelEx(&cfg, qattn_combine_kernel<T, D>, p));
+    return check_launch(dev, "qattn_combine_kernel");
 }
 
 // 16-bit types with 4- or 8-bit codes run on the tensor cores (switch: NUVEC_QATTN_MMA=0)
@@ -513,15 +533,13 @@ static int32_t qattn_launch(nvc_device *dev, const QAttnParams &p, int gs) {
         else if (gs == 64) qattn_launch_mma<T, BITS, D, 64>(dev, p, grid);
         else qattn_launch_mma<T, BITS, D, D == 128 ? 128 : 64>(dev, p, grid);
         NVC_TRY(check_launch(dev, "qattn_mma_kernel"));
-        qattn_combine_kernel<T, D><<<dim3((unsigned)p.Hq, (unsigned)p.B), D, 0, dev->stream>>>(p);
-        return check_launch(dev, "qattn_combine_kernel");
+        return qattn_combine<T, D>(dev, p);
     }
     if (gs == 32) qattn_split_kernel<T, BITS, D, 32><<<grid, QA_THREADS, 0, dev->stream>>>(p);
     else if (gs == 64) qattn_split_kernel<T, BITS, D, 64><<<grid, QA_THREADS, 0, dev->stream>>>(p);
     else if (D == 128) qattn_split_kernel<T, BITS, D, D == 128 ? 128 : 64><<<grid, QA_THREADS, 0, dev->stream>>>(p);
     NVC_TRY(check_launch(dev, "qattn_split_kernel"));
-    qattn_combine_kernel<T, D><<<dim3((unsigned)p.Hq, (unsigned)p.B), D, 0, dev->stream>>>(p);
-    return check_launch(dev, "qattn_combine_kernel");
+    return qattn_combine<T, D>(dev, p);
 }
 
 template <typename T>
