@@ -247,8 +247,9 @@ int32_t nvc_row_exact(nvc_device *dev);
  * softmax's denominator only).  `capacity` >= S is the number of rows between consecutive heads of every cache
  * tensor (a cache is a view of a longer allocation).  The shapes the reference's kernel takes: D 64 or 128; 3, 4 or
  * 8 bits; groups of 32, 64 or 128 within a head; Hq / Hkv 1, 2, 4 or 8.  Float32 throughout: within the float bound
- * of attention over the dequantized cache (crates/nuvec-core/tests/quantized.rs:1964-2031).  Takes scratch from the
- * pool: not inside a recorded step.  `causal` != 0: query row l stands at position S - L + l and attends to the keys
+ * of attention over the dequantized cache (crates/nuvec-core/tests/quantized.rs:1964-2031).  The splits' partial
+ * results use the handle's scratch block: inside a recorded step only shapes whose scratch (B * Hq * splits *
+ * (D + 2) floats, at most a few MB) the handle already holds -- run the shape once before recording.  `causal` != 0: query row l stands at position S - L + l and attends to the keys
  * up to it (AttentionMask::Causal over a cache that already holds the L new keys, crates/nuvec-lm/src/model.rs:1293-1340). */
 int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *quant, int32_t dtype, const void *q,
                                 const uint32_t *k_codes, const void *k_scales, const void *k_biases,

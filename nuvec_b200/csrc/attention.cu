@@ -580,7 +580,7 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
     if (!q || !out || (S > 0 && (!k_codes || !k_scales || !k_biases || !v_codes || !v_scales || !v_biases)))
         return set_error(NVC_ERR_INVALID_ARGUMENT, "quantized_attention: null operand");
     if (((uintptr_t)k_codes | (uintptr_t)v_codes) % 16 != 0) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: the codes must be 16-byte aligned");
-    if (dev->capturing) return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: not inside a recorded step (it takes scratch from the pool)");
+
     // splits: one wave of as many blocks as stay resident together (what their registers allow: three of the
     // tensor-core kernel, five of the other, per multiprocessor), whole tiles of 128 keys each
     const int64_t tiles = S > 0 ? (S + QA_TILE - 1) / QA_TILE : 1;
@@ -590,8 +590,14 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
     if (splits < 1) splits = 1;
     const int64_t chunk = (tiles + splits - 1) / splits * QA_TILE;
     splits = S > 0 ? (S + chunk - 1) / chunk : 1;
+    // the splits' partial results: the handle's scratch block (reused between calls in stream order; it grows outside
+    // recorded steps only)
+    const size_t part_bytes = (size_t)B * Hq * splits * (D + 2) * sizeof(float);
+    if (dev->capturing && dev->scratch_bytes < part_bytes)
+        return set_error(NVC_ERR_UNSUPPORTED, "quantized_attention: %zu bytes of scratch inside a recorded step (run the shape once before recording)",
+                         part_bytes);
     void *part = nullptr;
-    NVC_TRY(dev->pool.alloc((size_t)B * Hq * splits * (D + 2) * sizeof(float), &part));
+    NVC_TRY(ensure_scratch(dev, part_bytes, &part));
     QAttnParams p{q, k_codes, v_codes, k_scales, k_biases, v_scales, v_biases, sinks, (float *)part, out,
                   (int32_t)B, (int32_t)Hq, (int32_t)Hkv, (int32_t)S, (int32_t)capacity, (int32_t)splits, (int32_t)chunk, (int32_t)L, 0, scale};
     int32_t rc = NVC_OK;
@@ -604,6 +610,5 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
         rc = dtype == NVC_F16 ? qattn_typed<__half>(dev, p, bits, (int)D, gs)
              : dtype == NVC_BF16 ? qattn_typed<__nv_bfloat16>(dev, p, bits, (int)D, gs) : qattn_typed<float>(dev, p, bits, (int)D, gs);
     }
-    dev->pool.free(part);  // (the pool hands the block out again in stream order)
     return rc;
 }

@@ -163,3 +163,33 @@ def test_batches_empty_caches_and_refusals():
     six = nv.Quantized(*_upload(nv, dev, k6, dtype), nv.Quant.affine(gs, 6))
     with pytest.raises(nv.UnsupportedError):
         nv.quantized_attention(q1, six, six, 0.1)
+
+
+@pytest.mark.gpu
+def test_attention_inside_a_recorded_step():
+    # the splits' partial results live in the handle's scratch block, so a call whose shape ran once before can be
+    # recorded with the rest of a decode step and replayed
+    import ctypes as C
+    import nuvec_b200 as nv
+    from nuvec_b200 import _ffi
+    dev = nv.Device.shared(0)
+    rng = np.random.default_rng(11)
+    dtype, D, gs, bits, Hq, Hkv, S = oracle.BF16, 128, 64, 4, 8, 2, 900
+    k, v = make_cache(rng, 1, Hkv, S, D, dtype, gs, bits), make_cache(rng, 1, Hkv, S, D, dtype, gs, bits)
+    q = oracle.from_f32(rng.standard_normal((1, Hq, 1, D)).astype(np.float32), dtype)
+    quant = nv.Quant.affine(gs, bits)
+    kq, vq = nv.Quantized(*_upload(nv, dev, k, dtype), quant), nv.Quantized(*_upload(nv, dev, v, dtype), quant)
+    (qd,) = _upload(nv, dev, [q], dtype)
+    direct = nv.quantized_attention(qd, kq, vq, 0.1).to_numpy()
+    out = dev.empty((1, Hq, 1, D), nv.BF16)
+    c = quant._c()
+
+    def call():
+        assert _ffi.lib().nvc_quantized_attention(dev._h, C.byref(c), nv.BF16, qd.ptr, kq.weight.ptr, kq.scales.ptr, kq.biases.ptr,
+                                                  vq.weight.ptr, vq.scales.ptr, vq.biases.ptr, None, 1, Hq, Hkv, 1, S, D, S, 0.1, 0,
+                                                  out.ptr) == 0, _ffi.last_error()
+    graph = dev.record(call)
+    for _ in range(2):
+        graph.launch()
+    dev.synchronize()
+    assert np.array_equal(out.to_numpy(), direct)
