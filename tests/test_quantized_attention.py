@@ -107,7 +107,7 @@ def test_kernel_equals_the_dequantized_attention(dt, D, bits, gs):
     dtype = DT[dt]
     rng = np.random.default_rng(17 + D + bits + gs)
     for Hq, Hkv, S, sinks in ((4, 1, 1, False), (8, 2, 37, True), (32, 8, 300, False), (4, 4, 2100, True), (16, 2, 9000, True),
-                              (8, 1, 777, False), (2, 2, 128, False), (8, 1, 129, True)):
+                              (8, 1, 777, False), (2, 2, 128, False), (8, 1, 129, True), (4, 2, 130, True), (16, 8, 257, False)):
         cap = S + 50
         k, v = make_cache(rng, 1, Hkv, cap, D, dtype, gs, bits), make_cache(rng, 1, Hkv, cap, D, dtype, gs, bits)
         q = oracle.from_f32(rng.standard_normal((1, Hq, 1, D)).astype(np.float32), dtype)
