@@ -25,6 +25,8 @@
 // both products on the tensor cores; see there.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace nvc {
 
 constexpr int QA_THREADS = 128, QA_TILE = 128, QA_MAX_REP = 8;
@@ -239,7 +241,8 @@ __global__ void __launch_bounds__(QA_THREADS, 5) qattn_split_kernel(QAttnParams 
 //            out[h, d] = O[h, d] + sum over keys of (p * b_g(d)[key] - 1024 * p * s_g(d)[key])
 // A warp owns 32 keys of a tile of 128: its score accumulators (C fragments, 16 heads x 8 keys) are, pairwise,
 // exactly the A fragments (16 heads x 16 keys) of its value products, so the probabilities never leave
-// registers; the four warps' outputs are added at the end.  q * scale and p * s are rounded to float16
+// registers; the four warps' outputs are added at the end.  A tile's codes travel into shared memory with cp.async a
+// tile ahead (two sets of buffers), its scales and biases through registers.  q * scale and p * s are rounded to float16
 // (11 significant bits, three more than the bfloat16 the reference's composition rounds them to).
 __device__ __forceinline__ void qa_mma(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     const uint32_t zero = 0u;  // rows 8-15 of A (no heads there)
@@ -253,10 +256,15 @@ __device__ __forceinline__ uint32_t qa_pack_f16(float lo, float hi) {
 }
 __device__ __forceinline__ float2 qa_unpack_f16(uint32_t v) { return __half22float2(*reinterpret_cast<const __half2 *>(&v)); }
 
+__device__ __forceinline__ void qa_cp16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ size_t head_row_of(const QAttnParams &p, int b, int hk) { return ((size_t)b * p.Hkv + hk) * p.capacity; }
+
 template <typename T, int BITS, int D, int GS>
 __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QAttnParams p) {
     static_assert(BITS == 4 || BITS == 8, "codes that fill bytes");
-    constexpr int W = D * BITS / 32, G = D / GS, KS = D / 16, NBD = D / 8, WP = W + 1;  // WP: padded row of the value tile
+    constexpr int W = D * BITS / 32, G = D / GS, KS = D / 16, NBD = D / 8, WP = W + 4;  // WP: padded row of the value tile
     constexpr int KS_PER_G = GS / 16, NBD_PER_G = GS / 8;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the combine kernel's blocks may become resident meanwhile
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -265,12 +273,34 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
     const int s0 = split * p.chunk, s1 = min(p.S, s0 + p.chunk);
     const bool head = g8 < rep;
 
+    // Two sets of tile buffers: the next tile's codes arrive (cp.async) while the current tile multiplies.  Rows are
+    // padded by four words: the eight rows (keys) or four rows (values) a fragment reads at once fall into distinct banks.
     __shared__ float wred[2][4][8];
-    __shared__ float4 sbt[QA_TILE][G];  // the tile's (key scale, key bias, value scale, value bias) per key and group
-    constexpr int KP = W + 4;  // padded row of the key tile: eight rows' 16-byte reads fall into distinct banks
-    __shared__ __align__(16) uint32_t ktile[QA_TILE * KP];
-    constexpr int VWORDS = QA_TILE * WP, RWORDS = 4 * 8 * D;
-    __shared__ __align__(16) uint32_t vtile[VWORDS > RWORDS ? VWORDS : RWORDS];
+    constexpr int KP = W + 4;
+    constexpr int TILE_WORDS = QA_TILE * KP, RWORDS = 4 * 8 * D;
+    extern __shared__ __align__(16) uint32_t qa_dyn[];
+    uint32_t *kbuf = qa_dyn;                        // [2][QA_TILE * KP]
+    uint32_t *vbuf = kbuf + 2 * TILE_WORDS;         // [2][QA_TILE * WP]; after the last tile the warps' sums [4][8][D]
+    float4 *sbuf = reinterpret_cast<float4 *>(vbuf + (2 * TILE_WORDS > RWORDS ? 2 * TILE_WORDS : RWORDS));  // [2][QA_TILE][G]
+    auto fetch_codes = [&](int base, int buf) {
+        const int keys = min(QA_TILE, s1 - base);
+        const uint32_t *ksrc = p.kw + (head_row_of(p, b, hk) + base) * W, *vsrc = p.vw + (head_row_of(p, b, hk) + base) * W;
+        for (int i = t; i < keys * W / 4; i += QA_THREADS) {
+            const int row = (4 * i) / W, col = (4 * i) % W;
+            qa_cp16(kbuf + buf * TILE_WORDS + row * KP + col, ksrc + 4 * i);
+            qa_cp16(vbuf + buf * TILE_WORDS + row * WP + col, vsrc + 4 * i);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto fetch_scales = [&](int base, float4 (&r)[G]) {  // thread t: key t of the tile
+        const int keys = min(QA_TILE, s1 - base);
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const size_t at = (head_row_of(p, b, hk) + base + min(t, keys - 1)) * G + g;
+            r[g] = make_float4(DT<T>::load((const T *)p.ks, at), DT<T>::load((const T *)p.kb, at), DT<T>::load((const T *)p.vs, at),
+                               DT<T>::load((const T *)p.vb, at));
+        }
+    };
 
     // the head's scaled queries as A fragments, and their sums per group (of the rounded values)
     uint32_t qa0[KS], qa2[KS];
@@ -294,7 +324,6 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
         }
     }
 
-    const size_t head_row = ((size_t)b * p.Hkv + hk) * p.capacity;
     float m = -INFINITY, l = 0.0f;  // of head g8
     float oc[NBD][4], side[G];      // outputs [head g8][dims 8 nbd + 2 c, + 1] (rows 8-15 idle); bias / offset terms per group
 #pragma unroll
@@ -302,27 +331,28 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
 #pragma unroll
     for (int g = 0; g < G; g++) side[g] = 0.0f;
 
-    for (int base = s0; base < s1; base += QA_TILE) {
+    float4 nsb[G];
+    if (s0 < s1) {
+        fetch_codes(s0, 0);
+        fetch_scales(s0, nsb);
+#pragma unroll
+        for (int g = 0; g < G; g++) sbuf[t * G + g] = nsb[g];
+    }
+    int buf = 0;
+    for (int base = s0; base < s1; base += QA_TILE, buf ^= 1) {
         const int keys = min(QA_TILE, s1 - base);
-        // ── the tile's codes into shared memory with 16-byte loads, all in flight together; value rows padded by a
-        //    word (the fragments read four rows at once), key rows by four ──
-        {
-            const uint4 *ksrc = reinterpret_cast<const uint4 *>(p.kw + (head_row + base) * W);
-            const uint4 *vsrc = reinterpret_cast<const uint4 *>(p.vw + (head_row + base) * W);
-            for (int i = t; i < keys * W / 4; i += QA_THREADS) {
-                const uint4 kv = ksrc[i], v = vsrc[i];
-                const int row = (4 * i) / W, col = (4 * i) % W;
-                *reinterpret_cast<uint4 *>(ktile + row * KP + col) = kv;
-                uint32_t *dst = vtile + row * WP + col;
-                dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
-            }
-            for (int i = t; i < keys * G; i += QA_THREADS) {
-                const size_t at = (head_row + base) * G + i;
-                sbt[0][i] = make_float4(DT<T>::load((const T *)p.ks, at), DT<T>::load((const T *)p.kb, at), DT<T>::load((const T *)p.vs, at),
-                                        DT<T>::load((const T *)p.vb, at));
-            }
+        const bool more = base + QA_TILE < s1;
+        // the next tile's codes start travelling into the other buffers, its scales into registers
+        if (more) {
+            fetch_codes(base + QA_TILE, buf ^ 1);
+            fetch_scales(base + QA_TILE, nsb);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const uint32_t *ktile = kbuf + buf * TILE_WORDS, *vtile = vbuf + buf * TILE_WORDS;
+        const float4(*sbt)[G] = reinterpret_cast<const float4(*)[G]>(sbuf + buf * QA_TILE * G);
         // ── scores of the warp's 32 keys: four blocks of 8 keys ──
         float sc[4][2];
 #pragma unroll
@@ -445,7 +475,11 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
                 qa_mma(oc[nbd], pa0[nbd / NBD_PER_G], pa2[nbd / NBD_PER_G], b0, b1);
             }
         }
-        __syncthreads();  // the value tile, the scales and wred are rewritten by the next tile
+        if (more) {
+#pragma unroll
+            for (int g = 0; g < G; g++) sbuf[((buf ^ 1) * QA_TILE + t) * G + g] = nsb[g];
+        }
+        __syncthreads();  // this tile's buffers are refilled from the next iteration on; wred is rewritten by the next tile
     }
 
     // ── the four warps' outputs together, then this split's partial result ──
@@ -454,7 +488,7 @@ __global__ void __launch_bounds__(QA_THREADS, QA_MMA_BLOCKS) qattn_mma_kernel(QA
         side[g] += __shfl_xor_sync(0xFFFFFFFFu, side[g], 1);
         side[g] += __shfl_xor_sync(0xFFFFFFFFu, side[g], 2);
     }
-    float *wsum = reinterpret_cast<float *>(vtile);  // [warp][head][D]
+    float *wsum = reinterpret_cast<float *>(vbuf);  // [warp][head][D]
     if (head) {
 #pragma unroll
         for (int nbd = 0; nbd < NBD; nbd++) {
@@ -522,7 +556,21 @@ static bool qattn_uses_mma(int dtype, int bits) {
 
 template <typename T, int BITS, int D, int GS>
 static void qattn_launch_mma(nvc_device *dev, const QAttnParams &p, dim3 grid) {
-    if constexpr (sizeof(T) == 2 && (BITS == 4 || BITS == 8) && D % GS == 0) qattn_mma_kernel<T, BITS, D, GS><<<grid, QA_THREADS, 0, dev->stream>>>(p);
+    if constexpr (sizeof(T) == 2 && (BITS == 4 || BITS == 8) && D % GS == 0) {
+        constexpr int W = D * BITS / 32, TILE_WORDS = QA_TILE * (W + 4), RWORDS = 4 * 8 * D;
+        constexpr size_t smem = (size_t)(2 * TILE_WORDS + (2 * TILE_WORDS > RWORDS ? 2 * TILE_WORDS : RWORDS)) * 4 + 2 * QA_TILE * (D / GS) * 16;
+        auto kernel = qattn_mma_kernel<T, BITS, D, GS>;
+        static bool configured[64] = {};
+        static std::mutex mu;
+        if (dev->ordinal >= 0 && dev->ordinal < 64) {
+            std::lock_guard<std::mutex> g(mu);
+            if (!configured[dev->ordinal]) {
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                configured[dev->ordinal] = true;
+            }
+        }
+        kernel<<<grid, QA_THREADS, smem, dev->stream>>>(p);
+    }
 }
 
 template <typename T, int BITS, int D>
@@ -584,7 +632,15 @@ extern "C" int32_t nvc_quantized_attention(nvc_device *dev, const nvc_quant *qua
     // splits: one wave of as many blocks as stay resident together (what their registers allow: three of the
     // tensor-core kernel, five of the other, per multiprocessor), whole tiles of 128 keys each
     const int64_t tiles = S > 0 ? (S + QA_TILE - 1) / QA_TILE : 1;
-    const int per_sm = qattn_uses_mma(dtype, bits) ? QA_MMA_BLOCKS : 5;
+    int per_sm = 5;
+    if (qattn_uses_mma(dtype, bits)) {
+        // (the tensor-core kernel's two sets of tile buffers decide how many blocks stay resident)
+        const int64_t tile_words = QA_TILE * (D * bits / 32 + 4), sum_words = 4 * 8 * D;
+        const int64_t smem = (2 * tile_words + (2 * tile_words > sum_words ? 2 * tile_words : sum_words)) * 4 + 2 * QA_TILE * (D / gs) * 16;
+        per_sm = (int)((227 * 1024) / (smem + 1024 + 256));
+        if (per_sm > QA_MMA_BLOCKS) per_sm = QA_MMA_BLOCKS;
+        if (per_sm < 1) per_sm = 1;
+    }
     int64_t splits = per_sm * (int64_t)dev->prop.multiProcessorCount / (B * Hkv);
     if (splits > tiles) splits = tiles;
     if (splits < 1) splits = 1;
