@@ -196,6 +196,22 @@ __device__ __forceinline__ uint4 dequant_word_fp4(uint32_t w, uint32_t scale2) {
     }
     return make_uint4(t[0], t[1], t[2], t[3]);
 }
+// 8-bit floating point (mxfp8: E4M3 codes): the code's seven magnitude bits become exponent[3:0] and mantissa[6:4] of
+// a bfloat16 (the value * 2^-120, subnormal codes as bfloat16 subnormals); times 2^120 and the scale (a power of two)
+// it is the reference's float32 decode exactly.  The two NaN codes, which the reference's quantizer never writes, read
+// as 480.  Halves: codes (0, 1) and (2, 3).
+__device__ __forceinline__ uint2 dequant_word_fp8(uint32_t w, uint32_t scale2) {
+    uint2 o;
+    {
+        const uint32_t x = q_prmt(w, w, 0x0100u);  // bytes 0, 1 in the low byte of each half
+        o.x = q_mul(q_mul(q_lop3(x << 8, 0x80008000u, (x << 4) & 0x07F007F0u), 0x7B807B80u), scale2);
+    }
+    {
+        const uint32_t x = q_prmt(w, w, 0x0302u);  // bytes 2, 3
+        o.y = q_mul(q_mul(q_lop3(x << 8, 0x80008000u, (x << 4) & 0x07F007F0u), 0x7B807B80u), scale2);
+    }
+    return o;
+}
 // bfloat16 pair {s, s} of a scale code: E8M0 (2^(code - 127); code 0 decodes to a float32 subnormal
 // that the reference flushes to zero) or E4M3.
 __device__ __forceinline__ uint32_t fp_scale2(uint32_t code, bool e8m0) {
@@ -324,7 +340,7 @@ template <int BT, bool PAIR = false> struct QmmTmem {
     static_assert(STAGES >= QMM_DQ_GROUPS, "token tile too wide for the weight ring");
 };
 
-template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 3 nvfp4*/, bool PAIR = false>
+template <int BITS, int BT, int STAGES, int MODE /*0 affine, 1 mxfp4, 2 mxfp8, 3 nvfp4*/, bool PAIR = false>
 __global__ void __launch_bounds__(QMM_THREADS, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, QmmKernelParams p,
            int total_tiles, int n_tiles) {
@@ -609,7 +625,7 @@ _Pragma("unroll")
                                 q[h].ns2 = q_mul(q[h].s2, 0xC300C300u);  // -128 s, exact
                             } else {
                                 // mxfp4: one scale per 32 values; nvfp4: one per 16 (two per half)
-                                fa[h] = fp_scale2(s_cur[h], MODE == 1);
+                                fa[h] = fp_scale2(s_cur[h], MODE != 3);
                                 fb[h] = MODE == 3 ? fp_scale2(b_cur[h], false) : fa[h];
                             }
                         }
@@ -632,7 +648,7 @@ _Pragma("unroll")
                                 const uint32_t wv[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
                                 for (int j = 0; j < 4; j++) {
-                                    const uint2 o = dequant_word8(wv[j], q[c >> 1]);
+                                    const uint2 o = MODE == 0 ? dequant_word8(wv[j], q[c >> 1]) : dequant_word_fp8(wv[j], fa[c >> 1]);
                                     v[8 * c + 2 * j] = o.x; v[8 * c + 2 * j + 1] = o.y;
                                 }
                             }
@@ -865,6 +881,8 @@ bool qmm_eligible(int32_t mode, int32_t gs, int32_t bits, int32_t dtype, int32_t
     if (dtype != NVC_BF16 || !transpose) return false;
     if (mode == NVC_AFFINE) {
         if (bits != 2 && bits != 4 && bits != 8) return false;
+    } else if (mode == NVC_MXFP8) {
+        if (bits != 8) return false;
     } else if (mode != NVC_MXFP4 && mode != NVC_NVFP4) {
         return false;
     }
@@ -1081,6 +1099,7 @@ int32_t launch_qmm(nvc_device *dev, const QmmParams &p) {
         default: return launch_bt<2, 0>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
         }
     }
+    if (p.mode == NVC_MXFP8) return launch_bt<8, 2>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
     if (p.mode == NVC_MXFP4) return launch_bt<4, 1>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
     return launch_bt<4, 3>(dev, bt, pair, mx, mw, kp, tt, n_tiles);
 }

@@ -417,6 +417,40 @@ def test_qmv_mxfp8(be, M, N, K):
     assert np.array_equal(got, dense[:, ks].T)
 
 
+@pytest.mark.parametrize("M,N,K", [(40, 128, 128), (130, 200, 2880), (300, 512, 1024)])
+def test_qmm_mxfp8(be, M, N, K):
+    # 9+ rows of MXFP8 weights on the tensor-core kernel: within one output rounding of the oracle; unit rows return the
+    # oracle's float32 decode bit for bit
+    rng = np.random.default_rng(M + N)
+    w = rand(rng, (N, K), oracle.BF16, 0.02)
+    w.reshape(-1)[:4] = oracle.from_f32(np.array([0.0, 1e-4, -0.5, 3.0], np.float32), oracle.BF16)
+    c, s, _ = oracle.quantize(w, oracle.BF16, oracle.MXFP8, 32, 8)
+    x = rand(rng, (M, K), oracle.BF16)
+    want = oracle.quantized_matmul(x, c, s, None, oracle.BF16, oracle.MXFP8, 32, 8)
+    got = be.quantized_matmul(x, c, s, None, oracle.BF16, oracle.MXFP8, 32, 8, True)
+    assert_product_tight(got, want, oracle.BF16)
+    dense = oracle.to_f32(oracle.dequantize(c, s, None, oracle.F32, oracle.MXFP8, 32, 8), oracle.F32)
+    ks = rng.permutation(K)[:64]
+    xu = np.zeros((64, K), np.float32)
+    xu[np.arange(64), ks] = 1.0
+    got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(xu, oracle.BF16), c, s, None, oracle.BF16, oracle.MXFP8, 32, 8, True), oracle.BF16)
+    assert np.array_equal(got, dense[:, ks].T)
+
+
+def test_qmm_mxfp8_every_code(be):
+    codes = np.array([v for v in range(256) if v & 0x7F != 0x7F], np.uint8)
+    K = 256
+    rows = np.resize(codes, (128, K))
+    for r in range(128):
+        rows[r] = np.roll(rows[r], 5 * r)
+    c = np.ascontiguousarray(rows).view(np.uint32)
+    s = np.random.default_rng(1).integers(110, 140, (128, K // 32), dtype=np.uint8)
+    dense = oracle.to_f32(oracle.dequantize(c, s, None, oracle.F32, oracle.MXFP8, 32, 8), oracle.F32)
+    xu = np.eye(K, dtype=np.float32)                       # 256 unit rows: the tensor-core kernel
+    got = oracle.to_f32(be.quantized_matmul(oracle.from_f32(xu, oracle.BF16), c, s, None, oracle.BF16, oracle.MXFP8, 32, 8, True), oracle.BF16)
+    assert np.array_equal(got, dense.T)
+
+
 def test_qmv_mxfp8_every_code(be):
     # every E4M3 code the quantizer can write (all but the two NaN codes), subnormals included, under several
     # scales: the kernel's operand is the oracle's decode
