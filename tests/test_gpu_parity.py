@@ -501,6 +501,17 @@ def test_gather_grouped_fp4(be, mode, gs):
         assert_product_tight(got, want, oracle.BF16, f"global={g is not None}")
 
 
+@pytest.mark.parametrize("T", [1, 96])
+def test_gather_mxfp8(be, T):
+    # MXFP8 experts: one token (per-row gather on the few-row kernel) and 96 tokens (sorted rows, grouped, tensor-core kernel)
+    rng = np.random.default_rng(T)
+    E, topk, N, K = 8, 4, 192, 1024
+    c, s, _, rhs, xr = moe_case(rng, T, E, topk, N, K, oracle.MXFP8, 32, 8)
+    want = oracle.gather_qmm(xr, c, s, None, np.arange(len(rhs)), rhs, oracle.BF16, oracle.MXFP8, 32, 8, True, None)
+    got = be.gather_qmm(xr, c, s, None, None, rhs, oracle.BF16, oracle.MXFP8, 32, 8, True, None, True)
+    assert_product_tight(got, want, oracle.BF16)
+
+
 @pytest.mark.parametrize("mode,gs", [(oracle.MXFP4, 32), (oracle.NVFP4, 16)])
 @pytest.mark.parametrize("sorted_rows", [True, False])
 def test_gather_few_rows_fp4(be, mode, gs, sorted_rows):
